@@ -1,0 +1,204 @@
+"""Generate golden vectors from the REFERENCE's own code, on CPU.
+
+Run in a container that has the reference checkout:
+
+    python tests/golden/make_golden.py [--ref /root/reference]
+
+It imports the reference's PyTorch twins of the hot path (third-party packages the reference imports
+but this image lacks are replaced by inert stand-ins) and, when ``oracle/_ref`` holds the compiled
+reference kernels, the CPU branch of the reference's ``cdist_top``.  Outputs: small ``.npz`` files next
+to this script.  The fixtures, not the reference, travel with the repository.
+
+What each fixture pins (paths inside the reference project):
+  transmat.npz    fast_compuate_transmat                renderer/gs_2d_fast_render.py:779-789  (+ autograd)
+  preprocess.npz  _GS_2D_fast_preprocess_py lines 86-205 (binning patched out: it is broken as shipped,
+                  :303/:318) incl. SH colours via utils/ops_3d/spherical_harmonics.py:242-302 (+ autograd)
+  rasterize.npz   GS_2D_fast_rasterize (python)         renderer/gs_2d_fast_render.py:433-555  (+ autograd)
+  cdist_top.npz   cdist_top / cdist_top_backward CPU branch  _C/src/other/cdist_top.cu:57-81,130-150
+"""
+import argparse
+import importlib.abc
+import importlib.machinery
+import os
+import sys
+import types
+from unittest import mock
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+
+_ABSENT = ("matplotlib", "seaborn", "torchmetrics", "imageio", "lietorch", "plyfile", "pytorch3d", "pykdtree",
+           "diff_surfel_rasterization", "diff_gaussian_rasterization", "dearpygui", "open3d", "trimesh", "lpips",
+           "tensorboard", "tensorboardX", "skimage", "kornia", "cv2", "PIL", "roma", "pycolmap", "mediapy")
+
+
+class _StubFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    def find_spec(self, name, path, target=None):
+        if name.split(".")[0] in _ABSENT:
+            try:
+                if name.split(".")[0] in ("cv2", "PIL"):
+                    return None  # present in this image: let the real one load
+            except Exception:
+                pass
+            return importlib.machinery.ModuleSpec(name, self, is_package=True)
+        return None
+
+    def create_module(self, spec):
+        m = mock.MagicMock(name=spec.name)
+        m.__path__ = []
+        m.__name__ = spec.name
+        m.__spec__ = spec
+        m.__loader__ = self
+        return m
+
+    def exec_module(self, module):
+        pass
+
+
+def import_reference(ref):
+    sys.meta_path.insert(0, _StubFinder())
+    sys.path.insert(0, ref)
+    import warnings
+    warnings.filterwarnings("ignore")
+    from fast_2d_gs.renderer import gs_2d_fast_render as R
+    from fast_2d_gs._C import get_python_function
+    from utils import ops_3d
+    return R, get_python_function, ops_3d
+
+
+def camera(ops_3d, W, H, eye=(0.3, -0.4, 4.0), fov=0.69):
+    Tw2v = ops_3d.opencv.look_at(torch.tensor(eye, dtype=torch.float32), torch.zeros(3))
+    f = 0.5 * W / np.tan(0.5 * fov)
+    Tv2s = torch.tensor([[f, 0, W / 2], [0, f, H / 2], [0, 0, 1]], dtype=torch.float32)
+    campos = torch.inverse(Tw2v)[:3, 3].contiguous()
+    return Tw2v.contiguous(), Tv2s, campos
+
+
+def scene(P, seed, log_scale=-2.5, spread=1.3):
+    g = torch.Generator().manual_seed(seed)
+    means = (torch.rand(P, 3, generator=g) * 2 - 1) * spread
+    scales = torch.exp(torch.randn(P, 2, generator=g) * 0.5 + log_scale)
+    rots = torch.nn.functional.normalize(torch.randn(P, 4, generator=g), dim=-1)
+    opac = torch.sigmoid(torch.randn(P, 1, generator=g))
+    sh_dc = torch.randn(P, 1, 3, generator=g) * 0.2 + 0.5
+    sh_rest = torch.randn(P, 15, 3, generator=g) * 0.05
+    return means, scales, rots, opac, sh_dc, sh_rest
+
+
+def npz(name, **arrs):
+    out = {}
+    for k, v in arrs.items():
+        out[k] = v.detach().cpu().numpy() if isinstance(v, torch.Tensor) else np.asarray(v)
+    path = os.path.join(HERE, name)
+    np.savez_compressed(path, **out)
+    print(f"wrote {path} ({os.path.getsize(path) / 1024:.1f} KiB)")
+
+
+def make_transmat(R, ops_3d):
+    P = 96
+    means, scales, rots, *_ = scene(P, 11)
+    Tw2v, Tv2s, _ = camera(ops_3d, 128, 96)
+    ins = [t.clone().requires_grad_() for t in (means, scales, rots)]
+    M, n = R.fast_compuate_transmat(*ins, Tw2v, Tv2s)
+    g = torch.Generator().manual_seed(12)
+    gM, gn = torch.randn(M.shape, generator=g), torch.randn(n.shape, generator=g)
+    torch.autograd.backward([M, n], [gM, gn])
+    npz("transmat.npz", means=means, scales=scales, rots=rots, Tw2v=Tw2v, Tv2s=Tv2s, M=M, normal=n, gM=gM, gn=gn,
+        g_means=ins[0].grad, g_scales=ins[1].grad, g_rots=ins[2].grad)
+
+
+def make_preprocess(R, ops_3d):
+    P, W, H = 384, 120, 90
+    means, scales, rots, opac, sh_dc, sh_rest = scene(P, 21)
+    means[:8, 2] = 5.0  # behind / too close to the camera: exercises the z <= 0.2 cull
+    Tw2v, Tv2s, campos = camera(ops_3d, W, H)
+    Tv2c = ops_3d.opencv.perspective(0.69, size=(W, H))
+    R._prepare_py = lambda *a, **k: (None, None)  # broken as shipped; binning is pinned elsewhere
+    ins = [t.clone().requires_grad_() for t in (means, scales, rots, opac, sh_dc, sh_rest)]
+    for deg in (3, 0):
+        for t in ins:
+            t.grad = None
+        out = R._GS_2D_fast_preprocess_py(W, H, deg, False, ins[0], ins[1], ins[2], ins[3], ins[4],
+                                          ins[5] if deg > 0 else None, Tw2v, Tv2c, Tv2s, campos)
+        means2D, colors, trans_mat, inverse_m, normal_opacity, depths, radii = out[:7]
+        g = torch.Generator().manual_seed(22 + deg)
+        ups = [torch.randn(t.shape, generator=g) for t in (means2D, colors, trans_mat, inverse_m, normal_opacity)]
+        torch.autograd.backward([means2D, colors, trans_mat, inverse_m, normal_opacity], ups)
+        grads = {f"g_{n}": (t.grad if t.grad is not None else torch.zeros_like(t))
+                 for n, t in zip(("means", "scales", "rots", "opac", "sh_dc", "sh_rest"), ins)}
+        npz(f"preprocess_deg{deg}.npz", W=W, H=H, deg=deg, means=means, scales=scales, rots=rots, opac=opac,
+            sh_dc=sh_dc, sh_rest=sh_rest, Tw2v=Tw2v, Tv2s=Tv2s, campos=campos, means2D=means2D, colors=colors,
+            trans_mat=trans_mat, inverse_m=inverse_m, normal_opacity=normal_opacity, depths=depths, radii=radii,
+            up_means2D=ups[0], up_colors=ups[1], up_trans_mat=ups[2], up_inverse_m=ups[3], up_normal_opacity=ups[4],
+            **grads)
+
+
+def make_rasterize(R, get_python_function, ops_3d):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as orc  # only to obtain per-tile lists to feed the reference's python compositor
+    P, W, H = 400, 72, 56
+    # seed chosen so that no splat sits on the alpha = 1/255 cut for any pixel: there the twin (cross products of
+    # trans_mat rows) and the CUDA formulation (inverse_m rows) may round to different sides
+    means, scales, rots, opac, sh_dc, sh_rest = scene(P, 32, log_scale=-1.6)
+    Tw2v, Tv2s, campos = camera(ops_3d, W, H)
+    pre = orc.preprocess_forward(W, H, 3, means, scales, rots, opac, sh_dc, sh_rest, Tw2v, Tv2s, campos)
+    means2D, colors, trans_mat, inverse_m, normal_opacity, depths, radii, ranges, point_list = pre[:9]
+    n_real = pre[10]
+    point_list = point_list[:n_real].contiguous()
+    rast = R.GS_2D_fast_rasterize  # without a compiled extension the decorator leaves the python twin in place
+    ins = [t.clone().requires_grad_() for t in (means2D, colors, normal_opacity, trans_mat)]
+    images, opacities, extras, n_contrib = rast(W, H, ins[0], ins[1], ins[2], ins[3], inverse_m, ranges,
+                                                point_list.long(), 0.2, 100., False)
+    g = torch.Generator().manual_seed(32)
+    g_img, g_op = torch.randn(images.shape, generator=g), torch.randn(opacities.shape, generator=g)
+    g_nrm = torch.randn(3, H, W, generator=g)
+    torch.autograd.backward([images, opacities, extras[1:4]], [g_img, g_op, g_nrm])
+    npz("rasterize.npz", W=W, H=H, means2D=means2D, colors=colors, normal_opacity=normal_opacity,
+        trans_mat=trans_mat, inverse_m=inverse_m, ranges=ranges, point_list=point_list, images=images,
+        opacities=opacities, extras=extras, n_contrib=n_contrib, g_img=g_img, g_op=g_op, g_nrm=g_nrm,
+        g_means2D=ins[0].grad, g_colors=ins[1].grad, g_normal_opacity=ins[2].grad, g_trans_mat=ins[3].grad)
+
+
+def make_cdist_top():
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    sys.path.insert(0, ref_dir)
+    try:
+        import _C as refC
+    except ImportError as e:
+        print(f"oracle/_ref not built ({e}); cdist_top.npz not regenerated")
+        return
+    g = torch.Generator().manual_seed(41)
+    x = torch.rand(2, 700, 3, generator=g) * 2 - 1
+    c = torch.rand(2, 48, 3, generator=g) * 2 - 1
+    c[:, 5] = c[:, 17]  # exact duplicates: exercises the tie rule
+    c[:, 30] = c[:, 17]
+    out = {}
+    for largest in (False, True):
+        d, i = refC.cdist_top(x, c, largest)
+        gd = torch.randn(d.shape, generator=g)
+        g1, g2 = refC.cdist_top_backward(x, c, d, i, gd)
+        tag = "far" if largest else "near"
+        out.update({f"dist_{tag}": d, f"idx_{tag}": i, f"gd_{tag}": gd, f"g1_{tag}": g1, f"g2_{tag}": g2})
+    x5 = torch.randn(300, 5, generator=g)
+    c5 = torch.randn(20, 5, generator=g)
+    d5, i5 = refC.cdist_top(x5, c5, False)
+    npz("cdist_top.npz", x=x, c=c, x5=x5, c5=c5, dist5=d5, idx5=i5, **out)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    torch.set_num_threads(4)
+    make_cdist_top()
+    R, get_python_function, ops_3d = import_reference(args.ref)
+    make_transmat(R, ops_3d)
+    make_preprocess(R, ops_3d)
+    make_rasterize(R, get_python_function, ops_3d)
+
+
+if __name__ == "__main__":
+    main()
