@@ -1,0 +1,502 @@
+// Per-tile alpha compositing, forward and backward.
+//
+// One block of 256 threads per 16x16 tile; each warp owns an 8x4 pixel sub-tile.  A tile's list is staged
+// through shared memory in batches of packed 112-byte render records.  Every warp skips the splats of a
+// batch whose alpha >= 1/255 box misses its sub-tile (the box is conservative, so results are unchanged),
+// pixels stop once their transmittance is spent, warps and blocks stop once all their pixels have.
+//
+// The backward walks each list back to front like the reference's per-pixel kernel
+// (gs_2d_fast_redner.cu:273-561) but sums the 21 gradient components of a splat across the warp with a
+// transposing shuffle reduction, then across the tile's warps in shared memory, and issues one global
+// reduction per (Gaussian, tile, component) instead of one per (Gaussian, pixel, component).
+//
+// Per-pixel arithmetic (ray-splat intersection, alpha, thresholds) keeps the reference's expression forms:
+// a splat flipping across the alpha >= 1/255 cut would move a pixel by more than the 1e-4 image tolerance.
+#include "fsgs_common.cuh"
+
+namespace fsgs {
+
+constexpr int kStage = 128;          // splats per shared-memory batch
+constexpr int kQ = kRecQuadsUsed;    // float4 per staged record
+constexpr int kGrad = 21;            // gradient components per splat
+constexpr unsigned kFull = 0xffffffffu;
+
+struct FwdDev {
+  int P, W, H, gx;
+  float near_n, far_n;
+  const float4 *records;
+  const int32_t *point_list;
+  const long long *ranges;
+  const int32_t *tile_order;
+  const float *m2;  // trans_mat_t2
+  float *out_color, *out_opacity, *out_extras;
+  float2 *out_flow;
+  int32_t *n_contrib;
+  int32_t *accum_max_count;
+  float *accum_weights_p;
+  int32_t *accum_weights_count;
+};
+
+// Cooperative load of one batch: records (7 float4 each), Gaussian ids and, for flow, the 3x3 matrices at t2.
+template <bool FLOW, bool REVERSE>
+__device__ __forceinline__ void load_stage(const float4 *__restrict__ records, const int32_t *__restrict__ list,
+    int cnt, const float *__restrict__ m2, float4 *s_rec, int *s_gid, float *s_m2) {
+  // list points at the first entry of the batch (REVERSE: entries are taken as list[-r])
+  for (int e = threadIdx.x; e < cnt * kQ; e += blockDim.x) {
+    const int r = e / kQ, qd = e - r * kQ;
+    const int g = REVERSE ? list[-r] : list[r];
+    s_rec[e] = __ldg(records + (size_t) g * (kRecFloats / 4) + qd);
+    if (qd == 0) s_gid[r] = g;
+  }
+  if (FLOW) {
+    for (int e = threadIdx.x; e < cnt * 9; e += blockDim.x) {
+      const int r = e / 9, k = e - r * 9;
+      const int g = REVERSE ? list[-r] : list[r];
+      s_m2[e] = __ldg(m2 + (size_t) g * 9 + k);
+    }
+  }
+}
+
+struct Hit {
+  float sx, sy, pz, rho3d, rho2d, depth, G, alpha, dx, dy;
+};
+
+// (pixel, splat) evaluation shared by both passes; false when the pair is skipped.
+// Same operations, in the same order, as the reference kernels (gs_2d_fast_redner.cu:152-186).
+__device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py, float near_n, Hit &h, float &opa,
+    float3 &Tw) {
+  const float4 q0 = rec[0], q1 = rec[1], q2 = rec[2], q3 = rec[3];
+  const float p0 = q1.x * px + q1.y * py + q1.z;
+  const float p1 = q1.w * px + q2.x * py + q2.y;
+  const float p2 = q2.z * px + q2.w * py + q3.x;
+  if (p2 == 0.0f) return false;
+  h.pz = p2;
+  h.sx = p0 / p2, h.sy = p1 / p2;
+  h.rho3d = (h.sx * h.sx + h.sy * h.sy);
+  h.dx = q0.x - px, h.dy = q0.y - py;
+  h.rho2d = 2.0f * (h.dx * h.dx + h.dy * h.dy);
+  const float rho = fminf(h.rho3d, h.rho2d);
+  Tw = make_float3(q3.y, q3.z, q3.w);
+  h.depth = (h.sx * Tw.x + h.sy * Tw.y) + Tw.z;
+  if (h.depth < near_n) return false;
+  opa = q0.z;
+  const float power = -0.5f * rho;
+  if (power > 0.0f) return false;
+  h.G = expf(power);
+  h.alpha = fminf(0.99f, opa * h.G);
+  if (h.alpha < 1.0f / 255.0f) return false;
+  return true;
+}
+
+template <bool AUX, bool FLOW>
+__global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
+  __shared__ float4 s_rec[kStage * kQ];
+  __shared__ int s_gid[kStage];
+  __shared__ float s_m2[FLOW ? kStage * 9 : 1];
+
+  const int tile = a.tile_order ? a.tile_order[blockIdx.x] : blockIdx.x;
+  const int tx = tile % a.gx, ty = tile / a.gx;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sx0 = tx * kTile + (warp & 1) * 8, sy0 = ty * kTile + (warp >> 1) * 4;
+  const int ix = sx0 + (lane & 7), iy = sy0 + (lane >> 3);
+  const bool inside = ix < a.W && iy < a.H;
+  const float px = (float) ix, py = (float) iy;
+  const float bx0 = (float) sx0, bx1 = (float) (sx0 + 7), by0 = (float) sy0, by1 = (float) (sy0 + 3);
+  const size_t HW = (size_t) a.H * a.W;
+  const size_t pix = (size_t) iy * a.W + ix;
+
+  const long long r0 = a.ranges[2 * tile], r1 = a.ranges[2 * tile + 1];
+  const int n = (int) (r1 - r0);
+
+  bool done = !inside;
+  float T = 1.0f, C0 = 0, C1 = 0, C2 = 0;
+  float N0 = 0, N1 = 0, N2 = 0, D = 0, M1 = 0, M2 = 0, dist = 0, med_depth = 0, F0 = 0, F1 = 0;
+  int last = 0, med_contrib = -1;
+  float wmax = 0;
+  int wmax_id = -1;
+  bool flag = false;
+
+  for (int base = 0; base < n; base += kStage) {
+    if (__syncthreads_and(done)) break;
+    const int cnt = min(kStage, n - base);
+    load_stage<FLOW, false>(a.records, a.point_list + r0 + base, cnt, a.m2, s_rec, s_gid, s_m2);
+    __syncthreads();
+    if (__all_sync(kFull, done)) continue;
+    for (int c = 0; c < cnt; c += 32) {
+      const int rr = c + lane;
+      bool hit = false;
+      if (rr < cnt) {
+        const float4 box = s_rec[rr * kQ + 4];
+        hit = box.x <= bx1 && box.y >= bx0 && box.z <= by1 && box.w >= by0;
+      }
+      unsigned mask = __ballot_sync(kFull, hit);
+      while (mask) {
+        const int j = __ffs(mask) - 1;
+        mask &= mask - 1;
+        if (done) continue;
+        const int r = c + j;
+        const float4 *rec = s_rec + r * kQ;
+        Hit h;
+        float opa;
+        float3 Tw;
+        if (!eval_pair(rec, px, py, a.near_n, h, opa, Tw)) continue;
+        const float test_T = T * (1 - h.alpha);
+        if (test_T < 0.0001f) {
+          done = true;
+          continue;
+        }
+        const float w = h.alpha * T;
+        const int contributor = base + r + 1;
+        const float4 q5 = rec[5];
+        if (AUX) {
+          const float4 q6 = rec[6];
+          const float A = 1 - T;
+          const float m = a.far_n / (a.far_n - a.near_n) * (1 - a.near_n / h.depth);
+          dist += (m * m * A + M2 - 2 * m * M1) * w;
+          D += h.depth * w;
+          M1 += m * w;
+          M2 += m * m * w;
+          if (T > 0.5f) {
+            med_depth = h.depth;
+            med_contrib = contributor;
+          }
+          N0 += q5.w * w, N1 += q6.x * w, N2 += q6.y * w;
+          if (a.accum_max_count || a.accum_weights_p || a.accum_weights_count) {
+            const int g = s_gid[r];
+            if (wmax < w) wmax = w, wmax_id = g, flag = true;
+            if (a.accum_weights_p) atomicAdd(a.accum_weights_p + g, w);
+            if (a.accum_weights_count) atomicAdd(a.accum_weights_count + g, 1);
+            // the flag is never cleared: every later contribution counts (gs_2d_fast_redner.cu:82,211-215,227)
+            if (flag && a.accum_max_count) atomicAdd(a.accum_max_count + wmax_id, 1);
+          }
+          if (FLOW) {
+            const float *m2 = s_m2 + r * 9;
+            const float u = m2[0] * h.sx + m2[1] * h.sy + m2[2];
+            const float v = m2[3] * h.sx + m2[4] * h.sy + m2[5];
+            float ww = m2[6] * h.sx + m2[7] * h.sy + m2[8];
+            ww = fabsf(ww) < 1e-5f ? 1e-5f : ww;
+            F0 += (u / ww - px) * w;
+            F1 += (v / ww - py) * w;
+          }
+        }
+        C0 += q5.x * w, C1 += q5.y * w, C2 += q5.z * w;
+        T = test_T;
+        last = contributor;
+      }
+      if (__all_sync(kFull, done)) break;
+    }
+  }
+
+  if (inside) {
+    const float A = 1.0f - T;
+    a.out_opacity[pix] = A;
+    a.n_contrib[pix] = last;
+    a.out_color[pix] = C0, a.out_color[HW + pix] = C1, a.out_color[2 * HW + pix] = C2;
+    if (AUX) {
+      a.n_contrib[HW + pix] = med_contrib;
+      a.out_extras[pix] = D;
+      a.out_extras[HW + pix] = N0, a.out_extras[2 * HW + pix] = N1, a.out_extras[3 * HW + pix] = N2;
+      a.out_extras[4 * HW + pix] = med_depth;
+      a.out_extras[5 * HW + pix] = dist;
+      a.out_extras[6 * HW + pix] = M1;
+      a.out_extras[7 * HW + pix] = M2;
+      if (FLOW) a.out_flow[pix] = make_float2(A > 0 ? F0 / A : 0.0f, A > 0 ? F1 / A : 0.0f);
+    } else {
+      a.n_contrib[HW + pix] = 0;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward
+// ------------------------------------------------------------------------------------------------
+
+struct BwdDev {
+  int P, W, H, gx;
+  float near_n, far_n;
+  const float4 *records;
+  const int32_t *point_list;
+  const long long *ranges;
+  const int32_t *tile_order;
+  const float *m2;
+  const float *out_opacity, *out_extras;
+  const int32_t *n_contrib;
+  const float *g_color, *g_opacity, *g_extras;
+  const float2 *g_flow;
+  float *g_colors, *g_means2D, *g_trans_mat, *g_inverse_m, *g_normal_opacity;
+};
+
+// Sum 32 per-lane vectors of up to 32 components; afterwards lane L holds the total of component L in v[0].
+// Components >= N are known zero (N = 21 here); every round halves the vector each lane carries.
+template <int N>
+__device__ __forceinline__ float warp_transpose_reduce(float (&v)[32], int lane) {
+#pragma unroll
+  for (int width = 16; width >= 1; width >>= 1) {
+    const bool up = lane & width;
+#pragma unroll
+    for (int k = 0; k < width; ++k) {
+      const float lo = v[k], hi = (k + width < N) ? v[k + width] : 0.0f;
+      const float send = up ? lo : hi;
+      const float keep = up ? hi : lo;
+      v[k] = keep + __shfl_xor_sync(kFull, send, width);
+    }
+  }
+  return v[0];
+}
+
+template <bool AUX, bool FLOW>
+__global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
+  __shared__ float4 s_rec[kStage * kQ];
+  __shared__ int s_gid[kStage];
+  __shared__ float s_grad[kStage * kGrad];
+  __shared__ float s_m2[FLOW ? kStage * 9 : 1];
+  __shared__ int s_max[8];
+
+  const int tile = a.tile_order ? a.tile_order[blockIdx.x] : blockIdx.x;
+  const int tx = tile % a.gx, ty = tile / a.gx;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sx0 = tx * kTile + (warp & 1) * 8, sy0 = ty * kTile + (warp >> 1) * 4;
+  const int ix = sx0 + (lane & 7), iy = sy0 + (lane >> 3);
+  const bool inside = ix < a.W && iy < a.H;
+  const float px = (float) ix, py = (float) iy;
+  const float bx0 = (float) sx0, bx1 = (float) (sx0 + 7), by0 = (float) sy0, by1 = (float) (sy0 + 3);
+  const size_t HW = (size_t) a.H * a.W;
+  const size_t pix = (size_t) iy * a.W + ix;
+
+  const long long r0 = a.ranges[2 * tile], r1 = a.ranges[2 * tile + 1];
+  const int n = (int) (r1 - r0);
+
+  const float T_final = inside ? 1 - a.out_opacity[pix] : 0;
+  float T = T_final;
+  const int last_contributor = inside ? a.n_contrib[pix] : 0;
+  const int median_contributor = (AUX && inside) ? a.n_contrib[HW + pix] : 0;
+
+  float gpix0 = 0, gpix1 = 0, gpix2 = 0;
+  float g_reg = 0, g_depth = 0, g_acc = 0, g_n0 = 0, g_n1 = 0, g_n2 = 0, g_med = 0;
+  float final_D = 0, final_D2 = 0;
+  float2 gflow = make_float2(0, 0);
+  if (inside) {
+    gpix0 = a.g_color[pix], gpix1 = a.g_color[HW + pix], gpix2 = a.g_color[2 * HW + pix];
+    if (AUX) {
+      g_acc = a.g_opacity[pix];
+      g_depth = a.g_extras[pix];
+      g_n0 = a.g_extras[HW + pix], g_n1 = a.g_extras[2 * HW + pix], g_n2 = a.g_extras[3 * HW + pix];
+      g_med = a.g_extras[4 * HW + pix];
+      g_reg = a.g_extras[5 * HW + pix];
+      final_D = a.out_extras[6 * HW + pix];
+      final_D2 = a.out_extras[7 * HW + pix];
+    }
+    if (FLOW) gflow = a.g_flow[pix];
+  }
+  const float final_A = 1 - T_final;
+
+  float acc_c0 = 0, acc_c1 = 0, acc_c2 = 0, last_c0 = 0, last_c1 = 0, last_c2 = 0;
+  float last_depth = 0, acc_depth = 0, acc_alpha = 0;
+  float last_n0 = 0, last_n1 = 0, last_n2 = 0, acc_n0 = 0, acc_n1 = 0, acc_n2 = 0;
+  float last_dL_dT = 0, last_alpha = 0;
+  float acc_f0 = 0, acc_f1 = 0, last_f0 = 0, last_f1 = 0;
+
+  // the deepest list position any pixel of the warp / the tile blended
+  int wmax = last_contributor;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(kFull, wmax, o));
+  if (lane == 0) s_max[warp] = wmax;
+  __syncthreads();
+  int tmax = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tmax = max(tmax, s_max[k]);
+  if (tmax == 0) return;
+
+  const int n_stages = (min(n, tmax) + kStage - 1) / kStage;
+  for (int st = n_stages - 1; st >= 0; --st) {
+    const int base = st * kStage;
+    const int cnt = min(kStage, n - base);
+    __syncthreads();  // previous batch fully flushed
+    // entry r of the batch is list position base + cnt - 1 - r (back to front)
+    load_stage<FLOW, true>(a.records, a.point_list + r0 + base + cnt - 1, cnt, a.m2, s_rec, s_gid, s_m2);
+    for (int e = threadIdx.x; e < cnt * kGrad; e += blockDim.x) s_grad[e] = 0.0f;
+    __syncthreads();
+
+    if (base < wmax) {
+      for (int c = 0; c < cnt; c += 32) {
+        const int rr = c + lane;
+        bool hit = false;
+        if (rr < cnt) {
+          const float4 box = s_rec[rr * kQ + 4];
+          hit = box.x <= bx1 && box.y >= bx0 && box.z <= by1 && box.w >= by0;
+        }
+        unsigned mask = __ballot_sync(kFull, hit);
+        while (mask) {
+          const int j = __ffs(mask) - 1;
+          mask &= mask - 1;
+          const int r = c + j;
+          const int contributor = base + cnt - 1 - r;  // 0-based list position
+          if (contributor >= wmax) continue;            // warp-uniform
+          const float4 *rec = s_rec + r * kQ;
+          float g[32];
+#pragma unroll
+          for (int k = 0; k < kGrad; ++k) g[k] = 0.0f;
+          bool active = contributor < last_contributor;
+          Hit h;
+          float opa = 0;
+          float3 Tw = make_float3(0, 0, 0);
+          if (active) active = eval_pair(rec, px, py, a.near_n, h, opa, Tw);
+          if (active) {
+            const float alpha = h.alpha, G = h.G;
+            T = T / (1.0f - alpha);
+            const float w = alpha * T;
+            const float4 q5 = rec[5];
+            float dL_dalpha = 0.0f;
+            acc_c0 = last_alpha * last_c0 + (1.0f - last_alpha) * acc_c0;
+            acc_c1 = last_alpha * last_c1 + (1.0f - last_alpha) * acc_c1;
+            acc_c2 = last_alpha * last_c2 + (1.0f - last_alpha) * acc_c2;
+            last_c0 = q5.x, last_c1 = q5.y, last_c2 = q5.z;
+            dL_dalpha += (q5.x - acc_c0) * gpix0;
+            dL_dalpha += (q5.y - acc_c1) * gpix1;
+            dL_dalpha += (q5.z - acc_c2) * gpix2;
+            g[0] = w * gpix0, g[1] = w * gpix1, g[2] = w * gpix2;
+
+            float dL_dz = 0.0f, dL_dweight = 0.0f, dL_dsx = 0.0f, dL_dsy = 0.0f;
+            if (AUX) {
+              const float4 q6 = rec[6];
+              const float m_d = a.far_n / (a.far_n - a.near_n) * (1 - a.near_n / h.depth);
+              const float dmd_dd = (a.far_n * a.near_n) / ((a.far_n - a.near_n) * h.depth * h.depth);
+              if (contributor == median_contributor - 1) dL_dz += g_med;
+              dL_dweight += (final_D2 + m_d * m_d * final_A - 2 * m_d * final_D) * g_reg;
+              dL_dalpha += dL_dweight - last_dL_dT;
+              last_dL_dT = dL_dweight * alpha + (1 - alpha) * last_dL_dT;
+              const float dL_dmd = 2.0f * (T * alpha) * (m_d * final_A - final_D) * g_reg;
+              dL_dz += dL_dmd * dmd_dd;
+              acc_depth = last_alpha * last_depth + (1.0f - last_alpha) * acc_depth;
+              last_depth = h.depth;
+              dL_dalpha += (h.depth - acc_depth) * g_depth;
+              acc_alpha = last_alpha * 1.0f + (1.0f - last_alpha) * acc_alpha;
+              dL_dalpha += (1 - acc_alpha) * g_acc;
+              acc_n0 = last_alpha * last_n0 + (1.0f - last_alpha) * acc_n0;
+              acc_n1 = last_alpha * last_n1 + (1.0f - last_alpha) * acc_n1;
+              acc_n2 = last_alpha * last_n2 + (1.0f - last_alpha) * acc_n2;
+              last_n0 = q5.w, last_n1 = q6.x, last_n2 = q6.y;
+              dL_dalpha += (q5.w - acc_n0) * g_n0;
+              dL_dalpha += (q6.x - acc_n1) * g_n1;
+              dL_dalpha += (q6.y - acc_n2) * g_n2;
+              g[3] = w * g_n0, g[4] = w * g_n1, g[5] = w * g_n2;
+              dL_dz += w * g_depth;
+            }
+            if (FLOW) {
+              const float *m2 = s_m2 + r * 9;
+              const float u = m2[0] * h.sx + m2[1] * h.sy + m2[2];
+              const float v = m2[3] * h.sx + m2[4] * h.sy + m2[5];
+              float ww = m2[6] * h.sx + m2[7] * h.sy + m2[8];
+              ww = fabsf(ww) < 1e-5f ? 1e-5f : ww;
+              acc_f0 = last_alpha * last_f0 + (1.0f - last_alpha) * acc_f0;
+              acc_f1 = last_alpha * last_f1 + (1.0f - last_alpha) * acc_f1;
+              last_f0 = u / ww - px, last_f1 = v / ww - py;
+              dL_dalpha += (last_f0 - acc_f0) * gflow.x + (last_f1 - acc_f1) * gflow.y;
+              const float gu = w / ww * gflow.x, gv = w / ww * gflow.y;
+              const float gw = -w / (ww * ww) * (u * gflow.x + v * gflow.y);
+              dL_dsx += m2[0] * gu + m2[3] * gv + m2[6] * gw;
+              dL_dsy += m2[1] * gu + m2[4] * gv + m2[7] * gw;
+            }
+            dL_dalpha *= T;
+            last_alpha = alpha;
+            const float dL_dG = opa * dL_dalpha;
+            if (h.rho3d <= h.rho2d) {
+              dL_dsx += dL_dG * -G * h.sx + dL_dz * Tw.x;
+              dL_dsy += dL_dG * -G * h.sy + dL_dz * Tw.y;
+              const float ga = dL_dsx / h.pz, gb = dL_dsy / h.pz;
+              const float gc = -(ga * h.sx + gb * h.sy);
+              g[12] = ga * px, g[13] = ga * py, g[14] = ga;
+              g[15] = gb * px, g[16] = gb * py, g[17] = gb;
+              g[18] = gc * px, g[19] = gc * py, g[20] = gc;
+            } else {
+              g[7] = dL_dG * (-G * 2.0f * h.dx);
+              g[8] = dL_dG * (-G * 2.0f * h.dy);
+            }
+            g[9] = dL_dz * h.sx, g[10] = dL_dz * h.sy, g[11] = dL_dz;
+            g[6] = G * dL_dalpha;
+          }
+          if (__ballot_sync(kFull, active) == 0) continue;
+          const float total = warp_transpose_reduce<kGrad>(g, lane);
+          if (lane < kGrad) atomicAdd(s_grad + r * kGrad + lane, total);
+        }
+      }
+    }
+    __syncthreads();
+    // one global reduction per (Gaussian, component) of this batch
+    for (int e = threadIdx.x; e < cnt * kGrad; e += blockDim.x) {
+      const float v = s_grad[e];
+      if (v == 0.0f) continue;
+      const int r = e / kGrad, c = e - r * kGrad;
+      const size_t g = (size_t) s_gid[r];
+      float *dst;
+      if (c < 3) dst = a.g_colors + g * 3 + c;
+      else if (c < 7) dst = a.g_normal_opacity + g * 4 + (c - 3);
+      else if (c < 9) dst = a.g_means2D + g * 2 + (c - 7);
+      else if (c < 12) dst = a.g_trans_mat + g * 9 + 6 + (c - 9);
+      else dst = a.g_inverse_m + g * 9 + (c - 12);
+      atomicAdd(dst, v);
+    }
+  }
+}
+
+}  // namespace fsgs
+
+using namespace fsgs;
+
+extern "C" int fsgs_render_forward(const fsgs_render_args *a, fsgs_stream_t stream) {
+  FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0);
+  FSGS_REQUIRE(a->ranges && a->out_color && a->out_opacity && a->n_contrib);
+  FSGS_REQUIRE(a->P == 0 || (a->records && a->point_list));
+  FSGS_REQUIRE(a->only_image || a->out_extras);
+  FSGS_REQUIRE(!a->trans_mat_t2 || a->only_image || a->out_flow);
+  FwdDev d;
+  d.P = a->P, d.W = a->W, d.H = a->H, d.gx = (a->W + kTile - 1) / kTile;
+  d.near_n = a->near_n, d.far_n = a->far_n;
+  d.records = (const float4 *) a->records, d.point_list = a->point_list, d.ranges = (const long long *) a->ranges;
+  d.tile_order = a->tile_order, d.m2 = a->trans_mat_t2;
+  d.out_color = a->out_color, d.out_opacity = a->out_opacity, d.out_extras = a->out_extras;
+  d.out_flow = (float2 *) a->out_flow, d.n_contrib = a->n_contrib;
+  d.accum_max_count = a->accum_max_count, d.accum_weights_p = a->accum_weights_p;
+  d.accum_weights_count = a->accum_weights_count;
+  const int T = d.gx * ((a->H + kTile - 1) / kTile);
+  cudaStream_t st = (cudaStream_t) stream;
+  if (a->only_image) blend_forward_kernel<false, false><<<T, 256, 0, st>>>(d);
+  else if (a->trans_mat_t2) blend_forward_kernel<true, true><<<T, 256, 0, st>>>(d);
+  else blend_forward_kernel<true, false><<<T, 256, 0, st>>>(d);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_render_backward(const fsgs_render_bwd_args *a, fsgs_stream_t stream) {
+  FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0);
+  FSGS_REQUIRE(a->ranges && a->out_opacity && a->n_contrib && a->dL_dcolor);
+  FSGS_REQUIRE(a->dL_dcolors && a->dL_dmeans2D && a->dL_dtrans_mat && a->dL_dinverse_m && a->dL_dnormal_opacity);
+  const bool aux = a->out_extras && a->dL_dextras;
+  FSGS_REQUIRE(!aux || a->dL_dopacity);
+  const bool flow = aux && a->dL_dflow && a->trans_mat_t2;
+  cudaStream_t st = (cudaStream_t) stream;
+  const size_t P = (size_t) a->P;
+  cudaMemsetAsync(a->dL_dcolors, 0, sizeof(float) * 3 * P, st);
+  cudaMemsetAsync(a->dL_dmeans2D, 0, sizeof(float) * 2 * P, st);
+  cudaMemsetAsync(a->dL_dtrans_mat, 0, sizeof(float) * 9 * P, st);
+  cudaMemsetAsync(a->dL_dinverse_m, 0, sizeof(float) * 9 * P, st);
+  cudaMemsetAsync(a->dL_dnormal_opacity, 0, sizeof(float) * 4 * P, st);
+  if (a->P == 0) return FSGS_OK;
+  FSGS_REQUIRE(a->records && a->point_list);
+  BwdDev d;
+  d.P = a->P, d.W = a->W, d.H = a->H, d.gx = (a->W + kTile - 1) / kTile;
+  d.near_n = a->near_n, d.far_n = a->far_n;
+  d.records = (const float4 *) a->records, d.point_list = a->point_list, d.ranges = (const long long *) a->ranges;
+  d.tile_order = a->tile_order, d.m2 = a->trans_mat_t2;
+  d.out_opacity = a->out_opacity, d.out_extras = a->out_extras, d.n_contrib = a->n_contrib;
+  d.g_color = a->dL_dcolor, d.g_opacity = a->dL_dopacity, d.g_extras = a->dL_dextras;
+  d.g_flow = (const float2 *) a->dL_dflow;
+  d.g_colors = a->dL_dcolors, d.g_means2D = a->dL_dmeans2D, d.g_trans_mat = a->dL_dtrans_mat;
+  d.g_inverse_m = a->dL_dinverse_m, d.g_normal_opacity = a->dL_dnormal_opacity;
+  const int T = d.gx * ((a->H + kTile - 1) / kTile);
+  if (!aux) blend_backward_kernel<false, false><<<T, 256, 0, st>>>(d);
+  else if (flow) blend_backward_kernel<true, true><<<T, 256, 0, st>>>(d);
+  else blend_backward_kernel<true, false><<<T, 256, 0, st>>>(d);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}

@@ -1,0 +1,204 @@
+// Shared device helpers of libfsgs: launch checks, the splat->screen matrix, the render-record layout.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fsgs.h"
+
+#define FSGS_LAUNCH_CHECK()                                  \
+  do {                                                       \
+    if (cudaGetLastError() != cudaSuccess) return FSGS_ERR_LAUNCH; \
+  } while (0)
+
+#define FSGS_REQUIRE(cond) \
+  do {                     \
+    if (!(cond)) return FSGS_ERR_INVALID_ARGUMENT; \
+  } while (0)
+
+namespace fsgs {
+
+constexpr int kTile = FSGS_TILE;
+constexpr int kTilePix = kTile * kTile;
+constexpr int kRecFloats = FSGS_RECORD_FLOATS;
+
+static inline int ceil_div(int64_t a, int64_t b) { return (int) ((a + b - 1) / b); }
+
+// Render record, 8 float4 per Gaussian (128 B, one cache line):
+//  q0: mean2D.x, mean2D.y, opacity, unused
+//  q1: A.x A.y A.z B.x        rows A, B, C of inverse_m (the adjugate of the splat->screen matrix)
+//  q2: B.y B.z C.x C.y
+//  q3: C.z Tw.x Tw.y Tw.z     Tw = row 2 of the splat->screen matrix (depth row)
+//  q4: xmin xmax ymin ymax    pixel box outside which alpha < 1/255 for certain
+//  q5: r g b normal.x
+//  q6: normal.y normal.z - -
+//  q7: unused
+constexpr int kRecQuadsUsed = 7;
+
+struct Mat3 {
+  float m[9];
+};
+
+// Tile rectangle [x0,x1) x [y0,y1) of a splat: centre +- integer radius, truncated toward zero, clamped.
+// (reference include/gaussian_render.h:33-40)
+__device__ __forceinline__ void tile_rect(float px, float py, int radius, int gx, int gy, int &x0, int &y0, int &x1,
+    int &y1) {
+  x0 = min(gx, max(0, (int) ((px - radius) / kTile)));
+  y0 = min(gy, max(0, (int) ((py - radius) / kTile)));
+  x1 = min(gx, max(0, (int) ((px + radius + kTile - 1) / kTile)));
+  y1 = min(gy, max(0, (int) ((py + radius + kTile - 1) / kTile)));
+}
+
+// Splat -> screen matrix M = Tv2s * (Tw2v[:3,:3] * [R(q)*diag(s) | p] + e_z * Tw2v[2,3]) and the view-space
+// normal.  Only the z translation of the camera enters M (reference gs_2d_fast_preprocess.cu:60-98).
+// The accumulation order of every dot product is k = 0, 1, 2 starting from zero, which fixes the
+// rounding of M; the binning's corner test downstream is sensitive to the last bit.
+__device__ __forceinline__ void splat_matrix(const float3 p, const float2 s, const float4 q, const float *__restrict__ Tw2v,
+    const float *__restrict__ Tv2s, float *M, float3 &normal) {
+  float L[9];
+  float3 n;
+  L[0] = (1 - 2 * (q.y * q.y + q.z * q.z)) * s.x;
+  L[1] = 2 * (q.x * q.y - q.z * q.w) * s.y;
+  L[2] = p.x;
+  n.x = 2 * (q.y * q.w + q.x * q.z);
+
+  L[3] = (2 * (q.x * q.y + q.z * q.w)) * s.x;
+  L[4] = (1 - 2 * (q.x * q.x + q.z * q.z)) * s.y;
+  L[5] = p.y;
+  n.y = 2 * (q.y * q.z - q.x * q.w);
+
+  L[6] = (2 * (q.x * q.z - q.y * q.w)) * s.x;
+  L[7] = 2 * (q.x * q.w + q.y * q.z) * s.y;
+  L[8] = p.z;
+  n.z = 1 - 2 * (q.x * q.x + q.y * q.y);
+
+  float t[9];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      float acc = 0;
+#pragma unroll
+      for (int k = 0; k < 3; ++k) acc += Tw2v[i * 4 + k] * L[k * 3 + j];
+      t[i * 3 + j] = acc;
+    }
+  }
+  t[8] += Tw2v[11];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) M[i] = 0;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+#pragma unroll
+      for (int k = 0; k < 3; ++k) M[i * 3 + j] += Tv2s[i * 3 + k] * t[k * 3 + j];
+    }
+  }
+  normal.x = Tw2v[0] * n.x + Tw2v[1] * n.y + Tw2v[2] * n.z;
+  normal.y = Tw2v[4] * n.x + Tw2v[5] * n.y + Tw2v[6] * n.z;
+  normal.z = Tw2v[8] * n.x + Tw2v[9] * n.y + Tw2v[10] * n.z;
+}
+
+// Adjugate of M, rows = cross products of M's columns (reference gs_2d_fast_preprocess.cu:247-255).
+__device__ __forceinline__ void adjugate(const float *m, float *im) {
+  im[0] = m[4] * m[8] - m[7] * m[5];
+  im[1] = m[7] * m[2] - m[1] * m[8];
+  im[2] = m[1] * m[5] - m[4] * m[2];
+  im[3] = m[6] * m[5] - m[3] * m[8];
+  im[4] = m[0] * m[8] - m[6] * m[2];
+  im[5] = m[3] * m[2] - m[0] * m[5];
+  im[6] = m[3] * m[7] - m[6] * m[4];
+  im[7] = m[6] * m[1] - m[0] * m[7];
+  im[8] = m[0] * m[4] - m[3] * m[1];
+}
+
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm volatile("lg2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// The six coefficients (tile units) of the conic  alpha >= 1/255  of a splat
+// (reference gs_2d_fast_preprocess.cu:282-300).
+struct Conic {
+  float xx, yy, xy, x_, y_, __;
+  __device__ __forceinline__ bool inside(float u, float v) const {
+    return xx * u * u + yy * v * v + xy * u * v + x_ * u + y_ * v + __ <= 0;
+  }
+};
+
+__device__ __forceinline__ Conic make_conic(const float *IM, float opacity) {
+  const float ln2 = 0.69314718055f;
+  float d = -2.0f * ln2 * (float(7.9886846867721655) + lg2_approx(opacity));
+  Conic c;
+  float Wxx = IM[0] * IM[0] + IM[3] * IM[3] + d * IM[6] * IM[6];
+  float Wyy = IM[1] * IM[1] + IM[4] * IM[4] + d * IM[7] * IM[7];
+  float W__ = IM[2] * IM[2] + IM[5] * IM[5] + d * IM[8] * IM[8];
+  float Wxy = 2 * (IM[0] * IM[1] + IM[3] * IM[4] + d * IM[6] * IM[7]);
+  float Wx_ = 2 * (IM[0] * IM[2] + IM[3] * IM[5] + d * IM[6] * IM[8]);
+  float Wy_ = 2 * (IM[1] * IM[2] + IM[4] * IM[5] + d * IM[7] * IM[8]);
+  c.xx = Wxx * kTile * kTile;
+  c.yy = Wyy * kTile * kTile;
+  c.xy = Wxy * kTile * kTile;
+  c.x_ = Wx_ * kTile;
+  c.y_ = Wy_ * kTile;
+  c.__ = W__;
+  return c;
+}
+
+// Calls f(tile_x, tile_y) for every tile of the rectangle with at least one corner inside the conic
+// (reference gs_2d_fast_preprocess.cu:301-318).  Column corners are evaluated once and carried down.
+template <typename F>
+__device__ __forceinline__ void for_each_covered_tile(const Conic &c, int x0, int y0, int x1, int y1, F f) {
+  for (int x = x0; x < x1; ++x) {
+    bool a = c.inside((float) x, (float) y0);
+    bool b = c.inside((float) (x + 1), (float) y0);
+    for (int y = y0; y < y1; ++y) {
+      const bool a2 = c.inside((float) x, (float) (y + 1));
+      const bool b2 = c.inside((float) (x + 1), (float) (y + 1));
+      if (a || b || a2 || b2) f(x, y);
+      a = a2, b = b2;
+    }
+  }
+}
+
+// Conservative pixel box of {alpha >= 1/255} for one splat: the projected disc u^2+v^2 <= tau plus the
+// low-pass disc around the 3-sigma box centre, padded against rounding.  An empty box (xmin > xmax)
+// means the splat can never pass the alpha cut; an infinite box means "cannot bound" (the disc crosses
+// the camera plane).  M is the splat->screen matrix, ctr the low-pass centre (means2D).
+__device__ __forceinline__ float4 alpha_box(const float *M, float2 ctr, float opacity) {
+  const float inf = __int_as_float(0x7f800000);
+  float tau = 2.0f * __logf(255.0f * opacity);  // alpha >= 1/255  <=>  rho <= tau
+  if (!(opacity > 0.0f) || !(tau == tau)) return make_float4(1.0f, -1.0f, 1.0f, -1.0f);
+  tau = tau * 1.002f + 0.02f;
+  if (tau <= 0.0f) return make_float4(1.0f, -1.0f, 1.0f, -1.0f);
+  const float r2d = sqrtf(0.5f * tau) + 0.5f;
+  float4 box = make_float4(ctr.x - r2d, ctr.x + r2d, ctr.y - r2d, ctr.y + r2d);
+  const float d = tau * (M[6] * M[6] + M[7] * M[7]) - M[8] * M[8];
+  if (!(d < -1e-6f * M[8] * M[8])) return make_float4(-inf, inf, -inf, inf);
+  const float fx = tau / d, fz = -1.0f / d;
+  const float cx = fx * (M[0] * M[6] + M[1] * M[7]) + fz * (M[2] * M[8]);
+  const float cy = fx * (M[3] * M[6] + M[4] * M[7]) + fz * (M[5] * M[8]);
+  const float hx2 = cx * cx - (fx * (M[0] * M[0] + M[1] * M[1]) + fz * (M[2] * M[2]));
+  const float hy2 = cy * cy - (fx * (M[3] * M[3] + M[4] * M[4]) + fz * (M[5] * M[5]));
+  const float hx = sqrtf(fmaxf(hx2, 0.0f)) * 1.01f + 0.5f + 1e-4f * fabsf(cx);
+  const float hy = sqrtf(fmaxf(hy2, 0.0f)) * 1.01f + 0.5f + 1e-4f * fabsf(cy);
+  if (!(hx == hx) || !(hy == hy)) return make_float4(-inf, inf, -inf, inf);
+  box.x = fminf(box.x, cx - hx);
+  box.y = fmaxf(box.y, cx + hx);
+  box.z = fminf(box.z, cy - hy);
+  box.w = fmaxf(box.w, cy + hy);
+  return box;
+}
+
+__device__ __forceinline__ void write_record(float4 *rec, float2 xy, float opacity, const float *im, const float *M,
+    float4 box, float3 rgb, float3 nrm) {
+  rec[0] = make_float4(xy.x, xy.y, opacity, 0.0f);
+  rec[1] = make_float4(im[0], im[1], im[2], im[3]);
+  rec[2] = make_float4(im[4], im[5], im[6], im[7]);
+  rec[3] = make_float4(im[8], M[6], M[7], M[8]);
+  rec[4] = box;
+  rec[5] = make_float4(rgb.x, rgb.y, rgb.z, nrm.x);
+  rec[6] = make_float4(nrm.y, nrm.z, 0.0f, 0.0f);
+}
+
+}  // namespace fsgs

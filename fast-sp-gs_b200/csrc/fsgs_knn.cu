@@ -1,0 +1,287 @@
+// Exact nearest control-point search in fp32 SIMT: top-1 (any dimension) and top-K (3-D).
+// Control points are staged through shared memory in chunks; every thread owns one query and scans the chunk
+// with broadcast reads.  Squared distances are accumulated by direct differences in dimension order
+// (reference src/other/cdist_top.cu:19-23) with the multiply and the add kept separate (no FMA), so indices
+// and distances are identical to a plain CPU loop.
+#include "fsgs_common.cuh"
+
+namespace fsgs {
+
+constexpr int kChunk = 1024;  // control points per shared-memory chunk (3-D path)
+
+template <int D>
+__global__ void __launch_bounds__(128) cdist_top_kernel(int N, int M, const float *__restrict__ x1,
+    const float *__restrict__ x2, int largest, float *__restrict__ dist, int64_t *__restrict__ index) {
+  __shared__ float s_c[kChunk * D];
+  const int b = blockIdx.y;
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const float *c = x2 + (size_t) b * M * D;
+  float p[D];
+  if (n < N) {
+#pragma unroll
+    for (int k = 0; k < D; ++k) p[k] = x1[((size_t) b * N + n) * D + k];
+  }
+  float best = 0;
+  int besti = 0;
+  for (int m0 = 0; m0 < M; m0 += kChunk) {
+    const int cnt = min(kChunk, M - m0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < cnt * D; e += blockDim.x) s_c[e] = c[(size_t) m0 * D + e];
+    __syncthreads();
+    if (n < N) {
+      for (int m = 0; m < cnt; ++m) {
+        float sum = 0;
+#pragma unroll
+        for (int k = 0; k < D; ++k) {
+          const float t = p[k] - s_c[m * D + k];
+          sum = __fadd_rn(sum, __fmul_rn(t, t));
+        }
+        // replace when (sum > best) == largest: exact ties go to the last index when searching the nearest
+        if ((m0 + m) == 0 || (int) (sum > best) == largest) best = sum, besti = m0 + m;
+      }
+    }
+  }
+  if (n < N) {
+    dist[(size_t) b * N + n] = sqrtf(best);
+    index[(size_t) b * N + n] = besti;
+  }
+}
+
+// any dimension: control points read through the cache
+__global__ void __launch_bounds__(128) cdist_top_generic_kernel(int N, int M, int D, const float *__restrict__ x1,
+    const float *__restrict__ x2, int largest, float *__restrict__ dist, int64_t *__restrict__ index) {
+  const int b = blockIdx.y;
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float *p = x1 + ((size_t) b * N + n) * D;
+  const float *c = x2 + (size_t) b * M * D;
+  float best = 0;
+  int besti = 0;
+  for (int m = 0; m < M; ++m) {
+    float sum = 0;
+    for (int k = 0; k < D; ++k) {
+      const float t = p[k] - __ldg(c + (size_t) m * D + k);
+      sum = __fadd_rn(sum, __fmul_rn(t, t));
+    }
+    if (m == 0 || (int) (sum > best) == largest) best = sum, besti = m;
+  }
+  dist[(size_t) b * N + n] = sqrtf(best);
+  index[(size_t) b * N + n] = besti;
+}
+
+// (reference src/other/cdist_top.cu:86-105)
+__global__ void __launch_bounds__(256) cdist_top_backward_kernel(int B, int N, int M, int D, const float *__restrict__ x1,
+    const float *__restrict__ x2, const float *__restrict__ dist, const int64_t *__restrict__ index,
+    const float *__restrict__ grad_dist, float *__restrict__ g1, float *__restrict__ g2) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * N) return;
+  const int b = i / N;
+  const size_t j = (size_t) b * M + (size_t) index[i];
+  const float g = grad_dist[i] / dist[i];
+  for (int k = 0; k < D; ++k) {
+    const float t = g * (x1[(size_t) i * D + k] - x2[j * D + k]);
+    g1[(size_t) i * D + k] = t;
+    atomicAdd(g2 + j * D + k, -t);
+  }
+}
+
+// K nearest, ascending by (distance, index).  A candidate replaces the current worst only when strictly
+// closer, and is inserted after entries of equal distance, so ties keep the lower index first.
+template <int K>
+__global__ void __launch_bounds__(128) knn3_kernel(int N, int M, const float *__restrict__ x, const float *__restrict__ c,
+    float *__restrict__ d2, int64_t *__restrict__ index) {
+  __shared__ float s_c[kChunk * 3];
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  float px = 0, py = 0, pz = 0;
+  if (n < N) px = x[3 * (size_t) n], py = x[3 * (size_t) n + 1], pz = x[3 * (size_t) n + 2];
+  float bd[K];
+  int bi[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) bd[k] = __int_as_float(0x7f800000), bi[k] = -1;
+  for (int m0 = 0; m0 < M; m0 += kChunk) {
+    const int cnt = min(kChunk, M - m0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < cnt * 3; e += blockDim.x) s_c[e] = c[(size_t) m0 * 3 + e];
+    __syncthreads();
+    if (n < N) {
+      for (int m = 0; m < cnt; ++m) {
+        const float tx = px - s_c[3 * m], ty = py - s_c[3 * m + 1], tz = pz - s_c[3 * m + 2];
+        const float sum = __fadd_rn(__fadd_rn(__fmul_rn(tx, tx), __fmul_rn(ty, ty)), __fmul_rn(tz, tz));
+        if (sum < bd[K - 1]) {
+          bd[K - 1] = sum, bi[K - 1] = m0 + m;
+#pragma unroll
+          for (int k = K - 1; k > 0; --k) {
+            if (bd[k - 1] > bd[k]) {
+              const float td = bd[k];
+              bd[k] = bd[k - 1], bd[k - 1] = td;
+              const int ti = bi[k];
+              bi[k] = bi[k - 1], bi[k - 1] = ti;
+            }
+          }
+        }
+      }
+    }
+  }
+  if (n < N) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) d2[(size_t) n * K + k] = bd[k], index[(size_t) n * K + k] = bi[k];
+  }
+}
+
+template <int K>
+static void launch_knn(int N, int M, const float *x, const float *c, float *d2, int64_t *index, cudaStream_t st) {
+  knn3_kernel<K><<<ceil_div(N, 128), 128, 0, st>>>(N, M, x, c, d2, index);
+}
+
+// ------------------------------------------------------------------------------------------------
+// masked Adam (reference src/other/adam_masked_update.cu:9-28): same operation order per element
+// ------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void adam_element(float &p, float g, float &m, float &v, float lr, float b1, float b2,
+    float eps) {
+  m = b1 * m + (1.0f - b1) * g;
+  v = b2 * v + (1.0f - b2) * g * g;
+  const float step = -lr * m / (sqrtf(v) + eps);
+  p += step;
+}
+
+__global__ void __launch_bounds__(256) adam_masked_kernel(float *__restrict__ param, const float *__restrict__ grad,
+    float *__restrict__ exp_avg, float *__restrict__ exp_avg_sq, const uint8_t *__restrict__ visible, float lr, float b1,
+    float b2, float eps, long long N, int M) {
+  const long long total = N * M;
+  for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long) gridDim.x * blockDim.x) {
+    if (!visible[i / M]) continue;
+    float p = param[i], m = exp_avg[i], v = exp_avg_sq[i];
+    adam_element(p, grad[i], m, v, lr, b1, b2, eps);
+    param[i] = p, exp_avg[i] = m, exp_avg_sq[i] = v;
+  }
+}
+
+struct AdamMulti {
+  fsgs_adam_tensor t[FSGS_ADAM_MAX_TENSORS];
+  int n;
+};
+
+// One launch for all tensors: a warp walks one Gaussian's rows of every tensor, so the mask is read once per
+// Gaussian and each tensor's row is touched with consecutive lanes.
+__global__ void __launch_bounds__(256) adam_masked_multi_kernel(AdamMulti a, const uint8_t *__restrict__ visible,
+    long long N, float b1, float b2) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long) gridDim.x * blockDim.x) >> 5;
+  for (long long n = warp0; n < N; n += nwarps) {
+    if (!visible[n]) continue;
+    for (int k = 0; k < a.n; ++k) {
+      const fsgs_adam_tensor &t = a.t[k];
+      for (int e = lane; e < t.M; e += 32) {
+        const long long i = n * t.M + e;
+        float p = t.param[i], m = t.exp_avg[i], v = t.exp_avg_sq[i];
+        adam_element(p, t.grad[i], m, v, t.lr, b1, b2, t.eps);
+        t.param[i] = p, t.exp_avg[i] = m, t.exp_avg_sq[i] = v;
+      }
+    }
+  }
+}
+
+}  // namespace fsgs
+
+using namespace fsgs;
+
+extern "C" const char *fsgs_status_string(int status) {
+  switch (status) {
+    case FSGS_OK: return "ok";
+    case FSGS_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case FSGS_ERR_UNSUPPORTED: return "unsupported option";
+    case FSGS_ERR_WORKSPACE: return "workspace too small";
+    case FSGS_ERR_LAUNCH: return "kernel launch failed";
+    case FSGS_ERR_LIMIT: return "size beyond the documented maximum";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int fsgs_version(void) { return 100; }
+
+extern "C" int fsgs_cdist_top(int B, int N, int M, int D, const float *x1, const float *x2, int largest, float *dist,
+    int64_t *index, fsgs_stream_t stream) {
+  FSGS_REQUIRE(B >= 0 && N >= 0 && M > 0 && D > 0 && x1 && x2 && dist && index);
+  if (B == 0 || N == 0) return FSGS_OK;
+  cudaStream_t st = (cudaStream_t) stream;
+  const dim3 grid(ceil_div(N, 128), B);
+  largest = largest ? 1 : 0;
+  if (D == 3) cdist_top_kernel<3><<<grid, 128, 0, st>>>(N, M, x1, x2, largest, dist, index);
+  else if (D == 2) cdist_top_kernel<2><<<grid, 128, 0, st>>>(N, M, x1, x2, largest, dist, index);
+  else cdist_top_generic_kernel<<<grid, 128, 0, st>>>(N, M, D, x1, x2, largest, dist, index);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_cdist_top_backward(int B, int N, int M, int D, const float *x1, const float *x2,
+    const float *dist, const int64_t *index, const float *grad_dist, float *g1, float *g2, fsgs_stream_t stream) {
+  FSGS_REQUIRE(B >= 0 && N >= 0 && M > 0 && D > 0 && x1 && x2 && dist && index && grad_dist && g1 && g2);
+  cudaStream_t st = (cudaStream_t) stream;
+  cudaMemsetAsync(g2, 0, sizeof(float) * (size_t) B * M * D, st);
+  if (B == 0 || N == 0) return FSGS_OK;
+  cdist_top_backward_kernel<<<ceil_div((int64_t) B * N, 256), 256, 0, st>>>(B, N, M, D, x1, x2, dist, index, grad_dist,
+      g1, g2);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_knn(int N, int M, int K, const float *x, const float *c, float *d2, int64_t *index,
+    fsgs_stream_t stream) {
+  FSGS_REQUIRE(N >= 0 && M > 0 && K > 0 && x && c && d2 && index);
+  if (K > FSGS_KNN_MAX_K) return FSGS_ERR_LIMIT;
+  if (N == 0) return FSGS_OK;
+  cudaStream_t st = (cudaStream_t) stream;
+  switch (K) {
+    case 1: launch_knn<1>(N, M, x, c, d2, index, st); break;
+    case 2: launch_knn<2>(N, M, x, c, d2, index, st); break;
+    case 3: launch_knn<3>(N, M, x, c, d2, index, st); break;
+    case 4: launch_knn<4>(N, M, x, c, d2, index, st); break;
+    case 5: launch_knn<5>(N, M, x, c, d2, index, st); break;
+    case 6: launch_knn<6>(N, M, x, c, d2, index, st); break;
+    case 7: launch_knn<7>(N, M, x, c, d2, index, st); break;
+    case 8: launch_knn<8>(N, M, x, c, d2, index, st); break;
+    case 9: launch_knn<9>(N, M, x, c, d2, index, st); break;
+    case 10: launch_knn<10>(N, M, x, c, d2, index, st); break;
+    case 11: launch_knn<11>(N, M, x, c, d2, index, st); break;
+    case 12: launch_knn<12>(N, M, x, c, d2, index, st); break;
+    case 13: launch_knn<13>(N, M, x, c, d2, index, st); break;
+    case 14: launch_knn<14>(N, M, x, c, d2, index, st); break;
+    case 15: launch_knn<15>(N, M, x, c, d2, index, st); break;
+    default: launch_knn<16>(N, M, x, c, d2, index, st); break;
+  }
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_adam_masked(float *param, const float *grad, float *exp_avg, float *exp_avg_sq,
+    const uint8_t *visible, float lr, float b1, float b2, float eps, int64_t N, int64_t M, fsgs_stream_t stream) {
+  FSGS_REQUIRE(param && grad && exp_avg && exp_avg_sq && visible && N >= 0 && M > 0 && M < (1ll << 31));
+  if (N == 0) return FSGS_OK;
+  const int64_t total = N * M;
+  const int blocks = (int) (total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+  adam_masked_kernel<<<blocks, 256, 0, (cudaStream_t) stream>>>(param, grad, exp_avg, exp_avg_sq, visible, lr, b1, b2,
+      eps, (long long) N, (int) M);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *tensors, const uint8_t *visible,
+    int64_t N, float b1, float b2, fsgs_stream_t stream) {
+  FSGS_REQUIRE(n_tensors > 0 && tensors && visible && N >= 0);
+  if (n_tensors > FSGS_ADAM_MAX_TENSORS) return FSGS_ERR_LIMIT;
+  AdamMulti a;
+  a.n = n_tensors;
+  for (int k = 0; k < n_tensors; ++k) {
+    FSGS_REQUIRE(tensors[k].param && tensors[k].grad && tensors[k].exp_avg && tensors[k].exp_avg_sq && tensors[k].M > 0);
+    a.t[k] = tensors[k];
+  }
+  if (N == 0) return FSGS_OK;
+  const int64_t warps_wanted = N;
+  const int blocks = (int) (warps_wanted / 8 + 1 < 148 * 16 ? warps_wanted / 8 + 1 : 148 * 16);
+  adam_masked_multi_kernel<<<blocks, 256, 0, (cudaStream_t) stream>>>(a, visible, (long long) N, b1, b2);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}

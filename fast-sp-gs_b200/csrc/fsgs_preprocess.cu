@@ -1,0 +1,718 @@
+// Per-Gaussian stages of the surfel renderer: LBS warp, projection (splat->screen matrix, bounds, SH colour),
+// their adjoints, and the packed render record.  One thread per Gaussian; every kernel is HBM bound.
+#include "fsgs_common.cuh"
+#include "fsgs_sh.cuh"
+
+namespace fsgs {
+
+// ------------------------------------------------------------------------------------------------
+// LBS warp
+// ------------------------------------------------------------------------------------------------
+
+struct LbsDev {
+  int K, M;
+  const float *xyz, *scaling_raw, *rotation_raw;
+  const int64_t *knn_idx;
+  const float *knn_w;
+  const float4 *sp_q;
+  const float *sp_t;
+  const float4 *sp_dr;
+  const float2 *sp_ds;
+};
+
+static LbsDev to_dev(const fsgs_lbs *l) {
+  LbsDev d;
+  d.K = l->K, d.M = l->M;
+  d.xyz = l->xyz, d.scaling_raw = l->scaling_raw, d.rotation_raw = l->rotation_raw;
+  d.knn_idx = l->knn_idx, d.knn_w = l->knn_w;
+  d.sp_q = (const float4 *) l->sp_q, d.sp_t = l->sp_t;
+  d.sp_dr = (const float4 *) l->sp_dr, d.sp_ds = (const float2 *) l->sp_ds;
+  return d;
+}
+
+static bool lbs_valid(const fsgs_lbs *l) {
+  return l->K > 0 && l->K <= FSGS_KNN_MAX_K && l->M > 0 && l->xyz && l->scaling_raw && l->rotation_raw &&
+         l->knn_idx && l->knn_w && l->sp_q && l->sp_t && l->sp_dr && l->sp_ds;
+}
+
+__device__ __forceinline__ float3 quat_rotate(const float4 q, const float3 p) {
+  const float r00 = 1 - 2 * (q.y * q.y + q.z * q.z), r01 = 2 * (q.x * q.y - q.z * q.w), r02 = 2 * (q.y * q.w + q.x * q.z);
+  const float r10 = 2 * (q.x * q.y + q.z * q.w), r11 = 1 - 2 * (q.x * q.x + q.z * q.z), r12 = 2 * (q.y * q.z - q.x * q.w);
+  const float r20 = 2 * (q.x * q.z - q.y * q.w), r21 = 2 * (q.x * q.w + q.y * q.z), r22 = 1 - 2 * (q.x * q.x + q.y * q.y);
+  return make_float3(r00 * p.x + r01 * p.y + r02 * p.z, r10 * p.x + r11 * p.y + r12 * p.z,
+      r20 * p.x + r21 * p.y + r22 * p.z);
+}
+
+__device__ __forceinline__ float3 quat_rotate_T(const float4 q, const float3 p) {
+  return quat_rotate(make_float4(-q.x, -q.y, -q.z, q.w), p);
+}
+
+// Adjoint of q -> R(q) given dL/dR (row major 3x3).  (reference include/ops_3d.h:126-134)
+__device__ __forceinline__ float4 quat_adjoint(const float4 q, const float *dR) {
+  float4 g;
+  g.x = 2 * (-2 * q.x * (dR[4] + dR[8]) + q.y * (dR[1] + dR[3]) + q.z * (dR[2] + dR[6]) + q.w * (dR[7] - dR[5]));
+  g.y = 2 * (q.x * (dR[1] + dR[3]) - 2 * q.y * (dR[0] + dR[8]) + q.z * (dR[5] + dR[7]) + q.w * (dR[2] - dR[6]));
+  g.z = 2 * (q.x * (dR[2] + dR[6]) + q.y * (dR[5] + dR[7]) - 2 * q.z * (dR[0] + dR[4]) + q.w * (dR[3] - dR[1]));
+  g.w = 2 * (q.x * (dR[7] - dR[5]) + q.y * (dR[2] - dR[6]) + q.z * (dR[3] - dR[1]));
+  return g;
+}
+
+__device__ __forceinline__ void lbs_warp_one(const LbsDev &l, int i, float3 &mean, float2 &scale, float4 &rot) {
+  const float3 p = make_float3(l.xyz[3 * i], l.xyz[3 * i + 1], l.xyz[3 * i + 2]);
+  float3 acc = make_float3(0, 0, 0);
+  float4 dr = make_float4(0, 0, 0, 0);
+  float2 ds = make_float2(0, 0);
+  for (int k = 0; k < l.K; ++k) {
+    const int m = (int) l.knn_idx[(size_t) i * l.K + k];
+    const float w = l.knn_w[(size_t) i * l.K + k];
+    const float4 q = __ldg(l.sp_q + m);
+    const float3 r = quat_rotate(q, p);
+    acc.x += (r.x + __ldg(l.sp_t + 3 * m + 0)) * w;
+    acc.y += (r.y + __ldg(l.sp_t + 3 * m + 1)) * w;
+    acc.z += (r.z + __ldg(l.sp_t + 3 * m + 2)) * w;
+    const float4 a = __ldg(l.sp_dr + m);
+    dr.x += a.x * w, dr.y += a.y * w, dr.z += a.z * w, dr.w += a.w * w;
+    const float2 b = __ldg(l.sp_ds + m);
+    ds.x += b.x * w, ds.y += b.y * w;
+  }
+  mean = make_float3(p.x + (acc.x - p.x), p.y + (acc.y - p.y), p.z + (acc.z - p.z));
+  scale = make_float2(expf(l.scaling_raw[2 * i]) + ds.x, expf(l.scaling_raw[2 * i + 1]) + ds.y);
+  const float4 r0 = reinterpret_cast<const float4 *>(l.rotation_raw)[i];
+  const float4 r = make_float4(r0.x + dr.x, r0.y + dr.y, r0.z + dr.z, r0.w + dr.w);
+  const float inv = 1.0f / fmaxf(sqrtf(r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w), 1e-12f);
+  rot = make_float4(r.x * inv, r.y * inv, r.z * inv, r.w * inv);
+}
+
+__global__ void __launch_bounds__(256) lbs_warp_forward_kernel(int P, LbsDev l, float *__restrict__ means,
+    float2 *__restrict__ scales, float4 *__restrict__ rots) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  float3 m;
+  float2 s;
+  float4 q;
+  lbs_warp_one(l, i, m, s, q);
+  means[3 * i] = m.x, means[3 * i + 1] = m.y, means[3 * i + 2] = m.z;
+  scales[i] = s;
+  rots[i] = q;
+}
+
+// Superpoint gradient table row: q(4) t(3) dr(4) ds(2) = 13 floats.
+constexpr int kSpRow = 13;
+
+template <bool SMEM_TABLE>
+__global__ void __launch_bounds__(256) lbs_warp_backward_kernel(int P, LbsDev l, const float *__restrict__ g_means,
+    const float2 *__restrict__ g_scales, const float4 *__restrict__ g_rots, float *__restrict__ g_xyz,
+    float2 *__restrict__ g_scaling_raw, float4 *__restrict__ g_rotation_raw, float *__restrict__ g_knn_w,
+    float *__restrict__ g_sp_q, float *__restrict__ g_sp_t, float *__restrict__ g_sp_dr, float *__restrict__ g_sp_ds) {
+  extern __shared__ float table[];  // [M, 13] when SMEM_TABLE
+  if (SMEM_TABLE) {
+    for (int k = threadIdx.x; k < l.M * kSpRow; k += blockDim.x) table[k] = 0.0f;
+    __syncthreads();
+  }
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < P; i += gridDim.x * blockDim.x) {
+    const float3 p = make_float3(l.xyz[3 * i], l.xyz[3 * i + 1], l.xyz[3 * i + 2]);
+    const float3 gm = make_float3(g_means[3 * i], g_means[3 * i + 1], g_means[3 * i + 2]);
+    const float2 gs = g_scales[i];
+    // adjoint of the quaternion normalisation
+    float4 dr = make_float4(0, 0, 0, 0);
+    for (int k = 0; k < l.K; ++k) {
+      const int m = (int) l.knn_idx[(size_t) i * l.K + k];
+      const float w = l.knn_w[(size_t) i * l.K + k];
+      const float4 a = __ldg(l.sp_dr + m);
+      dr.x += a.x * w, dr.y += a.y * w, dr.z += a.z * w, dr.w += a.w * w;
+    }
+    const float4 r0 = reinterpret_cast<const float4 *>(l.rotation_raw)[i];
+    const float4 r = make_float4(r0.x + dr.x, r0.y + dr.y, r0.z + dr.z, r0.w + dr.w);
+    const float nrm = fmaxf(sqrtf(r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w), 1e-12f);
+    const float inv = 1.0f / nrm;
+    const float4 y = make_float4(r.x * inv, r.y * inv, r.z * inv, r.w * inv);
+    const float4 gy = g_rots[i];
+    const float yd = y.x * gy.x + y.y * gy.y + y.z * gy.z + y.w * gy.w;
+    const float4 gr = make_float4((gy.x - y.x * yd) * inv, (gy.y - y.y * yd) * inv, (gy.z - y.z * yd) * inv,
+        (gy.w - y.w * yd) * inv);
+    g_rotation_raw[i] = gr;
+    g_scaling_raw[i] = make_float2(gs.x * expf(l.scaling_raw[2 * i]), gs.y * expf(l.scaling_raw[2 * i + 1]));
+
+    float3 gx = make_float3(0, 0, 0);
+    for (int k = 0; k < l.K; ++k) {
+      const int m = (int) l.knn_idx[(size_t) i * l.K + k];
+      const float w = l.knn_w[(size_t) i * l.K + k];
+      const float4 q = __ldg(l.sp_q + m);
+      const float3 rp = quat_rotate(q, p);
+      const float3 moved = make_float3(rp.x + __ldg(l.sp_t + 3 * m), rp.y + __ldg(l.sp_t + 3 * m + 1),
+          rp.z + __ldg(l.sp_t + 3 * m + 2));
+      const float4 a = __ldg(l.sp_dr + m);
+      const float2 b = __ldg(l.sp_ds + m);
+      g_knn_w[(size_t) i * l.K + k] = gm.x * moved.x + gm.y * moved.y + gm.z * moved.z +
+                                      (gr.x * a.x + gr.y * a.y + gr.z * a.z + gr.w * a.w) + (gs.x * b.x + gs.y * b.y);
+      const float3 back = quat_rotate_T(q, gm);
+      gx.x += w * back.x, gx.y += w * back.y, gx.z += w * back.z;
+      // dL/dR = w * gm (outer) p
+      float dR[9];
+      dR[0] = w * gm.x * p.x, dR[1] = w * gm.x * p.y, dR[2] = w * gm.x * p.z;
+      dR[3] = w * gm.y * p.x, dR[4] = w * gm.y * p.y, dR[5] = w * gm.y * p.z;
+      dR[6] = w * gm.z * p.x, dR[7] = w * gm.z * p.y, dR[8] = w * gm.z * p.z;
+      const float4 gq = quat_adjoint(q, dR);
+      const float row[kSpRow] = {gq.x, gq.y, gq.z, gq.w, w * gm.x, w * gm.y, w * gm.z, w * gr.x, w * gr.y, w * gr.z,
+          w * gr.w, w * gs.x, w * gs.y};
+      if (SMEM_TABLE) {
+#pragma unroll
+        for (int c = 0; c < kSpRow; ++c) atomicAdd(table + m * kSpRow + c, row[c]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) atomicAdd(g_sp_q + 4 * m + c, row[c]);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) atomicAdd(g_sp_t + 3 * m + c, row[4 + c]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) atomicAdd(g_sp_dr + 4 * m + c, row[7 + c]);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) atomicAdd(g_sp_ds + 2 * m + c, row[11 + c]);
+      }
+    }
+    g_xyz[3 * i] = gx.x, g_xyz[3 * i + 1] = gx.y, g_xyz[3 * i + 2] = gx.z;
+  }
+  if (SMEM_TABLE) {
+    __syncthreads();
+    for (int k = threadIdx.x; k < l.M * kSpRow; k += blockDim.x) {
+      const float v = table[k];
+      if (v == 0.0f) continue;
+      const int m = k / kSpRow, c = k % kSpRow;
+      if (c < 4) atomicAdd(g_sp_q + 4 * m + c, v);
+      else if (c < 7) atomicAdd(g_sp_t + 3 * m + (c - 4), v);
+      else if (c < 11) atomicAdd(g_sp_dr + 4 * m + (c - 7), v);
+      else atomicAdd(g_sp_ds + 2 * m + (c - 11), v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// preprocess forward
+// ------------------------------------------------------------------------------------------------
+
+struct PreDev {
+  int P, W, H, sh_degree, n_dc, n_rest, gx, gy;
+  const float *means;
+  const float2 *scales;
+  const float4 *rots;
+  const float *opac, *shs, *sh_rest, *Tw2v, *Tv2s, *campos, *trans_precomp;
+  const uint8_t *culling;
+  float *warped_means;
+  float2 *warped_scales;
+  float4 *warped_rots;
+  float2 *means2D;
+  float *colors, *trans_mat, *inverse_m;
+  float4 *normal_opacity;
+  float *depths;
+  int32_t *radii, *tiles_touched;
+  float4 *records;
+  int32_t *tile_counts;
+  unsigned long long *counters;
+};
+
+__device__ __forceinline__ const float *sh_coef(const PreDev &a, int i, int k) {
+  if (a.sh_rest == nullptr) return a.shs + ((size_t) i * a.n_dc + k) * 3;
+  return k == 0 ? a.shs + (size_t) i * a.n_dc * 3 : a.sh_rest + ((size_t) i * a.n_rest + (k - 1)) * 3;
+}
+
+template <bool LBS>
+__global__ void __launch_bounds__(256) preprocess_forward_kernel(PreDev a, LbsDev lbs) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ float cam[16 + 9 + 3];
+  if (threadIdx.x < 16) cam[threadIdx.x] = a.Tw2v[threadIdx.x];
+  else if (threadIdx.x < 25) cam[threadIdx.x] = a.Tv2s[threadIdx.x - 16];
+  else if (threadIdx.x < 28) cam[threadIdx.x] = a.campos[threadIdx.x - 25];
+  __syncthreads();
+  const float *Tw2v = cam, *Tv2s = cam + 16, *campos = cam + 25;
+
+  int area = 0, real = 0;
+  if (i < a.P) {
+    float3 p;
+    float2 s;
+    float4 q;
+    if (LBS) {
+      lbs_warp_one(lbs, i, p, s, q);
+      a.warped_means[3 * i] = p.x, a.warped_means[3 * i + 1] = p.y, a.warped_means[3 * i + 2] = p.z;
+      a.warped_scales[i] = s;
+      a.warped_rots[i] = q;
+    } else {
+      p = make_float3(a.means[3 * i], a.means[3 * i + 1], a.means[3 * i + 2]);
+    }
+    bool vis = !(a.culling && a.culling[i]);
+    float M[9], IM[9];
+    float3 nrm = make_float3(0, 0, 0), rgb = make_float3(0, 0, 0);
+    float2 ctr = make_float2(0, 0);
+    float vz = 0, opacity = 0, radius = 0;
+    int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
+    if (vis) {
+      const float vx = Tw2v[0] * p.x + Tw2v[1] * p.y + Tw2v[2] * p.z + Tw2v[3];
+      const float vy = Tw2v[4] * p.x + Tw2v[5] * p.y + Tw2v[6] * p.z + Tw2v[7];
+      vz = Tw2v[8] * p.x + Tw2v[9] * p.y + Tw2v[10] * p.z + Tw2v[11];
+      vis = !(vz <= 0.2f);
+      if (vis) {
+        opacity = a.opac[i];
+        if (a.trans_precomp == nullptr) {
+          if (!LBS) s = a.scales[i], q = a.rots[i];
+          splat_matrix(p, s, q, Tw2v, Tv2s, M, nrm);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 9; ++k) M[k] = a.trans_precomp[(size_t) 9 * i + k];
+          nrm = make_float3(0.0f, 0.0f, 1.0f);
+        }
+        const float tx = vx * nrm.x, ty = vy * nrm.y, tz = vz * nrm.z;
+        const float c = -(tx + ty + tz);
+        if (c == 0) vis = false;
+        const float sgn = c > 0 ? 1.0f : -1.0f;
+        nrm = make_float3(sgn * nrm.x, sgn * nrm.y, sgn * nrm.z);
+      }
+      if (vis) {
+        // bounding box at cutoff 3 (reference gs_2d_fast_preprocess.cu:143-158)
+        const float t0 = 3.0f * 3.0f, t2 = -1.0f;
+        const float d = t0 * (M[6] * M[6]) + t0 * (M[7] * M[7]) + t2 * (M[8] * M[8]);
+        if (d == 0.0f) {
+          vis = false;
+        } else {
+          const float inv_d = 1 / d;
+          const float f0 = inv_d * t0, f2 = inv_d * t2;
+          ctr.x = f0 * (M[0] * M[6]) + f0 * (M[1] * M[7]) + f2 * (M[2] * M[8]);
+          ctr.y = f0 * (M[3] * M[6]) + f0 * (M[4] * M[7]) + f2 * (M[5] * M[8]);
+          const float hx = ctr.x * ctr.x - (f0 * (M[0] * M[0]) + f0 * (M[1] * M[1]) + f2 * (M[2] * M[2]));
+          const float hy = ctr.y * ctr.y - (f0 * (M[3] * M[3]) + f0 * (M[4] * M[4]) + f2 * (M[5] * M[5]));
+          const float ex = sqrtf(fmaxf(1e-4f, hx)), ey = sqrtf(fmaxf(1e-4f, hy));
+          radius = ceilf(fmaxf(fmaxf(ex, ey), 3.0f * float(0.707106)));
+          tile_rect(ctr.x, ctr.y, (int) radius, a.gx, a.gy, x0, y0, x1, y1);
+          if ((x1 - x0) * (y1 - y0) == 0) vis = false;
+        }
+      }
+    }
+    if (vis) {
+      if (a.sh_degree >= 0) {
+        float x = p.x - campos[0], y = p.y - campos[1], z = p.z - campos[2];
+        const float n = rsqrtf(x * x + y * y + z * z + 1e-12f);
+        x *= n, y *= n, z *= n;
+        float b[16];
+        sh_basis(a.sh_degree, x, y, z, b);
+        const int nb = (a.sh_degree + 1) * (a.sh_degree + 1);
+        for (int k = 0; k < nb; ++k) {
+          const float *c = sh_coef(a, i, k);
+          rgb.x += __ldg(c) * b[k], rgb.y += __ldg(c + 1) * b[k], rgb.z += __ldg(c + 2) * b[k];
+        }
+        rgb = make_float3(fmaxf(rgb.x + 0.5f, 0.0f), fmaxf(rgb.y + 0.5f, 0.0f), fmaxf(rgb.z + 0.5f, 0.0f));
+      } else {
+        rgb = make_float3(a.shs[3 * i], a.shs[3 * i + 1], a.shs[3 * i + 2]);
+      }
+      adjugate(M, IM);
+      area = (y1 - y0) * (x1 - x0);
+      // count (and histogram) the tiles with a corner inside the alpha >= 1/255 conic
+      const Conic cn = make_conic(IM, opacity);
+      const int gx = a.gx;
+      int32_t *tc = a.tile_counts;
+      for_each_covered_tile(cn, x0, y0, x1, y1, [&](int x, int y) {
+        atomicAdd(tc + y * gx + x, 1);
+        ++real;
+      });
+    } else {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) M[k] = 0.0f, IM[k] = 0.0f;
+      nrm = make_float3(0, 0, 0);
+      ctr = make_float2(0, 0);
+      vz = 0, opacity = 0, radius = 0;
+    }
+    // every row is written: zeros for culled Gaussians
+    a.means2D[i] = ctr;
+    if (a.sh_degree >= 0) a.colors[3 * i] = rgb.x, a.colors[3 * i + 1] = rgb.y, a.colors[3 * i + 2] = rgb.z;
+    if (a.trans_precomp == nullptr) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) a.trans_mat[(size_t) 9 * i + k] = M[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 9; ++k) a.inverse_m[(size_t) 9 * i + k] = IM[k];
+    a.normal_opacity[i] = make_float4(nrm.x, nrm.y, nrm.z, opacity);
+    a.depths[i] = vz;
+    a.radii[i] = (int) radius;
+    a.tiles_touched[i] = area;
+    if (a.records) {
+      const float4 box = vis ? alpha_box(M, ctr, opacity) : make_float4(1.0f, -1.0f, 1.0f, -1.0f);
+      write_record(a.records + (size_t) i * (kRecFloats / 4), ctr, opacity, IM, M, box, rgb, nrm);
+    }
+  }
+  // block totals -> two global atomics per block
+  __shared__ int s_area[8], s_real[8];
+  for (int o = 16; o > 0; o >>= 1) {
+    area += __shfl_xor_sync(0xffffffffu, area, o);
+    real += __shfl_xor_sync(0xffffffffu, real, o);
+  }
+  if ((threadIdx.x & 31) == 0) s_area[threadIdx.x >> 5] = area, s_real[threadIdx.x >> 5] = real;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long ta = 0, tr = 0;
+    for (int w = 0; w < 8; ++w) ta += s_area[w], tr += s_real[w];
+    if (ta) atomicAdd(a.counters + FSGS_CNT_SLOTS, (unsigned long long) ta);
+    if (tr) atomicAdd(a.counters + FSGS_CNT_PAIRS, (unsigned long long) tr);
+  }
+}
+
+__global__ void __launch_bounds__(256) pack_records_kernel(int P, const float2 *__restrict__ means2D,
+    const float *__restrict__ colors, const float4 *__restrict__ normal_opacity, const float *__restrict__ trans_mat,
+    const float *__restrict__ inverse_m, float4 *__restrict__ records) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  float M[9], IM[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) M[k] = trans_mat[(size_t) 9 * i + k], IM[k] = inverse_m[(size_t) 9 * i + k];
+  const float4 no = normal_opacity[i];
+  const float2 ctr = means2D[i];
+  const float3 rgb = make_float3(colors[3 * i], colors[3 * i + 1], colors[3 * i + 2]);
+  write_record(records + (size_t) i * (kRecFloats / 4), ctr, no.w, IM, M, alpha_box(M, ctr, no.w), rgb,
+      make_float3(no.x, no.y, no.z));
+}
+
+// ------------------------------------------------------------------------------------------------
+// standalone splat matrix, forward / backward
+// ------------------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256) transmat_forward_kernel(int P, const float *__restrict__ means,
+    const float2 *__restrict__ scales, const float4 *__restrict__ rots, const float *__restrict__ Tw2v,
+    const float *__restrict__ Tv2s, float *__restrict__ trans_mat, float *__restrict__ normals) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  float M[9];
+  float3 n;
+  splat_matrix(make_float3(means[3 * i], means[3 * i + 1], means[3 * i + 2]), scales[i], rots[i], Tw2v, Tv2s, M, n);
+#pragma unroll
+  for (int k = 0; k < 9; ++k) trans_mat[(size_t) 9 * i + k] = M[k];
+  normals[3 * i] = n.x, normals[3 * i + 1] = n.y, normals[3 * i + 2] = n.z;
+}
+
+// Adjoint of splat_matrix: gT = dL/dM, gn = dL/dnormal (view space).
+// (reference gs_2d_fast_preprocess.cu:100-139)
+__device__ __forceinline__ void splat_matrix_adjoint(const float2 s, const float4 q, const float *__restrict__ Tw2v,
+    const float *__restrict__ Tv2s, const float *gT, const float3 gn, float3 &g_mean, float2 &g_scale, float4 &g_rot) {
+  float gL[9], dR[9];
+#pragma unroll
+  for (int a = 0; a < 3; ++a)
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+      float acc = 0;
+#pragma unroll
+      for (int k = 0; k < 3; ++k) acc += Tv2s[k * 3 + a] * gT[k * 3 + b];
+      gL[a * 3 + b] = acc;
+    }
+#pragma unroll
+  for (int a = 0; a < 3; ++a)
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+      float acc = 0;
+#pragma unroll
+      for (int k = 0; k < 3; ++k) acc += Tw2v[k * 4 + a] * gL[k * 3 + b];
+      dR[a * 3 + b] = acc;
+    }
+  g_mean = make_float3(dR[2], dR[5], dR[8]);
+  dR[2] = gn.x * Tw2v[0] + gn.y * Tw2v[4] + gn.z * Tw2v[8];
+  dR[5] = gn.x * Tw2v[1] + gn.y * Tw2v[5] + gn.z * Tw2v[9];
+  dR[8] = gn.x * Tw2v[2] + gn.y * Tw2v[6] + gn.z * Tw2v[10];
+  g_scale.x = dR[0] * (1 - 2 * (q.y * q.y + q.z * q.z)) + dR[3] * (2 * (q.x * q.y + q.z * q.w)) +
+              dR[6] * (2 * (q.x * q.z - q.y * q.w));
+  g_scale.y = dR[1] * (2 * (q.x * q.y - q.z * q.w)) + dR[4] * (1 - 2 * (q.x * q.x + q.z * q.z)) +
+              dR[7] * (2 * (q.x * q.w + q.y * q.z));
+  dR[0] *= s.x, dR[3] *= s.x, dR[6] *= s.x;
+  dR[1] *= s.y, dR[4] *= s.y, dR[7] *= s.y;
+  g_rot = quat_adjoint(q, dR);
+}
+
+__global__ void __launch_bounds__(256) transmat_backward_kernel(int P, const float2 *__restrict__ scales,
+    const float4 *__restrict__ rots, const float *__restrict__ Tw2v, const float *__restrict__ Tv2s,
+    const float *__restrict__ g_trans_mat, const float *__restrict__ g_normals, float *__restrict__ g_means,
+    float2 *__restrict__ g_scales, float4 *__restrict__ g_rots) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  float gT[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) gT[k] = g_trans_mat[(size_t) 9 * i + k];
+  float3 gm;
+  float2 gs;
+  float4 gq;
+  splat_matrix_adjoint(scales[i], rots[i], Tw2v, Tv2s, gT,
+      make_float3(g_normals[3 * i], g_normals[3 * i + 1], g_normals[3 * i + 2]), gm, gs, gq);
+  g_means[3 * i] = gm.x, g_means[3 * i + 1] = gm.y, g_means[3 * i + 2] = gm.z;
+  g_scales[i] = gs;
+  g_rots[i] = gq;
+}
+
+// ------------------------------------------------------------------------------------------------
+// preprocess backward  (reference gs_2d_fast_preprocess.cu:516-609)
+// ------------------------------------------------------------------------------------------------
+
+struct PreBwdDev {
+  int P, W, H, sh_degree, n_dc, n_rest;
+  const float *means;
+  const float2 *scales;
+  const float4 *rots;
+  const float *shs, *sh_rest, *Tw2v, *Tv2s, *campos, *trans_mat, *colors;
+  const int32_t *radii;
+  float2 *g_means2D;
+  const float *g_trans_mat, *g_inverse_m, *g_colors;
+  const float4 *g_normal_opacity;
+  float *g_means;
+  float2 *g_scales;
+  float4 *g_rots;
+  float *g_opac, *g_shs, *g_sh_rest;
+};
+
+__device__ __forceinline__ float3 cross3(const float3 a, const float3 b) {
+  return make_float3(a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x);
+}
+
+__global__ void __launch_bounds__(256) preprocess_backward_kernel(PreBwdDev a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ float cam[16 + 9 + 3];
+  if (threadIdx.x < 16) cam[threadIdx.x] = a.Tw2v[threadIdx.x];
+  else if (threadIdx.x < 25) cam[threadIdx.x] = a.Tv2s[threadIdx.x - 16];
+  else if (threadIdx.x < 28) cam[threadIdx.x] = a.campos[threadIdx.x - 25];
+  __syncthreads();
+  const float *Tw2v = cam, *Tv2s = cam + 16, *campos = cam + 25;
+  if (i >= a.P || a.radii[i] <= 0) return;
+
+  const float4 gno = a.g_normal_opacity[i];
+  a.g_opac[i] = gno.w;
+  float m[9], gT[9], G[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) {
+    m[k] = a.trans_mat[(size_t) 9 * i + k];
+    gT[k] = a.g_trans_mat[(size_t) 9 * i + k];
+    G[k] = a.g_inverse_m[(size_t) 9 * i + k];
+  }
+  // adjoint of the adjugate: inverse_m rows are c1 x c2, c2 x c0, c0 x c1 with c_j the columns of M
+  {
+    const float3 c0 = make_float3(m[0], m[3], m[6]), c1 = make_float3(m[1], m[4], m[7]), c2 = make_float3(m[2], m[5], m[8]);
+    const float3 G0 = make_float3(G[0], G[1], G[2]), G1 = make_float3(G[3], G[4], G[5]), G2 = make_float3(G[6], G[7], G[8]);
+    const float3 a0 = cross3(G1, c2), b0 = cross3(c1, G2);   // d/dc0
+    const float3 a1 = cross3(c2, G0), b1 = cross3(G2, c0);   // d/dc1
+    const float3 a2 = cross3(G0, c1), b2 = cross3(c0, G1);   // d/dc2
+    gT[0] += a0.x + b0.x, gT[3] += a0.y + b0.y, gT[6] += a0.z + b0.z;
+    gT[1] += a1.x + b1.x, gT[4] += a1.y + b1.y, gT[7] += a1.z + b1.z;
+    gT[2] += a2.x + b2.x, gT[5] += a2.y + b2.y, gT[8] += a2.z + b2.z;
+  }
+  // adjoint of the bounding-box centre
+  {
+    const float2 g = a.g_means2D[i];
+    const float tv[3] = {9.0f, 9.0f, -1.0f};
+    const float d = tv[0] * (m[6] * m[6]) + tv[1] * (m[7] * m[7]) + tv[2] * (m[8] * m[8]);
+    const float inv_d = 1.0f / d;
+    float f[3], df[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      f[k] = tv[k] * inv_d;
+      df[k] = g.x * m[k] * m[6 + k] + g.y * m[3 + k] * m[6 + k];
+    }
+    const float dd = (df[0] * f[0] + df[1] * f[1] + df[2] * f[2]) * -inv_d;
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      gT[k] += g.x * f[k] * m[6 + k];
+      gT[3 + k] += g.y * f[k] * m[6 + k];
+      gT[6 + k] += (g.x * f[k] * m[k] + g.y * f[k] * m[3 + k]) + dd * (tv[k] * m[6 + k] * 2.0f);
+    }
+  }
+  const float3 p = make_float3(a.means[3 * i], a.means[3 * i + 1], a.means[3 * i + 2]);
+  const float4 q = a.rots[i];
+  const float2 s = a.scales[i];
+  // the stored normal was flipped to face the camera
+  float3 gn = make_float3(gno.x, gno.y, gno.z);
+  {
+    const float3 n = make_float3(2 * (q.y * q.w + q.x * q.z), 2 * (q.y * q.z - q.x * q.w), 1 - 2 * (q.x * q.x + q.y * q.y));
+    const float nx = Tw2v[0] * n.x + Tw2v[1] * n.y + Tw2v[2] * n.z;
+    const float ny = Tw2v[4] * n.x + Tw2v[5] * n.y + Tw2v[6] * n.z;
+    const float nz = Tw2v[8] * n.x + Tw2v[9] * n.y + Tw2v[10] * n.z;
+    const float vx = Tw2v[0] * p.x + Tw2v[1] * p.y + Tw2v[2] * p.z + Tw2v[3];
+    const float vy = Tw2v[4] * p.x + Tw2v[5] * p.y + Tw2v[6] * p.z + Tw2v[7];
+    const float vz = Tw2v[8] * p.x + Tw2v[9] * p.y + Tw2v[10] * p.z + Tw2v[11];
+    const float c = -(vx * nx + vy * ny + vz * nz);
+    const float sgn = c > 0 ? 1.0f : -1.0f;
+    gn = make_float3(sgn * gn.x, sgn * gn.y, sgn * gn.z);
+  }
+  float3 gm;
+  float2 gs;
+  float4 gq;
+  splat_matrix_adjoint(s, q, Tw2v, Tv2s, gT, gn, gm, gs, gq);
+
+  if (a.sh_degree >= 0) {
+    const float ux = p.x - campos[0], uy = p.y - campos[1], uz = p.z - campos[2];
+    const float n = rsqrtf(ux * ux + uy * uy + uz * uz + 1e-12f);
+    const float x = ux * n, y = uy * n, z = uz * n;
+    float3 grgb;
+    grgb.x = a.colors[3 * i] > 0 ? a.g_colors[3 * i] : 0.0f;
+    grgb.y = a.colors[3 * i + 1] > 0 ? a.g_colors[3 * i + 1] : 0.0f;
+    grgb.z = a.colors[3 * i + 2] > 0 ? a.g_colors[3 * i + 2] : 0.0f;
+    float b[16];
+    sh_basis(a.sh_degree, x, y, z, b);
+    const int nb = (a.sh_degree + 1) * (a.sh_degree + 1);
+    float dx = 0, dy = 0, dz = 0;
+    for (int k = 0; k < nb; ++k) {
+      const float *c = a.sh_rest == nullptr ? a.shs + ((size_t) i * a.n_dc + k) * 3
+                                            : (k == 0 ? a.shs + (size_t) i * a.n_dc * 3
+                                                      : a.sh_rest + ((size_t) i * a.n_rest + (k - 1)) * 3);
+      float *gc = nullptr;
+      if (a.sh_rest == nullptr) {
+        if (a.g_shs) gc = a.g_shs + ((size_t) i * a.n_dc + k) * 3;
+      } else if (k == 0) {
+        if (a.g_shs) gc = a.g_shs + (size_t) i * a.n_dc * 3;
+      } else if (a.g_sh_rest) {
+        gc = a.g_sh_rest + ((size_t) i * a.n_rest + (k - 1)) * 3;
+      }
+      if (gc) gc[0] = grgb.x * b[k], gc[1] = grgb.y * b[k], gc[2] = grgb.z * b[k];
+      if (k > 0) {
+        const float t = grgb.x * __ldg(c) + grgb.y * __ldg(c + 1) + grgb.z * __ldg(c + 2);
+        const float3 db = sh_basis_grad(k, x, y, z);
+        dx += t * db.x, dy += t * db.y, dz += t * db.z;
+      }
+    }
+    const float t = -(ux * dx + uy * dy + uz * dz) * n * n * n;
+    gm.x += dx * n + t * ux;
+    gm.y += dy * n + t * uy;
+    gm.z += dz * n + t * uz;
+  }
+  a.g_means[3 * i] = gm.x, a.g_means[3 * i + 1] = gm.y, a.g_means[3 * i + 2] = gm.z;
+  a.g_scales[i] = gs;
+  a.g_rots[i] = gq;
+  // densification proxy replaces the consumed mean2D gradient (reference gs_2d_fast_preprocess.cu:605-608)
+  a.g_means2D[i] = make_float2(gT[2] * m[8] * 0.5f * (float) a.W, gT[5] * m[8] * 0.5f * (float) a.H);
+}
+
+}  // namespace fsgs
+
+using namespace fsgs;
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+
+extern "C" int fsgs_lbs_warp_forward(int P, const fsgs_lbs *lbs, float *means, float *scales, float *rots,
+    fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && lbs && means && scales && rots && lbs_valid(lbs));
+  if (P == 0) return FSGS_OK;
+  lbs_warp_forward_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, to_dev(lbs), means, (float2 *) scales,
+      (float4 *) rots);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs, const float *g_means, const float *g_scales,
+    const float *g_rots, const fsgs_lbs_grads *g, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && lbs && g && lbs_valid(lbs) && g_means && g_scales && g_rots);
+  FSGS_REQUIRE(g->g_xyz && g->g_scaling_raw && g->g_rotation_raw && g->g_knn_w && g->g_sp_q && g->g_sp_t &&
+               g->g_sp_dr && g->g_sp_ds);
+  cudaStream_t st = (cudaStream_t) stream;
+  const int M = lbs->M;
+  cudaMemsetAsync(g->g_sp_q, 0, sizeof(float) * 4 * M, st);
+  cudaMemsetAsync(g->g_sp_t, 0, sizeof(float) * 3 * M, st);
+  cudaMemsetAsync(g->g_sp_dr, 0, sizeof(float) * 4 * M, st);
+  cudaMemsetAsync(g->g_sp_ds, 0, sizeof(float) * 2 * M, st);
+  if (P == 0) return FSGS_OK;
+  const size_t table_bytes = sizeof(float) * kSpRow * (size_t) M;
+  if (table_bytes <= 40 * 1024) {
+    // one table per block in shared memory; few, fat blocks so that the flush stays cheap
+    const int blocks = min(ceil_div(P, 256), 148 * 4);
+    lbs_warp_backward_kernel<true><<<blocks, 256, table_bytes, st>>>(P, to_dev(lbs), g_means, (const float2 *) g_scales,
+        (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw, (float4 *) g->g_rotation_raw, g->g_knn_w,
+        g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+  } else {
+    lbs_warp_backward_kernel<false><<<ceil_div(P, 256), 256, 0, st>>>(P, to_dev(lbs), g_means,
+        (const float2 *) g_scales, (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw,
+        (float4 *) g->g_rotation_raw, g->g_knn_w, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+  }
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_preprocess_forward(const fsgs_preprocess_args *a, fsgs_stream_t stream) {
+  FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0);
+  FSGS_REQUIRE(a->opac && a->shs && a->Tw2v && a->Tv2s && a->campos);
+  FSGS_REQUIRE(a->means2D && a->inverse_m && a->normal_opacity && a->depths && a->radii && a->tiles_touched);
+  FSGS_REQUIRE(a->tile_counts && a->counters);
+  FSGS_REQUIRE(a->trans_precomp || a->trans_mat);
+  if (a->sh_degree > FSGS_MAX_SH_DEGREE) return FSGS_ERR_UNSUPPORTED;
+  if (a->sh_degree >= 0) {
+    FSGS_REQUIRE(a->colors);
+    const int nb = (a->sh_degree + 1) * (a->sh_degree + 1);
+    if (a->sh_rest) FSGS_REQUIRE(a->n_dc >= 1 && a->n_rest >= nb - 1);
+    else FSGS_REQUIRE(a->n_dc >= nb);
+  }
+  if (a->lbs) FSGS_REQUIRE(lbs_valid(a->lbs) && a->warped_means && a->warped_scales && a->warped_rots);
+  else FSGS_REQUIRE(a->means && (a->trans_precomp || (a->scales && a->rots)));
+  cudaStream_t st = (cudaStream_t) stream;
+  PreDev d;
+  d.P = a->P, d.W = a->W, d.H = a->H, d.sh_degree = a->sh_degree, d.n_dc = a->n_dc, d.n_rest = a->n_rest;
+  d.gx = (a->W + kTile - 1) / kTile, d.gy = (a->H + kTile - 1) / kTile;
+  d.means = a->lbs ? a->warped_means : a->means;
+  d.scales = (const float2 *) a->scales, d.rots = (const float4 *) a->rots;
+  d.opac = a->opac, d.shs = a->shs, d.sh_rest = a->n_rest > 0 ? a->sh_rest : nullptr;
+  d.Tw2v = a->Tw2v, d.Tv2s = a->Tv2s, d.campos = a->campos, d.trans_precomp = a->trans_precomp;
+  d.culling = a->culling;
+  d.warped_means = a->warped_means, d.warped_scales = (float2 *) a->warped_scales, d.warped_rots = (float4 *) a->warped_rots;
+  d.means2D = (float2 *) a->means2D, d.colors = a->colors, d.trans_mat = a->trans_mat, d.inverse_m = a->inverse_m;
+  d.normal_opacity = (float4 *) a->normal_opacity, d.depths = a->depths, d.radii = a->radii;
+  d.tiles_touched = a->tiles_touched, d.records = (float4 *) a->records, d.tile_counts = a->tile_counts;
+  d.counters = (unsigned long long *) a->counters;
+  cudaMemsetAsync(a->tile_counts, 0, sizeof(int32_t) * (size_t) d.gx * d.gy, st);
+  cudaMemsetAsync(a->counters, 0, sizeof(int64_t) * FSGS_NUM_COUNTERS, st);
+  if (a->P == 0) return FSGS_OK;
+  if (a->lbs) preprocess_forward_kernel<true><<<ceil_div(a->P, 256), 256, 0, st>>>(d, to_dev(a->lbs));
+  else preprocess_forward_kernel<false><<<ceil_div(a->P, 256), 256, 0, st>>>(d, LbsDev());
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_pack_records(int P, const float *means2D, const float *colors, const float *normal_opacity,
+    const float *trans_mat, const float *inverse_m, float *records, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && means2D && colors && normal_opacity && trans_mat && inverse_m && records);
+  if (P == 0) return FSGS_OK;
+  pack_records_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, (const float2 *) means2D, colors,
+      (const float4 *) normal_opacity, trans_mat, inverse_m, (float4 *) records);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_transmat_forward(int P, const float *means, const float *scales, const float *rots,
+    const float *Tw2v, const float *Tv2s, float *trans_mat, float *normals, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && means && scales && rots && Tw2v && Tv2s && trans_mat && normals);
+  if (P == 0) return FSGS_OK;
+  transmat_forward_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, means, (const float2 *) scales,
+      (const float4 *) rots, Tw2v, Tv2s, trans_mat, normals);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_transmat_backward(int P, const float *scales, const float *rots, const float *Tw2v,
+    const float *Tv2s, const float *grad_trans_mat, const float *grad_normals, float *grad_means, float *grad_scales,
+    float *grad_rots, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && scales && rots && Tw2v && Tv2s && grad_trans_mat && grad_normals && grad_means &&
+               grad_scales && grad_rots);
+  if (P == 0) return FSGS_OK;
+  transmat_backward_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, (const float2 *) scales,
+      (const float4 *) rots, Tw2v, Tv2s, grad_trans_mat, grad_normals, grad_means, (float2 *) grad_scales,
+      (float4 *) grad_rots);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_stream_t stream) {
+  FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0);
+  FSGS_REQUIRE(a->means && a->scales && a->rots && a->Tw2v && a->Tv2s && a->campos && a->trans_mat && a->radii);
+  FSGS_REQUIRE(a->grad_means2D && a->grad_trans_mat && a->grad_inverse_m && a->grad_normal_opacity);
+  FSGS_REQUIRE(a->grad_means && a->grad_scales && a->grad_rots && a->grad_opac);
+  if (a->sh_degree > FSGS_MAX_SH_DEGREE) return FSGS_ERR_UNSUPPORTED;
+  if (a->sh_degree >= 0) FSGS_REQUIRE(a->shs && a->colors && a->grad_colors);
+  if (a->P == 0) return FSGS_OK;
+  PreBwdDev d;
+  d.P = a->P, d.W = a->W, d.H = a->H, d.sh_degree = a->sh_degree, d.n_dc = a->n_dc, d.n_rest = a->n_rest;
+  d.means = a->means, d.scales = (const float2 *) a->scales, d.rots = (const float4 *) a->rots;
+  d.shs = a->shs, d.sh_rest = a->n_rest > 0 ? a->sh_rest : nullptr;
+  d.Tw2v = a->Tw2v, d.Tv2s = a->Tv2s, d.campos = a->campos, d.trans_mat = a->trans_mat, d.colors = a->colors;
+  d.radii = a->radii, d.g_means2D = (float2 *) a->grad_means2D, d.g_trans_mat = a->grad_trans_mat;
+  d.g_inverse_m = a->grad_inverse_m, d.g_colors = a->grad_colors;
+  d.g_normal_opacity = (const float4 *) a->grad_normal_opacity;
+  d.g_means = a->grad_means, d.g_scales = (float2 *) a->grad_scales, d.g_rots = (float4 *) a->grad_rots;
+  d.g_opac = a->grad_opac, d.g_shs = a->grad_shs, d.g_sh_rest = d.sh_rest ? a->grad_sh_rest : nullptr;
+  preprocess_backward_kernel<<<ceil_div(a->P, 256), 256, 0, (cudaStream_t) stream>>>(d);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}

@@ -1,0 +1,268 @@
+/*
+ * fsgs.h -- C ABI of libfsgs.so: the B200 (sm_100a) surfel-rendering hot path of Fast-SP-GS.
+ *
+ * Every entry point takes raw DEVICE pointers (unless a parameter says "host"), plain sizes and a
+ * CUDA stream handle, launches asynchronously on that stream and returns FSGS_OK or a negative
+ * fsgs_status.  Nothing here allocates or frees device memory, throws, or synchronises the device;
+ * scratch memory is passed in by the caller after a *_workspace_bytes() query.  All floating point
+ * data is contiguous fp32; quaternions are (x, y, z, w); matrices are row major.
+ *
+ * Each declaration names the reference interface it stands in for (paths inside the Fast-SP-GS
+ * project, fast_2d_gs/_C/...).  The PyTorch-facing operators with the reference's own names live in
+ * the python package (fsgs/ops.py) and call only what is declared here.
+ */
+#ifndef FSGS_H_
+#define FSGS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *fsgs_stream_t; /* a cudaStream_t */
+
+typedef enum fsgs_status {
+  FSGS_OK = 0,
+  FSGS_ERR_INVALID_ARGUMENT = -1, /* null pointer, negative size, unsupported option */
+  FSGS_ERR_UNSUPPORTED = -2,      /* e.g. SH degree above the built maximum */
+  FSGS_ERR_WORKSPACE = -3,        /* workspace too small */
+  FSGS_ERR_LAUNCH = -4,           /* cudaGetLastError() reported a launch failure */
+  FSGS_ERR_LIMIT = -5             /* size beyond a documented maximum */
+} fsgs_status;
+
+#define FSGS_TILE 16           /* tiles are 16 x 16 pixels (include/gaussian_render.h:27-31) */
+#define FSGS_RECORD_FLOATS 32  /* one packed per-Gaussian render record = 128 bytes */
+#define FSGS_MAX_SH_DEGREE 3
+#define FSGS_KNN_MAX_K 16
+
+/* counters[] written by fsgs_preprocess_forward / fsgs_bin_tiles (int64 each) */
+#define FSGS_CNT_SLOTS 0     /* R  = sum of tile-rectangle areas = numel of the reference's point_list */
+#define FSGS_CNT_PAIRS 1     /* R* = (Gaussian, tile) pairs that pass the 4-corner test */
+#define FSGS_CNT_OVERFLOW 2  /* pairs dropped because point_list capacity < R* (0 when healthy) */
+#define FSGS_CNT_STATUS 3    /* device-side error bits (bounded wait ran out, ...), 0 when healthy */
+#define FSGS_NUM_COUNTERS 4
+
+const char *fsgs_status_string(int status);
+int fsgs_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Nearest / farthest control point.
+ * Replaces cdist_top / cdist_top_backward   (src/other/cdist_top.cu:34-84, 107-154).
+ * x1 [B,N,D], x2 [B,M,D] -> dist [B,N] (sqrt of the squared distance), index [B,N] int64.
+ * Exact ties: nearest keeps the LAST index, farthest the FIRST (cdist_top.cu:24).
+ * Backward: g1 [B,N,D] is written, g2 [B,M,D] is zeroed then accumulated.
+ * ---------------------------------------------------------------------------------------------- */
+int fsgs_cdist_top(int B, int N, int M, int D, const float *x1, const float *x2, int largest, float *dist,
+    int64_t *index, fsgs_stream_t stream);
+int fsgs_cdist_top_backward(int B, int N, int M, int D, const float *x1, const float *x2, const float *dist,
+    const int64_t *index, const float *grad_dist, float *g1, float *g2, fsgs_stream_t stream);
+
+/* Exact K nearest control points (3-D), squared L2 by direct differences, ascending by (distance, index):
+ * ties go to the lower index.  x [N,3], c [M,3] -> d2 [N,K], index [N,K] int64.  K <= FSGS_KNN_MAX_K.
+ * Stands in for the pytorch3d.ops.knn_points call of fast_2d_gs/network.py:504 (third party; additive). */
+int fsgs_knn(int N, int M, int K, const float *x, const float *c, float *d2, int64_t *index, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Visibility-masked Adam.
+ * Replaces AdamMasksedUpdated   (src/other/adam_masked_update.cu:9-36): one [N,M] tensor per call.
+ * fsgs_adam_masked_multi updates up to 8 tensors that share N and the mask in ONE launch
+ * (the six per-step launches of fast_2d_gs/sparse_gaussian_adam.py:20-46 folded together).
+ * ---------------------------------------------------------------------------------------------- */
+int fsgs_adam_masked(float *param, const float *grad, float *exp_avg, float *exp_avg_sq, const uint8_t *visible,
+    float lr, float b1, float b2, float eps, int64_t N, int64_t M, fsgs_stream_t stream);
+
+typedef struct fsgs_adam_tensor {
+  float *param;
+  const float *grad;
+  float *exp_avg;
+  float *exp_avg_sq;
+  int32_t M;    /* elements per Gaussian */
+  float lr;     /* bias-corrected learning rate for this tensor */
+  float eps;
+} fsgs_adam_tensor;
+
+#define FSGS_ADAM_MAX_TENSORS 8
+int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *tensors /* host */, const uint8_t *visible,
+    int64_t N, float b1, float b2, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Splat -> screen matrix, standalone.
+ * Replaces gs_2d_fast_compute_transmat_forward / gs_2d_fast_compute_trans_mat_backward
+ * (src/gaussian_splatting/gs_2d_fast_preprocess.cu:871-909, 923-958).
+ * ---------------------------------------------------------------------------------------------- */
+int fsgs_transmat_forward(int P, const float *means, const float *scales, const float *rots, const float *Tw2v,
+    const float *Tv2s, float *trans_mat, float *normals, fsgs_stream_t stream);
+int fsgs_transmat_backward(int P, const float *scales, const float *rots, const float *Tw2v, const float *Tv2s,
+    const float *grad_trans_mat, const float *grad_normals, float *grad_means, float *grad_scales, float *grad_rots,
+    fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Superpoint LBS warp (rigid blend), optionally fused into the preprocess.
+ * Restates fast_2d_gs/network.py:545-573, 630-645 (PyTorch + lietorch in the reference; additive).
+ *   means  = sum_k w_k (R(q_k) xyz + t_k)          scales = exp(scaling_raw) + sum_k w_k ds_k
+ *   rots   = normalize(rotation_raw + sum_k w_k dr_k)
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fsgs_lbs {
+  int32_t K, M;
+  const float *xyz;          /* [P,3] canonical positions */
+  const float *scaling_raw;  /* [P,2] log scales */
+  const float *rotation_raw; /* [P,4] */
+  const int64_t *knn_idx;    /* [P,K] */
+  const float *knn_w;        /* [P,K] */
+  const float *sp_q;         /* [M,4] unit quaternions */
+  const float *sp_t;         /* [M,3] translations */
+  const float *sp_dr;        /* [M,4] additive rotation deltas */
+  const float *sp_ds;        /* [M,2] additive scale deltas */
+} fsgs_lbs;
+
+int fsgs_lbs_warp_forward(int P, const fsgs_lbs *lbs /* host */, float *means, float *scales, float *rots,
+    fsgs_stream_t stream);
+
+typedef struct fsgs_lbs_grads {
+  float *g_xyz, *g_scaling_raw, *g_rotation_raw; /* [P,3] [P,2] [P,4]  written */
+  float *g_knn_w;                                /* [P,K]              written */
+  float *g_sp_q, *g_sp_t, *g_sp_dr, *g_sp_ds;    /* [M,*]              zeroed then accumulated */
+} fsgs_lbs_grads;
+
+int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs /* host */, const float *g_means, const float *g_scales,
+    const float *g_rots, const fsgs_lbs_grads *grads /* host */, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Per-Gaussian preprocess.
+ * Replaces the kernel stage of gs_2d_fast_preprocess_forward
+ * (gs_2d_fast_preprocess.cu:160-262 launched at :688) and counts, in the same pass, the tiles
+ * each splat really covers (the 4-corner conic test of duplicateWithKeys, :264-327).
+ * Every output row is written (zeros for culled Gaussians): no pre-zeroing needed.
+ * With sh_degree < 0, shs holds [P,3] colours, colors may alias shs and is left untouched.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fsgs_preprocess_args {
+  int32_t P, W, H, sh_degree;
+  int32_t n_dc;   /* coefficients per Gaussian in shs (1 when sh_rest is given) */
+  int32_t n_rest; /* coefficients per Gaussian in sh_rest, 0 when absent */
+  const float *means, *scales, *rots; /* [P,3] [P,2] [P,4]; ignored when lbs != NULL */
+  const float *opac;                  /* [P,1] */
+  const float *shs, *sh_rest;         /* [P,n_dc,3], [P,n_rest,3] or NULL */
+  const float *Tw2v, *Tv2s, *campos;  /* [4,4] [3,3] [3] */
+  const float *trans_precomp;         /* [P,3,3] or NULL */
+  const uint8_t *culling;             /* [P] or NULL */
+  const fsgs_lbs *lbs;                /* host pointer or NULL; when set, warped_* receive the warped set */
+  float *warped_means, *warped_scales, *warped_rots;
+  /* outputs */
+  float *means2D, *colors, *trans_mat, *inverse_m, *normal_opacity, *depths; /* [P,2|3|9|9|4|1] */
+  int32_t *radii;         /* [P] */
+  int32_t *tiles_touched; /* [P] tile-rectangle area (the reference's slot count) */
+  float *records;         /* [P,32] packed render records, or NULL */
+  int32_t *tile_counts;   /* [T] pairs per tile; zeroed by the call */
+  int64_t *counters;      /* [FSGS_NUM_COUNTERS]; zeroed by the call */
+} fsgs_preprocess_args;
+
+int fsgs_preprocess_forward(const fsgs_preprocess_args *args /* host */, fsgs_stream_t stream);
+
+/* Builds the packed render records from the reference-layout tensors (used when the compositing
+ * operators are called on their own, as GS_2D_fast_render_forward is). */
+int fsgs_pack_records(int P, const float *means2D, const float *colors, const float *normal_opacity,
+    const float *trans_mat, const float *inverse_m, float *records, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Tile binning.
+ * Replaces InclusiveSum + duplicateWithKeys + DeviceRadixSort::SortPairs + identifyTileRanges
+ * (gs_2d_fast_preprocess.cu:716-778).  Output order is identical to the reference's: per tile by
+ * (depth bits, Gaussian index); point_list[R*..min(R,capacity)) = -1; ranges of empty tiles = (0,0).
+ * tile_order [T] lists tile ids by decreasing list length (launch order for the compositing kernels).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fsgs_bin_args {
+  int32_t P, W, H;
+  const float *means2D, *inverse_m, *depths, *opac;
+  const int32_t *radii;
+  const int32_t *tile_counts; /* from fsgs_preprocess_forward */
+  int64_t *counters;
+  int64_t capacity;     /* entries available in point_list */
+  int32_t *point_list;  /* [capacity] */
+  int64_t *ranges;      /* [T,2] */
+  int32_t *tile_order;  /* [T] */
+  void *workspace;
+  size_t workspace_bytes;
+} fsgs_bin_args;
+
+size_t fsgs_bin_workspace_bytes(int W, int H, int64_t capacity);
+int fsgs_bin_tiles(const fsgs_bin_args *args /* host */, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Per-tile alpha compositing.
+ * Replaces GS_2D_fast_render_forward / GS_2D_fast_render_backward
+ * (src/gaussian_splatting/gs_2d_fast_redner.cu:839-953, 955-1074; kernels :22-271, :273-561).
+ * The backward follows the semantics of the per-pixel variant that training uses, with the
+ * per-Gaussian sums reduced across each warp and across the tile in shared memory before one global
+ * reduction per (Gaussian, tile, component).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fsgs_render_args {
+  int32_t P, W, H;
+  float near_n, far_n;
+  int32_t only_image;         /* 1: colour + opacity only */
+  const float *records;       /* [P,32] */
+  const int32_t *point_list;
+  const int64_t *ranges;      /* [T,2] */
+  const int32_t *tile_order;  /* [T] or NULL */
+  const float *trans_mat_t2;  /* [P,3,3] or NULL (flow) */
+  /* outputs: every pixel is written */
+  float *out_color;    /* [3,H,W] */
+  float *out_opacity;  /* [H,W] */
+  float *out_extras;   /* [8,H,W] or NULL when only_image */
+  float *out_flow;     /* [H,W,2] or NULL */
+  int32_t *n_contrib;  /* [2,H,W] */
+  int32_t *accum_max_count;     /* [P] or NULL */
+  float *accum_weights_p;       /* [P] or NULL */
+  int32_t *accum_weights_count; /* [P] or NULL */
+  int64_t *counters;            /* or NULL */
+} fsgs_render_args;
+
+int fsgs_render_forward(const fsgs_render_args *args /* host */, fsgs_stream_t stream);
+
+typedef struct fsgs_render_bwd_args {
+  int32_t P, W, H;
+  float near_n, far_n;
+  const float *records;
+  const int32_t *point_list;
+  const int64_t *ranges;
+  const int32_t *tile_order;
+  const float *trans_mat_t2;
+  const float *out_opacity, *out_extras; /* forward outputs; out_extras NULL selects the colour-only adjoint */
+  const int32_t *n_contrib;
+  const float *dL_dcolor, *dL_dopacity, *dL_dextras, *dL_dflow; /* contiguous; dL_dextras/dL_dflow may be NULL */
+  /* outputs, zeroed by the call */
+  float *dL_dcolors;         /* [P,3] */
+  float *dL_dmeans2D;        /* [P,2] */
+  float *dL_dtrans_mat;      /* [P,3,3] (row 2 only) */
+  float *dL_dinverse_m;      /* [P,3,3] */
+  float *dL_dnormal_opacity; /* [P,4] */
+  int64_t *counters;
+} fsgs_render_bwd_args;
+
+int fsgs_render_backward(const fsgs_render_bwd_args *args /* host */, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Preprocess backward.
+ * Replaces gs_2d_fast_preprocess_backward   (gs_2d_fast_preprocess.cu:536-609, 784-859).
+ * grad_means2D is consumed and then overwritten with the densification proxy, as in the reference.
+ * Gradient rows of invisible Gaussians are left untouched (the caller zero-initialises, as the
+ * reference's Python does).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fsgs_preprocess_bwd_args {
+  int32_t P, W, H, sh_degree, n_dc, n_rest;
+  const float *means, *scales, *rots, *shs, *sh_rest;
+  const float *Tw2v, *Tv2s, *campos;
+  const float *trans_mat, *colors;
+  const int32_t *radii;
+  float *grad_means2D;
+  const float *grad_trans_mat, *grad_inverse_m, *grad_colors, *grad_normal_opacity;
+  float *grad_means, *grad_scales, *grad_rots, *grad_opac, *grad_shs, *grad_sh_rest; /* last two may be NULL */
+} fsgs_preprocess_bwd_args;
+
+int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *args /* host */, fsgs_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FSGS_H_ */
