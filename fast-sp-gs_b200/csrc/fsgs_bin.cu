@@ -223,7 +223,8 @@ extern "C" size_t fsgs_bin_workspace_bytes(int W, int H, int64_t capacity) {
 
 extern "C" int fsgs_bin_tiles(const fsgs_bin_args *a, fsgs_stream_t stream) {
   FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0 && a->capacity >= 0);
-  FSGS_REQUIRE(a->means2D && a->inverse_m && a->depths && a->opac && a->radii && a->tile_counts && a->counters);
+  FSGS_REQUIRE(a->tile_counts && a->counters);
+  FSGS_REQUIRE(a->P == 0 || (a->means2D && a->inverse_m && a->depths && a->opac && a->radii));
   FSGS_REQUIRE(a->ranges && a->tile_order && a->workspace && (a->point_list || a->capacity == 0));
   if (a->workspace_bytes < fsgs_bin_workspace_bytes(a->W, a->H, a->capacity)) return FSGS_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t) stream;

@@ -48,67 +48,104 @@ __device__ __forceinline__ void tile_rect(float px, float py, int radius, int gx
   y1 = min(gy, max(0, (int) ((py + radius + kTile - 1) / kTile)));
 }
 
+// ---- pinned fp32 arithmetic -------------------------------------------------------------------------------
+// The binning's corner test flips on the last bit of its inputs, and tile lists have to equal the reference's
+// bit for bit.  nvcc decides per kernel which multiply feeds which fused multiply-add, so equal source does not
+// give equal bits.  Every operation below that reaches the corner test is therefore written with explicit
+// round-to-nearest intrinsics, in the association that reproduces the reference build (-O3, default -fmad,
+// sm_100) bit for bit; the sequence was established by comparing against the reference kernels' outputs.
+#define FMUL(a, b) __fmul_rn((a), (b))
+#define FADD(a, b) __fadd_rn((a), (b))
+#define FSUB(a, b) __fsub_rn((a), (b))
+#define FFMA(a, b, c) __fmaf_rn((a), (b), (c))
+
+// a0*b0 + a1*b1 + a2*b2 accumulated from zero in index order: fma(a2,b2, fma(a1,b1, a0*b0))
+__device__ __forceinline__ float dot3_chain(float a0, float b0, float a1, float b1, float a2, float b2) {
+  return FFMA(a2, b2, FFMA(a1, b1, FMUL(a0, b0)));
+}
+// the same sum written as one expression: fma(a2,b2, fma(a0,b0, a1*b1))
+__device__ __forceinline__ float dot3_expr(float a0, float b0, float a1, float b1, float a2, float b2) {
+  return FFMA(a2, b2, FFMA(a0, b0, FMUL(a1, b1)));
+}
+
+// View-space position; the products are shared with the third column of the splat matrix, so nothing is fused.
+__device__ __forceinline__ float3 view_point(const float3 p, const float *__restrict__ Tw2v) {
+  float3 v;
+  v.x = FADD(FADD(FADD(FMUL(Tw2v[0], p.x), FMUL(Tw2v[1], p.y)), FMUL(Tw2v[2], p.z)), Tw2v[3]);
+  v.y = FADD(FADD(FADD(FMUL(Tw2v[4], p.x), FMUL(Tw2v[5], p.y)), FMUL(Tw2v[6], p.z)), Tw2v[7]);
+  v.z = FADD(FADD(FADD(FMUL(Tw2v[8], p.x), FMUL(Tw2v[9], p.y)), FMUL(Tw2v[10], p.z)), Tw2v[11]);
+  return v;
+}
+
 // Splat -> screen matrix M = Tv2s * (Tw2v[:3,:3] * [R(q)*diag(s) | p] + e_z * Tw2v[2,3]) and the view-space
 // normal.  Only the z translation of the camera enters M (reference gs_2d_fast_preprocess.cu:60-98).
-// The accumulation order of every dot product is k = 0, 1, 2 starting from zero, which fixes the
-// rounding of M; the binning's corner test downstream is sensitive to the last bit.
 __device__ __forceinline__ void splat_matrix(const float3 p, const float2 s, const float4 q, const float *__restrict__ Tw2v,
     const float *__restrict__ Tv2s, float *M, float3 &normal) {
   float L[9];
   float3 n;
-  L[0] = (1 - 2 * (q.y * q.y + q.z * q.z)) * s.x;
-  L[1] = 2 * (q.x * q.y - q.z * q.w) * s.y;
+  const float xx = FMUL(q.x, q.x), yy = FMUL(q.y, q.y), zz = FMUL(q.z, q.z);
+  const float xz = FMUL(q.x, q.z), zw = FMUL(q.z, q.w), xw = FMUL(q.x, q.w);
+  L[0] = FMUL(FSUB(1.0f, FMUL(2.0f, FADD(yy, zz))), s.x);
+  L[1] = FMUL(FMUL(2.0f, FFMA(q.x, q.y, -zw)), s.y);
   L[2] = p.x;
-  n.x = 2 * (q.y * q.w + q.x * q.z);
+  n.x = FMUL(2.0f, FFMA(q.y, q.w, xz));
 
-  L[3] = (2 * (q.x * q.y + q.z * q.w)) * s.x;
-  L[4] = (1 - 2 * (q.x * q.x + q.z * q.z)) * s.y;
+  L[3] = FMUL(FMUL(2.0f, FFMA(q.x, q.y, zw)), s.x);
+  L[4] = FMUL(FSUB(1.0f, FMUL(2.0f, FFMA(q.x, q.x, zz))), s.y);
   L[5] = p.y;
-  n.y = 2 * (q.y * q.z - q.x * q.w);
+  n.y = FMUL(2.0f, FFMA(q.y, q.z, -xw));
 
-  L[6] = (2 * (q.x * q.z - q.y * q.w)) * s.x;
-  L[7] = 2 * (q.x * q.w + q.y * q.z) * s.y;
+  L[6] = FMUL(FMUL(2.0f, FFMA(-q.y, q.w, xz)), s.x);
+  L[7] = FMUL(FMUL(2.0f, FFMA(q.y, q.z, xw)), s.y);
   L[8] = p.z;
-  n.z = 1 - 2 * (q.x * q.x + q.y * q.y);
+  n.z = FSUB(1.0f, FMUL(2.0f, FFMA(q.x, q.x, yy)));
 
   float t[9];
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
-#pragma unroll
-    for (int j = 0; j < 3; ++j) {
-      float acc = 0;
-#pragma unroll
-      for (int k = 0; k < 3; ++k) acc += Tw2v[i * 4 + k] * L[k * 3 + j];
-      t[i * 3 + j] = acc;
-    }
+    t[i * 3 + 0] = dot3_chain(Tw2v[i * 4], L[0], Tw2v[i * 4 + 1], L[3], Tw2v[i * 4 + 2], L[6]);
+    t[i * 3 + 1] = dot3_chain(Tw2v[i * 4], L[1], Tw2v[i * 4 + 1], L[4], Tw2v[i * 4 + 2], L[7]);
+    t[i * 3 + 2] = FADD(FADD(FMUL(Tw2v[i * 4], L[2]), FMUL(Tw2v[i * 4 + 1], L[5])), FMUL(Tw2v[i * 4 + 2], L[8]));
   }
-  t[8] += Tw2v[11];
-#pragma unroll
-  for (int i = 0; i < 9; ++i) M[i] = 0;
+  t[8] = FADD(t[8], Tw2v[11]);
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
 #pragma unroll
-    for (int j = 0; j < 3; ++j) {
-#pragma unroll
-      for (int k = 0; k < 3; ++k) M[i * 3 + j] += Tv2s[i * 3 + k] * t[k * 3 + j];
-    }
+    for (int j = 0; j < 3; ++j)
+      M[i * 3 + j] = dot3_chain(Tv2s[i * 3], t[j], Tv2s[i * 3 + 1], t[3 + j], Tv2s[i * 3 + 2], t[6 + j]);
   }
-  normal.x = Tw2v[0] * n.x + Tw2v[1] * n.y + Tw2v[2] * n.z;
-  normal.y = Tw2v[4] * n.x + Tw2v[5] * n.y + Tw2v[6] * n.z;
-  normal.z = Tw2v[8] * n.x + Tw2v[9] * n.y + Tw2v[10] * n.z;
+  normal.x = dot3_expr(Tw2v[0], n.x, Tw2v[1], n.y, Tw2v[2], n.z);
+  normal.y = dot3_expr(Tw2v[4], n.x, Tw2v[5], n.y, Tw2v[6], n.z);
+  normal.z = dot3_expr(Tw2v[8], n.x, Tw2v[9], n.y, Tw2v[10], n.z);
 }
 
 // Adjugate of M, rows = cross products of M's columns (reference gs_2d_fast_preprocess.cu:247-255).
 __device__ __forceinline__ void adjugate(const float *m, float *im) {
-  im[0] = m[4] * m[8] - m[7] * m[5];
-  im[1] = m[7] * m[2] - m[1] * m[8];
-  im[2] = m[1] * m[5] - m[4] * m[2];
-  im[3] = m[6] * m[5] - m[3] * m[8];
-  im[4] = m[0] * m[8] - m[6] * m[2];
-  im[5] = m[3] * m[2] - m[0] * m[5];
-  im[6] = m[3] * m[7] - m[6] * m[4];
-  im[7] = m[6] * m[1] - m[0] * m[7];
-  im[8] = m[0] * m[4] - m[3] * m[1];
+  im[0] = FFMA(m[4], m[8], -FMUL(m[7], m[5]));
+  im[1] = FFMA(m[7], m[2], -FMUL(m[1], m[8]));
+  im[2] = FFMA(m[1], m[5], -FMUL(m[4], m[2]));
+  im[3] = FFMA(m[6], m[5], -FMUL(m[3], m[8]));
+  im[4] = FFMA(m[0], m[8], -FMUL(m[6], m[2]));
+  im[5] = FFMA(m[3], m[2], -FMUL(m[0], m[5]));
+  im[6] = FFMA(m[3], m[7], -FMUL(m[6], m[4]));
+  im[7] = FFMA(m[6], m[1], -FMUL(m[0], m[7]));
+  im[8] = FFMA(m[0], m[4], -FMUL(m[3], m[1]));
+}
+
+// 3-sigma bounding box of the projected splat: centre and ceil'd radius.  false when degenerate.
+// (reference gs_2d_fast_preprocess.cu:143-158, 227)
+__device__ __forceinline__ bool splat_bounds(const float *M, float2 &ctr, float &radius) {
+  const float d = FFMA(-M[8], M[8], FFMA(9.0f, FMUL(M[6], M[6]), FMUL(9.0f, FMUL(M[7], M[7]))));
+  if (d == 0.0f) return false;
+  const float inv_d = __fdiv_rn(1.0f, d);
+  const float f0 = FMUL(inv_d, 9.0f), f2 = -inv_d;
+  ctr.x = dot3_expr(f0, FMUL(M[0], M[6]), f0, FMUL(M[1], M[7]), f2, FMUL(M[2], M[8]));
+  ctr.y = dot3_expr(f0, FMUL(M[3], M[6]), f0, FMUL(M[4], M[7]), f2, FMUL(M[5], M[8]));
+  const float hx = FFMA(ctr.x, ctr.x, -dot3_expr(f0, FMUL(M[0], M[0]), f0, FMUL(M[1], M[1]), f2, FMUL(M[2], M[2])));
+  const float hy = FFMA(ctr.y, ctr.y, -dot3_expr(f0, FMUL(M[3], M[3]), f0, FMUL(M[4], M[4]), f2, FMUL(M[5], M[5])));
+  const float ex = __fsqrt_rn(fmaxf(1e-4f, hx)), ey = __fsqrt_rn(fmaxf(1e-4f, hy));
+  radius = ceilf(fmaxf(fmaxf(ex, ey), 3.0f * float(0.707106)));
+  return true;
 }
 
 __device__ __forceinline__ float lg2_approx(float x) {
@@ -118,27 +155,33 @@ __device__ __forceinline__ float lg2_approx(float x) {
 }
 
 // The six coefficients (tile units) of the conic  alpha >= 1/255  of a splat
-// (reference gs_2d_fast_preprocess.cu:282-300).
+// (reference gs_2d_fast_preprocess.cu:282-300) and the corner test (:301).
 struct Conic {
   float xx, yy, xy, x_, y_, __;
+  // ((((xx*u*u + yy*v*v) + xy*u*v) + x_*u) + y_*v) + __ <= 0; only the cross term is fused, as in the reference build
   __device__ __forceinline__ bool inside(float u, float v) const {
-    return xx * u * u + yy * v * v + xy * u * v + x_ * u + y_ * v + __ <= 0;
+    float s = FADD(FMUL(FMUL(xx, u), u), FMUL(FMUL(yy, v), v));
+    s = FFMA(FMUL(xy, u), v, s);
+    s = FADD(s, FMUL(x_, u));
+    s = FADD(s, FMUL(y_, v));
+    return FADD(s, __) <= 0;
   }
 };
 
 __device__ __forceinline__ Conic make_conic(const float *IM, float opacity) {
   const float ln2 = 0.69314718055f;
-  float d = -2.0f * ln2 * (float(7.9886846867721655) + lg2_approx(opacity));
+  const float d = FMUL(-2.0f * ln2, FADD(float(7.9886846867721655), lg2_approx(opacity)));
+  const float d6 = FMUL(d, IM[6]), d7 = FMUL(d, IM[7]), d8 = FMUL(d, IM[8]);
   Conic c;
-  float Wxx = IM[0] * IM[0] + IM[3] * IM[3] + d * IM[6] * IM[6];
-  float Wyy = IM[1] * IM[1] + IM[4] * IM[4] + d * IM[7] * IM[7];
-  float W__ = IM[2] * IM[2] + IM[5] * IM[5] + d * IM[8] * IM[8];
-  float Wxy = 2 * (IM[0] * IM[1] + IM[3] * IM[4] + d * IM[6] * IM[7]);
-  float Wx_ = 2 * (IM[0] * IM[2] + IM[3] * IM[5] + d * IM[6] * IM[8]);
-  float Wy_ = 2 * (IM[1] * IM[2] + IM[4] * IM[5] + d * IM[7] * IM[8]);
-  c.xx = Wxx * kTile * kTile;
-  c.yy = Wyy * kTile * kTile;
-  c.xy = Wxy * kTile * kTile;
+  const float Wxx = dot3_expr(IM[0], IM[0], IM[3], IM[3], d6, IM[6]);
+  const float Wyy = dot3_expr(IM[1], IM[1], IM[4], IM[4], d7, IM[7]);
+  const float W__ = dot3_expr(IM[2], IM[2], IM[5], IM[5], d8, IM[8]);
+  const float Wxy = FMUL(2.0f, dot3_expr(IM[0], IM[1], IM[3], IM[4], d6, IM[7]));
+  const float Wx_ = FMUL(2.0f, dot3_expr(IM[0], IM[2], IM[3], IM[5], d6, IM[8]));
+  const float Wy_ = FMUL(2.0f, dot3_expr(IM[1], IM[2], IM[4], IM[5], d7, IM[8]));
+  c.xx = Wxx * (kTile * kTile);
+  c.yy = Wyy * (kTile * kTile);
+  c.xy = Wxy * (kTile * kTile);
   c.x_ = Wx_ * kTile;
   c.y_ = Wy_ * kTile;
   c.__ = W__;
@@ -146,7 +189,8 @@ __device__ __forceinline__ Conic make_conic(const float *IM, float opacity) {
 }
 
 // Calls f(tile_x, tile_y) for every tile of the rectangle with at least one corner inside the conic
-// (reference gs_2d_fast_preprocess.cu:301-318).  Column corners are evaluated once and carried down.
+// (reference gs_2d_fast_preprocess.cu:301-318).  The value at a corner does not depend on which tile asks, so
+// each column's corners are evaluated once and carried down.
 template <typename F>
 __device__ __forceinline__ void for_each_covered_tile(const Conic &c, int x0, int y0, int x1, int y1, F f) {
   for (int x = x0; x < x1; ++x) {

@@ -137,12 +137,14 @@ static void launch_knn(int N, int M, const float *x, const float *c, float *d2, 
 // masked Adam (reference src/other/adam_masked_update.cu:9-28): same operation order per element
 // ------------------------------------------------------------------------------------------------
 
+// m = b1 m + (1-b1) g ; v = b2 v + (1-b2) g g ; p += -lr m / (sqrt(v) + eps).  The two accumulations are fused the
+// way the reference build fuses them, so parameters and moments equal the reference's bit for bit.
 __device__ __forceinline__ void adam_element(float &p, float g, float &m, float &v, float lr, float b1, float b2,
     float eps) {
-  m = b1 * m + (1.0f - b1) * g;
-  v = b2 * v + (1.0f - b2) * g * g;
-  const float step = -lr * m / (sqrtf(v) + eps);
-  p += step;
+  m = __fmaf_rn(__fsub_rn(1.0f, b1), g, __fmul_rn(b1, m));
+  v = __fmaf_rn(__fmul_rn(__fsub_rn(1.0f, b2), g), g, __fmul_rn(b2, v));
+  const float step = __fdiv_rn(__fmul_rn(-lr, m), __fadd_rn(__fsqrt_rn(v), eps));
+  p = __fadd_rn(p, step);
 }
 
 __global__ void __launch_bounds__(256) adam_masked_kernel(float *__restrict__ param, const float *__restrict__ grad,
@@ -204,8 +206,9 @@ extern "C" int fsgs_version(void) { return 100; }
 
 extern "C" int fsgs_cdist_top(int B, int N, int M, int D, const float *x1, const float *x2, int largest, float *dist,
     int64_t *index, fsgs_stream_t stream) {
-  FSGS_REQUIRE(B >= 0 && N >= 0 && M > 0 && D > 0 && x1 && x2 && dist && index);
+  FSGS_REQUIRE(B >= 0 && N >= 0 && M > 0 && D > 0);
   if (B == 0 || N == 0) return FSGS_OK;
+  FSGS_REQUIRE(x1 && x2 && dist && index);
   cudaStream_t st = (cudaStream_t) stream;
   const dim3 grid(ceil_div(N, 128), B);
   largest = largest ? 1 : 0;

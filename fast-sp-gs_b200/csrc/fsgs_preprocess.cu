@@ -244,9 +244,8 @@ __global__ void __launch_bounds__(256) preprocess_forward_kernel(PreDev a, LbsDe
     float vz = 0, opacity = 0, radius = 0;
     int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
     if (vis) {
-      const float vx = Tw2v[0] * p.x + Tw2v[1] * p.y + Tw2v[2] * p.z + Tw2v[3];
-      const float vy = Tw2v[4] * p.x + Tw2v[5] * p.y + Tw2v[6] * p.z + Tw2v[7];
-      vz = Tw2v[8] * p.x + Tw2v[9] * p.y + Tw2v[10] * p.z + Tw2v[11];
+      const float3 pv = view_point(p, Tw2v);
+      vz = pv.z;
       vis = !(vz <= 0.2f);
       if (vis) {
         opacity = a.opac[i];
@@ -258,27 +257,15 @@ __global__ void __launch_bounds__(256) preprocess_forward_kernel(PreDev a, LbsDe
           for (int k = 0; k < 9; ++k) M[k] = a.trans_precomp[(size_t) 9 * i + k];
           nrm = make_float3(0.0f, 0.0f, 1.0f);
         }
-        const float tx = vx * nrm.x, ty = vy * nrm.y, tz = vz * nrm.z;
-        const float c = -(tx + ty + tz);
+        const float c = -(pv.x * nrm.x + pv.y * nrm.y + pv.z * nrm.z);
         if (c == 0) vis = false;
         const float sgn = c > 0 ? 1.0f : -1.0f;
         nrm = make_float3(sgn * nrm.x, sgn * nrm.y, sgn * nrm.z);
       }
       if (vis) {
-        // bounding box at cutoff 3 (reference gs_2d_fast_preprocess.cu:143-158)
-        const float t0 = 3.0f * 3.0f, t2 = -1.0f;
-        const float d = t0 * (M[6] * M[6]) + t0 * (M[7] * M[7]) + t2 * (M[8] * M[8]);
-        if (d == 0.0f) {
+        if (!splat_bounds(M, ctr, radius)) {
           vis = false;
         } else {
-          const float inv_d = 1 / d;
-          const float f0 = inv_d * t0, f2 = inv_d * t2;
-          ctr.x = f0 * (M[0] * M[6]) + f0 * (M[1] * M[7]) + f2 * (M[2] * M[8]);
-          ctr.y = f0 * (M[3] * M[6]) + f0 * (M[4] * M[7]) + f2 * (M[5] * M[8]);
-          const float hx = ctr.x * ctr.x - (f0 * (M[0] * M[0]) + f0 * (M[1] * M[1]) + f2 * (M[2] * M[2]));
-          const float hy = ctr.y * ctr.y - (f0 * (M[3] * M[3]) + f0 * (M[4] * M[4]) + f2 * (M[5] * M[5]));
-          const float ex = sqrtf(fmaxf(1e-4f, hx)), ey = sqrtf(fmaxf(1e-4f, hy));
-          radius = ceilf(fmaxf(fmaxf(ex, ey), 3.0f * float(0.707106)));
           tile_rect(ctr.x, ctr.y, (int) radius, a.gx, a.gy, x0, y0, x1, y1);
           if ((x1 - x0) * (y1 - y0) == 0) vis = false;
         }
@@ -625,15 +612,21 @@ extern "C" int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs, const float *g
 
 extern "C" int fsgs_preprocess_forward(const fsgs_preprocess_args *a, fsgs_stream_t stream) {
   FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0);
+  FSGS_REQUIRE(a->tile_counts && a->counters);
+  if (a->P == 0) {
+    const size_t T = (size_t) ((a->W + kTile - 1) / kTile) * ((a->H + kTile - 1) / kTile);
+    cudaMemsetAsync(a->tile_counts, 0, sizeof(int32_t) * T, (cudaStream_t) stream);
+    cudaMemsetAsync(a->counters, 0, sizeof(int64_t) * FSGS_NUM_COUNTERS, (cudaStream_t) stream);
+    return FSGS_OK;
+  }
   FSGS_REQUIRE(a->opac && a->shs && a->Tw2v && a->Tv2s && a->campos);
   FSGS_REQUIRE(a->means2D && a->inverse_m && a->normal_opacity && a->depths && a->radii && a->tiles_touched);
-  FSGS_REQUIRE(a->tile_counts && a->counters);
   FSGS_REQUIRE(a->trans_precomp || a->trans_mat);
   if (a->sh_degree > FSGS_MAX_SH_DEGREE) return FSGS_ERR_UNSUPPORTED;
   if (a->sh_degree >= 0) {
     FSGS_REQUIRE(a->colors);
     const int nb = (a->sh_degree + 1) * (a->sh_degree + 1);
-    if (a->sh_rest) FSGS_REQUIRE(a->n_dc >= 1 && a->n_rest >= nb - 1);
+    if (a->sh_rest && a->n_rest > 0) FSGS_REQUIRE(a->n_dc >= 1 && a->n_rest >= nb - 1);
     else FSGS_REQUIRE(a->n_dc >= nb);
   }
   if (a->lbs) FSGS_REQUIRE(lbs_valid(a->lbs) && a->warped_means && a->warped_scales && a->warped_rots);

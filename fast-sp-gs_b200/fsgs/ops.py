@@ -396,7 +396,9 @@ def _batch_dims(x1, x2):
     _need(x1.dtype == torch.float32 and x2.dtype == torch.float32, "cdist_top: float32 only")
     N, D, M = x1.shape[-2], x1.shape[-1], x2.shape[-2]
     _need(x2.shape[-1] == D, f"The dimenstion of point must be {D}")
-    B = x1.numel() // max(N * D, 1)
+    B = 1
+    for n in x1.shape[:-2]:
+        B *= n
     _need(x2.numel() == B * M * D, "The shape[:-2] of x2 must be same with x1")
     return B, N, M, D
 
@@ -408,6 +410,8 @@ def cdist_top(x1, x2, largest=False):
     x1, x2 = x1.contiguous(), x2.contiguous()
     dist = torch.empty(x1.shape[:-1], device=x1.device, dtype=torch.float32)
     index = torch.empty(x1.shape[:-1], device=x1.device, dtype=torch.int64)
+    if dist.numel() == 0:
+        return [dist, index]
     check(lib().fsgs_cdist_top(B, N, M, D, _ptr(x1), _ptr(x2), int(bool(largest)), _ptr(dist), _ptr(index), _stream()),
           "fsgs_cdist_top")
     return [dist, index]
