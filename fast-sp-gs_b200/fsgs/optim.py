@@ -1,0 +1,64 @@
+"""``SparseGaussianAdam``: the reference's visibility-masked Adam (``fast_2d_gs/sparse_gaussian_adam.py:10-49``)
+with every parameter group updated by ONE kernel launch instead of one launch per group."""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+from .ops import _ptr, _stream
+
+
+class SparseGaussianAdam(torch.optim.Adam):
+    """Same constructor, ``set_before_step(visibility, N)`` and ``step()`` as the reference class; beta1 = 0.9 and
+    beta2 = 0.999 are fixed and the bias correction is folded into the learning rate, as there.
+    State layout (``step`` as a CPU float32 tensor, ``exp_avg``, ``exp_avg_sq``) is the reference's, so its
+    checkpoints load."""
+
+    def __init__(self, params, lr, eps):
+        super().__init__(params=params, lr=lr, eps=eps)
+        self.N = None
+        self.visibility = None
+
+    def set_before_step(self, visibility, N):
+        self.visibility, self.N = visibility, N
+
+    @torch.no_grad()
+    def step(self):
+        batch = []
+        for group in self.param_groups:
+            assert len(group["params"]) == 1, "more than one tensor in group"
+            param = group["params"][0]
+            if param.grad is None or param.grad.numel() == 0:
+                continue
+            state = self.state[param]
+            if len(state) == 0:
+                state["step"] = torch.tensor(0.0, dtype=torch.float32)
+                state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+                state["exp_avg_sq"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+            state["step"] += 1
+            step = state["step"]
+            lr_eff = group["lr"] * (1 - 0.999 ** step) ** 0.5 / (1 - 0.9 ** step)
+            batch.append((param, param.grad, state["exp_avg"], state["exp_avg_sq"], float(lr_eff), group["eps"]))
+        if not batch:
+            return
+        assert self.N is not None, "call set_before_step(visibility, N) before step()"
+        masked_adam_step(batch, self.visibility, self.N)
+
+
+def masked_adam_step(batch, visibility, N, b1=0.9, b2=0.999):
+    """``batch``: list of (param, grad, exp_avg, exp_avg_sq, lr_eff, eps) with ``param.numel() % N == 0``.
+    Launches ``fsgs_adam_masked_multi`` once per eight tensors."""
+    vis = visibility.contiguous()
+    for i in range(0, len(batch), 8):
+        chunk = batch[i:i + 8]
+        arr = (_lib.AdamTensor * len(chunk))()
+        keep = []
+        for k, (p, g, m, v, lr, eps) in enumerate(chunk):
+            assert p.is_cuda and p.is_contiguous() and p.dtype == torch.float32
+            g = g.contiguous()
+            keep.append(g)
+            arr[k].param, arr[k].grad, arr[k].exp_avg, arr[k].exp_avg_sq = p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr()
+            arr[k].M, arr[k].lr, arr[k].eps = p.numel() // N, lr, eps
+        check(lib().fsgs_adam_masked_multi(len(chunk), arr, _ptr(vis), int(N), b1, b2, _stream()),
+              "fsgs_adam_masked_multi")

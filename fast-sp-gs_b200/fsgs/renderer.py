@@ -1,0 +1,303 @@
+"""``GS_2D_fast_render`` with the reference's signature and result dictionary
+(``fast_2d_gs/renderer/gs_2d_fast_render.py:670-754``) on top of ``libfsgs.so``.
+
+Differences from routing the reference's own ``_Fast_Render`` through ``fsgs.install``:
+  * the packed render records made by the preprocess kernel go straight to the compositing kernels;
+  * no device-to-host read sizes the tile lists: they are written into a buffer whose capacity follows the
+    pair count seen on earlier frames (``ListCapacity``); the counters come back asynchronously and an
+    overflow raises on the next call or on ``check_overflow()``;
+  * optionally the superpoint LBS warp is evaluated inside the preprocess kernel (``lbs=...``).
+Results are the same tensors, bit for bit, as through the operator-by-operator path.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from . import ops
+from ._lib import lib, check
+
+
+class ListCapacity:
+    """Capacity policy for the tile lists of one device: at least ``floor`` entries, else ``growth`` x the largest
+    pair count seen so far.  Counter read-backs are asynchronous (pinned buffer + event)."""
+
+    def __init__(self, growth=1.5, floor=1 << 16):
+        self.growth, self.floor = growth, floor
+        self.high_water = 0
+        self._pending = []  # (event, pinned counters, capacity)
+        self.overflowed = 0
+
+    def capacity(self, P):
+        self.poll()
+        if self.high_water == 0:
+            return max(self.floor, 8 * P)
+        return max(self.floor, int(self.high_water * self.growth))
+
+    def submit(self, counters, capacity):
+        host = torch.empty(4, dtype=torch.int64, pin_memory=True)
+        host.copy_(counters, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pending.append((ev, host, capacity))
+
+    def poll(self, wait=False):
+        keep = []
+        for ev, host, cap in self._pending:
+            if wait:
+                ev.synchronize()
+            if ev.query():
+                pairs = int(host[1])
+                self.high_water = max(self.high_water, pairs)
+                if int(host[2]) > 0:
+                    self.overflowed += 1
+                    self.high_water = max(self.high_water, pairs)
+            else:
+                keep.append((ev, host, cap))
+        self._pending = keep
+
+    def check_overflow(self, wait=True):
+        """Raise if an earlier frame's tile lists did not fit (that frame was rendered from truncated lists)."""
+        self.poll(wait)
+        if self.overflowed:
+            n, self.overflowed = self.overflowed, 0
+            raise RuntimeError(f"fsgs: tile lists overflowed their buffer on {n} earlier frame(s); "
+                               "those frames are invalid.  The capacity has been raised; render them again.")
+
+
+_capacity = {}
+
+
+def list_capacity(device=None):
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev not in _capacity:
+        _capacity[dev] = ListCapacity()
+    return _capacity[dev]
+
+
+def make_lbs(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds):
+    """ctypes view of the LBS inputs (all contiguous CUDA tensors; ``knn_idx`` int64)."""
+    l = _lib.LBS()
+    l.K, l.M = knn_idx.shape[1], sp_q.shape[0]
+    for name, t in (("xyz", xyz), ("scaling_raw", scaling_raw), ("rotation_raw", rotation_raw), ("knn_idx", knn_idx),
+                    ("knn_w", knn_w), ("sp_q", sp_q), ("sp_t", sp_t), ("sp_dr", sp_dr), ("sp_ds", sp_ds)):
+        ops._need(t.is_cuda and t.is_contiguous(), f"lbs.{name} must be a contiguous CUDA tensor")
+        setattr(l, name, t.data_ptr())
+    ops._need(knn_idx.dtype == torch.int64, "lbs.knn_idx must be int64")
+    return l
+
+
+class _LbsWarp(torch.autograd.Function):
+    """Rigid LBS blend as its own operator (restates fast_2d_gs/network.py:545-573, 630-645)."""
+
+    @staticmethod
+    def forward(ctx, xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds):
+        ts = [t.contiguous() for t in (xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds)]
+        P = ts[0].shape[0]
+        l = make_lbs(*ts)
+        f32 = dict(device=xyz.device, dtype=torch.float32)
+        means, scales, rots = torch.empty(P, 3, **f32), torch.empty(P, 2, **f32), torch.empty(P, 4, **f32)
+        check(lib().fsgs_lbs_warp_forward(P, ctypes.byref(l), ops._ptr(means), ops._ptr(scales), ops._ptr(rots),
+                                          ops._stream()), "fsgs_lbs_warp_forward")
+        ctx.save_for_backward(*ts)
+        return means, scales, rots
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g_means, g_scales, g_rots):
+        ts = ctx.saved_tensors
+        grads = lbs_backward(ts, g_means.contiguous(), g_scales.contiguous(), g_rots.contiguous())
+        return grads[0], grads[1], grads[2], None, grads[3], grads[4], grads[5], grads[6], grads[7]
+
+
+def lbs_backward(ts, g_means, g_scales, g_rots):
+    xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds = ts
+    P = xyz.shape[0]
+    l = make_lbs(*ts)
+    outs = [torch.empty_like(t) for t in (xyz, scaling_raw, rotation_raw, knn_w, sp_q, sp_t, sp_dr, sp_ds)]
+    g = _lib.LBSGrads()
+    for name, t in zip(("g_xyz", "g_scaling_raw", "g_rotation_raw", "g_knn_w", "g_sp_q", "g_sp_t", "g_sp_dr",
+                        "g_sp_ds"), outs):
+        setattr(g, name, t.data_ptr())
+    check(lib().fsgs_lbs_warp_backward(P, ctypes.byref(l), ops._ptr(g_means), ops._ptr(g_scales), ops._ptr(g_rots),
+                                       ctypes.byref(g), ops._stream()), "fsgs_lbs_warp_backward")
+    return outs
+
+
+def lbs_warp(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds):
+    """-> (means [P,3], scales [P,2], rotations [P,4]) of the warped Gaussians; differentiable in every float input."""
+    return _LbsWarp.apply(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds)
+
+
+class _FastRender(torch.autograd.Function):
+    """preprocess -> tile binning -> compositing, and the chain of adjoints
+    (the reference's ``_Fast_Render``, renderer/gs_2d_fast_render.py:592-667)."""
+
+    @staticmethod
+    def forward(ctx, means3D, scales, rotations, opacities, shs, sh_rest, Tw2v, Tv2c, Tv2s, campos, cfg, trans_mat_t2,
+                culling, accum_max_count, accum_weights_p, accum_weights_count, means2D, *lbs_tensors):
+        W, H, sh_degree, near_n, far_n, only_image = cfg
+        use_lbs = len(lbs_tensors) == 9
+        P = opacities.shape[0]
+        lbs = warped = None
+        if use_lbs:
+            lbs_tensors = tuple(t.contiguous() for t in lbs_tensors)
+            lbs = make_lbs(*lbs_tensors)
+            f32 = dict(device=opacities.device, dtype=torch.float32)
+            warped = (torch.empty(P, 3, **f32), torch.empty(P, 2, **f32), torch.empty(P, 4, **f32))
+            means3D, scales, rotations = warped
+        o = ops.preprocess_launch(W, H, sh_degree, means3D, scales, rotations, opacities, shs, sh_rest, Tw2v, Tv2s,
+                                  campos, None, means2D, culling, lbs, warped)
+        cap_policy = list_capacity(opacities.device)
+        capacity = cap_policy.capacity(P)
+        ranges, point_list, tile_order = ops.bin_launch(W, H, o, opacities, capacity)
+        cap_policy.submit(o["counters"], capacity)
+        outs = ops.render_forward_launch(W, H, near_n, far_n, only_image, P, o["records"], point_list, ranges,
+                                         tile_order, trans_mat_t2, accum_max_count, accum_weights_p,
+                                         accum_weights_count)
+        pixel_colors, pixel_opacity, pixel_extras, pixel_flow, n_contrib = outs
+        ctx.cfg = cfg
+        ctx.use_lbs = use_lbs
+        ctx.has = (sh_rest is not None, trans_mat_t2 is not None, pixel_extras is not None, pixel_flow is not None)
+        saved = [means3D, scales, rotations, opacities, shs, Tw2v, Tv2s, campos, o["means2D"], o["trans_mat"],
+                 o["radii"], o["colors"], o["records"], ranges, point_list, tile_order, pixel_opacity, n_contrib]
+        saved += [t for t in (sh_rest, trans_mat_t2, pixel_extras, pixel_flow) if t is not None]
+        saved += list(lbs_tensors) if use_lbs else []
+        ctx.save_for_backward(*saved)
+        ctx.mark_non_differentiable(n_contrib, o["radii"])
+        return pixel_colors, pixel_opacity, pixel_extras, pixel_flow, n_contrib, o["radii"]
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g_colors, g_opacity, g_extras, g_flow, _g_nc, _g_radii):
+        W, H, sh_degree, near_n, far_n, only_image = ctx.cfg
+        sv = list(ctx.saved_tensors)
+        (means3D, scales, rotations, opacities, shs, Tw2v, Tv2s, campos, means2D, trans_mat, radii, colors, records,
+         ranges, point_list, tile_order, pixel_opacity, n_contrib) = sv[:18]
+        rest = sv[18:]
+        has_rest, has_t2, has_extras, has_flow = ctx.has
+        sh_rest = rest.pop(0) if has_rest else None
+        trans_mat_t2 = rest.pop(0) if has_t2 else None
+        pixel_extras = rest.pop(0) if has_extras else None
+        rest.pop(0) if has_flow else None
+        lbs_tensors = rest if ctx.use_lbs else None
+        P = opacities.shape[0]
+        dev = opacities.device
+        zeros = lambda *s: torch.zeros(*s, device=dev, dtype=torch.float32)
+        g_colors = g_colors.contiguous() if g_colors is not None else zeros(3, H, W)
+        g_opacity = g_opacity.contiguous() if g_opacity is not None else zeros(H, W)
+        aux = has_extras
+        if aux and g_extras is None:
+            g_extras = zeros(8, H, W)
+        flow = aux and has_flow and g_flow is not None
+        g_col, g_m2d, g_tm, g_im, g_no = ops.render_backward_launch(
+            W, H, near_n, far_n, P, records, point_list, ranges, tile_order, trans_mat_t2 if flow else None,
+            pixel_opacity, pixel_extras if aux else None, n_contrib, g_colors, g_opacity,
+            g_extras.contiguous() if aux else None, g_flow.contiguous() if flow else None)
+        # one zero-filled block for all parameter gradients
+        n_sh = shs.numel() // max(P, 1)
+        n_rest = sh_rest.numel() // max(P, 1) if has_rest else 0
+        want_sh = sh_degree >= 0
+        width = 3 + 2 + 4 + 1 + (n_sh if want_sh else 0) + (n_rest if want_sh else 0)
+        block = torch.zeros(P * width, device=dev, dtype=torch.float32)
+        off = 0
+
+        def take(n, shape):
+            nonlocal off
+            v = block[off * P:(off + n) * P].view(shape)
+            off += n
+            return v
+
+        gm, gs, gr, go = take(3, (P, 3)), take(2, (P, 2)), take(4, (P, 4)), take(1, (P, 1))
+        gsh = take(n_sh, shs.shape) if want_sh else None
+        grest = take(n_rest, sh_rest.shape) if (want_sh and has_rest) else None
+        a = _lib.PreprocessBwdArgs()
+        a.P, a.W, a.H, a.sh_degree = P, W, H, sh_degree
+        a.n_dc = shs.shape[1] if sh_degree >= 0 else 1
+        a.n_rest = sh_rest.shape[1] if has_rest else 0
+        p = ops._ptr
+        a.means, a.scales, a.rots, a.shs, a.sh_rest = p(means3D), p(scales), p(rotations), p(shs), p(sh_rest)
+        a.Tw2v, a.Tv2s, a.campos, a.trans_mat, a.colors, a.radii = p(Tw2v), p(Tv2s), p(campos), p(trans_mat), p(colors), p(radii)
+        a.grad_means2D, a.grad_trans_mat, a.grad_inverse_m = p(g_m2d), p(g_tm), p(g_im)
+        a.grad_colors, a.grad_normal_opacity = p(g_col), p(g_no)
+        a.grad_means, a.grad_scales, a.grad_rots, a.grad_opac = p(gm), p(gs), p(gr), p(go)
+        a.grad_shs, a.grad_sh_rest = p(gsh), p(grest)
+        check(lib().fsgs_preprocess_backward(ctypes.byref(a), ops._stream()), "fsgs_preprocess_backward")
+        if sh_degree < 0:
+            gsh = g_col  # colours were an input: their gradient is the compositing gradient itself
+        grads = [gm, gs, gr, go, gsh, grest, None, None, None, None, None, None, None, None, None, None, g_m2d]
+        if ctx.use_lbs:
+            lg = lbs_backward(lbs_tensors, gm, gs, gr)
+            grads[0] = grads[1] = grads[2] = None
+            grads += [lg[0], lg[1], lg[2], None, lg[3], lg[4], lg[5], lg[6], lg[7]]
+        return tuple(grads)
+
+
+def depths_to_points(Tw2v, Tv2c, size, depthmap):
+    """Back-project a depth map to world points (renderer/gs_2d_fast_render.py:558-575; device-agnostic here)."""
+    c2w = Tw2v.inverse()
+    W, H = size
+    ndc2pix = torch.tensor([[W / 2, 0, 0, W / 2], [0, H / 2, 0, H / 2], [0, 0, 0, 1]], dtype=torch.float32,
+                           device=Tw2v.device).T
+    projection_matrix = c2w.T @ (Tv2c @ Tw2v).T
+    intrins = (projection_matrix @ ndc2pix)[:3, :3].T
+    gx, gy = torch.meshgrid(torch.arange(W, device=c2w.device).float(), torch.arange(H, device=c2w.device).float(),
+                            indexing="xy")
+    points = torch.stack([gx, gy, torch.ones_like(gx)], dim=-1).reshape(-1, 3)
+    rays_d = points @ intrins.inverse().T @ c2w[:3, :3].T
+    return depthmap.reshape(-1, 1) * rays_d + c2w[:3, 3]
+
+
+def depth_to_normal(Tw2v, Tv2c, size, depth):
+    """Pseudo surface normal from a depth map (renderer/gs_2d_fast_render.py:578-589)."""
+    points = depths_to_points(Tw2v, Tv2c, size, depth).reshape(*depth.shape[1:], 3)
+    output = torch.zeros_like(points)
+    dx = points[2:, 1:-1] - points[:-2, 1:-1]
+    dy = points[1:-1, 2:] - points[1:-1, :-2]
+    output[1:-1, 1:-1, :] = torch.nn.functional.normalize(torch.linalg.cross(dx, dy, dim=-1), dim=-1)
+    return output
+
+
+def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s, campos=None, focals=None, FoV=None,
+                      is_opengl=False, near=0.2, far=100, sh_degree=0, colors=None, sh_features=None,
+                      sh_features_rest=None, depth_ratio=1., culling=None, accum_max_count=None,
+                      accum_weights_p=None, accum_weights_count=None, trans_mat_t2=None, lbs=None, only_image=False,
+                      **kwargs):
+    """Render one view.  Same arguments and result dictionary as the reference's ``GS_2D_fast_render``
+    (renderer/gs_2d_fast_render.py:670-754): ``images [3,H,W]``, ``normals`` (world space), ``opacity``,
+    ``distortion``, ``surf_depth``, ``surf_normal``, ``radii``, ``viewspace_points`` (its ``.grad`` receives the
+    densification proxy), ``visibility_filter``, ``flows``.  No background is composited.
+
+    Extra, optional: ``lbs=(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds)`` evaluates the
+    superpoint warp inside the preprocess kernel (then ``points/scales/rotations`` are ignored);
+    ``only_image=True`` skips the auxiliary channels and returns only images / opacity / radii entries.
+    """
+    P = opacity.shape[0]
+    means2D = torch.zeros(P, 2, device=opacity.device, dtype=torch.float32, requires_grad=True)
+    W, H = (int(v) for v in size)
+    if campos is None:
+        campos = Tw2v.inverse()[:3, 3].contiguous()
+    feats = sh_features if colors is None else colors
+    cfg = (W, H, int(sh_degree) if colors is None else -1, float(near), float(far), bool(only_image))
+    geom = (points, scales, rotations)
+    if lbs is None:
+        geom = tuple(t.contiguous() for t in geom)
+    lbs_args = tuple(lbs) if lbs is not None else ()
+    images, opacities, out_extras, flows, n_contrib, radii = _FastRender.apply(
+        geom[0], geom[1], geom[2], opacity.contiguous(), feats.contiguous(),
+        None if sh_features_rest is None or colors is not None else sh_features_rest.contiguous(),
+        Tw2v.contiguous(), Tv2c.contiguous(), Tv2s.contiguous(), campos.contiguous(), cfg, trans_mat_t2, culling,
+        accum_max_count, accum_weights_p, accum_weights_count, means2D, *lbs_args)
+    out = {"images": images, "opacity": opacities, "radii": radii, "viewspace_points": means2D,
+           "visibility_filter": radii > 0, "flows": flows}
+    if only_image:
+        return out
+    depths, normals, median_depths, distortion, _ = out_extras.split([1, 3, 1, 1, 2], dim=0)
+    normals = (normals.permute(1, 2, 0) @ Tw2v[:3, :3]).permute(2, 0, 1)
+    median_depths = torch.nan_to_num(median_depths, 0, 0)
+    depths = torch.nan_to_num(depths, 0, 0)
+    surf_depth = depths * (1 - depth_ratio) + depth_ratio * median_depths
+    surf_normal = depth_to_normal(Tw2v, Tv2c, (W, H), surf_depth).permute(2, 0, 1)
+    surf_normal = surf_normal * opacities.detach()
+    out.update(normals=normals, distortion=distortion, surf_depth=surf_depth, surf_normal=surf_normal)
+    return out

@@ -1,0 +1,171 @@
+"""GPU tests of the host-side mirror: GS_2D_fast_render, the fused LBS warp, SparseGaussianAdam, install()."""
+import sys
+
+import pytest
+import torch
+
+import oracle as orc
+from util import cpu, make_scene, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _lbs_inputs(s, M=64, K=3, seed=0):
+    from fsgs import ops, workloads as wl
+    sp = wl.superpoints(s["means"].cpu(), M=M, seed=seed)
+    c = sp["centres"].cuda()
+    d2, idx = ops.knn(s["means"], c, K)
+    w = torch.softmax(-d2, dim=-1).contiguous()
+    q = sp["sp_q"].cuda()
+    t = (sp["sp_t_raw"].cuda() + c - orc.quat_rotate(q, c)).contiguous()  # rotation about the superpoint's own centre
+    return dict(xyz=s["means"], scaling_raw=s["log_scales"], rotation_raw=s["rots_raw"], knn_idx=idx, knn_w=w,
+                sp_q=q, sp_t=t, sp_dr=sp["sp_dr"].cuda(), sp_ds=sp["sp_ds"].cuda())
+
+
+def test_lbs_warp_forward_backward_vs_torch():
+    from fsgs.renderer import lbs_warp
+    s, cam = make_scene(5000, 64, 64, seed=3)
+    L = _lbs_inputs(s)
+    names = ["xyz", "scaling_raw", "rotation_raw", "knn_w", "sp_q", "sp_t", "sp_dr", "sp_ds"]
+    a = {k: (v.clone().requires_grad_() if k in names else v) for k, v in L.items()}
+    b = {k: (v.clone().requires_grad_() if k in names else v) for k, v in L.items()}
+    order = ["xyz", "scaling_raw", "rotation_raw", "knn_idx", "knn_w", "sp_q", "sp_t", "sp_dr", "sp_ds"]
+    out_a = lbs_warp(*[a[k] for k in order])
+    out_b = orc.lbs_warp(*[b[k] for k in order])
+    for x, y in zip(out_a, out_b):
+        assert torch.allclose(x, y, rtol=1e-5, atol=1e-6)
+    g = torch.Generator().manual_seed(1)
+    ups = [torch.randn(x.shape, generator=g).cuda() for x in out_a]
+    torch.autograd.backward(out_a, ups)
+    torch.autograd.backward(out_b, ups)
+    for k in names:
+        assert rel_l2(a[k].grad, b[k].grad) < 1e-4, k
+
+
+def _render(s, cam, W, H, **kw):
+    from fsgs.renderer import GS_2D_fast_render
+    return GS_2D_fast_render(s.get("means"), s.get("scales"), s.get("rots"), s["opac"], (W, H), cam["Tw2v"],
+                             cam["Tv2c"], cam["Tv2s"], cam["campos"], sh_degree=3, sh_features=s["sh_dc"],
+                             sh_features_rest=s["sh_rest"], **kw)
+
+
+def test_render_api_matches_operator_chain():
+    from fsgs import ops
+    P, W, H = 20_000, 256, 192
+    s, cam = make_scene(P, W, H, seed=8)
+    leaves = {k: s[k].clone().requires_grad_() for k in ("means", "scales", "rots", "opac", "sh_dc", "sh_rest")}
+    out = _render(leaves, cam, W, H)
+    assert set(out) >= {"images", "normals", "opacity", "distortion", "surf_depth", "surf_normal", "radii",
+                        "viewspace_points", "visibility_filter", "flows"}
+    assert out["images"].shape == (3, H, W) and out["surf_normal"].shape == (3, H, W) and out["flows"] is None
+    pre = ops.gs_2d_fast_preprocess_forward(W, H, 3, False, s["means"], s["scales"], s["rots"], s["opac"], s["sh_dc"],
+                                            s["sh_rest"], cam["Tw2v"], cam["Tv2c"], cam["Tv2s"], cam["campos"], None,
+                                            None, None, True)
+    fw = ops.GS_2D_fast_render_forward(W, H, 0.2, 100.0, False, pre[0], pre[1], pre[4], pre[2], pre[3], pre[8],
+                                       pre[7], None, None, None, None, None)
+    assert torch.equal(out["images"], fw[0]) and torch.equal(out["opacity"], fw[1])
+    assert torch.equal(out["radii"], pre[6])
+    g = torch.Generator().manual_seed(2)
+    g_img, g_op = torch.randn(3, H, W, generator=g).cuda(), torch.randn(H, W, generator=g).cuda()
+    (out["images"] * g_img).sum().backward(retain_graph=True)
+    g1 = {k: v.grad.clone() for k, v in leaves.items()}
+    gr = ops.GS_2D_fast_render_backward(pre[0], pre[4], pre[1], pre[2], pre[3], None, fw[0], fw[1], fw[2], None,
+                                        g_img, torch.zeros_like(g_op), torch.zeros(8, H, W, device="cuda"), None,
+                                        pre[7], pre[8], fw[4], 0.2, 100.0, None, None, None, None, None, None)
+    gm, gs, gq, go = (torch.zeros(P, k, device="cuda") for k in (3, 2, 4, 1))
+    gsh, grest = torch.zeros_like(s["sh_dc"]), torch.zeros_like(s["sh_rest"])
+    ops.gs_2d_fast_preprocess_backward(W, H, 3, False, s["means"], s["scales"], s["rots"], s["opac"], s["sh_dc"],
+                                       s["sh_rest"], cam["Tw2v"], cam["Tv2s"], cam["campos"], pre[2], pre[6], pre[1],
+                                       pre[4], gr[1], gr[2], gr[3], None, gr[0], gr[4], gm, gs, gq, go, gsh, grest,
+                                       None, None)
+    for k, ref in (("means", gm), ("scales", gs), ("rots", gq), ("opac", go), ("sh_dc", gsh), ("sh_rest", grest)):
+        assert rel_l2(g1[k], ref) < 1e-4, k  # same kernels; only the order of float atomics differs
+    assert rel_l2(out["viewspace_points"].grad, gr[1]) < 1e-4  # the densification proxy
+
+
+def test_render_fused_lbs_equals_unfused():
+    from fsgs.renderer import lbs_warp
+    P, W, H = 20_000, 200, 160
+    s, cam = make_scene(P, W, H, seed=9)
+    L = _lbs_inputs(s, M=128)
+    order = ["xyz", "scaling_raw", "rotation_raw", "knn_idx", "knn_w", "sp_q", "sp_t", "sp_dr", "sp_ds"]
+    flt = [k for k in order if k != "knn_idx"]
+    a = {k: (v.clone().requires_grad_() if k in flt else v) for k, v in L.items()}
+    b = {k: (v.clone().requires_grad_() if k in flt else v) for k, v in L.items()}
+    rest = {k: s[k] for k in ("opac", "sh_dc", "sh_rest")}
+    out_a = _render(dict(rest), cam, W, H, lbs=[a[k] for k in order])
+    m, sc, r = lbs_warp(*[b[k] for k in order])
+    out_b = _render(dict(rest, means=m, scales=sc, rots=r), cam, W, H)
+    assert torch.equal(out_a["images"], out_b["images"])
+    g = torch.randn(3, H, W, generator=torch.Generator().manual_seed(4)).cuda()
+    (out_a["images"] * g).sum().backward()
+    (out_b["images"] * g).sum().backward()
+    for k in flt:
+        assert rel_l2(a[k].grad, b[k].grad) < 1e-4, k
+
+
+def test_sparse_adam_fused_equals_per_tensor():
+    from fsgs import ops
+    from fsgs.optim import SparseGaussianAdam
+    g = torch.Generator().manual_seed(5)
+    N = 3001
+    shapes = [(N, 3), (N, 1, 3), (N, 15, 3), (N, 1), (N, 2), (N, 4)]
+    params = [torch.nn.Parameter(torch.randn(*sh, generator=g).cuda()) for sh in shapes]
+    copies = [p.detach().clone() for p in params]
+    lrs = [1.6e-4, 2.5e-3, 1.25e-4, 0.05, 5e-3, 1e-3]
+    opt = SparseGaussianAdam([{"params": [p], "lr": lr} for p, lr in zip(params, lrs)], lr=0.0, eps=1e-15)
+    ms = [torch.zeros_like(c) for c in copies]
+    vs = [torch.zeros_like(c) for c in copies]
+    for step in range(1, 4):
+        vis = (torch.rand(N, generator=g) > 0.3).cuda()
+        grads = [torch.randn(*sh, generator=g).cuda() for sh in shapes]
+        for p, gr in zip(params, grads):
+            p.grad = gr
+        opt.set_before_step(vis, N)
+        opt.step()
+        for c, gr, m, v, lr in zip(copies, grads, ms, vs, lrs):
+            t = torch.tensor(float(step), dtype=torch.float32)
+            lr_eff = lr * (1 - 0.999 ** t) ** 0.5 / (1 - 0.9 ** t)
+            ops.AdamMasksedUpdated(c, gr, m, v, vis, lr_eff, 0.9, 0.999, 1e-15, N, c.numel() // N)
+        for p, c in zip(params, copies):
+            assert torch.equal(p.detach(), c)
+    assert opt.state[params[0]]["step"].item() == 3.0
+
+
+def test_install_exposes_the_nine_operator_names():
+    import fsgs
+    mod = fsgs.install("fast_2d_gs_test._C._C")
+    names = ["gs_2d_fast_preprocess_forward", "gs_2d_fast_preprocess_backward", "GS_2D_fast_render_forward",
+             "GS_2D_fast_render_backward", "gs_2d_fast_compute_transmat_forward",
+             "gs_2d_fast_compute_trans_mat_backward", "cdist_top", "cdist_top_backward", "AdamMasksedUpdated"]
+    assert all(callable(getattr(mod, n)) for n in names)
+    assert sys.modules["fast_2d_gs_test._C._C"] is mod
+
+    class Holder:  # the reference stores operators as class attributes and calls them through self
+        op = mod.cdist_top
+
+    d, i = Holder().op(torch.rand(10, 3, device="cuda"), torch.rand(4, 3, device="cuda"))
+    assert d.shape == (10,)
+
+
+def test_list_overflow_is_reported():
+    from fsgs import renderer
+    P, W, H = 20_000, 256, 192
+    s, cam = make_scene(P, W, H, seed=8)
+    dev = torch.cuda.current_device()
+    saved = renderer._capacity.get(dev)
+    renderer._capacity[dev] = renderer.ListCapacity(floor=16)
+    renderer._capacity[dev].high_water = 1  # pretend earlier frames were almost empty
+    try:
+        out = _render(s, cam, W, H, only_image=True)
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="overflowed"):
+            renderer._capacity[dev].check_overflow()
+        out2 = _render(s, cam, W, H, only_image=True)  # capacity has grown: this frame is whole
+        renderer._capacity[dev].check_overflow()
+        assert float(out2["opacity"].max()) > 0.5
+    finally:
+        if saved is not None:
+            renderer._capacity[dev] = saved
+        else:
+            del renderer._capacity[dev]

@@ -1,0 +1,96 @@
+"""CPU-only checks: the C ABI library loads and exports every declared symbol, headers and bindings agree,
+synthetic workloads are reproducible, and the oracle's k-NN / Adam restatements hold against plain torch."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import oracle as orc
+from conftest import ROOT
+
+
+def test_library_exports_every_declared_symbol():
+    from fsgs import _lib
+    from fsgs.build import LIB, build
+    build()
+    handle = ctypes.CDLL(LIB)
+    header = open(os.path.join(ROOT, "include", "fsgs.h")).read()
+    declared = set(re.findall(r"\b(fsgs_[a-z0-9_]+)\s*\(", header))
+    declared -= {"fsgs_status"}
+    assert declared, "no declarations found"
+    for name in sorted(declared):
+        assert hasattr(handle, name), f"{name} declared in include/fsgs.h but not exported"
+    assert declared == set(_lib.SYMBOLS), "python binding table and header disagree"
+    _lib.lib()
+    assert _lib.lib().fsgs_version() >= 100
+    assert _lib.lib().fsgs_status_string(-3) == b"workspace too small"
+
+
+def test_ctypes_structs_match_header_field_order():
+    from fsgs import _lib
+    header = open(os.path.join(ROOT, "include", "fsgs.h")).read()
+    for cname, cls in (("fsgs_preprocess_args", _lib.PreprocessArgs), ("fsgs_bin_args", _lib.BinArgs),
+                       ("fsgs_render_args", _lib.RenderArgs), ("fsgs_render_bwd_args", _lib.RenderBwdArgs),
+                       ("fsgs_preprocess_bwd_args", _lib.PreprocessBwdArgs), ("fsgs_lbs", _lib.LBS),
+                       ("fsgs_lbs_grads", _lib.LBSGrads), ("fsgs_adam_tensor", _lib.AdamTensor)):
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        fields = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            names = re.sub(r"^(const\s+)?[A-Za-z_0-9]+\s*", "", decl)
+            fields += [n.strip().lstrip("*").strip() for n in names.split(",")]
+        assert fields == [f[0] for f in cls._fields_], cname
+
+
+def test_operators_refuse_cpu_tensors():
+    from fsgs import ops
+    with pytest.raises(RuntimeError):
+        ops.cdist_top(torch.zeros(4, 3), torch.zeros(2, 3))
+    with pytest.raises(RuntimeError):
+        ops.AdamMasksedUpdated(torch.zeros(4, 3), torch.zeros(4, 3), torch.zeros(4, 3), torch.zeros(4, 3),
+                               torch.ones(4, dtype=torch.bool), 1e-3, 0.9, 0.999, 1e-8, 4, 3)
+
+
+def test_workloads_are_reproducible_and_shaped():
+    from fsgs import workloads as wl
+    a, b = wl.surfels(1000, seed=3), wl.surfels(1000, seed=3)
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    assert a["sh_rest"].shape == (1000, 15, 3) and a["scales"].shape == (1000, 2)
+    assert torch.allclose(a["rots"].norm(dim=-1), torch.ones(1000), atol=1e-6)
+    cam = wl.camera(800, 800)
+    assert torch.allclose(cam["Tw2v"][:3, 3], torch.tensor([0.0, 0.0, 4.0]))  # looks at the origin: no x/y translation
+    assert abs(float(cam["Tv2s"][0, 0]) - 0.5 * 800 / torch.tan(torch.tensor(0.345)).item()) < 1e-2
+    x, c = wl.knn_points_c1(2000, 64, seed=0)
+    assert x.shape == (2000, 3) and c.shape == (64, 3) and float(x.abs().max()) <= 1.0
+
+
+def test_oracle_knn_against_torch():
+    from fsgs import workloads as wl
+    x, c = wl.knn_points_c1(3000, 100, seed=1)
+    d2, idx = orc.knn(x, c, 3)
+    full = ((x[:, None, :] - c[None]) ** 2).sum(-1)
+    ref_d, ref_i = torch.topk(full, 3, dim=-1, largest=False)
+    assert torch.allclose(d2, ref_d, rtol=1e-5, atol=1e-7)
+    assert float((idx == ref_i).float().mean()) > 0.999  # torch breaks near-ties its own way
+    dist, i1 = orc.cdist_top(x, c)
+    assert torch.equal(i1, idx[:, 0]) and torch.allclose(dist, d2[:, 0].sqrt())
+
+
+def test_oracle_adam_against_torch():
+    g = torch.Generator().manual_seed(0)
+    N, M = 100, 5
+    p, gr = torch.randn(N, M, generator=g), torch.randn(N, M, generator=g)
+    m, v = torch.zeros(N, M), torch.zeros(N, M)
+    vis = torch.rand(N, generator=g) > 0.5
+    p0 = p.clone()
+    orc.adam(p, gr, m, v, vis, 1e-2, 0.9, 0.999, 1e-8, N, M)
+    m_ref = 0.1 * gr
+    v_ref = 0.001 * gr * gr
+    p_ref = p0 - 1e-2 * m_ref / (v_ref.sqrt() + 1e-8)
+    assert torch.allclose(p[vis], p_ref[vis], rtol=1e-5, atol=1e-6) and torch.equal(p[~vis], p0[~vis])
+    assert torch.allclose(m[vis], m_ref[vis], rtol=1e-5, atol=1e-8) and bool((m[~vis] == 0).all())
