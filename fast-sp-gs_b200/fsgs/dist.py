@@ -1,0 +1,58 @@
+"""Multi-GPU layer: one process per GPU, views sharded across ranks, per-Gaussian gradients summed by one
+all-reduce over a flat bucket (NCCL on GPUs, gloo in the CPU tests).  The reference renders a batch of views in a
+serial loop on one device (``fast_2d_gs/network.py:683-745``); every view only reads the replicated parameters,
+so views are independent units and the only exchange is the gradient sum before the optimizer step.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_views(n_views, rank, world_size):
+    """Views of a batch handled by ``rank``: rank, rank + world_size, ...  (sums are taken in this order)."""
+    return list(range(rank, n_views, world_size))
+
+
+class GradBucket:
+    """A flat fp32 buffer holding the gradients of ``params`` back to back.  ``reduce()`` copies the current
+    ``.grad`` tensors in, all-reduces the buffer once and re-points every ``.grad`` at its slice."""
+
+    def __init__(self, params):
+        self.params = list(params)
+        self.sizes = [p.numel() for p in self.params]
+        self.flat = torch.zeros(sum(self.sizes), dtype=torch.float32, device=self.params[0].device)
+        self.views, off = [], 0
+        for p, n in zip(self.params, self.sizes):
+            self.views.append(self.flat[off:off + n].view(p.shape))
+            off += n
+
+    def nbytes(self):
+        return self.flat.numel() * 4
+
+    def pack(self):
+        src = [p.grad if p.grad is not None else torch.zeros_like(p) for p in self.params]
+        torch._foreach_copy_(self.views, src)
+
+    def reduce(self, group=None, async_op=False):
+        self.pack()
+        work = None
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            work = dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+        for p, v in zip(self.params, self.views):
+            p.grad = v
+        return work
+
+
+def reduce_visibility(visible, group=None):
+    """Union of the per-rank visibility masks (bool [P]) -> bool [P] on every rank."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return visible
+    v = visible.to(torch.uint8)
+    dist.all_reduce(v, op=dist.ReduceOp.MAX, group=group)
+    return v.bool()
+
+
+def reduce_max_(t, group=None):
+    """In-place element-wise maximum across ranks (radii, running maxima of the densification statistics)."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return t

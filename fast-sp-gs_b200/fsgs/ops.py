@@ -34,6 +34,32 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# Optional per-launch timing: set TIMERS = {} and every C-ABI launch below is bracketed by a pair of CUDA events
+# recorded on the launching stream; read them back with timer_summary() after a synchronize.
+TIMERS = None
+
+
+class _timed:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if TIMERS is not None:
+            self.ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            self.ev[0].record()
+
+    def __exit__(self, *exc):
+        if TIMERS is not None:
+            self.ev[1].record()
+            TIMERS.setdefault(self.name, []).append(self.ev)
+
+
+def timer_summary():
+    """{name: (launches, mean ms)} of everything recorded since TIMERS was set (synchronises)."""
+    torch.cuda.synchronize()
+    return {k: (len(v), sum(a.elapsed_time(b) for a, b in v) / len(v)) for k, v in (TIMERS or {}).items()}
+
+
 def _ptr(t):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
@@ -113,7 +139,8 @@ def preprocess_launch(W, H, sh_degree, means3D, scales, rotations, opacities, sh
     a.inverse_m, a.normal_opacity, a.depths = _ptr(o["inverse_m"]), _ptr(o["normal_opacity"]), _ptr(o["depths"])
     a.radii, a.tiles_touched, a.records = _ptr(o["radii"]), _ptr(o["tiles_touched"]), _ptr(o["records"])
     a.tile_counts, a.counters = _ptr(o["tile_counts"]), _ptr(o["counters"])
-    check(lib().fsgs_preprocess_forward(ctypes.byref(a), _stream()), "fsgs_preprocess_forward")
+    with _timed("preprocess_forward"):
+        check(lib().fsgs_preprocess_forward(ctypes.byref(a), _stream()), "fsgs_preprocess_forward")
     return o
 
 
@@ -133,7 +160,8 @@ def bin_launch(W, H, o, opacities, capacity):
     b.radii, b.tile_counts, b.counters = _ptr(o["radii"]), _ptr(o["tile_counts"]), _ptr(o["counters"])
     b.capacity, b.point_list, b.ranges, b.tile_order = capacity, _ptr(point_list), _ptr(ranges), _ptr(tile_order)
     b.workspace, b.workspace_bytes = _ptr(ws), ws_bytes
-    check(lib().fsgs_bin_tiles(ctypes.byref(b), _stream()), "fsgs_bin_tiles")
+    with _timed("bin_tiles"):
+        check(lib().fsgs_bin_tiles(ctypes.byref(b), _stream()), "fsgs_bin_tiles")
     return ranges, point_list, tile_order
 
 
@@ -216,7 +244,8 @@ def render_forward_launch(W, H, near_n, far_n, only_image, P, records, point_lis
     a.out_flow, a.n_contrib = _ptr(pixel_flow), _ptr(n_contrib)
     a.accum_max_count, a.accum_weights_p = _ptr(accum_max_count), _ptr(accum_weights_p)
     a.accum_weights_count = _ptr(accum_weights_count)
-    check(lib().fsgs_render_forward(ctypes.byref(a), _stream()), "fsgs_render_forward")
+    with _timed("blend_forward"):
+        check(lib().fsgs_render_forward(ctypes.byref(a), _stream()), "fsgs_render_forward")
     return pixel_colors, pixel_opacity, pixel_extras, pixel_flow, n_contrib
 
 
@@ -282,7 +311,8 @@ def render_backward_launch(W, H, near_n, far_n, P, records, point_list, ranges, 
     a.dL_dcolor, a.dL_dopacity, a.dL_dextras, a.dL_dflow = _ptr(dL_dcolor), _ptr(dL_dopacity), _ptr(dL_dextras), _ptr(dL_dflow)
     a.dL_dcolors, a.dL_dmeans2D, a.dL_dtrans_mat = _ptr(g_col), _ptr(g_m2d), _ptr(g_tm)
     a.dL_dinverse_m, a.dL_dnormal_opacity = _ptr(g_im), _ptr(g_no)
-    check(lib().fsgs_render_backward(ctypes.byref(a), _stream()), "fsgs_render_backward")
+    with _timed("blend_backward"):
+        check(lib().fsgs_render_backward(ctypes.byref(a), _stream()), "fsgs_render_backward")
     return g_col, g_m2d, g_tm, g_im, g_no
 
 

@@ -6,7 +6,7 @@ import torch
 
 from . import _lib
 from ._lib import lib, check
-from .ops import _ptr, _stream
+from .ops import _ptr, _stream, _timed
 
 
 class SparseGaussianAdam(torch.optim.Adam):
@@ -60,5 +60,6 @@ def masked_adam_step(batch, visibility, N, b1=0.9, b2=0.999):
             keep.append(g)
             arr[k].param, arr[k].grad, arr[k].exp_avg, arr[k].exp_avg_sq = p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr()
             arr[k].M, arr[k].lr, arr[k].eps = p.numel() // N, lr, eps
-        check(lib().fsgs_adam_masked_multi(len(chunk), arr, _ptr(vis), int(N), b1, b2, _stream()),
-              "fsgs_adam_masked_multi")
+        with _timed("adam_masked_multi"):
+            check(lib().fsgs_adam_masked_multi(len(chunk), arr, _ptr(vis), int(N), b1, b2, _stream()),
+                  "fsgs_adam_masked_multi")

@@ -119,8 +119,9 @@ def lbs_backward(ts, g_means, g_scales, g_rots):
     for name, t in zip(("g_xyz", "g_scaling_raw", "g_rotation_raw", "g_knn_w", "g_sp_q", "g_sp_t", "g_sp_dr",
                         "g_sp_ds"), outs):
         setattr(g, name, t.data_ptr())
-    check(lib().fsgs_lbs_warp_backward(P, ctypes.byref(l), ops._ptr(g_means), ops._ptr(g_scales), ops._ptr(g_rots),
-                                       ctypes.byref(g), ops._stream()), "fsgs_lbs_warp_backward")
+    with ops._timed("lbs_warp_backward"):
+        check(lib().fsgs_lbs_warp_backward(P, ctypes.byref(l), ops._ptr(g_means), ops._ptr(g_scales),
+                                           ops._ptr(g_rots), ctypes.byref(g), ops._stream()), "fsgs_lbs_warp_backward")
     return outs
 
 
@@ -222,7 +223,8 @@ class _FastRender(torch.autograd.Function):
         a.grad_colors, a.grad_normal_opacity = p(g_col), p(g_no)
         a.grad_means, a.grad_scales, a.grad_rots, a.grad_opac = p(gm), p(gs), p(gr), p(go)
         a.grad_shs, a.grad_sh_rest = p(gsh), p(grest)
-        check(lib().fsgs_preprocess_backward(ctypes.byref(a), ops._stream()), "fsgs_preprocess_backward")
+        with ops._timed("preprocess_backward"):
+            check(lib().fsgs_preprocess_backward(ctypes.byref(a), ops._stream()), "fsgs_preprocess_backward")
         if sh_degree < 0:
             gsh = g_col  # colours were an input: their gradient is the compositing gradient itself
         grads = [gm, gs, gr, go, gsh, grest, None, None, None, None, None, None, None, None, None, None, g_m2d]
@@ -235,7 +237,7 @@ class _FastRender(torch.autograd.Function):
 
 def depths_to_points(Tw2v, Tv2c, size, depthmap):
     """Back-project a depth map to world points (renderer/gs_2d_fast_render.py:558-575; device-agnostic here)."""
-    c2w = Tw2v.inverse()
+    c2w = torch.linalg.inv_ex(Tw2v).inverse  # no device-to-host error check
     W, H = size
     ndc2pix = torch.tensor([[W / 2, 0, 0, W / 2], [0, H / 2, 0, H / 2], [0, 0, 0, 1]], dtype=torch.float32,
                            device=Tw2v.device).T
@@ -244,7 +246,7 @@ def depths_to_points(Tw2v, Tv2c, size, depthmap):
     gx, gy = torch.meshgrid(torch.arange(W, device=c2w.device).float(), torch.arange(H, device=c2w.device).float(),
                             indexing="xy")
     points = torch.stack([gx, gy, torch.ones_like(gx)], dim=-1).reshape(-1, 3)
-    rays_d = points @ intrins.inverse().T @ c2w[:3, :3].T
+    rays_d = points @ torch.linalg.inv_ex(intrins).inverse.T @ c2w[:3, :3].T
     return depthmap.reshape(-1, 1) * rays_d + c2w[:3, 3]
 
 
@@ -276,7 +278,7 @@ def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s
     means2D = torch.zeros(P, 2, device=opacity.device, dtype=torch.float32, requires_grad=True)
     W, H = (int(v) for v in size)
     if campos is None:
-        campos = Tw2v.inverse()[:3, 3].contiguous()
+        campos = torch.linalg.inv_ex(Tw2v).inverse[:3, 3].contiguous()
     feats = sh_features if colors is None else colors
     cfg = (W, H, int(sh_degree) if colors is None else -1, float(near), float(far), bool(only_image))
     geom = (points, scales, rotations)

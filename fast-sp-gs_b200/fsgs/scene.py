@@ -1,0 +1,92 @@
+"""A minimal dynamic surfel scene: the parameters the reference model owns (``fast_2d_gs/network.py:357``:
+positions, 2 log-scales, rotation, opacity logit, SH DC + 15 rest coefficients = 58 floats per Gaussian), the
+superpoint k-NN / LBS weights (``network.py:498-521``, 'dist' weighting) and one training step
+(warp -> render -> backward -> visibility-masked Adam) as ``train.py:343-412`` runs it, minus losses: the
+upstream image gradient is an input.
+"""
+import torch
+
+from . import ops
+from .dist import GradBucket, reduce_visibility
+from .optim import SparseGaussianAdam
+from .renderer import GS_2D_fast_render, list_capacity
+
+# learning rates of exps/d_nerf.yaml (position lr at its initial value)
+LRS = dict(xyz=1.6e-4, sh_dc=2.5e-3, sh_rest=1.25e-4, opacity=0.05, scaling=5e-3, rotation=1e-3)
+
+
+class DynamicScene:
+    def __init__(self, surfels, centres, K=3, eps=1e-15, device="cuda"):
+        P = lambda t: torch.nn.Parameter(t.to(device).contiguous())
+        self.xyz = P(surfels["means"])
+        self.scaling = P(surfels["log_scales"])
+        self.rotation = P(surfels["rots_raw"])
+        self.opacity = P(surfels["opac_raw"])
+        self.sh_dc = P(surfels["sh_dc"])
+        self.sh_rest = P(surfels["sh_rest"])
+        self.centres = centres.to(device).contiguous()
+        self.K = K
+        self.refresh_knn()
+        groups = [dict(params=[self.xyz], lr=LRS["xyz"]), dict(params=[self.sh_dc], lr=LRS["sh_dc"]),
+                  dict(params=[self.sh_rest], lr=LRS["sh_rest"]), dict(params=[self.opacity], lr=LRS["opacity"]),
+                  dict(params=[self.scaling], lr=LRS["scaling"]), dict(params=[self.rotation], lr=LRS["rotation"])]
+        self.optimizer = SparseGaussianAdam(groups, lr=0.0, eps=eps)
+        self.bucket = None
+
+    @property
+    def params(self):
+        return [self.xyz, self.sh_dc, self.sh_rest, self.opacity, self.scaling, self.rotation]
+
+    @property
+    def num_points(self):
+        return self.xyz.shape[0]
+
+    @torch.no_grad()
+    def refresh_knn(self):
+        """K nearest superpoints of every Gaussian and softmax(-d^2) blend weights."""
+        d2, idx = ops.knn(self.xyz.detach(), self.centres, self.K)
+        self.knn_idx = idx
+        self.knn_w = torch.softmax(-d2, dim=-1).contiguous()
+
+    def render(self, cam, size, motion, only_image=False):
+        """``motion``: dict sp_q [M,4] unit quaternions, sp_t [M,3], sp_dr [M,4], sp_ds [M,2] for this time step."""
+        lbs = (self.xyz, self.scaling, self.rotation, self.knn_idx, self.knn_w, motion["sp_q"], motion["sp_t"],
+               motion["sp_dr"], motion["sp_ds"])
+        return GS_2D_fast_render(None, None, None, torch.sigmoid(self.opacity), size, cam["Tw2v"], cam["Tv2c"],
+                                 cam["Tv2s"], cam["campos"], sh_degree=3, sh_features=self.sh_dc,
+                                 sh_features_rest=self.sh_rest, lbs=lbs, only_image=only_image)
+
+    def train_step(self, cam, size, motion, g_images, g_opacity, group=None, distributed=False):
+        """One iteration: forward, backward with the given upstream gradients on images [3,H,W] and opacity [H,W],
+        (all-reduce of the gradients and of the visibility mask when ``distributed``), fused masked Adam.
+        Returns the render dictionary."""
+        out = self.render(cam, size, motion)
+        torch.autograd.backward([out["images"], out["opacity"]], [g_images, g_opacity])
+        visible = out["visibility_filter"]
+        if distributed:
+            if self.bucket is None:
+                self.bucket = GradBucket(self.params)
+            self.bucket.reduce(group)
+            visible = reduce_visibility(visible, group)
+        self.optimizer.set_before_step(visible, self.num_points)
+        self.optimizer.step()
+        self.optimizer.zero_grad(set_to_none=True)
+        return out
+
+    def check(self):
+        list_capacity(self.xyz.device).check_overflow()
+
+
+def motion_at(sp, centres, device="cuda"):
+    """Superpoint motion of ``workloads.superpoints`` as the renderer wants it: translation re-centred so that each
+    superpoint rotates about its own centre (``network.py:549``)."""
+    from .workloads import superpoints  # noqa: F401  (documentation pointer)
+    q = sp["sp_q"].to(device)
+    c = centres.to(device)
+    x, y, z, w = q.unbind(-1)
+    R = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (y * w + x * z),
+                     2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w),
+                     2 * (x * z - y * w), 2 * (x * w + y * z), 1 - 2 * (x * x + y * y)], dim=-1).reshape(-1, 3, 3)
+    t = sp["sp_t_raw"].to(device) + c - (R @ c[..., None])[..., 0]
+    return dict(sp_q=q.contiguous(), sp_t=t.contiguous(), sp_dr=sp["sp_dr"].to(device).contiguous(),
+                sp_ds=sp["sp_ds"].to(device).contiguous())

@@ -28,6 +28,12 @@
 #endif
 
 #define TILE 16
+/* accumulation shared between threads that work on different tiles */
+#define ATOMIC_ADD(dst, val)        \
+  do {                              \
+    const float v_ = (val);         \
+    _Pragma("omp atomic")(dst) += v_; \
+  } while (0)
 #define TILE_PIX 256
 
 /* ------------------------------------------------------------------------- */
@@ -524,6 +530,7 @@ void orc_blend_bwd(int W, int H, float near_n, float far_n, const float *means2D
   const int gx = (W + TILE - 1) / TILE, gy = (H + TILE - 1) / TILE;
   const size_t HW = (size_t) H * W;
   const int aux = dL_dextras != NULL && out_extras != NULL;
+#pragma omp parallel for schedule(dynamic, 1)
   for (int tile = 0; tile < gx * gy; ++tile) {
     const int tx = tile % gx, ty = tile / gx;
     const int64_t r0 = ranges[2 * tile], r1 = ranges[2 * tile + 1];
@@ -572,7 +579,7 @@ void orc_blend_bwd(int W, int H, float near_n, float far_n, const float *means2D
             accum_rec[ch] = last_alpha * last_color[ch] + (1.0f - last_alpha) * accum_rec[ch];
             last_color[ch] = c;
             dL_dalpha += (c - accum_rec[ch]) * gpix[ch];
-            g_colors[3 * g + ch] += w * gpix[ch];
+            ATOMIC_ADD(g_colors[3 * g + ch], w * gpix[ch]);
           }
           float dL_dz = 0, dL_dweight = 0, dL_dsx = 0, dL_dsy = 0;
           if (aux) {
@@ -594,7 +601,7 @@ void orc_blend_bwd(int W, int H, float near_n, float far_n, const float *means2D
               acc_normal[ch] = last_alpha * last_normal[ch] + (1.0f - last_alpha) * acc_normal[ch];
               last_normal[ch] = nc;
               dL_dalpha += (nc - acc_normal[ch]) * g_n2d[ch];
-              g_normal_opacity[4 * g + ch] += w * g_n2d[ch];
+              ATOMIC_ADD(g_normal_opacity[4 * g + ch], w * g_n2d[ch]);
             }
             dL_dz += w * g_depth;
           }
@@ -622,17 +629,17 @@ void orc_blend_bwd(int W, int H, float near_n, float far_n, const float *means2D
             const float a = dL_dsx / h.pz, b = dL_dsy / h.pz;
             const float c = -(a * h.sx + b * h.sy);
             float *gi = g_inverse_m + 9 * g;
-            gi[0] += a * px, gi[1] += a * py, gi[2] += a;
-            gi[3] += b * px, gi[4] += b * py, gi[5] += b;
-            gi[6] += c * px, gi[7] += c * py, gi[8] += c;
+            ATOMIC_ADD(gi[0], a * px); ATOMIC_ADD(gi[1], a * py); ATOMIC_ADD(gi[2], a);
+            ATOMIC_ADD(gi[3], b * px); ATOMIC_ADD(gi[4], b * py); ATOMIC_ADD(gi[5], b);
+            ATOMIC_ADD(gi[6], c * px); ATOMIC_ADD(gi[7], c * py); ATOMIC_ADD(gi[8], c);
           } else {
-            g_means2D[2 * g + 0] += dL_dG * (-G * 2.0f * h.dx);
-            g_means2D[2 * g + 1] += dL_dG * (-G * 2.0f * h.dy);
+            ATOMIC_ADD(g_means2D[2 * g + 0], dL_dG * (-G * 2.0f * h.dx));
+            ATOMIC_ADD(g_means2D[2 * g + 1], dL_dG * (-G * 2.0f * h.dy));
           }
-          g_trans_mat[9 * g + 6] += dL_dz * h.sx;
-          g_trans_mat[9 * g + 7] += dL_dz * h.sy;
-          g_trans_mat[9 * g + 8] += dL_dz;
-          g_normal_opacity[4 * g + 3] += G * dL_dalpha;
+          ATOMIC_ADD(g_trans_mat[9 * g + 6], dL_dz * h.sx);
+          ATOMIC_ADD(g_trans_mat[9 * g + 7], dL_dz * h.sy);
+          ATOMIC_ADD(g_trans_mat[9 * g + 8], dL_dz);
+          ATOMIC_ADD(g_normal_opacity[4 * g + 3], G * dL_dalpha);
         }
       }
   }
