@@ -282,7 +282,7 @@ def run_ours(args):
         m = {k: v.to(dev, non_blocking=True) for k, v in host["motion"].items()}
         gi, go = host["g_img"].to(dev, non_blocking=True), host["g_op"].to(dev, non_blocking=True)
         out = scene.train_step(c, (W, H), m, gi, go, distributed=distributed)
-        sink.append(float(out["opacity"].mean()))  # device -> host read of the step's result
+        sink.append(float(out["opacity"].detach().mean()))  # device -> host read of the step's result
 
     for _ in range(3):
         e2e_step()

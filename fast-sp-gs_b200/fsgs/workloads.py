@@ -100,6 +100,7 @@ def knn_points_c1(N=100_000, M=512, seed=0):
 
 CONFIGS = {
     "fwd_100k_800": dict(P=100_000, W=800, H=800, log_scale_mean=-4.5, log_scale_std=0.5),
+    "train_100k_800": dict(P=100_000, W=800, H=800, log_scale_mean=-4.5, log_scale_std=0.5, M=512, K=3),
     "train_300k_800": dict(P=300_000, W=800, H=800, log_scale_mean=-4.5, log_scale_std=0.5, M=512, K=3),
     "multiview_500k_1352x1014": dict(P=500_000, W=1352, H=1014, log_scale_mean=-4.5, log_scale_std=0.5, M=512, K=3,
                                      views=16, radius=3.0),
