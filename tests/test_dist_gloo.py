@@ -1,0 +1,58 @@
+"""Host logic of the multi-GPU layer on CPU: two gloo ranks share views and sum gradients through GradBucket."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, os.path.join(ROOT, "fast-sp-gs_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from fsgs.dist import GradBucket, reduce_max_, reduce_visibility, shard_views
+    views = shard_views(5, rank, world)
+    g = torch.Generator().manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(7, 3, generator=g)), torch.nn.Parameter(torch.randn(7, 15, 3, generator=g)),
+              torch.nn.Parameter(torch.randn(7, 1, generator=g))]
+    # every view contributes a gradient that depends on the view only: the sum over ranks must equal the serial sum
+    for p in params:
+        p.grad = sum(torch.full_like(p, float(v + 1)) * p.detach() for v in views)
+    bucket = GradBucket(params)
+    bucket.reduce()
+    expect = [sum(float(v + 1) for v in range(5)) * p.detach() for p in params]
+    ok = all(torch.allclose(p.grad, e, rtol=1e-6) for p, e in zip(params, expect))
+    ok &= all(p.grad.data_ptr() == v.data_ptr() for p, v in zip(params, bucket.views))
+    vis = torch.zeros(7, dtype=torch.bool)
+    vis[rank::3] = True
+    vis = reduce_visibility(vis)
+    ok &= vis.tolist() == [True, True, False, True, True, False, True]
+    radii = torch.tensor([rank, 5 - rank, 2], dtype=torch.int32)
+    ok &= reduce_max_(radii).tolist() == [1, 5, 2]
+    out[rank] = (bool(ok), views)
+    dist.destroy_process_group()
+
+
+def test_two_ranks_shard_views_and_sum_gradients():
+    mp.set_start_method("spawn", force=True)
+    with mp.Manager() as m:
+        out = m.dict()
+        port = 29500 + os.getpid() % 2000
+        mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+        assert out[0][0] and out[1][0]
+        assert out[0][1] == [0, 2, 4] and out[1][1] == [1, 3]
+
+
+def test_single_process_bucket_is_a_noop_reduce():
+    sys.path.insert(0, os.path.join(ROOT, "fast-sp-gs_b200"))
+    from fsgs.dist import GradBucket, reduce_visibility, shard_views
+    assert shard_views(16, 3, 8) == [3, 11] and shard_views(2, 5, 8) == []
+    p = torch.nn.Parameter(torch.ones(4, 2))
+    p.grad = torch.full((4, 2), 3.0)
+    b = GradBucket([p])
+    assert b.reduce() is None and torch.equal(p.grad, torch.full((4, 2), 3.0)) and b.nbytes() == 32
+    v = torch.tensor([True, False])
+    assert reduce_visibility(v) is v
