@@ -63,6 +63,9 @@ struct Hit {
 
 // (pixel, splat) evaluation shared by both passes; false when the pair is skipped.
 // Same operations, in the same order, as the reference kernels (gs_2d_fast_redner.cu:152-186).
+// FAST replaces the two IEEE divisions and expf by their approximate forms: used by the backward pass only, whose
+// tolerance is relative (1e-3 per tensor); the forward pass decides the alpha and transmittance cuts and stays exact.
+template <bool FAST>
 __device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py, float near_n, Hit &h, float &opa,
     float3 &Tw) {
   const float4 q0 = rec[0], q1 = rec[1], q2 = rec[2], q3 = rec[3];
@@ -71,7 +74,12 @@ __device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py,
   const float p2 = q2.z * px + q2.w * py + q3.x;
   if (p2 == 0.0f) return false;
   h.pz = p2;
-  h.sx = p0 / p2, h.sy = p1 / p2;
+  if (FAST) {
+    const float inv = __frcp_rn(p2);
+    h.sx = p0 * inv, h.sy = p1 * inv;
+  } else {
+    h.sx = p0 / p2, h.sy = p1 / p2;
+  }
   h.rho3d = (h.sx * h.sx + h.sy * h.sy);
   h.dx = q0.x - px, h.dy = q0.y - py;
   h.rho2d = 2.0f * (h.dx * h.dx + h.dy * h.dy);
@@ -82,7 +90,7 @@ __device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py,
   opa = q0.z;
   const float power = -0.5f * rho;
   if (power > 0.0f) return false;
-  h.G = expf(power);
+  h.G = FAST ? __expf(power) : expf(power);
   h.alpha = fminf(0.99f, opa * h.G);
   if (h.alpha < 1.0f / 255.0f) return false;
   return true;
@@ -139,7 +147,7 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
         Hit h;
         float opa;
         float3 Tw;
-        if (!eval_pair(rec, px, py, a.near_n, h, opa, Tw)) continue;
+        if (!eval_pair<false>(rec, px, py, a.near_n, h, opa, Tw)) continue;
         const float test_T = T * (1 - h.alpha);
         if (test_T < 0.0001f) {
           done = true;
@@ -289,12 +297,14 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
     if (FLOW) gflow = a.g_flow[pix];
   }
   const float final_A = 1 - T_final;
+  const float far_scale = a.far_n / (a.far_n - a.near_n);
 
-  float acc_c0 = 0, acc_c1 = 0, acc_c2 = 0, last_c0 = 0, last_c1 = 0, last_c2 = 0;
-  float last_depth = 0, acc_depth = 0, acc_alpha = 0;
-  float last_n0 = 0, last_n1 = 0, last_n2 = 0, acc_n0 = 0, acc_n1 = 0, acc_n2 = 0;
+  // The reference keeps, per output channel, the colour accumulated behind the current splat
+  // (acc = last_alpha * last_value + (1 - last_alpha) * acc) and sums (value - acc) * upstream over channels.
+  // The recurrence is linear in the values, so one scalar recurrence on q = sum_ch value_ch * upstream_ch gives
+  // the same dL/dalpha with a fifth of the state.
+  float acc_q = 0, last_q = 0;
   float last_dL_dT = 0, last_alpha = 0;
-  float acc_f0 = 0, acc_f1 = 0, last_f0 = 0, last_f1 = 0;
 
   // the deepest list position any pixel of the warp / the tile blended
   int wmax = last_contributor;
@@ -340,45 +350,29 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
           Hit h;
           float opa = 0;
           float3 Tw = make_float3(0, 0, 0);
-          if (active) active = eval_pair(rec, px, py, a.near_n, h, opa, Tw);
+          if (active) active = eval_pair<true>(rec, px, py, a.near_n, h, opa, Tw);
           if (active) {
             const float alpha = h.alpha, G = h.G;
-            T = T / (1.0f - alpha);
+            T = __fdividef(T, 1.0f - alpha);
             const float w = alpha * T;
             const float4 q5 = rec[5];
+            float q = q5.x * gpix0 + q5.y * gpix1 + q5.z * gpix2;
             float dL_dalpha = 0.0f;
-            acc_c0 = last_alpha * last_c0 + (1.0f - last_alpha) * acc_c0;
-            acc_c1 = last_alpha * last_c1 + (1.0f - last_alpha) * acc_c1;
-            acc_c2 = last_alpha * last_c2 + (1.0f - last_alpha) * acc_c2;
-            last_c0 = q5.x, last_c1 = q5.y, last_c2 = q5.z;
-            dL_dalpha += (q5.x - acc_c0) * gpix0;
-            dL_dalpha += (q5.y - acc_c1) * gpix1;
-            dL_dalpha += (q5.z - acc_c2) * gpix2;
             g[0] = w * gpix0, g[1] = w * gpix1, g[2] = w * gpix2;
 
             float dL_dz = 0.0f, dL_dweight = 0.0f, dL_dsx = 0.0f, dL_dsy = 0.0f;
             if (AUX) {
               const float4 q6 = rec[6];
-              const float m_d = a.far_n / (a.far_n - a.near_n) * (1 - a.near_n / h.depth);
-              const float dmd_dd = (a.far_n * a.near_n) / ((a.far_n - a.near_n) * h.depth * h.depth);
+              const float inv_depth = __frcp_rn(h.depth);
+              const float m_d = far_scale * (1 - a.near_n * inv_depth);
+              const float dmd_dd = far_scale * a.near_n * inv_depth * inv_depth;
               if (contributor == median_contributor - 1) dL_dz += g_med;
               dL_dweight += (final_D2 + m_d * m_d * final_A - 2 * m_d * final_D) * g_reg;
               dL_dalpha += dL_dweight - last_dL_dT;
               last_dL_dT = dL_dweight * alpha + (1 - alpha) * last_dL_dT;
               const float dL_dmd = 2.0f * (T * alpha) * (m_d * final_A - final_D) * g_reg;
               dL_dz += dL_dmd * dmd_dd;
-              acc_depth = last_alpha * last_depth + (1.0f - last_alpha) * acc_depth;
-              last_depth = h.depth;
-              dL_dalpha += (h.depth - acc_depth) * g_depth;
-              acc_alpha = last_alpha * 1.0f + (1.0f - last_alpha) * acc_alpha;
-              dL_dalpha += (1 - acc_alpha) * g_acc;
-              acc_n0 = last_alpha * last_n0 + (1.0f - last_alpha) * acc_n0;
-              acc_n1 = last_alpha * last_n1 + (1.0f - last_alpha) * acc_n1;
-              acc_n2 = last_alpha * last_n2 + (1.0f - last_alpha) * acc_n2;
-              last_n0 = q5.w, last_n1 = q6.x, last_n2 = q6.y;
-              dL_dalpha += (q5.w - acc_n0) * g_n0;
-              dL_dalpha += (q6.x - acc_n1) * g_n1;
-              dL_dalpha += (q6.y - acc_n2) * g_n2;
+              q += h.depth * g_depth + g_acc + q5.w * g_n0 + q6.x * g_n1 + q6.y * g_n2;
               g[3] = w * g_n0, g[4] = w * g_n1, g[5] = w * g_n2;
               dL_dz += w * g_depth;
             }
@@ -388,22 +382,23 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
               const float v = m2[3] * h.sx + m2[4] * h.sy + m2[5];
               float ww = m2[6] * h.sx + m2[7] * h.sy + m2[8];
               ww = fabsf(ww) < 1e-5f ? 1e-5f : ww;
-              acc_f0 = last_alpha * last_f0 + (1.0f - last_alpha) * acc_f0;
-              acc_f1 = last_alpha * last_f1 + (1.0f - last_alpha) * acc_f1;
-              last_f0 = u / ww - px, last_f1 = v / ww - py;
-              dL_dalpha += (last_f0 - acc_f0) * gflow.x + (last_f1 - acc_f1) * gflow.y;
+              q += (u / ww - px) * gflow.x + (v / ww - py) * gflow.y;
               const float gu = w / ww * gflow.x, gv = w / ww * gflow.y;
               const float gw = -w / (ww * ww) * (u * gflow.x + v * gflow.y);
               dL_dsx += m2[0] * gu + m2[3] * gv + m2[6] * gw;
               dL_dsy += m2[1] * gu + m2[4] * gv + m2[7] * gw;
             }
+            acc_q = last_alpha * last_q + (1.0f - last_alpha) * acc_q;
+            last_q = q;
+            dL_dalpha += q - acc_q;
             dL_dalpha *= T;
             last_alpha = alpha;
             const float dL_dG = opa * dL_dalpha;
             if (h.rho3d <= h.rho2d) {
               dL_dsx += dL_dG * -G * h.sx + dL_dz * Tw.x;
               dL_dsy += dL_dG * -G * h.sy + dL_dz * Tw.y;
-              const float ga = dL_dsx / h.pz, gb = dL_dsy / h.pz;
+              const float inv_pz = __frcp_rn(h.pz);
+              const float ga = dL_dsx * inv_pz, gb = dL_dsy * inv_pz;
               const float gc = -(ga * h.sx + gb * h.sy);
               g[12] = ga * px, g[13] = ga * py, g[14] = ga;
               g[15] = gb * px, g[16] = gb * py, g[17] = gb;

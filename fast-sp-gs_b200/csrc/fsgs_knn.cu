@@ -162,22 +162,53 @@ __global__ void __launch_bounds__(256) adam_masked_kernel(float *__restrict__ pa
 
 struct AdamMulti {
   fsgs_adam_tensor t[FSGS_ADAM_MAX_TENSORS];
+  long long chunk_start[FSGS_ADAM_MAX_TENSORS + 1];  // prefix sums of ceil(N * M / 4)
+  int vec[FSGS_ADAM_MAX_TENSORS];                     // all four arrays 16-byte aligned
   int n;
 };
 
-// One launch for all tensors: a warp walks one Gaussian's rows of every tensor, so the mask is read once per
-// Gaussian and each tensor's row is touched with consecutive lanes.
+// One launch for all tensors.  Each tensor is walked as a flat array in chunks of four consecutive floats (one
+// 16-byte access per array), consecutive threads taking consecutive chunks, so every access is fully coalesced
+// whatever the row length.  A chunk may straddle two Gaussians: elements of an invisible one keep their bits.
+// Chunks without a visible element touch nothing but the mask.
 __global__ void __launch_bounds__(256) adam_masked_multi_kernel(AdamMulti a, const uint8_t *__restrict__ visible,
     long long N, float b1, float b2) {
-  const int lane = threadIdx.x & 31;
-  const long long warp0 = ((long long) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = ((long long) gridDim.x * blockDim.x) >> 5;
-  for (long long n = warp0; n < N; n += nwarps) {
-    if (!visible[n]) continue;
-    for (int k = 0; k < a.n; ++k) {
-      const fsgs_adam_tensor &t = a.t[k];
-      for (int e = lane; e < t.M; e += 32) {
-        const long long i = n * t.M + e;
+  const long long total = a.chunk_start[a.n];
+  for (long long chunk = (long long) blockIdx.x * blockDim.x + threadIdx.x; chunk < total;
+       chunk += (long long) gridDim.x * blockDim.x) {
+    int k = 0;
+    while (k + 1 < a.n && chunk >= a.chunk_start[k + 1]) ++k;
+    const fsgs_adam_tensor &t = a.t[k];
+    const long long e0 = (chunk - a.chunk_start[k]) * 4;
+    const long long n_el = N * t.M;
+    const int cnt = (int) (n_el - e0 < 4 ? n_el - e0 : 4);
+    long long row = e0 / t.M;
+    int col = (int) (e0 - row * t.M);
+    bool vis[4];
+    bool any = false;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      vis[u] = u < cnt && visible[row] != 0;
+      any |= vis[u];
+      if (++col == t.M) col = 0, ++row;
+    }
+    if (!any) continue;
+    if (a.vec[k] && cnt == 4) {
+      float4 p = *reinterpret_cast<const float4 *>(t.param + e0);
+      const float4 g = *reinterpret_cast<const float4 *>(t.grad + e0);
+      float4 m = *reinterpret_cast<const float4 *>(t.exp_avg + e0);
+      float4 v = *reinterpret_cast<const float4 *>(t.exp_avg_sq + e0);
+      if (vis[0]) adam_element(p.x, g.x, m.x, v.x, t.lr, b1, b2, t.eps);
+      if (vis[1]) adam_element(p.y, g.y, m.y, v.y, t.lr, b1, b2, t.eps);
+      if (vis[2]) adam_element(p.z, g.z, m.z, v.z, t.lr, b1, b2, t.eps);
+      if (vis[3]) adam_element(p.w, g.w, m.w, v.w, t.lr, b1, b2, t.eps);
+      *reinterpret_cast<float4 *>(t.param + e0) = p;
+      *reinterpret_cast<float4 *>(t.exp_avg + e0) = m;
+      *reinterpret_cast<float4 *>(t.exp_avg_sq + e0) = v;
+    } else {
+      for (int u = 0; u < cnt; ++u) {
+        if (!vis[u]) continue;
+        const long long i = e0 + u;
         float p = t.param[i], m = t.exp_avg[i], v = t.exp_avg_sq[i];
         adam_element(p, t.grad[i], m, v, t.lr, b1, b2, t.eps);
         t.param[i] = p, t.exp_avg[i] = m, t.exp_avg_sq[i] = v;
@@ -277,13 +308,17 @@ extern "C" int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *ten
   if (n_tensors > FSGS_ADAM_MAX_TENSORS) return FSGS_ERR_LIMIT;
   AdamMulti a;
   a.n = n_tensors;
+  a.chunk_start[0] = 0;
   for (int k = 0; k < n_tensors; ++k) {
-    FSGS_REQUIRE(tensors[k].param && tensors[k].grad && tensors[k].exp_avg && tensors[k].exp_avg_sq && tensors[k].M > 0);
-    a.t[k] = tensors[k];
+    const fsgs_adam_tensor &t = tensors[k];
+    FSGS_REQUIRE(t.param && t.grad && t.exp_avg && t.exp_avg_sq && t.M > 0);
+    a.t[k] = t;
+    a.chunk_start[k + 1] = a.chunk_start[k] + (N * t.M + 3) / 4;
+    a.vec[k] = ((((uintptr_t) t.param) | ((uintptr_t) t.grad) | ((uintptr_t) t.exp_avg) | ((uintptr_t) t.exp_avg_sq)) & 15) == 0;
   }
   if (N == 0) return FSGS_OK;
-  const int64_t warps_wanted = N;
-  const int blocks = (int) (warps_wanted / 8 + 1 < 148 * 16 ? warps_wanted / 8 + 1 : 148 * 16);
+  const long long total = a.chunk_start[n_tensors];
+  const int blocks = (int) ((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
   adam_masked_multi_kernel<<<blocks, 256, 0, (cudaStream_t) stream>>>(a, visible, (long long) N, b1, b2);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;

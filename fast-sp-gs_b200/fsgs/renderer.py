@@ -235,18 +235,30 @@ class _FastRender(torch.autograd.Function):
         return tuple(grads)
 
 
+_pixel_grid = {}
+
+
+def _homogeneous_pixels(W, H, device):
+    """[H*W, 3] rows (x, y, 1), cached per image size and device."""
+    key = (W, H, str(device))
+    if key not in _pixel_grid:
+        gx, gy = torch.meshgrid(torch.arange(W, device=device).float(), torch.arange(H, device=device).float(),
+                                indexing="xy")
+        _pixel_grid[key] = torch.stack([gx, gy, torch.ones_like(gx)], dim=-1).reshape(-1, 3).contiguous()
+    return _pixel_grid[key]
+
+
 def depths_to_points(Tw2v, Tv2c, size, depthmap):
-    """Back-project a depth map to world points (renderer/gs_2d_fast_render.py:558-575; device-agnostic here)."""
-    c2w = torch.linalg.inv_ex(Tw2v).inverse  # no device-to-host error check
+    """Back-project a depth map to world points (renderer/gs_2d_fast_render.py:558-575).  Same arithmetic, but
+    device-agnostic, without the error-checking (synchronising) matrix inverses, with the pixel grid cached and the
+    two 3x3 factors multiplied together before they meet the [H*W,3] pixel matrix."""
+    c2w = torch.linalg.inv_ex(Tw2v).inverse
     W, H = size
     ndc2pix = torch.tensor([[W / 2, 0, 0, W / 2], [0, H / 2, 0, H / 2], [0, 0, 0, 1]], dtype=torch.float32,
                            device=Tw2v.device).T
     projection_matrix = c2w.T @ (Tv2c @ Tw2v).T
     intrins = (projection_matrix @ ndc2pix)[:3, :3].T
-    gx, gy = torch.meshgrid(torch.arange(W, device=c2w.device).float(), torch.arange(H, device=c2w.device).float(),
-                            indexing="xy")
-    points = torch.stack([gx, gy, torch.ones_like(gx)], dim=-1).reshape(-1, 3)
-    rays_d = points @ torch.linalg.inv_ex(intrins).inverse.T @ c2w[:3, :3].T
+    rays_d = _homogeneous_pixels(W, H, Tw2v.device) @ (torch.linalg.inv_ex(intrins).inverse.T @ c2w[:3, :3].T)
     return depthmap.reshape(-1, 1) * rays_d + c2w[:3, 3]
 
 
@@ -258,6 +270,39 @@ def depth_to_normal(Tw2v, Tv2c, size, depth):
     dy = points[1:-1, 2:] - points[1:-1, :-2]
     output[1:-1, 1:-1, :] = torch.nn.functional.normalize(torch.linalg.cross(dx, dy, dim=-1), dim=-1)
     return output
+
+
+class _SurfaceEpilogue(torch.autograd.Function):
+    """normals to world space, surface depth, pseudo surface normal: one kernel forward, one backward."""
+
+    @staticmethod
+    def forward(ctx, out_extras, opacities, Tw2v, Tv2c, depth_ratio):
+        _, H, W = out_extras.shape
+        f32 = dict(device=out_extras.device, dtype=torch.float32)
+        normals, surf_depth, surf_normal = torch.empty(3, H, W, **f32), torch.empty(1, H, W, **f32), torch.empty(3, H, W, **f32)
+        p = ops._ptr
+        with ops._timed("epilogue_forward"):
+            check(lib().fsgs_epilogue_forward(W, H, float(depth_ratio), p(Tw2v), p(Tv2c), p(out_extras), p(opacities),
+                                              p(normals), p(surf_depth), p(surf_normal), ops._stream()),
+                  "fsgs_epilogue_forward")
+        ctx.save_for_backward(out_extras, opacities, Tw2v, Tv2c)
+        ctx.ratio = float(depth_ratio)
+        return normals, surf_depth, surf_normal
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g_normals, g_depth, g_surf_normal):
+        out_extras, opacities, Tw2v, Tv2c = ctx.saved_tensors
+        _, H, W = out_extras.shape
+        g_extras = torch.empty_like(out_extras)
+        p = ops._ptr
+        c = lambda t: None if t is None else t.contiguous()
+        g_normals, g_depth, g_surf_normal = c(g_normals), c(g_depth), c(g_surf_normal)
+        with ops._timed("epilogue_backward"):
+            check(lib().fsgs_epilogue_backward(W, H, ctx.ratio, p(Tw2v), p(Tv2c), p(out_extras), p(opacities),
+                                               p(g_normals), p(g_depth), p(g_surf_normal), p(g_extras), ops._stream()),
+                  "fsgs_epilogue_backward")
+        return g_extras, None, None, None, None
 
 
 def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s, campos=None, focals=None, FoV=None,
@@ -294,12 +339,9 @@ def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s
            "visibility_filter": radii > 0, "flows": flows}
     if only_image:
         return out
-    depths, normals, median_depths, distortion, _ = out_extras.split([1, 3, 1, 1, 2], dim=0)
-    normals = (normals.permute(1, 2, 0) @ Tw2v[:3, :3]).permute(2, 0, 1)
-    median_depths = torch.nan_to_num(median_depths, 0, 0)
-    depths = torch.nan_to_num(depths, 0, 0)
-    surf_depth = depths * (1 - depth_ratio) + depth_ratio * median_depths
-    surf_normal = depth_to_normal(Tw2v, Tv2c, (W, H), surf_depth).permute(2, 0, 1)
-    surf_normal = surf_normal * opacities.detach()
+    Tw2v_c, Tv2c_c = Tw2v.contiguous(), Tv2c.contiguous()
+    normals, surf_depth, surf_normal = _SurfaceEpilogue.apply(out_extras, opacities.detach(), Tw2v_c, Tv2c_c,
+                                                              depth_ratio)
+    distortion = out_extras[5:6]
     out.update(normals=normals, distortion=distortion, surf_depth=surf_depth, surf_normal=surf_normal)
     return out

@@ -262,6 +262,23 @@ typedef struct fsgs_preprocess_bwd_args {
 
 int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *args /* host */, fsgs_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Per-pixel epilogue of GS_2D_fast_render, one kernel each way.
+ * Replaces the PyTorch operator chain of renderer/gs_2d_fast_render.py:731-740 with depths_to_points /
+ * depth_to_normal (:558-589): normals_world [3,H,W] = view normals (out_extras[1:4]) rotated by Tw2v[:3,:3];
+ * surf_depth [1,H,W] = expected depth * (1 - depth_ratio) + depth_ratio * median depth, non-finite values
+ * zeroed; surf_normal [3,H,W] = normalised cross product of the central differences of the back-projected
+ * depth map, times the pixel's opacity (opacity is treated as a constant, as the reference detaches it),
+ * zero on the image border.  The backward writes g_extras [8,H,W] (channels 5..7 zero); any of the three
+ * upstream gradients may be NULL.
+ * ---------------------------------------------------------------------------------------------- */
+int fsgs_epilogue_forward(int W, int H, float depth_ratio, const float *Tw2v, const float *Tv2c,
+    const float *out_extras, const float *out_opacity, float *normals_world, float *surf_depth, float *surf_normal,
+    fsgs_stream_t stream);
+int fsgs_epilogue_backward(int W, int H, float depth_ratio, const float *Tw2v, const float *Tv2c,
+    const float *out_extras, const float *out_opacity, const float *g_normals_world, const float *g_surf_depth,
+    const float *g_surf_normal, float *g_extras, fsgs_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -169,3 +169,36 @@ def test_list_overflow_is_reported():
             renderer._capacity[dev] = saved
         else:
             del renderer._capacity[dev]
+
+
+def test_epilogue_kernel_vs_torch_chain():
+    """The fused epilogue against the reference's PyTorch operator chain (restated in fsgs.renderer), forward and
+    backward."""
+    from fsgs import renderer as R
+    from fsgs import workloads as wl
+    W, H = 200, 152
+    cam = wl.camera(W, H, eye=(0.6, -0.5, 3.5), device="cuda")
+    g = torch.Generator().manual_seed(3)
+    extras = torch.rand(8, H, W, generator=g).cuda()
+    extras[0] = extras[0] * 2 + 2
+    extras[4] = extras[4] * 2 + 2
+    extras[0, 5, 7] = float("nan")
+    extras[4, 9, 3] = float("inf")
+    opac = torch.rand(H, W, generator=g).cuda()
+    ratio = 0.7
+    a = extras.clone().requires_grad_()
+    b = extras.clone().requires_grad_()
+    n_a, sd_a, sn_a = R._SurfaceEpilogue.apply(a, opac, cam["Tw2v"], cam["Tv2c"], ratio)
+    depths, normals, median, _d, _ = b.split([1, 3, 1, 1, 2], dim=0)
+    n_b = (normals.permute(1, 2, 0) @ cam["Tw2v"][:3, :3]).permute(2, 0, 1)
+    sd_b = torch.nan_to_num(depths, 0, 0) * (1 - ratio) + ratio * torch.nan_to_num(median, 0, 0)
+    sn_b = R.depth_to_normal(cam["Tw2v"], cam["Tv2c"], (W, H), sd_b).permute(2, 0, 1) * opac
+    assert torch.allclose(n_a, n_b, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(sd_a, sd_b, rtol=1e-6, atol=1e-6)
+    assert float((sn_a - sn_b).abs().max()) < 2e-3 and rel_l2(sn_a, sn_b) < 1e-4
+    ups = [torch.randn(t.shape, generator=g).cuda() for t in (n_a, sd_a, sn_a)]
+    torch.autograd.backward([n_a, sd_a, sn_a], ups)
+    torch.autograd.backward([n_b, sd_b, sn_b], ups)
+    assert rel_l2(a.grad[1:4], b.grad[1:4]) < 1e-5
+    assert rel_l2(a.grad[[0, 4]], b.grad[[0, 4]]) < 2e-3
+    assert float(a.grad[5:].abs().max()) == 0
