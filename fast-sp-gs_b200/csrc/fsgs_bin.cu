@@ -253,3 +253,65 @@ extern "C" int fsgs_bin_tiles(const fsgs_bin_args *a, fsgs_stream_t stream) {
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Binning without a caller workspace: the scratch is a fixed device array of this library.
+// ------------------------------------------------------------------------------------------------
+
+namespace fsgs {
+constexpr size_t kNoallocKeysBytes = sizeof(unsigned long long) * (size_t) FSGS_NOALLOC_MAX_PAIRS;
+constexpr size_t kNoallocTileBytes = (sizeof(int32_t) + sizeof(long long) + sizeof(int32_t)) * (size_t) FSGS_NOALLOC_MAX_TILES;
+constexpr size_t kNoallocBytes = kNoallocKeysBytes + kNoallocTileBytes + 3 * 256;
+// Held by every device that loads the library.  In host code this name is only a handle: the device address
+// comes from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_bin_scratch[kNoallocBytes];
+constexpr int kMaxDevices = 64;
+static void *g_bin_scratch_ptr[kMaxDevices] = {nullptr};
+}  // namespace fsgs
+
+extern "C" int fsgs_bin_tiles_noalloc(const fsgs_bin_args *a, fsgs_stream_t stream) {
+  FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0 && a->capacity >= 0);
+  FSGS_REQUIRE(a->tile_counts && a->counters);
+  FSGS_REQUIRE(a->P == 0 || (a->means2D && a->inverse_m && a->depths && a->opac && a->radii));
+  FSGS_REQUIRE(a->ranges && a->tile_order && (a->point_list || a->capacity == 0));
+  const int gx = (a->W + kTile - 1) / kTile, gy = (a->H + kTile - 1) / kTile, T = gx * gy;
+  if (a->capacity > FSGS_NOALLOC_MAX_PAIRS || T > FSGS_NOALLOC_MAX_TILES) return FSGS_ERR_LIMIT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FSGS_ERR_LAUNCH;
+  if (g_bin_scratch_ptr[dev] == nullptr) {  // set-up: first call on this device
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_bin_scratch) != cudaSuccess || ptr == nullptr) return FSGS_ERR_LAUNCH;
+    g_bin_scratch_ptr[dev] = ptr;
+  }
+  cudaStream_t st = (cudaStream_t) stream;
+  // same layout as a caller workspace sized for the maximum: keys | cursors | starts | effective counts
+  BinWorkspace w;
+  char *p = (char *) g_bin_scratch_ptr[dev];
+  w.keys = (unsigned long long *) p;
+  p += align_up(kNoallocKeysBytes);
+  w.cursors = (int32_t *) p;
+  p += align_up(sizeof(int32_t) * (size_t) FSGS_NOALLOC_MAX_TILES);
+  w.starts = (long long *) p;
+  p += align_up(sizeof(long long) * (size_t) FSGS_NOALLOC_MAX_TILES);
+  w.eff_counts = (int32_t *) p;
+  // every scratch word that is read is written first: the scan kernel fills cursors / starts / counts for all
+  // tiles, the emit kernel fills exactly the key slots the sort kernels read
+  tile_scan_kernel<<<1, 1024, 0, st>>>(T, a->tile_counts, (long long) a->capacity, (long long *) a->ranges, w.starts,
+      w.eff_counts, w.cursors, a->tile_order, (unsigned long long *) a->counters);
+  FSGS_LAUNCH_CHECK();
+  const int blocks = max(1, ceil_div(a->P, 256));
+  emit_pairs_kernel<<<blocks, 256, 0, st>>>(a->P, gx, gy, (const float2 *) a->means2D, a->inverse_m, a->depths, a->opac,
+      a->radii, w.starts, w.eff_counts, w.cursors, w.keys, a->point_list, (long long) a->capacity,
+      (const unsigned long long *) a->counters);
+  FSGS_LAUNCH_CHECK();
+  tile_sort_small_kernel<<<T, 256, 0, st>>>(T, a->tile_order, w.starts, w.eff_counts, w.keys, a->point_list);
+  FSGS_LAUNCH_CHECK();
+  const size_t dyn = sizeof(unsigned long long) * kSortLarge;
+  if (cudaFuncSetAttribute(tile_sort_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) dyn) !=
+      cudaSuccess)
+    return FSGS_ERR_LAUNCH;
+  tile_sort_large_kernel<<<min(T, 148), 1024, dyn, st>>>(T, a->tile_order, w.starts, w.eff_counts, w.keys,
+      a->point_list);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}

@@ -89,6 +89,7 @@ SYMBOLS = {
     "fsgs_pack_records": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_bin_workspace_bytes": (c_size_t, [c_int, c_int, c_int64]),
     "fsgs_bin_tiles": (c_int, [POINTER(BinArgs), _vp]),
+    "fsgs_bin_tiles_noalloc": (c_int, [POINTER(BinArgs), _vp]),
     "fsgs_render_forward": (c_int, [POINTER(RenderArgs), _vp]),
     "fsgs_render_backward": (c_int, [POINTER(RenderBwdArgs), _vp]),
     "fsgs_preprocess_backward": (c_int, [POINTER(PreprocessBwdArgs), _vp]),

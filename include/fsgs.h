@@ -189,6 +189,24 @@ typedef struct fsgs_bin_args {
 size_t fsgs_bin_workspace_bytes(int W, int H, int64_t capacity);
 int fsgs_bin_tiles(const fsgs_bin_args *args /* host */, fsgs_stream_t stream);
 
+/* Tile binning for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Same inputs, outputs and results as fsgs_bin_tiles, but the scratch memory (pair keys, per-tile cursors and
+ * offsets) lives in a fixed array inside the library instead of a caller-provided workspace, and the call makes
+ * no cudaMalloc / cudaFree / allocating library call.  It is meant for hosts that get their device memory once at
+ * start-up and may not go back to the CUDA allocator while frames are being produced -- a viewer or engine
+ * plug-in with a fixed memory budget, or a plain C caller that has no caching allocator and would otherwise pay a
+ * device-synchronising cudaMalloc/cudaFree per frame.  args->workspace and args->workspace_bytes are ignored.
+ *
+ * Limits: capacity <= FSGS_NOALLOC_MAX_PAIRS and tiles <= FSGS_NOALLOC_MAX_TILES, else FSGS_ERR_LIMIT and
+ * nothing is launched.  The array (about 8.6 MB) is held by every GPU that loads the library until the process
+ * exits.  The first call on each device looks up the array's device address (with that device current); make
+ * that first call before any stream capture.  All calls on a device share the array: calls that overlap on the
+ * GPU (different streams) race; calls on one stream are safe.  Nothing has to be cleared between calls. */
+#define FSGS_NOALLOC_MAX_PAIRS (1 << 20)
+#define FSGS_NOALLOC_MAX_TILES 16384
+int fsgs_bin_tiles_noalloc(const fsgs_bin_args *args /* host */, fsgs_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Per-tile alpha compositing.
  * Replaces GS_2D_fast_render_forward / GS_2D_fast_render_backward
