@@ -22,6 +22,9 @@ constexpr int kGrad = 21;            // gradient components per splat
 constexpr unsigned kFull = 0xffffffffu;
 
 struct FwdDev {
+#ifdef FSGS_STATS
+  unsigned long long *stats;  // [0] warp-entries visited, [1] box hits, [2] hits with >= 1 blending lane, [3] blending lanes
+#endif
   int P, W, H, gx;
   float near_n, far_n;
   const float4 *records;
@@ -75,7 +78,7 @@ __device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py,
   if (p2 == 0.0f) return false;
   h.pz = p2;
   if (FAST) {
-    const float inv = __frcp_rn(p2);
+    const float inv = __fdividef(1.0f, p2);
     h.sx = p0 * inv, h.sy = p1 * inv;
   } else {
     h.sx = p0 / p2, h.sy = p1 / p2;
@@ -138,9 +141,20 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
         hit = box.x <= bx1 && box.y >= bx0 && box.z <= by1 && box.w >= by0;
       }
       unsigned mask = __ballot_sync(kFull, hit);
+#ifdef FSGS_STATS
+      if (lane == 0) atomicAdd(a.stats + 0, (unsigned long long) min(32, cnt - c)), atomicAdd(a.stats + 1, (unsigned long long) __popc(mask));
+#endif
       while (mask) {
         const int j = __ffs(mask) - 1;
         mask &= mask - 1;
+#ifdef FSGS_STATS
+        {
+          Hit h2; float o2; float3 t2;
+          const bool bl = !done && eval_pair<false>(s_rec + (c + j) * kQ, px, py, a.near_n, h2, o2, t2);
+          const unsigned bm = __ballot_sync(kFull, bl);
+          if (lane == 0 && bm) atomicAdd(a.stats + 2, 1ull), atomicAdd(a.stats + 3, (unsigned long long) __popc(bm));
+        }
+#endif
         if (done) continue;
         const int r = c + j;
         const float4 *rec = s_rec + r * kQ;
@@ -363,7 +377,7 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
             float dL_dz = 0.0f, dL_dweight = 0.0f, dL_dsx = 0.0f, dL_dsy = 0.0f;
             if (AUX) {
               const float4 q6 = rec[6];
-              const float inv_depth = __frcp_rn(h.depth);
+              const float inv_depth = __fdividef(1.0f, h.depth);
               const float m_d = far_scale * (1 - a.near_n * inv_depth);
               const float dmd_dd = far_scale * a.near_n * inv_depth * inv_depth;
               if (contributor == median_contributor - 1) dL_dz += g_med;
@@ -397,7 +411,7 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
             if (h.rho3d <= h.rho2d) {
               dL_dsx += dL_dG * -G * h.sx + dL_dz * Tw.x;
               dL_dsy += dL_dG * -G * h.sy + dL_dz * Tw.y;
-              const float inv_pz = __frcp_rn(h.pz);
+              const float inv_pz = __fdividef(1.0f, h.pz);
               const float ga = dL_dsx * inv_pz, gb = dL_dsy * inv_pz;
               const float gc = -(ga * h.sx + gb * h.sy);
               g[12] = ga * px, g[13] = ga * py, g[14] = ga;
@@ -453,6 +467,9 @@ extern "C" int fsgs_render_forward(const fsgs_render_args *a, fsgs_stream_t stre
   d.out_flow = (float2 *) a->out_flow, d.n_contrib = a->n_contrib;
   d.accum_max_count = a->accum_max_count, d.accum_weights_p = a->accum_weights_p;
   d.accum_weights_count = a->accum_weights_count;
+#ifdef FSGS_STATS
+  d.stats = (unsigned long long *) a->counters;
+#endif
   const int T = d.gx * ((a->H + kTile - 1) / kTile);
   cudaStream_t st = (cudaStream_t) stream;
   if (a->only_image) blend_forward_kernel<false, false><<<T, 256, 0, st>>>(d);
