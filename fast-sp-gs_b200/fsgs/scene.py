@@ -16,7 +16,7 @@ LRS = dict(xyz=1.6e-4, sh_dc=2.5e-3, sh_rest=1.25e-4, opacity=0.05, scaling=5e-3
 
 
 class DynamicScene:
-    def __init__(self, surfels, centres, K=3, eps=1e-15, device="cuda"):
+    def __init__(self, surfels, centres, K=3, eps=1e-15, device="cuda", lrs=None):
         P = lambda t: torch.nn.Parameter(t.to(device).contiguous())
         self.xyz = P(surfels["means"])
         self.scaling = P(surfels["log_scales"])
@@ -27,6 +27,7 @@ class DynamicScene:
         self.centres = centres.to(device).contiguous()
         self.K = K
         self.refresh_knn()
+        LRS = dict(globals()["LRS"], **(lrs or {}))
         groups = [dict(params=[self.xyz], lr=LRS["xyz"]), dict(params=[self.sh_dc], lr=LRS["sh_dc"]),
                   dict(params=[self.sh_rest], lr=LRS["sh_rest"]), dict(params=[self.opacity], lr=LRS["opacity"]),
                   dict(params=[self.scaling], lr=LRS["scaling"]), dict(params=[self.rotation], lr=LRS["rotation"])]
