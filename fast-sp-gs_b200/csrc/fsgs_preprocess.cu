@@ -2,6 +2,7 @@
 // their adjoints, and the packed render record.  One thread per Gaussian; every kernel is HBM bound.
 #include "fsgs_common.cuh"
 #include "fsgs_sh.cuh"
+#include "fsgs_tma.cuh"
 
 namespace fsgs {
 
@@ -214,35 +215,68 @@ __device__ __forceinline__ const float *sh_coef(const PreDev &a, int i, int k) {
   return k == 0 ? a.shs + (size_t) i * a.n_dc * 3 : a.sh_rest + ((size_t) i * a.n_rest + (k - 1)) * 3;
 }
 
+// One Gaussian per thread, 128 per block.  The wide AoS arrays go through shared memory so that global memory sees
+// only contiguous traffic: the block's slice of the SH coefficients arrives by one bulk asynchronous copy that is in
+// flight while the threads do the geometry, and the 9-float matrices, the colours, the warped means and the 128-byte
+// render records leave through a staging buffer (records by one bulk store).
+constexpr int kPreBlock = 128;
+constexpr int kWideMax = 48;                                    // SH floats per Gaussian that can be staged
+constexpr int kStageTm = 0, kStageIm = kPreBlock * 9, kStageCol = kPreBlock * 18, kStageWm = kPreBlock * 21;
+constexpr int kStageRec = kPreBlock * 24;                       // float offset of the record staging (16-B aligned)
+constexpr int kStageFloats = kStageRec + kPreBlock * kRecFloats;
+
+// rows x N floats, contiguous in global memory, from the staging buffer
+template <int N>
+__device__ __forceinline__ void store_rows(float *__restrict__ dst, const float *src, int rows) {
+  const int n = rows * N;
+  for (int e = threadIdx.x; e < n; e += kPreBlock) dst[e] = src[e];
+}
+
 template <bool LBS>
-__global__ void __launch_bounds__(256) preprocess_forward_kernel(PreDev a, LbsDev lbs) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a, LbsDev lbs) {
+  // the SH slice is dead once the colours are known; the output staging reuses its space
+  __shared__ __align__(128) float s_mem[kStageFloats > kPreBlock * kWideMax ? kStageFloats : kPreBlock * kWideMax];
+  float *s_wide = s_mem, *s_stage = s_mem;
+  __shared__ __align__(8) uint64_t s_bar;
   __shared__ float cam[16 + 9 + 3];
-  if (threadIdx.x < 16) cam[threadIdx.x] = a.Tw2v[threadIdx.x];
-  else if (threadIdx.x < 25) cam[threadIdx.x] = a.Tv2s[threadIdx.x - 16];
-  else if (threadIdx.x < 28) cam[threadIdx.x] = a.campos[threadIdx.x - 25];
-  __syncthreads();
+  __shared__ int s_area[kPreBlock / 32], s_real[kPreBlock / 32];
+  const int t = threadIdx.x, base = blockIdx.x * kPreBlock, rows = min(kPreBlock, a.P - base), i = base + t;
+  if (t < 16) cam[t] = a.Tw2v[t];
+  else if (t < 25) cam[t] = a.Tv2s[t - 16];
+  else if (t < 28) cam[t] = a.campos[t - 25];
   const float *Tw2v = cam, *Tv2s = cam + 16, *campos = cam + 25;
 
-  int area = 0, real = 0;
-  if (i < a.P) {
-    float3 p;
-    float2 s;
-    float4 q;
-    if (LBS) {
-      lbs_warp_one(lbs, i, p, s, q);
-      a.warped_means[3 * i] = p.x, a.warped_means[3 * i + 1] = p.y, a.warped_means[3 * i + 2] = p.z;
-      a.warped_scales[i] = s;
-      a.warped_rots[i] = q;
-    } else {
-      p = make_float3(a.means[3 * i], a.means[3 * i + 1], a.means[3 * i + 2]);
+  // the wide SH array: sh_rest when the caller keeps DC and the rest apart, else shs
+  const int wide = a.sh_rest ? a.n_rest * 3 : a.n_dc * 3;
+  const float *wide_src = (a.sh_rest ? a.sh_rest : a.shs) + (size_t) base * wide;
+  const bool staged = a.sh_degree >= 1 && wide <= kWideMax;
+  const uint32_t wide_bytes = (uint32_t) rows * wide * 4u;
+  const bool bulk = staged && ((uintptr_t) wide_src & 15) == 0 && (wide_bytes & 15u) == 0;
+  if (bulk && t == 0) mbar_init(&s_bar, 1);
+  __syncthreads();
+  if (bulk) {
+    if (t == 0) {
+      mbar_arrive_expect_tx(&s_bar, wide_bytes);
+      bulk_load(s_wide, wide_src, wide_bytes, &s_bar);
     }
-    bool vis = !(a.culling && a.culling[i]);
-    float M[9], IM[9];
-    float3 nrm = make_float3(0, 0, 0), rgb = make_float3(0, 0, 0);
-    float2 ctr = make_float2(0, 0);
-    float vz = 0, opacity = 0, radius = 0;
-    int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
+  } else if (staged) {
+    for (int e = t; e < rows * wide; e += kPreBlock) s_wide[e] = __ldg(wide_src + e);
+  }
+
+  int area = 0, real = 0;
+  float3 p = make_float3(0, 0, 0);
+  float2 s = make_float2(0, 0);
+  float4 q = make_float4(0, 0, 0, 0);
+  bool vis = false;
+  float M[9], IM[9];
+  float3 nrm = make_float3(0, 0, 0), rgb = make_float3(0, 0, 0);
+  float2 ctr = make_float2(0, 0);
+  float vz = 0, opacity = 0, radius = 0;
+  int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
+  if (i < a.P) {
+    if (LBS) lbs_warp_one(lbs, i, p, s, q);
+    else p = make_float3(a.means[3 * i], a.means[3 * i + 1], a.means[3 * i + 2]);
+    vis = !(a.culling && a.culling[i]);
     if (vis) {
       const float3 pv = view_point(p, Tw2v);
       vz = pv.z;
@@ -272,21 +306,6 @@ __global__ void __launch_bounds__(256) preprocess_forward_kernel(PreDev a, LbsDe
       }
     }
     if (vis) {
-      if (a.sh_degree >= 0) {
-        float x = p.x - campos[0], y = p.y - campos[1], z = p.z - campos[2];
-        const float n = rsqrtf(x * x + y * y + z * z + 1e-12f);
-        x *= n, y *= n, z *= n;
-        float b[16];
-        sh_basis(a.sh_degree, x, y, z, b);
-        const int nb = (a.sh_degree + 1) * (a.sh_degree + 1);
-        for (int k = 0; k < nb; ++k) {
-          const float *c = sh_coef(a, i, k);
-          rgb.x += __ldg(c) * b[k], rgb.y += __ldg(c + 1) * b[k], rgb.z += __ldg(c + 2) * b[k];
-        }
-        rgb = make_float3(fmaxf(rgb.x + 0.5f, 0.0f), fmaxf(rgb.y + 0.5f, 0.0f), fmaxf(rgb.z + 0.5f, 0.0f));
-      } else {
-        rgb = make_float3(a.shs[3 * i], a.shs[3 * i + 1], a.shs[3 * i + 2]);
-      }
       adjugate(M, IM);
       area = (y1 - y0) * (x1 - x0);
       // count (and histogram) the tiles with a corner inside the alpha >= 1/255 conic
@@ -304,37 +323,92 @@ __global__ void __launch_bounds__(256) preprocess_forward_kernel(PreDev a, LbsDe
       ctr = make_float2(0, 0);
       vz = 0, opacity = 0, radius = 0;
     }
-    // every row is written: zeros for culled Gaussians
-    a.means2D[i] = ctr;
-    if (a.sh_degree >= 0) a.colors[3 * i] = rgb.x, a.colors[3 * i + 1] = rgb.y, a.colors[3 * i + 2] = rgb.z;
-    if (a.trans_precomp == nullptr) {
-#pragma unroll
-      for (int k = 0; k < 9; ++k) a.trans_mat[(size_t) 9 * i + k] = M[k];
+  }
+
+  // the SH slice must have landed before the colours are evaluated
+  if (staged) {
+    const bool late = bulk && !mbar_wait_bounded(&s_bar, 0);
+    if (__syncthreads_or(late)) {
+      // the copy never reported completion: note it and read the slice with plain loads instead
+      if (t == 0) atomicOr(a.counters + FSGS_CNT_STATUS, 1ull);
+      for (int e = t; e < rows * wide; e += kPreBlock) s_wide[e] = __ldg(wide_src + e);
+      __syncthreads();
     }
+  }
+  if (vis) {
+    if (a.sh_degree >= 0) {
+      float x = p.x - campos[0], y = p.y - campos[1], z = p.z - campos[2];
+      const float n = rsqrtf(x * x + y * y + z * z + 1e-12f);
+      x *= n, y *= n, z *= n;
+      float b[16];
+      sh_basis(a.sh_degree, x, y, z, b);
+      const int nb = (a.sh_degree + 1) * (a.sh_degree + 1);
+      const float *c0 = a.shs + (size_t) i * a.n_dc * 3;          // coefficient 0
+      const float *cw = staged ? s_wide + t * wide : (a.sh_rest ? a.sh_rest + (size_t) i * wide : c0);
+      if (a.sh_rest) cw -= 3;                                     // the rest array starts at coefficient 1
+      rgb.x += c0[0] * b[0], rgb.y += c0[1] * b[0], rgb.z += c0[2] * b[0];
 #pragma unroll
-    for (int k = 0; k < 9; ++k) a.inverse_m[(size_t) 9 * i + k] = IM[k];
+      for (int k = 1; k < 16; ++k) {
+        if (k < nb) {
+          const float *c = cw + 3 * k;
+          rgb.x += c[0] * b[k], rgb.y += c[1] * b[k], rgb.z += c[2] * b[k];
+        }
+      }
+      rgb = make_float3(fmaxf(rgb.x + 0.5f, 0.0f), fmaxf(rgb.y + 0.5f, 0.0f), fmaxf(rgb.z + 0.5f, 0.0f));
+    } else {
+      rgb = make_float3(a.shs[3 * i], a.shs[3 * i + 1], a.shs[3 * i + 2]);
+    }
+  }
+
+  if (staged) __syncthreads();   // all reads of the SH slice are done
+  // every row is written: zeros for culled Gaussians
+  if (i < a.P) {
+#pragma unroll
+    for (int k = 0; k < 9; ++k) s_stage[kStageTm + 9 * t + k] = M[k], s_stage[kStageIm + 9 * t + k] = IM[k];
+    s_stage[kStageCol + 3 * t] = rgb.x, s_stage[kStageCol + 3 * t + 1] = rgb.y, s_stage[kStageCol + 3 * t + 2] = rgb.z;
+    if (LBS) s_stage[kStageWm + 3 * t] = p.x, s_stage[kStageWm + 3 * t + 1] = p.y, s_stage[kStageWm + 3 * t + 2] = p.z;
+    if (a.records) {
+      const float4 box = vis ? alpha_box(M, ctr, opacity) : make_float4(1.0f, -1.0f, 1.0f, -1.0f);
+      float4 *rec = reinterpret_cast<float4 *>(s_stage + kStageRec) + t * (kRecFloats / 4);
+      write_record(rec, ctr, opacity, IM, M, box, rgb, nrm);
+      rec[7] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    a.means2D[i] = ctr;
     a.normal_opacity[i] = make_float4(nrm.x, nrm.y, nrm.z, opacity);
     a.depths[i] = vz;
     a.radii[i] = (int) radius;
     a.tiles_touched[i] = area;
-    if (a.records) {
-      const float4 box = vis ? alpha_box(M, ctr, opacity) : make_float4(1.0f, -1.0f, 1.0f, -1.0f);
-      write_record(a.records + (size_t) i * (kRecFloats / 4), ctr, opacity, IM, M, box, rgb, nrm);
-    }
+    if (LBS) a.warped_scales[i] = s, a.warped_rots[i] = q;
   }
-  // block totals -> two global atomics per block
-  __shared__ int s_area[8], s_real[8];
   for (int o = 16; o > 0; o >>= 1) {
     area += __shfl_xor_sync(0xffffffffu, area, o);
     real += __shfl_xor_sync(0xffffffffu, real, o);
   }
-  if ((threadIdx.x & 31) == 0) s_area[threadIdx.x >> 5] = area, s_real[threadIdx.x >> 5] = real;
+  if ((t & 31) == 0) s_area[t >> 5] = area, s_real[t >> 5] = real;
+  fence_async_smem();
   __syncthreads();
-  if (threadIdx.x == 0) {
+
+  bool rec_bulk = false;
+  if (a.records) {
+    float4 *dst = a.records + (size_t) base * (kRecFloats / 4);
+    rec_bulk = ((uintptr_t) dst & 15) == 0;
+    if (rec_bulk) {
+      if (t == 0) bulk_store(dst, s_stage + kStageRec, (uint32_t) rows * kRecFloats * 4u);
+    } else {
+      store_rows<kRecFloats>(reinterpret_cast<float *>(dst), s_stage + kStageRec, rows);
+    }
+  }
+  if (a.trans_precomp == nullptr) store_rows<9>(a.trans_mat + (size_t) base * 9, s_stage + kStageTm, rows);
+  store_rows<9>(a.inverse_m + (size_t) base * 9, s_stage + kStageIm, rows);
+  if (a.sh_degree >= 0) store_rows<3>(a.colors + (size_t) base * 3, s_stage + kStageCol, rows);
+  if (LBS) store_rows<3>(a.warped_means + (size_t) base * 3, s_stage + kStageWm, rows);
+  // block totals -> two global atomics per block
+  if (t == 0) {
     long long ta = 0, tr = 0;
-    for (int w = 0; w < 8; ++w) ta += s_area[w], tr += s_real[w];
+    for (int w = 0; w < kPreBlock / 32; ++w) ta += s_area[w], tr += s_real[w];
     if (ta) atomicAdd(a.counters + FSGS_CNT_SLOTS, (unsigned long long) ta);
     if (tr) atomicAdd(a.counters + FSGS_CNT_PAIRS, (unsigned long long) tr);
+    if (rec_bulk) bulk_store_wait();   // the staging buffer must outlive the copy
   }
 }
 
@@ -449,119 +523,230 @@ __device__ __forceinline__ float3 cross3(const float3 a, const float3 b) {
   return make_float3(a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x);
 }
 
-__global__ void __launch_bounds__(256) preprocess_backward_kernel(PreBwdDev a) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// Adjoint of the preprocess, one Gaussian per thread, 128 per block.  All per-Gaussian rows that are wider than a
+// vector load come in by bulk asynchronous copies on one mbarrier (SH coefficients, the three 3x3 matrices, means,
+// colours and their gradients); the SH gradient is formed in place over the coefficients it was computed from and
+// leaves by one bulk store.  Every output row is written, zeros for Gaussians that were culled in the forward pass,
+// except grad_means2D, which is updated in place for visible Gaussians only.
+constexpr int kBwdWide = 0, kBwdTm = kPreBlock * kWideMax, kBwdGtm = kBwdTm + kPreBlock * 9;
+constexpr int kBwdGim = kBwdGtm + kPreBlock * 9, kBwdMeans = kBwdGim + kPreBlock * 9;
+constexpr int kBwdCol = kBwdMeans + kPreBlock * 3, kBwdGcol = kBwdCol + kPreBlock * 3;
+constexpr int kBwdFloats = kBwdGcol + kPreBlock * 3;
+
+__device__ __forceinline__ bool bulk_ok(const void *g, uint32_t bytes) {
+  return ((uintptr_t) g & 15) == 0 && (bytes & 15u) == 0 && bytes > 0;
+}
+
+__global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDev a) {
+  __shared__ __align__(128) float s_mem[kBwdFloats];
+  __shared__ __align__(8) uint64_t s_bar;
   __shared__ float cam[16 + 9 + 3];
-  if (threadIdx.x < 16) cam[threadIdx.x] = a.Tw2v[threadIdx.x];
-  else if (threadIdx.x < 25) cam[threadIdx.x] = a.Tv2s[threadIdx.x - 16];
-  else if (threadIdx.x < 28) cam[threadIdx.x] = a.campos[threadIdx.x - 25];
-  __syncthreads();
+  const int t = threadIdx.x, base = blockIdx.x * kPreBlock, rows = min(kPreBlock, a.P - base), i = base + t;
+  if (t < 16) cam[t] = a.Tw2v[t];
+  else if (t < 25) cam[t] = a.Tv2s[t - 16];
+  else if (t < 28) cam[t] = a.campos[t - 25];
   const float *Tw2v = cam, *Tv2s = cam + 16, *campos = cam + 25;
-  if (i >= a.P || a.radii[i] <= 0) return;
 
-  const float4 gno = a.g_normal_opacity[i];
-  a.g_opac[i] = gno.w;
-  float m[9], gT[9], G[9];
+  const bool want_sh = a.sh_degree >= 0;
+  const int wide = a.sh_rest ? a.n_rest * 3 : a.n_dc * 3;
+  const bool staged = a.sh_degree >= 1 && wide <= kWideMax;
+  // slices staged through shared memory: {destination offset, source, floats per row}
+  const float *src[7] = {(a.sh_rest ? a.sh_rest : a.shs) + (size_t) base * wide, a.trans_mat + (size_t) base * 9,
+      a.g_trans_mat + (size_t) base * 9, a.g_inverse_m + (size_t) base * 9, a.means + (size_t) base * 3,
+      want_sh ? a.colors + (size_t) base * 3 : nullptr, want_sh ? a.g_colors + (size_t) base * 3 : nullptr};
+  const int dst[7] = {kBwdWide, kBwdTm, kBwdGtm, kBwdGim, kBwdMeans, kBwdCol, kBwdGcol};
+  const int per_row[7] = {staged ? wide : 0, 9, 9, 9, 3, want_sh ? 3 : 0, want_sh ? 3 : 0};
+  uint32_t bulk_bytes = 0;
 #pragma unroll
-  for (int k = 0; k < 9; ++k) {
-    m[k] = a.trans_mat[(size_t) 9 * i + k];
-    gT[k] = a.g_trans_mat[(size_t) 9 * i + k];
-    G[k] = a.g_inverse_m[(size_t) 9 * i + k];
+  for (int k = 0; k < 7; ++k) {
+    const uint32_t bytes = (uint32_t) rows * per_row[k] * 4u;
+    if (bulk_ok(src[k], bytes)) bulk_bytes += bytes;
   }
-  // adjoint of the adjugate: inverse_m rows are c1 x c2, c2 x c0, c0 x c1 with c_j the columns of M
-  {
-    const float3 c0 = make_float3(m[0], m[3], m[6]), c1 = make_float3(m[1], m[4], m[7]), c2 = make_float3(m[2], m[5], m[8]);
-    const float3 G0 = make_float3(G[0], G[1], G[2]), G1 = make_float3(G[3], G[4], G[5]), G2 = make_float3(G[6], G[7], G[8]);
-    const float3 a0 = cross3(G1, c2), b0 = cross3(c1, G2);   // d/dc0
-    const float3 a1 = cross3(c2, G0), b1 = cross3(G2, c0);   // d/dc1
-    const float3 a2 = cross3(G0, c1), b2 = cross3(c0, G1);   // d/dc2
-    gT[0] += a0.x + b0.x, gT[3] += a0.y + b0.y, gT[6] += a0.z + b0.z;
-    gT[1] += a1.x + b1.x, gT[4] += a1.y + b1.y, gT[7] += a1.z + b1.z;
-    gT[2] += a2.x + b2.x, gT[5] += a2.y + b2.y, gT[8] += a2.z + b2.z;
-  }
-  // adjoint of the bounding-box centre
-  {
-    const float2 g = a.g_means2D[i];
-    const float tv[3] = {9.0f, 9.0f, -1.0f};
-    const float d = tv[0] * (m[6] * m[6]) + tv[1] * (m[7] * m[7]) + tv[2] * (m[8] * m[8]);
-    const float inv_d = 1.0f / d;
-    float f[3], df[3];
+  if (bulk_bytes && t == 0) mbar_init(&s_bar, 1);
+  __syncthreads();
+  if (bulk_bytes && t == 0) {
+    mbar_arrive_expect_tx(&s_bar, bulk_bytes);
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
-      f[k] = tv[k] * inv_d;
-      df[k] = g.x * m[k] * m[6 + k] + g.y * m[3 + k] * m[6 + k];
-    }
-    const float dd = (df[0] * f[0] + df[1] * f[1] + df[2] * f[2]) * -inv_d;
-#pragma unroll
-    for (int k = 0; k < 3; ++k) {
-      gT[k] += g.x * f[k] * m[6 + k];
-      gT[3 + k] += g.y * f[k] * m[6 + k];
-      gT[6 + k] += (g.x * f[k] * m[k] + g.y * f[k] * m[3 + k]) + dd * (tv[k] * m[6 + k] * 2.0f);
+    for (int k = 0; k < 7; ++k) {
+      const uint32_t bytes = (uint32_t) rows * per_row[k] * 4u;
+      if (bulk_ok(src[k], bytes)) bulk_load(s_mem + dst[k], src[k], bytes, &s_bar);
     }
   }
-  const float3 p = make_float3(a.means[3 * i], a.means[3 * i + 1], a.means[3 * i + 2]);
-  const float4 q = a.rots[i];
-  const float2 s = a.scales[i];
-  // the stored normal was flipped to face the camera
-  float3 gn = make_float3(gno.x, gno.y, gno.z);
-  {
-    const float3 n = make_float3(2 * (q.y * q.w + q.x * q.z), 2 * (q.y * q.z - q.x * q.w), 1 - 2 * (q.x * q.x + q.y * q.y));
-    const float nx = Tw2v[0] * n.x + Tw2v[1] * n.y + Tw2v[2] * n.z;
-    const float ny = Tw2v[4] * n.x + Tw2v[5] * n.y + Tw2v[6] * n.z;
-    const float nz = Tw2v[8] * n.x + Tw2v[9] * n.y + Tw2v[10] * n.z;
-    const float vx = Tw2v[0] * p.x + Tw2v[1] * p.y + Tw2v[2] * p.z + Tw2v[3];
-    const float vy = Tw2v[4] * p.x + Tw2v[5] * p.y + Tw2v[6] * p.z + Tw2v[7];
-    const float vz = Tw2v[8] * p.x + Tw2v[9] * p.y + Tw2v[10] * p.z + Tw2v[11];
-    const float c = -(vx * nx + vy * ny + vz * nz);
-    const float sgn = c > 0 ? 1.0f : -1.0f;
-    gn = make_float3(sgn * gn.x, sgn * gn.y, sgn * gn.z);
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    const int n = rows * per_row[k];
+    if (n > 0 && !bulk_ok(src[k], (uint32_t) n * 4u))
+      for (int e = t; e < n; e += kPreBlock) s_mem[dst[k] + e] = __ldg(src[k] + e);
   }
-  float3 gm;
-  float2 gs;
-  float4 gq;
-  splat_matrix_adjoint(s, q, Tw2v, Tv2s, gT, gn, gm, gs, gq);
+  // rows that need no staging are fetched while the copies fly
+  const bool live = i < a.P && a.radii[i] > 0;
+  float4 gno = make_float4(0, 0, 0, 0), q = make_float4(0, 0, 0, 1);
+  float2 s = make_float2(0, 0), g2 = make_float2(0, 0);
+  if (live) gno = a.g_normal_opacity[i], q = a.rots[i], s = a.scales[i], g2 = a.g_means2D[i];
+  {
+    const bool late = bulk_bytes && !mbar_wait_bounded(&s_bar, 0);
+    if (__syncthreads_or(late)) {
+      // a copy never reported completion: read everything with plain loads (no status word on this path; the
+      // forward kernel of the same frame reports the condition)
+#pragma unroll
+      for (int k = 0; k < 7; ++k) {
+        const int n = rows * per_row[k];
+        for (int e = t; e < n; e += kPreBlock) s_mem[dst[k] + e] = __ldg(src[k] + e);
+      }
+      __syncthreads();
+    }
+  }
 
-  if (a.sh_degree >= 0) {
-    const float ux = p.x - campos[0], uy = p.y - campos[1], uz = p.z - campos[2];
-    const float n = rsqrtf(ux * ux + uy * uy + uz * uz + 1e-12f);
-    const float x = ux * n, y = uy * n, z = uz * n;
-    float3 grgb;
-    grgb.x = a.colors[3 * i] > 0 ? a.g_colors[3 * i] : 0.0f;
-    grgb.y = a.colors[3 * i + 1] > 0 ? a.g_colors[3 * i + 1] : 0.0f;
-    grgb.z = a.colors[3 * i + 2] > 0 ? a.g_colors[3 * i + 2] : 0.0f;
-    float b[16];
-    sh_basis(a.sh_degree, x, y, z, b);
-    const int nb = (a.sh_degree + 1) * (a.sh_degree + 1);
-    float dx = 0, dy = 0, dz = 0;
-    for (int k = 0; k < nb; ++k) {
-      const float *c = a.sh_rest == nullptr ? a.shs + ((size_t) i * a.n_dc + k) * 3
-                                            : (k == 0 ? a.shs + (size_t) i * a.n_dc * 3
-                                                      : a.sh_rest + ((size_t) i * a.n_rest + (k - 1)) * 3);
-      float *gc = nullptr;
-      if (a.sh_rest == nullptr) {
-        if (a.g_shs) gc = a.g_shs + ((size_t) i * a.n_dc + k) * 3;
-      } else if (k == 0) {
-        if (a.g_shs) gc = a.g_shs + (size_t) i * a.n_dc * 3;
-      } else if (a.g_sh_rest) {
-        gc = a.g_sh_rest + ((size_t) i * a.n_rest + (k - 1)) * 3;
+  float *w_row = s_mem + kBwdWide + t * wide;   // this thread's SH coefficients, then their gradient
+  float3 gm = make_float3(0, 0, 0), gdc = make_float3(0, 0, 0);
+  float2 gs = make_float2(0, 0);
+  float4 gq = make_float4(0, 0, 0, 0);
+  if (live) {
+    float m[9], gT[9], G[9];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) {
+      m[k] = s_mem[kBwdTm + 9 * t + k];
+      gT[k] = s_mem[kBwdGtm + 9 * t + k];
+      G[k] = s_mem[kBwdGim + 9 * t + k];
+    }
+    // adjoint of the adjugate: inverse_m rows are c1 x c2, c2 x c0, c0 x c1 with c_j the columns of M
+    {
+      const float3 c0 = make_float3(m[0], m[3], m[6]), c1 = make_float3(m[1], m[4], m[7]), c2 = make_float3(m[2], m[5], m[8]);
+      const float3 G0 = make_float3(G[0], G[1], G[2]), G1 = make_float3(G[3], G[4], G[5]), G2 = make_float3(G[6], G[7], G[8]);
+      const float3 a0 = cross3(G1, c2), b0 = cross3(c1, G2);   // d/dc0
+      const float3 a1 = cross3(c2, G0), b1 = cross3(G2, c0);   // d/dc1
+      const float3 a2 = cross3(G0, c1), b2 = cross3(c0, G1);   // d/dc2
+      gT[0] += a0.x + b0.x, gT[3] += a0.y + b0.y, gT[6] += a0.z + b0.z;
+      gT[1] += a1.x + b1.x, gT[4] += a1.y + b1.y, gT[7] += a1.z + b1.z;
+      gT[2] += a2.x + b2.x, gT[5] += a2.y + b2.y, gT[8] += a2.z + b2.z;
+    }
+    // adjoint of the bounding-box centre
+    {
+      const float2 g = g2;
+      const float tv[3] = {9.0f, 9.0f, -1.0f};
+      const float d = tv[0] * (m[6] * m[6]) + tv[1] * (m[7] * m[7]) + tv[2] * (m[8] * m[8]);
+      const float inv_d = 1.0f / d;
+      float f[3], df[3];
+#pragma unroll
+      for (int k = 0; k < 3; ++k) {
+        f[k] = tv[k] * inv_d;
+        df[k] = g.x * m[k] * m[6 + k] + g.y * m[3 + k] * m[6 + k];
       }
-      if (gc) gc[0] = grgb.x * b[k], gc[1] = grgb.y * b[k], gc[2] = grgb.z * b[k];
-      if (k > 0) {
-        const float t = grgb.x * __ldg(c) + grgb.y * __ldg(c + 1) + grgb.z * __ldg(c + 2);
-        const float3 db = sh_basis_grad(k, x, y, z);
-        dx += t * db.x, dy += t * db.y, dz += t * db.z;
+      const float dd = (df[0] * f[0] + df[1] * f[1] + df[2] * f[2]) * -inv_d;
+#pragma unroll
+      for (int k = 0; k < 3; ++k) {
+        gT[k] += g.x * f[k] * m[6 + k];
+        gT[3 + k] += g.y * f[k] * m[6 + k];
+        gT[6 + k] += (g.x * f[k] * m[k] + g.y * f[k] * m[3 + k]) + dd * (tv[k] * m[6 + k] * 2.0f);
       }
     }
-    const float t = -(ux * dx + uy * dy + uz * dz) * n * n * n;
-    gm.x += dx * n + t * ux;
-    gm.y += dy * n + t * uy;
-    gm.z += dz * n + t * uz;
+    const float3 p = make_float3(s_mem[kBwdMeans + 3 * t], s_mem[kBwdMeans + 3 * t + 1], s_mem[kBwdMeans + 3 * t + 2]);
+    // the stored normal was flipped to face the camera
+    float3 gn = make_float3(gno.x, gno.y, gno.z);
+    {
+      const float3 n = make_float3(2 * (q.y * q.w + q.x * q.z), 2 * (q.y * q.z - q.x * q.w), 1 - 2 * (q.x * q.x + q.y * q.y));
+      const float nx = Tw2v[0] * n.x + Tw2v[1] * n.y + Tw2v[2] * n.z;
+      const float ny = Tw2v[4] * n.x + Tw2v[5] * n.y + Tw2v[6] * n.z;
+      const float nz = Tw2v[8] * n.x + Tw2v[9] * n.y + Tw2v[10] * n.z;
+      const float vx = Tw2v[0] * p.x + Tw2v[1] * p.y + Tw2v[2] * p.z + Tw2v[3];
+      const float vy = Tw2v[4] * p.x + Tw2v[5] * p.y + Tw2v[6] * p.z + Tw2v[7];
+      const float vz = Tw2v[8] * p.x + Tw2v[9] * p.y + Tw2v[10] * p.z + Tw2v[11];
+      const float c = -(vx * nx + vy * ny + vz * nz);
+      const float sgn = c > 0 ? 1.0f : -1.0f;
+      gn = make_float3(sgn * gn.x, sgn * gn.y, sgn * gn.z);
+    }
+    splat_matrix_adjoint(s, q, Tw2v, Tv2s, gT, gn, gm, gs, gq);
+
+    if (want_sh) {
+      const float ux = p.x - campos[0], uy = p.y - campos[1], uz = p.z - campos[2];
+      const float n = rsqrtf(ux * ux + uy * uy + uz * uz + 1e-12f);
+      const float x = ux * n, y = uy * n, z = uz * n;
+      float3 grgb;
+      grgb.x = s_mem[kBwdCol + 3 * t] > 0 ? s_mem[kBwdGcol + 3 * t] : 0.0f;
+      grgb.y = s_mem[kBwdCol + 3 * t + 1] > 0 ? s_mem[kBwdGcol + 3 * t + 1] : 0.0f;
+      grgb.z = s_mem[kBwdCol + 3 * t + 2] > 0 ? s_mem[kBwdGcol + 3 * t + 2] : 0.0f;
+      float b[16];
+      sh_basis(a.sh_degree, x, y, z, b);
+      const int nb = (a.sh_degree + 1) * (a.sh_degree + 1);
+      gdc = make_float3(grgb.x * b[0], grgb.y * b[0], grgb.z * b[0]);
+      float dx = 0, dy = 0, dz = 0;
+      // coefficient k >= 1 lives at row offset 3*(k - first)
+      const int first = a.sh_rest ? 1 : 0;
+      const float *c_g = (a.sh_rest ? a.sh_rest : a.shs) + (size_t) i * wide;           // unstaged source
+      float *g_g = a.sh_rest ? a.g_sh_rest : a.g_shs;                                    // unstaged destination
+      if (g_g) g_g += (size_t) i * wide;
+#pragma unroll
+      for (int k = 1; k < 16; ++k) {
+        if (k < nb) {
+          const int o = 3 * (k - first);
+          float c0, c1, c2;
+          if (staged) c0 = w_row[o], c1 = w_row[o + 1], c2 = w_row[o + 2];
+          else c0 = __ldg(c_g + o), c1 = __ldg(c_g + o + 1), c2 = __ldg(c_g + o + 2);
+          const float tt = grgb.x * c0 + grgb.y * c1 + grgb.z * c2;
+          const float3 db = sh_basis_grad(k, x, y, z);
+          dx += tt * db.x, dy += tt * db.y, dz += tt * db.z;
+          if (staged) w_row[o] = grgb.x * b[k], w_row[o + 1] = grgb.y * b[k], w_row[o + 2] = grgb.z * b[k];
+          else if (g_g) g_g[o] = grgb.x * b[k], g_g[o + 1] = grgb.y * b[k], g_g[o + 2] = grgb.z * b[k];
+        }
+      }
+      // coefficients beyond the active degree get no gradient
+      if (staged) {
+        for (int o = 3 * (nb - first); o < wide; ++o) w_row[o] = 0.0f;
+        if (!a.sh_rest) w_row[0] = gdc.x, w_row[1] = gdc.y, w_row[2] = gdc.z;
+      } else if (g_g) {
+        for (int o = 3 * (nb - first); o < wide; ++o) g_g[o] = 0.0f;
+        if (!a.sh_rest) g_g[0] = gdc.x, g_g[1] = gdc.y, g_g[2] = gdc.z;
+      }
+      const float tt = -(ux * dx + uy * dy + uz * dz) * n * n * n;
+      gm.x += dx * n + tt * ux;
+      gm.y += dy * n + tt * uy;
+      gm.z += dz * n + tt * uz;
+    }
+    // densification proxy replaces the consumed mean2D gradient (reference gs_2d_fast_preprocess.cu:605-608)
+    a.g_means2D[i] = make_float2(gT[2] * m[8] * 0.5f * (float) a.W, gT[5] * m[8] * 0.5f * (float) a.H);
+  } else if (i < a.P && want_sh) {
+    if (staged) {
+      for (int o = 0; o < wide; ++o) w_row[o] = 0.0f;
+    } else {
+      float *g_g = a.sh_rest ? a.g_sh_rest : a.g_shs;
+      if (g_g)
+        for (int o = 0; o < wide; ++o) g_g[(size_t) i * wide + o] = 0.0f;
+    }
   }
-  a.g_means[3 * i] = gm.x, a.g_means[3 * i + 1] = gm.y, a.g_means[3 * i + 2] = gm.z;
-  a.g_scales[i] = gs;
-  a.g_rots[i] = gq;
-  // densification proxy replaces the consumed mean2D gradient (reference gs_2d_fast_preprocess.cu:605-608)
-  a.g_means2D[i] = make_float2(gT[2] * m[8] * 0.5f * (float) a.W, gT[5] * m[8] * 0.5f * (float) a.H);
+  if (i < a.P) {
+    a.g_opac[i] = gno.w;
+    a.g_scales[i] = gs;
+    a.g_rots[i] = gq;
+    s_mem[kBwdMeans + 3 * t] = gm.x, s_mem[kBwdMeans + 3 * t + 1] = gm.y, s_mem[kBwdMeans + 3 * t + 2] = gm.z;
+    s_mem[kBwdCol + 3 * t] = gdc.x, s_mem[kBwdCol + 3 * t + 1] = gdc.y, s_mem[kBwdCol + 3 * t + 2] = gdc.z;
+  }
+  fence_async_smem();
+  __syncthreads();
+  bool out_bulk = false;
+  if (want_sh && staged) {
+    float *g_wide = a.sh_rest ? a.g_sh_rest : a.g_shs;
+    if (g_wide) {
+      g_wide += (size_t) base * wide;
+      const uint32_t bytes = (uint32_t) rows * wide * 4u;
+      out_bulk = bulk_ok(g_wide, bytes);
+      if (out_bulk) {
+        if (t == 0) bulk_store(g_wide, s_mem + kBwdWide, bytes);
+      } else {
+        for (int e = t; e < rows * wide; e += kPreBlock) g_wide[e] = s_mem[kBwdWide + e];
+      }
+    }
+  }
+  store_rows<3>(a.g_means + (size_t) base * 3, s_mem + kBwdMeans, rows);
+  if (want_sh && a.sh_rest && a.g_shs) {
+    // the DC gradient; n_dc is 1 in this layout
+    if (a.n_dc == 1) store_rows<3>(a.g_shs + (size_t) base * 3, s_mem + kBwdCol, rows);
+    else if (i < a.P) {
+      float *g = a.g_shs + (size_t) i * a.n_dc * 3;
+      g[0] = s_mem[kBwdCol + 3 * t], g[1] = s_mem[kBwdCol + 3 * t + 1], g[2] = s_mem[kBwdCol + 3 * t + 2];
+      for (int o = 3; o < a.n_dc * 3; ++o) g[o] = 0.0f;
+    }
+  }
+  if (out_bulk && t == 0) bulk_store_wait();
 }
 
 }  // namespace fsgs
@@ -648,8 +833,8 @@ extern "C" int fsgs_preprocess_forward(const fsgs_preprocess_args *a, fsgs_strea
   cudaMemsetAsync(a->tile_counts, 0, sizeof(int32_t) * (size_t) d.gx * d.gy, st);
   cudaMemsetAsync(a->counters, 0, sizeof(int64_t) * FSGS_NUM_COUNTERS, st);
   if (a->P == 0) return FSGS_OK;
-  if (a->lbs) preprocess_forward_kernel<true><<<ceil_div(a->P, 256), 256, 0, st>>>(d, to_dev(a->lbs));
-  else preprocess_forward_kernel<false><<<ceil_div(a->P, 256), 256, 0, st>>>(d, LbsDev());
+  if (a->lbs) preprocess_forward_kernel<true><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, st>>>(d, to_dev(a->lbs));
+  else preprocess_forward_kernel<false><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, st>>>(d, LbsDev());
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }
@@ -705,7 +890,7 @@ extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_
   d.g_normal_opacity = (const float4 *) a->grad_normal_opacity;
   d.g_means = a->grad_means, d.g_scales = (float2 *) a->grad_scales, d.g_rots = (float4 *) a->grad_rots;
   d.g_opac = a->grad_opac, d.g_shs = a->grad_shs, d.g_sh_rest = d.sh_rest ? a->grad_sh_rest : nullptr;
-  preprocess_backward_kernel<<<ceil_div(a->P, 256), 256, 0, (cudaStream_t) stream>>>(d);
+  preprocess_backward_kernel<<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

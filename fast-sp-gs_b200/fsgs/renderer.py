@@ -195,12 +195,12 @@ class _FastRender(torch.autograd.Function):
             W, H, near_n, far_n, P, records, point_list, ranges, tile_order, trans_mat_t2 if flow else None,
             pixel_opacity, pixel_extras if aux else None, n_contrib, g_colors, g_opacity,
             g_extras.contiguous() if aux else None, g_flow.contiguous() if flow else None)
-        # one zero-filled block for all parameter gradients
+        # one block for all parameter gradients; the kernel writes every row (zeros for culled Gaussians)
         n_sh = shs.numel() // max(P, 1)
         n_rest = sh_rest.numel() // max(P, 1) if has_rest else 0
         want_sh = sh_degree >= 0
         width = 3 + 2 + 4 + 1 + (n_sh if want_sh else 0) + (n_rest if want_sh else 0)
-        block = torch.zeros(P * width, device=dev, dtype=torch.float32)
+        block = torch.empty(P * width, device=dev, dtype=torch.float32)
         off = 0
 
         def take(n, shape):

@@ -264,8 +264,9 @@ int fsgs_render_backward(const fsgs_render_bwd_args *args /* host */, fsgs_strea
  * Preprocess backward.
  * Replaces gs_2d_fast_preprocess_backward   (gs_2d_fast_preprocess.cu:536-609, 784-859).
  * grad_means2D is consumed and then overwritten with the densification proxy, as in the reference.
- * Gradient rows of invisible Gaussians are left untouched (the caller zero-initialises, as the
- * reference's Python does).
+ * Every row of every grad_* output is written: zeros for Gaussians the forward pass culled (radii <= 0),
+ * so the outputs need no initialisation (the reference's Python zero-fills them before its kernel, which
+ * writes visible rows only: same result).  grad_means2D rows of culled Gaussians are left as they are.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct fsgs_preprocess_bwd_args {
   int32_t P, W, H, sh_degree, n_dc, n_rest;

@@ -386,6 +386,76 @@ def test_preprocess_backward_golden(ops, deg):
     assert rel_l2(gm2d, o[6]) < GRAD_TOL
 
 
+def _shifted(t):
+    """The same values in a buffer that starts one row later: 16-byte alignment of the rows is lost."""
+    big = torch.empty(t.shape[0] + 1, *t.shape[1:], dtype=t.dtype, device=t.device)
+    big[1:] = t
+    return big[1:]
+
+
+def _preprocess_backward(ops, s, cam, W, H, deg, fwd, ups, fill):
+    P = s["means"].shape[0]
+    new = lambda *shape: torch.full(shape, fill, device="cuda")
+    gm, gs, gr, go = new(P, 3), new(P, 2), new(P, 4), new(P, 1)
+    gsh, grest = new(*s["sh_dc"].shape), (new(*s["sh_rest"].shape) if s["sh_rest"] is not None else None)
+    gm2d = ups[0].clone()
+    ops.gs_2d_fast_preprocess_backward(W, H, deg, False, s["means"], s["scales"], s["rots"], s["opac"], s["sh_dc"],
+                                       s["sh_rest"], cam["Tw2v"], cam["Tv2s"], cam["campos"], fwd[2], fwd[6], fwd[1],
+                                       fwd[4], gm2d, ups[1], ups[2], None, ups[3], ups[4], gm, gs, gr, go, gsh, grest,
+                                       None, None)
+    return gm, gs, gr, go, gsh, grest, gm2d
+
+
+@pytest.mark.parametrize("P,deg", [(1003, 3), (1003, 1), (130, 2), (1003, 0)])
+def test_preprocess_io_paths(ops, P, deg):
+    """The bulk-copy path (aligned rows, sizes a multiple of 16 bytes), the plain-load path (shifted buffers, ragged
+    tail block) and both SH layouts give the same bits; every gradient row is written."""
+    W, H = 160, 120
+    s, cam = make_scene(P, W, H, seed=12, log_scale_mean=-2.5)
+    cul = torch.zeros(P, dtype=torch.bool, device="cuda")
+    cul[5::7] = True
+    run = lambda sc: ops.gs_2d_fast_preprocess_forward(
+        W, H, deg, False, sc["means"], sc["scales"], sc["rots"], sc["opac"], sc["sh_dc"], sc["sh_rest"], cam["Tw2v"],
+        cam["Tv2c"], cam["Tv2s"], cam["campos"], None, None, cul, True)
+    base = dict(s)
+    fwd = run(base)
+    shifted = {k: _shifted(v) for k, v in s.items()}
+    assert any(v.data_ptr() % 16 for v in shifted.values())
+    for a, b in zip(fwd, run(shifted)):
+        assert torch.equal(a, b)
+    both = dict(s, sh_dc=torch.cat([s["sh_dc"], s["sh_rest"]], dim=1).contiguous(), sh_rest=None)
+    for n, (a, b) in enumerate(zip(fwd, run(both))):
+        assert torch.equal(a, b), n
+    assert bool((fwd[6][5::7] == 0).all()) and int((fwd[6] > 0).sum()) > P // 2
+
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    ups = [torch.randn(P, k, device="cuda", generator=gen) for k in (2, 9, 9, 3, 4)]
+    ref_g = _preprocess_backward(ops, base, cam, W, H, deg, fwd, ups, 0.0)
+    nan_g = _preprocess_backward(ops, base, cam, W, H, deg, fwd, ups, float("nan"))
+    for a, b in zip(ref_g, nan_g):
+        assert torch.equal(a, b)          # NaN-filled outputs come back fully written
+    dead = fwd[6] <= 0
+    for t in ref_g[:6]:
+        assert bool((t[dead] == 0).all())
+    assert torch.equal(ref_g[6][dead], ups[0][dead])   # grad_means2D of culled rows is left alone
+    sh_ups = [_shifted(u) for u in ups]
+    sh_fwd = [_shifted(f) if f.shape[:1] == (P,) else f for f in fwd]
+    for a, b in zip(ref_g, _preprocess_backward(ops, shifted, cam, W, H, deg, sh_fwd, sh_ups, float("nan"))):
+        assert torch.equal(a, b)
+    g_both = _preprocess_backward(ops, both, cam, W, H, deg, fwd, ups, float("nan"))
+    assert torch.equal(g_both[4], torch.cat([ref_g[4], ref_g[5]], dim=1))
+    for k in (0, 1, 2, 3, 6):
+        assert torch.equal(g_both[k], ref_g[k])
+    # against the CPU oracle
+    c = lambda t: cpu(t) if t is not None else None
+    o = orc.preprocess_backward(W, H, deg, c(s["means"]), c(s["scales"]), c(s["rots"]), c(s["sh_dc"]), c(s["sh_rest"]),
+                                c(cam["Tw2v"]), c(cam["Tv2s"]), c(cam["campos"]), c(fwd[2]), c(fwd[6]), c(fwd[1]),
+                                c(ups[0]), c(ups[1]), c(ups[2]), c(ups[3]), c(ups[4]))
+    for k in range(7):
+        if o[k] is not None and float(o[k].abs().max()) > 0:
+            assert rel_l2(ref_g[k], o[k]) < GRAD_TOL, k
+
+
 def test_preprocess_forward_golden(ops):
     g = load_golden("preprocess_deg3.npz", "cuda")
     W, H = int(g["W"]), int(g["H"])
