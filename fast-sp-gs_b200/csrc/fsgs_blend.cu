@@ -248,20 +248,30 @@ struct BwdDev {
   float *g_colors, *g_means2D, *g_trans_mat, *g_inverse_m, *g_normal_opacity;
 };
 
-// Sum 32 per-lane vectors of up to 32 components; afterwards lane L holds the total of component L in v[0].
-// Components >= N are known zero (N = 21 here); every round halves the vector each lane carries.
+// Sums N per-lane components across the warp.  Five exchange rounds; in each, the lanes whose bit `width` is clear
+// keep the lower half of the values they carry and the others the upper half, so the count a lane carries goes
+// 21 -> 11 -> 6 -> 3 -> 2 -> 1 and the whole reduction takes 11+6+3+2+1 = 23 shuffles.  Afterwards the lane holds the
+// warp total of component `comp` (lanes whose path ran into the padding of an odd split hold 0 and a comp that may
+// be >= N).
 template <int N>
-__device__ __forceinline__ float warp_transpose_reduce(float (&v)[32], int lane) {
+__device__ __forceinline__ float warp_transpose_reduce(float (&v)[32], int lane, int &comp) {
+  int n = N;
+  comp = 0;
 #pragma unroll
   for (int width = 16; width >= 1; width >>= 1) {
+    const int h = (n + 1) / 2;
     const bool up = lane & width;
 #pragma unroll
-    for (int k = 0; k < width; ++k) {
-      const float lo = v[k], hi = (k + width < N) ? v[k + width] : 0.0f;
-      const float send = up ? lo : hi;
-      const float keep = up ? hi : lo;
-      v[k] = keep + __shfl_xor_sync(kFull, send, width);
+    for (int k = 0; k < 16; ++k) {
+      if (k < h) {
+        const float lo = v[k], hi = (k + h < n) ? v[k + h] : 0.0f;
+        const float send = up ? lo : hi;
+        const float keep = up ? hi : lo;
+        v[k] = keep + __shfl_xor_sync(kFull, send, width);
+      }
     }
+    comp += up ? h : 0;
+    n = h;
   }
   return v[0];
 }
@@ -425,8 +435,9 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
             g[6] = G * dL_dalpha;
           }
           if (__ballot_sync(kFull, active) == 0) continue;
-          const float total = warp_transpose_reduce<kGrad>(g, lane);
-          if (lane < kGrad) atomicAdd(s_grad + r * kGrad + lane, total);
+          int comp;
+          const float total = warp_transpose_reduce<kGrad>(g, lane, comp);
+          if (comp < kGrad && total != 0.0f) atomicAdd(s_grad + r * kGrad + comp, total);
         }
       }
     }
