@@ -9,7 +9,9 @@ renders its own view and the per-Gaussian gradients are all-reduced (NCCL) befor
 
   value      view-iterations / s over all ranks, inputs resident in HBM, device-timed (CUDA events, max over ranks)
   e2e        the same step through fsgs.scene.DynamicScene.train_step with the step's inputs (camera, superpoint
-             motion, upstream gradient) copied from pinned host memory and a scalar read back, every step
+             motion, upstream gradient) copied from pinned host memory and a scalar read back, every step; the
+             upload of step i+1 runs on a copy stream beside step i and the scalar is read one step late
+             (fsgs.feed.HostFeed / ScalarReader)
   roofline   the dominant kernel (compositing backward): algorithmic HBM bytes per launch / mean launch time
   cpu_baseline  the CPU oracle (a port of the reference's algorithm) on the host cores, same workload
   reference_cuda  the reference's own CUDA kernels (oracle/_ref, when built) on the same GPU, same step
@@ -168,10 +170,13 @@ def reference_cuda_step(wlk, steps, warmup):
     q = sp["sp_q"]
     t = sp["sp_t_raw"] + c - orc.quat_rotate(q, c)
     g_img, g_op, g_ext = wlk["g_img"].to(dev), wlk["g_op"].to(dev), torch.zeros(8, H, W, device=dev)
+    g_sets, tick = [(g_img, g_op), (-g_img, -g_op)], [0]   # sign alternates as in run_ours
     leaves = [s[k].clone().requires_grad_() for k in ("means", "log_scales", "rots_raw", "opac_raw", "sh_dc", "sh_rest")]
     state = [(torch.zeros_like(p), torch.zeros_like(p)) for p in leaves]
 
     def step():
+        g_img, g_op = g_sets[tick[0] & 1]
+        tick[0] += 1
         xyz, ls, rr, orw, dc, rest = leaves
         means, scales, rots = orc.lbs_warp(xyz, ls, rr, idx, w, q, t, sp["sp_dr"], sp["sp_ds"])
         opac = torch.sigmoid(orw)
@@ -224,14 +229,18 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     wlk = build_workload(args.workload, rank, dev)
     W, H, P = wlk["W"], wlk["H"], wlk["P"]
-    # every group at the position learning rate: with Adam's unit-size steps the scene then moves by < 2 % of a
-    # logit / of a pixel over the whole run, so every phase of the benchmark sees the same workload
+    # every group at the position learning rate
     lr = 1.6e-4
     scene = DynamicScene(wlk["surf"], wlk["centres"], K=wlk["K"], device=dev,
                          lrs=dict(xyz=lr, sh_dc=lr, sh_rest=lr, opacity=lr, scaling=lr, rotation=lr))
     cam = {k: v.to(dev) for k, v in wlk["cam"].items()}
     motion = motion_at(wlk["sp"], wlk["centres"], dev)
+    # The upstream gradient changes sign every step: Adam's first moment then oscillates about zero and the scene
+    # stays where it is, so every phase of the run (and the reference arm) sees the same workload.  With a fixed
+    # gradient Adam walks the scales and opacities steadily one way and the step gets cheaper as the run goes on.
     g_img, g_op = wlk["g_img"].to(dev), wlk["g_op"].to(dev)
+    g_sets = [(g_img, g_op), (-g_img, -g_op)]
+    tick = [0]
 
     def barrier():
         if distributed:
@@ -253,7 +262,9 @@ def run_ours(args):
 
     # ---- device-resident steps (value) ----
     def step():
-        scene.train_step(cam, (W, H), motion, g_img, g_op, distributed=distributed)
+        gi, go = g_sets[tick[0] & 1]
+        tick[0] += 1
+        scene.train_step(cam, (W, H), motion, gi, go, distributed=distributed)
 
     def fwd_only():
         with torch.no_grad():
@@ -262,6 +273,7 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     scene.check()
+    pairs_first = last_pairs(scene)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -276,19 +288,28 @@ def run_ours(args):
     ms_fwd = timed(fwd_only, args.steps)
 
     # ---- end to end: inputs from pinned host memory, a scalar back, every step ----
-    host = {"cam": {k: v.pin_memory() for k, v in wlk["cam"].items()},
-            "motion": {k: v.cpu().pin_memory() for k, v in motion.items()},
-            "g_img": wlk["g_img"].pin_memory(), "g_op": wlk["g_op"].pin_memory()}
+    hosts = [{"cam": {k: v.pin_memory() for k, v in wlk["cam"].items()},
+              "motion": {k: v.cpu().pin_memory() for k, v in motion.items()},
+              "g_img": (sgn * wlk["g_img"]).pin_memory(), "g_op": (sgn * wlk["g_op"]).pin_memory()}
+             for sgn in (1.0, -1.0)]
+    host = hosts[0]
     h2d = sum(v.numel() * 4 for v in host["cam"].values()) + sum(v.numel() * 4 for v in host["motion"].values()) + \
         host["g_img"].numel() * 4 + host["g_op"].numel() * 4
     sink = []
+    from fsgs.feed import HostFeed, ScalarReader
+    feed, reader = HostFeed(dev), ScalarReader(lag=1)
+    feed.stage(hosts[tick[0] & 1])
 
     def e2e_step():
-        c = {k: v.to(dev, non_blocking=True) for k, v in host["cam"].items()}
-        m = {k: v.to(dev, non_blocking=True) for k, v in host["motion"].items()}
-        gi, go = host["g_img"].to(dev, non_blocking=True), host["g_op"].to(dev, non_blocking=True)
-        out = scene.train_step(c, (W, H), m, gi, go, distributed=distributed)
-        sink.append(float(out["opacity"].detach().mean()))  # device -> host read of the step's result
+        tick[0] += 1
+        feed.stage(hosts[tick[0] & 1])   # the next step's upload runs beside this step's kernels
+        x = feed.take()
+        out = scene.train_step(x["cam"], (W, H), x["motion"], x["g_img"], x["g_op"], distributed=distributed)
+        feed.release()
+        reader.push(out["opacity"].detach().mean())
+        v = reader.pop()                 # device -> host read of the previous step's result, every step
+        if v is not None:
+            sink.append(float(v))
 
     for _ in range(3):
         e2e_step()
@@ -296,6 +317,7 @@ def run_ours(args):
     scene.check()
 
     pairs = list_pairs(scene)
+    pairs_last = last_pairs(scene)
     line = None
     if rank == 0:
         peak, peak_kind = peaks()
@@ -303,13 +325,29 @@ def run_ours(args):
         HW = W * H
         bwd_bytes = pairs * (72 + 4) + HW * 4 * (3 + 1 + 8 + 1 + 2 + 2) + 4 * 21 * pairs
         achieved = bwd_bytes / (ms_bwd * 1e-3) / 1e9
+        # algorithmic HBM bytes per launch of the bandwidth-bound stages (P Gaussians, V visible, 4-byte floats):
+        #   adam: 58 floats x (param, grad, 2 moments read; param, 2 moments written) per visible Gaussian + the mask
+        #   preprocess forward (LBS fused): 256 B of parameters in, 284 B of per-Gaussian outputs out (128 B record)
+        #   preprocess backward: 376 B in (matrices, their gradients, SH), 240 B of parameter gradients out
+        #   LBS backward: 96 B in, 48 B out
+        with torch.no_grad():
+            V = int(scene.render(cam, (W, H), motion)["visibility_filter"].sum())
+        stage_bytes = {"adam_masked_multi": V * 58 * 28 + P, "preprocess_forward": P * 540,
+                       "preprocess_backward": P * 616, "lbs_warp_backward": P * 144}
+        hbm_stages = {}
+        for k, b in stage_bytes.items():
+            if k in per_kernel:
+                gbs = b / (per_kernel[k][1] * 1e-3) / 1e9
+                hbm_stages[k] = {"bytes": b, "GB/s": round(gbs, 1), "frac": round(gbs / peak, 3)}
         launches_per_step = sum(n for n, _ in per_kernel.values()) / args.steps + 3  # bin_tiles = 4 kernels
         line = {
             "metric": METRIC, "value": world * 1e3 / ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "surfels": P, "image": [W, H], "superpoints": wlk["M"],
-                       "knn": wlk["K"], "sh_degree": 3, "adam_lr": 1.6e-4, "views_per_step_per_gpu": 1, "pairs_per_view": pairs,
+                       "knn": wlk["K"], "sh_degree": 3, "adam_lr": 1.6e-4, "views_per_step_per_gpu": 1,
+                       "pairs_per_view": pairs, "pairs_first_last": [pairs_first, pairs_last],
+                       "upstream_gradient": "fixed random image gradient, sign flipped every step",
                        "l2": "per-step working set (parameters, Adam state, gradients, records, images: > 400 MB) "
                              "exceeds the 126 MB L2; no explicit flush"},
             "fwd_frames_per_s": world * 1e3 / ms_fwd, "ms_per_fwd_frame": ms_fwd,
@@ -322,6 +360,7 @@ def run_ours(args):
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_bytes": bwd_bytes,
                          "note": "compositing is FP32-issue bound, not HBM bound: see DESIGN.md"},
+            "hbm_stages": hbm_stages,
             "clocks": clocks,
         }
         if world == 1 and not args.no_baselines:
@@ -346,6 +385,13 @@ def list_pairs(scene):
     cap = list_capacity(scene.xyz.device)
     cap.poll(wait=True)
     return int(cap.high_water)
+
+
+def last_pairs(scene):
+    from fsgs.renderer import list_capacity
+    cap = list_capacity(scene.xyz.device)
+    cap.poll(wait=True)
+    return int(cap.last_pairs)
 
 
 def run_reference(args):

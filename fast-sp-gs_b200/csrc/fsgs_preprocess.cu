@@ -3,6 +3,9 @@
 #include "fsgs_common.cuh"
 #include "fsgs_sh.cuh"
 #include "fsgs_tma.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace fsgs {
 
@@ -99,6 +102,7 @@ __global__ void __launch_bounds__(256) lbs_warp_forward_kernel(int P, LbsDev l, 
 
 // Superpoint gradient table row: q(4) t(3) dr(4) ds(2) = 13 floats.
 constexpr int kSpRow = 13;
+constexpr int kLbsCluster = 8;  // blocks per cluster in the backward (portable maximum)
 
 template <bool SMEM_TABLE>
 __global__ void __launch_bounds__(256) lbs_warp_backward_kernel(int P, LbsDev l, const float *__restrict__ g_means,
@@ -173,9 +177,15 @@ __global__ void __launch_bounds__(256) lbs_warp_backward_kernel(int P, LbsDev l,
     g_xyz[3 * i] = gx.x, g_xyz[3 * i + 1] = gx.y, g_xyz[3 * i + 2] = gx.z;
   }
   if (SMEM_TABLE) {
-    __syncthreads();
-    for (int k = threadIdx.x; k < l.M * kSpRow; k += blockDim.x) {
-      const float v = table[k];
+    // The blocks of a cluster add their tables up through distributed shared memory, each block taking one slice
+    // of the rows, so that global memory sees one reduction per (cluster, entry) instead of one per (block, entry).
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int nr = (int) cluster.num_blocks(), len = l.M * kSpRow;
+    const int per = (len + nr - 1) / nr, lo = (int) cluster.block_rank() * per, hi = min(len, lo + per);
+    for (int k = lo + threadIdx.x; k < hi; k += blockDim.x) {
+      float v = 0.0f;
+      for (int r = 0; r < nr; ++r) v += cluster.map_shared_rank(table, r)[k];
       if (v == 0.0f) continue;
       const int m = k / kSpRow, c = k % kSpRow;
       if (c < 4) atomicAdd(g_sp_q + 4 * m + c, v);
@@ -183,6 +193,7 @@ __global__ void __launch_bounds__(256) lbs_warp_backward_kernel(int P, LbsDev l,
       else if (c < 11) atomicAdd(g_sp_dr + 4 * m + (c - 7), v);
       else atomicAdd(g_sp_ds + 2 * m + (c - 11), v);
     }
+    cluster.sync();  // no block leaves while its table may still be read
   }
 }
 
@@ -782,10 +793,17 @@ extern "C" int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs, const float *g
   const size_t table_bytes = sizeof(float) * kSpRow * (size_t) M;
   if (table_bytes <= 40 * 1024) {
     // one table per block in shared memory; few, fat blocks so that the flush stays cheap
-    const int blocks = min(ceil_div(P, 256), 148 * 4);
-    lbs_warp_backward_kernel<true><<<blocks, 256, table_bytes, st>>>(P, to_dev(lbs), g_means, (const float2 *) g_scales,
-        (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw, (float4 *) g->g_rotation_raw, g->g_knn_w,
-        g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+    const int blocks = ceil_div(min(ceil_div(P, 256), 148 * 4), kLbsCluster) * kLbsCluster;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(256), cfg.dynamicSmemBytes = table_bytes, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kLbsCluster, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, lbs_warp_backward_kernel<true>, P, to_dev(lbs), g_means,
+        (const float2 *) g_scales, (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw,
+        (float4 *) g->g_rotation_raw, g->g_knn_w, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+    if (err != cudaSuccess) return FSGS_ERR_LAUNCH;
   } else {
     lbs_warp_backward_kernel<false><<<ceil_div(P, 256), 256, 0, st>>>(P, to_dev(lbs), g_means,
         (const float2 *) g_scales, (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw,

@@ -1,0 +1,95 @@
+"""Host <-> device plumbing for a training loop: uploads that overlap the previous step and a result read-back that
+does not drain the GPU.
+
+``HostFeed`` keeps two sets of device buffers.  ``stage(host_tensors)`` copies a step's inputs from pinned host memory
+on a side stream; ``take()`` hands the oldest staged set to the compute stream.  Staging step i+1 before calling
+``take()`` for step i makes the copy run beside step i's kernels.
+
+``ScalarReader`` copies a device scalar (or small tensor) to pinned memory asynchronously; ``pop()`` returns the value
+pushed ``lag`` steps earlier, so the host waits for a step that has (almost) finished while the next one is queued.
+
+The reference's loop (train.py:343-412) uploads each camera and reads ``loss.item()`` synchronously every iteration.
+"""
+import collections
+
+import torch
+
+
+class HostFeed:
+    def __init__(self, device, slots=2):
+        self.device = torch.device(device)
+        self.copy_stream = torch.cuda.Stream(device=self.device)
+        self.slots = [dict(buffers=None, ready=torch.cuda.Event(), released=None) for _ in range(slots)]
+        self.queue = collections.deque()
+        self.next_slot = 0
+
+    def stage(self, host_tensors):
+        """Start copying ``host_tensors`` (dict name -> pinned CPU tensor, or nested dicts of them)."""
+        if len(self.queue) == len(self.slots):
+            raise RuntimeError("HostFeed: every slot is staged; call take() first")
+        slot = self.slots[self.next_slot]
+        self.next_slot = (self.next_slot + 1) % len(self.slots)
+        if slot["released"] is not None:
+            self.copy_stream.wait_event(slot["released"])  # the step that last used these buffers has finished
+        with torch.cuda.stream(self.copy_stream):
+            slot["buffers"] = self._copy(host_tensors, slot["buffers"])
+            slot["ready"].record(self.copy_stream)
+        self.queue.append(slot)
+
+    def _copy(self, src, dst):
+        if isinstance(src, dict):
+            dst = dst if isinstance(dst, dict) else {}
+            return {k: self._copy(v, dst.get(k)) for k, v in src.items()}
+        if not src.is_pinned():
+            raise RuntimeError("HostFeed: inputs must live in pinned host memory")
+        if dst is None or dst.shape != src.shape or dst.dtype != src.dtype:
+            dst = torch.empty(src.shape, dtype=src.dtype, device=self.device)
+        dst.copy_(src, non_blocking=True)
+        return dst
+
+    def take(self):
+        """Device tensors of the oldest staged set; the current stream waits for their copy.  Call ``release()`` after
+        the last kernel that reads them has been queued."""
+        slot = self.queue.popleft()
+        torch.cuda.current_stream(self.device).wait_event(slot["ready"])
+        self._in_use = slot
+        return slot["buffers"]
+
+    def release(self):
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._in_use["released"] = ev
+
+
+class ScalarReader:
+    def __init__(self, lag=1, slots=4, numel=1):
+        assert slots > lag
+        self.lag = lag
+        self.host = [torch.empty(numel, dtype=torch.float32).pin_memory() for _ in range(slots)]
+        self.events = [torch.cuda.Event() for _ in range(slots)]
+        self.pending = collections.deque()
+        self.n = 0
+
+    def push(self, value):
+        """Queue the read-back of ``value`` (device tensor with ``numel`` elements)."""
+        k = self.n % len(self.host)
+        self.n += 1
+        self.host[k].copy_(value.detach().reshape(-1), non_blocking=True)
+        self.events[k].record()
+        self.pending.append(k)
+
+    def pop(self):
+        """The value pushed ``lag`` pushes ago (None while fewer are pending); blocks until that copy has landed."""
+        if len(self.pending) <= self.lag:
+            return None
+        k = self.pending.popleft()
+        self.events[k].synchronize()
+        return self.host[k].clone()
+
+    def drain(self):
+        out = []
+        while self.pending:
+            k = self.pending.popleft()
+            self.events[k].synchronize()
+            out.append(self.host[k].clone())
+        return out

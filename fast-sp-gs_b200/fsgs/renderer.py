@@ -25,6 +25,7 @@ class ListCapacity:
     def __init__(self, growth=1.5, floor=1 << 16):
         self.growth, self.floor = growth, floor
         self.high_water = 0
+        self.last_pairs = 0  # pair count of the most recent frame whose counters have arrived
         self._pending = []  # (event, pinned counters, capacity)
         self.overflowed = 0
 
@@ -48,6 +49,7 @@ class ListCapacity:
                 ev.synchronize()
             if ev.query():
                 pairs = int(host[1])
+                self.last_pairs = pairs
                 self.high_water = max(self.high_water, pairs)
                 if int(host[2]) > 0:
                     self.overflowed += 1

@@ -202,3 +202,31 @@ def test_epilogue_kernel_vs_torch_chain():
     assert rel_l2(a.grad[1:4], b.grad[1:4]) < 1e-5
     assert rel_l2(a.grad[[0, 4]], b.grad[[0, 4]]) < 2e-3
     assert float(a.grad[5:].abs().max()) == 0
+
+
+def test_host_feed_and_scalar_reader():
+    """Double-buffered uploads arrive intact and in order; the scalar reader returns values one step late."""
+    from fsgs.feed import HostFeed, ScalarReader
+    feed, reader = HostFeed("cuda"), ScalarReader(lag=1)
+    batches = [{"a": torch.full((1 << 20,), float(i)).pin_memory(),
+                "n": {"b": torch.arange(8, dtype=torch.float32).add_(i).pin_memory()}} for i in range(6)]
+    feed.stage(batches[0])
+    got = []
+    for i in range(6):
+        if i + 1 < 6:
+            feed.stage(batches[i + 1])
+        x = feed.take()
+        y = x["a"].sum() / x["a"].numel() + x["n"]["b"][0]      # consumes the buffers on the compute stream
+        feed.release()
+        reader.push(y)
+        v = reader.pop()
+        if v is not None:
+            got.append(float(v))
+    got += [float(v) for v in reader.drain()]
+    assert got == [2.0 * i for i in range(6)]
+    with pytest.raises(RuntimeError):
+        feed.stage({"a": torch.zeros(4)})                       # not pinned
+    feed2 = HostFeed("cuda")
+    feed2.stage(batches[0]); feed2.stage(batches[1])
+    with pytest.raises(RuntimeError):
+        feed2.stage(batches[2])                                 # both slots staged
