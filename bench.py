@@ -57,39 +57,63 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle samples while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """SM clock and clock-event (throttle) reasons sampled through NVML while the timed region runs: read-only
+    queries from a thread of this process, one every few milliseconds (a timed region lasts tens of milliseconds, too
+    short for an external nvidia-smi loop to see)."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, gpu_index):
-        self.rows, self.proc, self.gpu = [], None, gpu_index
+    def __init__(self, gpu_index, period=0.004):
+        self.samples, self.period, self.handle, self.nv = [], period, None, None
+        self.running = False
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid)
+                self.handle = nv.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self.handle = nv.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.nv = nv
+        except Exception as e:  # no NVML: reported, not fatal
+            self.error = f"NVML unavailable: {e}"
+
+    def _loop(self):
+        nv = self.nv
+        while self.running:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except AttributeError:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((mhz, bits))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+        if self.nv is None:
+            return
+        self.running = True
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error], "samples": 0}
+        self.running = False
         self.thread.join(timeout=2)
-        sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
-        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower() == "active"})
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+        sm = sorted(m for m, _ in self.samples)
+        bits = 0
+        for _, b in self.samples:
+            bits |= b
+        try:
+            mx = self.nv.nvmlDeviceGetMaxClockInfo(self.handle, self.nv.NVML_CLOCK_SM)
+        except Exception:
+            mx = None
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(n for b, n in self.REASONS.items() if bits & b), "samples": len(sm)}
 
 
 def build_workload(name, rank, device):

@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
   const long long r0 = a.ranges[2 * tile], r1 = a.ranges[2 * tile + 1];
   const int n = (int) (r1 - r0);
 
+  const float far_scale = a.far_n / (a.far_n - a.near_n);
   bool done = !inside;
   float T = 1.0f, C0 = 0, C1 = 0, C2 = 0;
   float N0 = 0, N1 = 0, N2 = 0, D = 0, M1 = 0, M2 = 0, dist = 0, med_depth = 0, F0 = 0, F1 = 0;
@@ -173,7 +174,8 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
         if (AUX) {
           const float4 q6 = rec[6];
           const float A = 1 - T;
-          const float m = a.far_n / (a.far_n - a.near_n) * (1 - a.near_n / h.depth);
+          // normalised depth for the distortion terms: feeds no cut, so the reciprocal may be approximate
+          const float m = far_scale * (1 - a.near_n * __fdividef(1.0f, h.depth));
           dist += (m * m * A + M2 - 2 * m * M1) * w;
           D += h.depth * w;
           M1 += m * w;
