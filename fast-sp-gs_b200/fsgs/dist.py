@@ -13,24 +13,42 @@ def shard_views(n_views, rank, world_size):
 
 
 class GradBucket:
-    """A flat fp32 buffer holding the gradients of ``params`` back to back.  ``reduce()`` copies the current
-    ``.grad`` tensors in, all-reduces the buffer once and re-points every ``.grad`` at its slice."""
+    """A flat fp32 buffer holding the gradients of ``params`` back to back, plus ``extra`` trailing floats that ride
+    in the same collective (the visibility mask as 0/1).  ``reduce()`` copies in only the ``.grad`` tensors that do
+    not already live in their slice (``view_of(p)`` handed to the backward kernels as the destination makes the copy
+    unnecessary), all-reduces the buffer once and re-points every ``.grad`` at its slice."""
 
-    def __init__(self, params):
+    def __init__(self, params, extra=0):
         self.params = list(params)
         self.sizes = [p.numel() for p in self.params]
-        self.flat = torch.zeros(sum(self.sizes), dtype=torch.float32, device=self.params[0].device)
+        self.flat = torch.zeros(sum(self.sizes) + extra, dtype=torch.float32, device=self.params[0].device)
         self.views, off = [], 0
         for p, n in zip(self.params, self.sizes):
             self.views.append(self.flat[off:off + n].view(p.shape))
             off += n
+        self.extra = self.flat[off:off + extra]
+        self.copied = 0  # gradients that had to be copied in by the last pack()
 
     def nbytes(self):
         return self.flat.numel() * 4
 
+    def view_of(self, param):
+        for p, v in zip(self.params, self.views):
+            if p is param:
+                return v
+        raise KeyError("parameter is not in this bucket")
+
     def pack(self):
-        src = [p.grad if p.grad is not None else torch.zeros_like(p) for p in self.params]
-        torch._foreach_copy_(self.views, src)
+        dst, src = [], []
+        for p, v in zip(self.params, self.views):
+            if p.grad is None:
+                v.zero_()
+            elif p.grad.data_ptr() != v.data_ptr():
+                dst.append(v)
+                src.append(p.grad)
+        self.copied = len(src)
+        if src:
+            torch._foreach_copy_(dst, src)
 
     def reduce(self, group=None, async_op=False):
         self.pack()

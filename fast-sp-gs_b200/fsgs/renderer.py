@@ -112,11 +112,14 @@ class _LbsWarp(torch.autograd.Function):
         return grads[0], grads[1], grads[2], None, grads[3], grads[4], grads[5], grads[6], grads[7]
 
 
-def lbs_backward(ts, g_means, g_scales, g_rots):
+def lbs_backward(ts, g_means, g_scales, g_rots, outs=()):
+    """Gradients of the warp's eight float inputs; ``outs`` may give destinations for the first of them."""
     xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds = ts
     P = xyz.shape[0]
     l = make_lbs(*ts)
-    outs = [torch.empty_like(t) for t in (xyz, scaling_raw, rotation_raw, knn_w, sp_q, sp_t, sp_dr, sp_ds)]
+    given = list(outs) + [None] * 8
+    outs = [g if g is not None else torch.empty_like(t)
+            for g, t in zip(given, (xyz, scaling_raw, rotation_raw, knn_w, sp_q, sp_t, sp_dr, sp_ds))]
     g = _lib.LBSGrads()
     for name, t in zip(("g_xyz", "g_scaling_raw", "g_rotation_raw", "g_knn_w", "g_sp_q", "g_sp_t", "g_sp_dr",
                         "g_sp_ds"), outs):
@@ -139,7 +142,7 @@ class _FastRender(torch.autograd.Function):
     @staticmethod
     def forward(ctx, means3D, scales, rotations, opacities, shs, sh_rest, Tw2v, Tv2c, Tv2s, campos, cfg, trans_mat_t2,
                 culling, accum_max_count, accum_weights_p, accum_weights_count, means2D, *lbs_tensors):
-        W, H, sh_degree, near_n, far_n, only_image = cfg
+        W, H, sh_degree, near_n, far_n, only_image = cfg[:6]
         use_lbs = len(lbs_tensors) == 9
         P = opacities.shape[0]
         lbs = warped = None
@@ -173,7 +176,19 @@ class _FastRender(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, g_colors, g_opacity, g_extras, g_flow, _g_nc, _g_radii):
-        W, H, sh_degree, near_n, far_n, only_image = ctx.cfg
+        W, H, sh_degree, near_n, far_n, only_image = ctx.cfg[:6]
+        grad_out = (ctx.cfg[6] if len(ctx.cfg) > 6 else None) or {}
+
+        def dest(name, like):
+            """A fresh alias of the caller's destination for this gradient (autograd can then adopt it as ``.grad``
+            without a copy), or None."""
+            t = grad_out.get(name)
+            if t is None or like is None:
+                return None
+            ops._need(t.is_cuda and t.is_contiguous() and t.dtype == torch.float32 and t.shape == like.shape,
+                      f"grad_out[{name!r}] must be a contiguous float32 CUDA tensor of shape {tuple(like.shape)}")
+            return t.detach()
+
         sv = list(ctx.saved_tensors)
         (means3D, scales, rotations, opacities, shs, Tw2v, Tv2s, campos, means2D, trans_mat, radii, colors, records,
          ranges, point_list, tile_order, pixel_opacity, n_contrib) = sv[:18]
@@ -201,7 +216,9 @@ class _FastRender(torch.autograd.Function):
         n_sh = shs.numel() // max(P, 1)
         n_rest = sh_rest.numel() // max(P, 1) if has_rest else 0
         want_sh = sh_degree >= 0
-        width = 3 + 2 + 4 + 1 + (n_sh if want_sh else 0) + (n_rest if want_sh else 0)
+        gsh = dest("sh_features", shs) if want_sh else None
+        grest = dest("sh_features_rest", sh_rest) if (want_sh and has_rest) else None
+        width = 3 + 2 + 4 + 1 + (n_sh if want_sh and gsh is None else 0) + (n_rest if want_sh and grest is None else 0)
         block = torch.empty(P * width, device=dev, dtype=torch.float32)
         off = 0
 
@@ -212,8 +229,10 @@ class _FastRender(torch.autograd.Function):
             return v
 
         gm, gs, gr, go = take(3, (P, 3)), take(2, (P, 2)), take(4, (P, 4)), take(1, (P, 1))
-        gsh = take(n_sh, shs.shape) if want_sh else None
-        grest = take(n_rest, sh_rest.shape) if (want_sh and has_rest) else None
+        if want_sh and gsh is None:
+            gsh = take(n_sh, shs.shape)
+        if want_sh and has_rest and grest is None:
+            grest = take(n_rest, sh_rest.shape)
         a = _lib.PreprocessBwdArgs()
         a.P, a.W, a.H, a.sh_degree = P, W, H, sh_degree
         a.n_dc = shs.shape[1] if sh_degree >= 0 else 1
@@ -231,7 +250,9 @@ class _FastRender(torch.autograd.Function):
             gsh = g_col  # colours were an input: their gradient is the compositing gradient itself
         grads = [gm, gs, gr, go, gsh, grest, None, None, None, None, None, None, None, None, None, None, g_m2d]
         if ctx.use_lbs:
-            lg = lbs_backward(lbs_tensors, gm, gs, gr)
+            lg = lbs_backward(lbs_tensors, gm, gs, gr,
+                              outs=(dest("xyz", lbs_tensors[0]), dest("scaling_raw", lbs_tensors[1]),
+                                    dest("rotation_raw", lbs_tensors[2])))
             grads[0] = grads[1] = grads[2] = None
             grads += [lg[0], lg[1], lg[2], None, lg[3], lg[4], lg[5], lg[6], lg[7]]
         return tuple(grads)
@@ -311,7 +332,7 @@ def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s
                       is_opengl=False, near=0.2, far=100, sh_degree=0, colors=None, sh_features=None,
                       sh_features_rest=None, depth_ratio=1., culling=None, accum_max_count=None,
                       accum_weights_p=None, accum_weights_count=None, trans_mat_t2=None, lbs=None, only_image=False,
-                      **kwargs):
+                      grad_out=None, **kwargs):
     """Render one view.  Same arguments and result dictionary as the reference's ``GS_2D_fast_render``
     (renderer/gs_2d_fast_render.py:670-754): ``images [3,H,W]``, ``normals`` (world space), ``opacity``,
     ``distortion``, ``surf_depth``, ``surf_normal``, ``radii``, ``viewspace_points`` (its ``.grad`` receives the
@@ -319,7 +340,11 @@ def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s
 
     Extra, optional: ``lbs=(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds)`` evaluates the
     superpoint warp inside the preprocess kernel (then ``points/scales/rotations`` are ignored);
-    ``only_image=True`` skips the auxiliary channels and returns only images / opacity / radii entries.
+    ``only_image=True`` skips the auxiliary channels and returns only images / opacity / radii entries;
+    ``grad_out={name: tensor}`` (names ``sh_features``, ``sh_features_rest`` and, with ``lbs``, ``xyz``,
+    ``scaling_raw``, ``rotation_raw``) makes the backward kernels write those gradients straight into the caller's
+    tensors (slices of a communication bucket, say) instead of fresh allocations; the tensors returned to autograd
+    alias them.  Only valid while the corresponding leaves have no ``.grad`` yet.
     """
     P = opacity.shape[0]
     means2D = torch.zeros(P, 2, device=opacity.device, dtype=torch.float32, requires_grad=True)
@@ -327,7 +352,7 @@ def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s
     if campos is None:
         campos = torch.linalg.inv_ex(Tw2v).inverse[:3, 3].contiguous()
     feats = sh_features if colors is None else colors
-    cfg = (W, H, int(sh_degree) if colors is None else -1, float(near), float(far), bool(only_image))
+    cfg = (W, H, int(sh_degree) if colors is None else -1, float(near), float(far), bool(only_image), grad_out)
     geom = (points, scales, rotations)
     if lbs is None:
         geom = tuple(t.contiguous() for t in geom)

@@ -49,26 +49,36 @@ class DynamicScene:
         self.knn_idx = idx
         self.knn_w = torch.softmax(-d2, dim=-1).contiguous()
 
-    def render(self, cam, size, motion, only_image=False):
+    def render(self, cam, size, motion, only_image=False, grad_out=None):
         """``motion``: dict sp_q [M,4] unit quaternions, sp_t [M,3], sp_dr [M,4], sp_ds [M,2] for this time step."""
         lbs = (self.xyz, self.scaling, self.rotation, self.knn_idx, self.knn_w, motion["sp_q"], motion["sp_t"],
                motion["sp_dr"], motion["sp_ds"])
         return GS_2D_fast_render(None, None, None, torch.sigmoid(self.opacity), size, cam["Tw2v"], cam["Tv2c"],
                                  cam["Tv2s"], cam["campos"], sh_degree=3, sh_features=self.sh_dc,
-                                 sh_features_rest=self.sh_rest, lbs=lbs, only_image=only_image)
+                                 sh_features_rest=self.sh_rest, lbs=lbs, only_image=only_image, grad_out=grad_out)
 
     def train_step(self, cam, size, motion, g_images, g_opacity, group=None, distributed=False):
         """One iteration: forward, backward with the given upstream gradients on images [3,H,W] and opacity [H,W],
         (all-reduce of the gradients and of the visibility mask when ``distributed``), fused masked Adam.
         Returns the render dictionary."""
-        out = self.render(cam, size, motion)
+        grad_out = None
+        if distributed:
+            if self.bucket is None:
+                self.bucket = GradBucket(self.params, extra=self.num_points)
+            if all(p.grad is None for p in self.params):
+                # the backward kernels write these gradients straight into the communication bucket
+                b = self.bucket
+                grad_out = dict(sh_features=b.view_of(self.sh_dc), sh_features_rest=b.view_of(self.sh_rest),
+                                xyz=b.view_of(self.xyz), scaling_raw=b.view_of(self.scaling),
+                                rotation_raw=b.view_of(self.rotation))
+        out = self.render(cam, size, motion, grad_out=grad_out)
         torch.autograd.backward([out["images"], out["opacity"]], [g_images, g_opacity])
         visible = out["visibility_filter"]
         if distributed:
-            if self.bucket is None:
-                self.bucket = GradBucket(self.params)
+            # one collective: the gradient sum, with the visibility masks (0/1) riding in the bucket's tail
+            self.bucket.extra.copy_(visible)
             self.bucket.reduce(group)
-            visible = reduce_visibility(visible, group)
+            visible = self.bucket.extra > 0
         self.optimizer.set_before_step(visible, self.num_points)
         self.optimizer.step()
         self.optimizer.zero_grad(set_to_none=True)

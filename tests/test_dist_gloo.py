@@ -21,10 +21,25 @@ def _worker(rank, world, port, out):
     # every view contributes a gradient that depends on the view only: the sum over ranks must equal the serial sum
     for p in params:
         p.grad = sum(torch.full_like(p, float(v + 1)) * p.detach() for v in views)
-    bucket = GradBucket(params)
+    # the second gradient is produced in place (as the backward kernels do), the others are copied in; the
+    # visibility mask rides in the bucket's tail
+    bucket = GradBucket(params, extra=7)
+    in_place = bucket.view_of(params[1])
+    in_place.copy_(params[1].grad)
+    params[1].grad = in_place.detach()
+    mask = torch.zeros(7, dtype=torch.bool)
+    mask[rank::3] = True
+    bucket.extra.copy_(mask)
+    bucket.reduce()
+    ok = bucket.copied == 2 and (bucket.extra > 0).tolist() == [True, True, False, True, True, False, True]
+    params[2].grad = None          # a parameter without gradient contributes zeros
+    bucket.reduce()
+    ok &= bool((params[2].grad == 0).all())
+    for p in params:
+        p.grad = sum(torch.full_like(p, float(v + 1)) * p.detach() for v in views)
     bucket.reduce()
     expect = [sum(float(v + 1) for v in range(5)) * p.detach() for p in params]
-    ok = all(torch.allclose(p.grad, e, rtol=1e-6) for p, e in zip(params, expect))
+    ok &= all(torch.allclose(p.grad, e, rtol=1e-6) for p, e in zip(params, expect))
     ok &= all(p.grad.data_ptr() == v.data_ptr() for p, v in zip(params, bucket.views))
     vis = torch.zeros(7, dtype=torch.bool)
     vis[rank::3] = True

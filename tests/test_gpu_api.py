@@ -230,3 +230,26 @@ def test_host_feed_and_scalar_reader():
     feed2.stage(batches[0]); feed2.stage(batches[1])
     with pytest.raises(RuntimeError):
         feed2.stage(batches[2])                                 # both slots staged
+
+
+def test_train_step_writes_gradients_into_the_bucket():
+    """The multi-GPU step (here with one rank): SH and LBS gradients are written by the kernels straight into the
+    communication bucket (only the opacity gradient, which comes out of torch's sigmoid, is copied) and the step
+    equals the single-GPU step."""
+    from fsgs import workloads as wl
+    from fsgs.scene import DynamicScene, motion_at
+    W, H, P = 160, 120, 5000
+    surf = wl.surfels(P, seed=5, log_scale_mean=-2.5)
+    sp = wl.superpoints(surf["means"], M=64, seed=1)
+    cam = {k: v.cuda() for k, v in wl.camera(W, H).items()}
+    motion = motion_at(sp, sp["centres"], "cuda")
+    g = torch.Generator().manual_seed(9)
+    g_img, g_op = torch.randn(3, H, W, generator=g).cuda(), torch.randn(H, W, generator=g).cuda()
+    scenes = [DynamicScene(surf, sp["centres"], K=3, device="cuda") for _ in range(2)]
+    for _ in range(2):
+        scenes[0].train_step(cam, (W, H), motion, g_img, g_op, distributed=False)
+        scenes[1].train_step(cam, (W, H), motion, g_img, g_op, distributed=True)
+    assert scenes[1].bucket.copied == 1
+    for a, b in zip(scenes[0].params, scenes[1].params):
+        # not bit-equal: the compositing backward sums a Gaussian's tiles with float atomics in arrival order
+        assert float((a - b).abs().max()) < 2e-5
