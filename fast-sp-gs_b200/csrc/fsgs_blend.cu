@@ -40,22 +40,31 @@ struct FwdDev {
   int32_t *accum_weights_count;
 };
 
-// Cooperative load of one batch: records (7 float4 each), Gaussian ids and, for flow, the 3x3 matrices at t2.
-template <bool FLOW, bool REVERSE>
-__device__ __forceinline__ void load_stage(const float4 *__restrict__ records, const int32_t *__restrict__ list,
-    int cnt, const float *__restrict__ m2, float4 *s_rec, int *s_gid, float *s_m2) {
-  // list points at the first entry of the batch (REVERSE: entries are taken as list[-r])
+// Staging.  A tile's list is consumed in batches of kStage entries.  The Gaussian ids of a batch are fetched two
+// batches ahead (plain loads into a register, parked in a small ring in shared memory), its records one batch ahead
+// with 16-byte asynchronous copies (global -> shared without passing through registers), so that the gather latency
+// of batch k+1 is hidden behind the arithmetic of batch k and the block meets at one barrier per batch.
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(smem)), "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Starts the copies of one batch: records (kQ float4 each) of the Gaussians in s_gid[0..cnt) and, for flow, their
+// 3x3 matrices at t2 (plain loads: 36-byte rows are not 16-byte aligned).
+template <bool FLOW>
+__device__ __forceinline__ void issue_stage(const float4 *__restrict__ records, const int *s_gid, int cnt,
+    const float *__restrict__ m2, float4 *s_rec, float *s_m2) {
   for (int e = threadIdx.x; e < cnt * kQ; e += blockDim.x) {
     const int r = e / kQ, qd = e - r * kQ;
-    const int g = REVERSE ? list[-r] : list[r];
-    s_rec[e] = __ldg(records + (size_t) g * (kRecFloats / 4) + qd);
-    if (qd == 0) s_gid[r] = g;
+    cp_async16(s_rec + e, records + (size_t) s_gid[r] * (kRecFloats / 4) + qd);
   }
+  cp_async_commit();
   if (FLOW) {
     for (int e = threadIdx.x; e < cnt * 9; e += blockDim.x) {
       const int r = e / 9, k = e - r * 9;
-      const int g = REVERSE ? list[-r] : list[r];
-      s_m2[e] = __ldg(m2 + (size_t) g * 9 + k);
+      s_m2[e] = __ldg(m2 + (size_t) s_gid[r] * 9 + k);
     }
   }
 }
@@ -101,9 +110,9 @@ __device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py,
 
 template <bool AUX, bool FLOW>
 __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
-  __shared__ float4 s_rec[kStage * kQ];
-  __shared__ int s_gid[kStage];
-  __shared__ float s_m2[FLOW ? kStage * 9 : 1];
+  __shared__ float4 s_recs[2][kStage * kQ];
+  __shared__ int s_gids[3][kStage];
+  __shared__ float s_m2s[2][FLOW ? kStage * 9 : 1];
 
   const int tile = a.tile_order ? a.tile_order[blockIdx.x] : blockIdx.x;
   const int tx = tile % a.gx, ty = tile / a.gx;
@@ -128,13 +137,30 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
   int wmax_id = -1;
   bool flag = false;
 
-  for (int base = 0; base < n; base += kStage) {
-    if (__syncthreads_and(done)) break;
+  // prologue: ids of batches 0 and 1, records of batch 0
+  const int32_t *list = a.point_list + r0;
+  const int n_st = (n + kStage - 1) / kStage;
+  if ((int) threadIdx.x < min(kStage, n)) s_gids[0][threadIdx.x] = list[threadIdx.x];
+  if ((int) threadIdx.x < min(kStage, n - kStage)) s_gids[1][threadIdx.x] = list[kStage + threadIdx.x];
+  __syncthreads();
+  if (n_st > 0) issue_stage<FLOW>(a.records, s_gids[0], min(kStage, n), a.m2, s_recs[0], s_m2s[0]);
+
+  for (int st = 0; st < n_st; ++st) {
+    const int base = st * kStage;
     const int cnt = min(kStage, n - base);
-    load_stage<FLOW, false>(a.records, a.point_list + r0 + base, cnt, a.m2, s_rec, s_gid, s_m2);
-    __syncthreads();
-    if (__all_sync(kFull, done)) continue;
-    for (int c = 0; c < cnt; c += 32) {
+    const float4 *s_rec = s_recs[st & 1];
+    const int *s_gid = s_gids[st % 3];
+    const float *s_m2 = s_m2s[st & 1];
+    // the ids of batch st+2 travel while this batch is composited
+    int id2 = 0;
+    const bool has2 = (int) threadIdx.x < min(kStage, n - base - 2 * kStage);
+    if (has2) id2 = list[base + 2 * kStage + threadIdx.x];
+    cp_async_wait_all();  // this thread's copies of batch st have landed
+    if (__syncthreads_and(done)) break;  // everybody's have, and the other buffer is free again
+    if (st + 1 < n_st)
+      issue_stage<FLOW>(a.records, s_gids[(st + 1) % 3], min(kStage, n - base - kStage), a.m2, s_recs[(st + 1) & 1],
+          s_m2s[(st + 1) & 1]);
+    for (int c = 0; c < cnt && !__all_sync(kFull, done); c += 32) {
       const int rr = c + lane;
       bool hit = false;
       if (rr < cnt) {
@@ -207,8 +233,8 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
         T = test_T;
         last = contributor;
       }
-      if (__all_sync(kFull, done)) break;
     }
+    if (has2) s_gids[(st + 2) % 3][threadIdx.x] = id2;  // read after the next barrier
   }
 
   if (inside) {
@@ -279,11 +305,13 @@ __device__ __forceinline__ float warp_transpose_reduce(float (&v)[32], int lane,
 }
 
 template <bool AUX, bool FLOW>
-__global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
-  __shared__ float4 s_rec[kStage * kQ];
-  __shared__ int s_gid[kStage];
-  __shared__ float s_grad[kStage * kGrad];
-  __shared__ float s_m2[FLOW ? kStage * 9 : 1];
+__global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
+  // dynamic shared memory: two record buffers, two gradient buffers, a ring of four id batches (+ flow matrices)
+  extern __shared__ float4 s_dyn[];
+  float4 *const s_recs = s_dyn;                                               // [2][kStage * kQ]
+  float *const s_grads = reinterpret_cast<float *>(s_recs + 2 * kStage * kQ);  // [2][kStage * kGrad]
+  int *const s_gids = reinterpret_cast<int *>(s_grads + 2 * kStage * kGrad);   // [4][kStage]
+  float *const s_m2s = reinterpret_cast<float *>(s_gids + 4 * kStage);         // [2][kStage * 9] when FLOW
   __shared__ int s_max[8];
 
   const int tile = a.tile_order ? a.tile_order[blockIdx.x] : blockIdx.x;
@@ -343,15 +371,54 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
   for (int k = 0; k < 8; ++k) tmax = max(tmax, s_max[k]);
   if (tmax == 0) return;
 
+  // Batches are taken back to front: step k works on list positions [base_k, base_k + cnt_k), entry r of the batch
+  // being position base_k + cnt_k - 1 - r.  Ids are fetched two steps ahead, records one step ahead; the gradients of
+  // step k-1 are flushed to global memory (and their buffer cleared) while step k accumulates into the other buffer.
   const int n_stages = (min(n, tmax) + kStage - 1) / kStage;
-  for (int st = n_stages - 1; st >= 0; --st) {
-    const int base = st * kStage;
-    const int cnt = min(kStage, n - base);
-    __syncthreads();  // previous batch fully flushed
-    // entry r of the batch is list position base + cnt - 1 - r (back to front)
-    load_stage<FLOW, true>(a.records, a.point_list + r0 + base + cnt - 1, cnt, a.m2, s_rec, s_gid, s_m2);
-    for (int e = threadIdx.x; e < cnt * kGrad; e += blockDim.x) s_grad[e] = 0.0f;
-    __syncthreads();
+  const int32_t *list = a.point_list + r0;
+  const int tid = threadIdx.x;
+  auto step_base = [&](int k) { return (n_stages - 1 - k) * kStage; };
+  auto step_cnt = [&](int k) { return min(kStage, n - step_base(k)); };
+  auto flush = [&](int k) {
+    float *s_grad = s_grads + (k & 1) * (kStage * kGrad);
+    const int *s_gid = s_gids + (k & 3) * kStage;
+    const int cnt = step_cnt(k);
+    // one global reduction per (Gaussian, component) of the batch
+    for (int e = tid; e < cnt * kGrad; e += blockDim.x) {
+      const float v = s_grad[e];
+      if (v == 0.0f) continue;
+      s_grad[e] = 0.0f;
+      const int r = e / kGrad, c = e - r * kGrad;
+      const size_t g = (size_t) s_gid[r];
+      float *dst;
+      if (c < 3) dst = a.g_colors + g * 3 + c;
+      else if (c < 7) dst = a.g_normal_opacity + g * 4 + (c - 3);
+      else if (c < 9) dst = a.g_means2D + g * 2 + (c - 7);
+      else if (c < 12) dst = a.g_trans_mat + g * 9 + 6 + (c - 9);
+      else dst = a.g_inverse_m + g * 9 + (c - 12);
+      atomicAdd(dst, v);
+    }
+  };
+  for (int e = tid; e < 2 * kStage * kGrad; e += blockDim.x) s_grads[e] = 0.0f;
+  for (int k = 0; k < 2 && k < n_stages; ++k)
+    if (tid < step_cnt(k)) s_gids[k * kStage + tid] = list[step_base(k) + step_cnt(k) - 1 - tid];
+  __syncthreads();
+  issue_stage<FLOW>(a.records, s_gids, step_cnt(0), a.m2, s_recs, s_m2s);
+
+  for (int k = 0; k < n_stages; ++k) {
+    const int base = step_base(k), cnt = step_cnt(k);
+    const float4 *s_rec = s_recs + (k & 1) * (kStage * kQ);
+    float *s_grad = s_grads + (k & 1) * (kStage * kGrad);
+    const float *s_m2 = s_m2s + (k & 1) * (kStage * 9);
+    int id2 = 0;
+    const bool has2 = k + 2 < n_stages && tid < step_cnt(k + 2);
+    if (has2) id2 = list[step_base(k + 2) + step_cnt(k + 2) - 1 - tid];
+    cp_async_wait_all();
+    __syncthreads();  // records of step k are in; step k-1 is complete in its gradient buffer
+    if (k + 1 < n_stages)
+      issue_stage<FLOW>(a.records, s_gids + ((k + 1) & 3) * kStage, step_cnt(k + 1), a.m2,
+          s_recs + ((k + 1) & 1) * (kStage * kQ), s_m2s + ((k + 1) & 1) * (kStage * 9));
+    if (k > 0) flush(k - 1);
 
     if (base < wmax) {
       for (int c = 0; c < cnt; c += 32) {
@@ -443,22 +510,15 @@ __global__ void __launch_bounds__(256) blend_backward_kernel(BwdDev a) {
         }
       }
     }
-    __syncthreads();
-    // one global reduction per (Gaussian, component) of this batch
-    for (int e = threadIdx.x; e < cnt * kGrad; e += blockDim.x) {
-      const float v = s_grad[e];
-      if (v == 0.0f) continue;
-      const int r = e / kGrad, c = e - r * kGrad;
-      const size_t g = (size_t) s_gid[r];
-      float *dst;
-      if (c < 3) dst = a.g_colors + g * 3 + c;
-      else if (c < 7) dst = a.g_normal_opacity + g * 4 + (c - 3);
-      else if (c < 9) dst = a.g_means2D + g * 2 + (c - 7);
-      else if (c < 12) dst = a.g_trans_mat + g * 9 + 6 + (c - 9);
-      else dst = a.g_inverse_m + g * 9 + (c - 12);
-      atomicAdd(dst, v);
-    }
+    if (has2) s_gids[((k + 2) & 3) * kStage + tid] = id2;  // read after the next barrier
   }
+  __syncthreads();
+  flush(n_stages - 1);
+}
+
+static size_t bwd_smem_bytes(bool flow) {
+  return sizeof(float4) * 2 * kStage * kQ + sizeof(float) * 2 * kStage * kGrad + sizeof(int) * 4 * kStage +
+         (flow ? sizeof(float) * 2 * kStage * 9 : 0);
 }
 
 }  // namespace fsgs
@@ -519,9 +579,21 @@ extern "C" int fsgs_render_backward(const fsgs_render_bwd_args *a, fsgs_stream_t
   d.g_colors = a->dL_dcolors, d.g_means2D = a->dL_dmeans2D, d.g_trans_mat = a->dL_dtrans_mat;
   d.g_inverse_m = a->dL_dinverse_m, d.g_normal_opacity = a->dL_dnormal_opacity;
   const int T = d.gx * ((a->H + kTile - 1) / kTile);
-  if (!aux) blend_backward_kernel<false, false><<<T, 256, 0, st>>>(d);
-  else if (flow) blend_backward_kernel<true, true><<<T, 256, 0, st>>>(d);
-  else blend_backward_kernel<true, false><<<T, 256, 0, st>>>(d);
+  const size_t smem = bwd_smem_bytes(false), smem_flow = bwd_smem_bytes(true);
+  static bool configured_dev[64] = {};  // the opt-in above 48 KB is a per-function, per-device attribute: set once
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FSGS_ERR_LAUNCH;
+  bool &configured = configured_dev[dev];
+  if (!configured) {
+    if (cudaFuncSetAttribute(blend_backward_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess ||
+        cudaFuncSetAttribute(blend_backward_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess ||
+        cudaFuncSetAttribute(blend_backward_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_flow) != cudaSuccess)
+      return FSGS_ERR_LAUNCH;
+    configured = true;
+  }
+  if (!aux) blend_backward_kernel<false, false><<<T, 256, smem, st>>>(d);
+  else if (flow) blend_backward_kernel<true, true><<<T, 256, smem_flow, st>>>(d);
+  else blend_backward_kernel<true, false><<<T, 256, smem, st>>>(d);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }
