@@ -18,7 +18,16 @@ namespace fsgs {
 
 constexpr int kStage = 128;          // splats per shared-memory batch
 constexpr int kQ = kRecQuadsUsed;    // float4 per staged record
-constexpr int kGrad = 21;            // gradient components per splat
+// Gradient components per splat.  With upstream gradients on the auxiliary channels: colour 0-2, normal 3-5,
+// opacity 6, mean2D 7-8, depth row of trans_mat 9-11, inverse_m 12-20.  Without (colour and opacity upstream only)
+// the normal and depth-row components are identically zero and are left out: colour 0-2, opacity 3, mean2D 4-5,
+// inverse_m 6-14.
+template <bool AUX>
+struct GradMap {
+  static constexpr int N = AUX ? 21 : 15;
+  static constexpr int kNrm = 3, kTw = 9;  // AUX only
+  static constexpr int kOpac = AUX ? 6 : 3, kM2d = AUX ? 7 : 4, kIm = AUX ? 12 : 6;
+};
 constexpr unsigned kFull = 0xffffffffu;
 
 struct FwdDev {
@@ -309,6 +318,8 @@ __global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
   // dynamic shared memory: two record buffers, two gradient buffers, a ring of four id batches (+ flow matrices)
   extern __shared__ float4 s_dyn[];
   float4 *const s_recs = s_dyn;                                               // [2][kStage * kQ]
+  using GM = GradMap<AUX>;
+  constexpr int kGrad = GM::N;
   float *const s_grads = reinterpret_cast<float *>(s_recs + 2 * kStage * kQ);  // [2][kStage * kGrad]
   int *const s_gids = reinterpret_cast<int *>(s_grads + 2 * kStage * kGrad);   // [4][kStage]
   float *const s_m2s = reinterpret_cast<float *>(s_gids + 4 * kStage);         // [2][kStage * 9] when FLOW
@@ -339,8 +350,8 @@ __global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
   float2 gflow = make_float2(0, 0);
   if (inside) {
     gpix0 = a.g_color[pix], gpix1 = a.g_color[HW + pix], gpix2 = a.g_color[2 * HW + pix];
+    if (a.g_opacity) g_acc = a.g_opacity[pix];
     if (AUX) {
-      g_acc = a.g_opacity[pix];
       g_depth = a.g_extras[pix];
       g_n0 = a.g_extras[HW + pix], g_n1 = a.g_extras[2 * HW + pix], g_n2 = a.g_extras[3 * HW + pix];
       g_med = a.g_extras[4 * HW + pix];
@@ -392,10 +403,11 @@ __global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
       const size_t g = (size_t) s_gid[r];
       float *dst;
       if (c < 3) dst = a.g_colors + g * 3 + c;
-      else if (c < 7) dst = a.g_normal_opacity + g * 4 + (c - 3);
-      else if (c < 9) dst = a.g_means2D + g * 2 + (c - 7);
-      else if (c < 12) dst = a.g_trans_mat + g * 9 + 6 + (c - 9);
-      else dst = a.g_inverse_m + g * 9 + (c - 12);
+      else if (AUX && c < GM::kOpac) dst = a.g_normal_opacity + g * 4 + (c - GM::kNrm);
+      else if (c == GM::kOpac) dst = a.g_normal_opacity + g * 4 + 3;
+      else if (c < GM::kM2d + 2) dst = a.g_means2D + g * 2 + (c - GM::kM2d);
+      else if (AUX && c < GM::kIm) dst = a.g_trans_mat + g * 9 + 6 + (c - GM::kTw);
+      else dst = a.g_inverse_m + g * 9 + (c - GM::kIm);
       atomicAdd(dst, v);
     }
   };
@@ -449,7 +461,7 @@ __global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
             T = __fdividef(T, 1.0f - alpha);
             const float w = alpha * T;
             const float4 q5 = rec[5];
-            float q = q5.x * gpix0 + q5.y * gpix1 + q5.z * gpix2;
+            float q = q5.x * gpix0 + q5.y * gpix1 + q5.z * gpix2 + g_acc;
             float dL_dalpha = 0.0f;
             g[0] = w * gpix0, g[1] = w * gpix1, g[2] = w * gpix2;
 
@@ -465,8 +477,8 @@ __global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
               last_dL_dT = dL_dweight * alpha + (1 - alpha) * last_dL_dT;
               const float dL_dmd = 2.0f * (T * alpha) * (m_d * final_A - final_D) * g_reg;
               dL_dz += dL_dmd * dmd_dd;
-              q += h.depth * g_depth + g_acc + q5.w * g_n0 + q6.x * g_n1 + q6.y * g_n2;
-              g[3] = w * g_n0, g[4] = w * g_n1, g[5] = w * g_n2;
+              q += h.depth * g_depth + q5.w * g_n0 + q6.x * g_n1 + q6.y * g_n2;
+              g[GM::kNrm] = w * g_n0, g[GM::kNrm + 1] = w * g_n1, g[GM::kNrm + 2] = w * g_n2;
               dL_dz += w * g_depth;
             }
             if (FLOW) {
@@ -493,15 +505,15 @@ __global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
               const float inv_pz = __fdividef(1.0f, h.pz);
               const float ga = dL_dsx * inv_pz, gb = dL_dsy * inv_pz;
               const float gc = -(ga * h.sx + gb * h.sy);
-              g[12] = ga * px, g[13] = ga * py, g[14] = ga;
-              g[15] = gb * px, g[16] = gb * py, g[17] = gb;
-              g[18] = gc * px, g[19] = gc * py, g[20] = gc;
+              g[GM::kIm] = ga * px, g[GM::kIm + 1] = ga * py, g[GM::kIm + 2] = ga;
+              g[GM::kIm + 3] = gb * px, g[GM::kIm + 4] = gb * py, g[GM::kIm + 5] = gb;
+              g[GM::kIm + 6] = gc * px, g[GM::kIm + 7] = gc * py, g[GM::kIm + 8] = gc;
             } else {
-              g[7] = dL_dG * (-G * 2.0f * h.dx);
-              g[8] = dL_dG * (-G * 2.0f * h.dy);
+              g[GM::kM2d] = dL_dG * (-G * 2.0f * h.dx);
+              g[GM::kM2d + 1] = dL_dG * (-G * 2.0f * h.dy);
             }
-            g[9] = dL_dz * h.sx, g[10] = dL_dz * h.sy, g[11] = dL_dz;
-            g[6] = G * dL_dalpha;
+            if (AUX) g[GM::kTw] = dL_dz * h.sx, g[GM::kTw + 1] = dL_dz * h.sy, g[GM::kTw + 2] = dL_dz;
+            g[GM::kOpac] = G * dL_dalpha;
           }
           if (__ballot_sync(kFull, active) == 0) continue;
           int comp;
@@ -516,8 +528,9 @@ __global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
   flush(n_stages - 1);
 }
 
-static size_t bwd_smem_bytes(bool flow) {
-  return sizeof(float4) * 2 * kStage * kQ + sizeof(float) * 2 * kStage * kGrad + sizeof(int) * 4 * kStage +
+static size_t bwd_smem_bytes(bool aux, bool flow) {
+  const int n = aux ? GradMap<true>::N : GradMap<false>::N;
+  return sizeof(float4) * 2 * kStage * kQ + sizeof(float) * 2 * kStage * n + sizeof(int) * 4 * kStage +
          (flow ? sizeof(float) * 2 * kStage * 9 : 0);
 }
 
@@ -579,19 +592,20 @@ extern "C" int fsgs_render_backward(const fsgs_render_bwd_args *a, fsgs_stream_t
   d.g_colors = a->dL_dcolors, d.g_means2D = a->dL_dmeans2D, d.g_trans_mat = a->dL_dtrans_mat;
   d.g_inverse_m = a->dL_dinverse_m, d.g_normal_opacity = a->dL_dnormal_opacity;
   const int T = d.gx * ((a->H + kTile - 1) / kTile);
-  const size_t smem = bwd_smem_bytes(false), smem_flow = bwd_smem_bytes(true);
+  const size_t smem_color = bwd_smem_bytes(false, false), smem = bwd_smem_bytes(true, false);
+  const size_t smem_flow = bwd_smem_bytes(true, true);
   static bool configured_dev[64] = {};  // the opt-in above 48 KB is a per-function, per-device attribute: set once
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FSGS_ERR_LAUNCH;
   bool &configured = configured_dev[dev];
   if (!configured) {
-    if (cudaFuncSetAttribute(blend_backward_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess ||
+    if (cudaFuncSetAttribute(blend_backward_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_color) != cudaSuccess ||
         cudaFuncSetAttribute(blend_backward_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess ||
         cudaFuncSetAttribute(blend_backward_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_flow) != cudaSuccess)
       return FSGS_ERR_LAUNCH;
     configured = true;
   }
-  if (!aux) blend_backward_kernel<false, false><<<T, 256, smem, st>>>(d);
+  if (!aux) blend_backward_kernel<false, false><<<T, 256, smem_color, st>>>(d);
   else if (flow) blend_backward_kernel<true, true><<<T, 256, smem_flow, st>>>(d);
   else blend_backward_kernel<true, false><<<T, 256, smem, st>>>(d);
   FSGS_LAUNCH_CHECK();

@@ -342,7 +342,9 @@ def GS_2D_fast_render_backward(means2D, normal_opacity, colors, trans_mat, inver
     g = render_backward_launch(
         W, H, float(near_n), float(far_n), P, records, point_list.contiguous(), ranges.contiguous(), tile_order,
         trans_mat2 if flow else None, out_opacity.contiguous(), out_others.contiguous() if aux else None,
-        n_contrib.contiguous(), dL_dout_color.contiguous(), dL_dout_opacity.contiguous(),
+        n_contrib.contiguous(), dL_dout_color.contiguous(),
+        # the reference's kernel without auxiliary channels ignores the opacity gradient (gs_2d_fast_redner.cu:338-341)
+        dL_dout_opacity.contiguous() if aux else None,
         dL_dothers.contiguous() if aux else None, dL_dout_flow.contiguous() if flow else None)
     return list(g)
 

@@ -248,7 +248,12 @@ typedef struct fsgs_render_bwd_args {
   const float *trans_mat_t2;
   const float *out_opacity, *out_extras; /* forward outputs; out_extras NULL selects the colour-only adjoint */
   const int32_t *n_contrib;
-  const float *dL_dcolor, *dL_dopacity, *dL_dextras, *dL_dflow; /* contiguous; dL_dextras/dL_dflow may be NULL */
+  /* Upstream gradients, contiguous.  dL_dextras (or out_extras) NULL selects the adjoint without auxiliary
+   * channels: 15 instead of 21 gradient components per splat, dL_dtrans_mat and the normal part of
+   * dL_dnormal_opacity stay zero.  In that variant dL_dopacity may be NULL, which reproduces the reference kernel
+   * instantiated without auxiliary channels (it ignores the opacity gradient, gs_2d_fast_redner.cu:338-341);
+   * non-NULL it is honoured.  dL_dflow may be NULL. */
+  const float *dL_dcolor, *dL_dopacity, *dL_dextras, *dL_dflow;
   /* outputs, zeroed by the call */
   float *dL_dcolors;         /* [P,3] */
   float *dL_dmeans2D;        /* [P,2] */

@@ -322,6 +322,29 @@ def test_render_backward_vs_oracle(ops, P, W, H, ls, aux, flow):
         assert rel_l2(a, b) < 1e-5
 
 
+def test_render_backward_without_aux_gradient_equals_zero_aux_gradient(ops):
+    """The 15-component adjoint (no upstream gradient on the auxiliary channels, opacity gradient honoured) gives what
+    the 21-component adjoint gives for an all-zero auxiliary gradient."""
+    P, W, H = 30_000, 320, 240
+    s, cam, pre, _ = _render_inputs(ops, P, W, H, -3.2)
+    means2D, colors, trans_mat, inverse_m, normal_opacity, depths, radii, ranges, point_list = pre
+    records, tile_order = ops._records_for(means2D, colors, normal_opacity, trans_mat, inverse_m, point_list)
+    pc, po, pe, pf, nc = ops.render_forward_launch(W, H, 0.2, 100.0, False, P, records, point_list, ranges,
+                                                   tile_order, None, None, None, None)
+    g = torch.Generator().manual_seed(23)
+    g_img, g_op = torch.randn(3, H, W, generator=g).cuda(), torch.randn(H, W, generator=g).cuda()
+    full = ops.render_backward_launch(W, H, 0.2, 100.0, P, records, point_list, ranges, tile_order, None, po, pe, nc,
+                                      g_img, g_op, torch.zeros(8, H, W, device="cuda"), None)
+    lean = ops.render_backward_launch(W, H, 0.2, 100.0, P, records, point_list, ranges, tile_order, None, po, None,
+                                      nc, g_img, g_op, None, None)
+    for name, a, b in zip(["colors", "means2D", "trans_mat", "inverse_m", "normal_opacity"], lean, full):
+        if float(b.abs().max()) == 0:
+            assert float(a.abs().max()) == 0, name
+        else:
+            assert rel_l2(a, b) < 1e-5, f"{name}: {rel_l2(a, b)}"
+    assert float(full[4][:, 3].abs().max()) > 0
+
+
 def test_render_vs_reference_cuda(ops, ref):
     if ref is None:
         pytest.skip("oracle/_ref not built")
