@@ -310,7 +310,6 @@ def run_ours(args):
     per_kernel = ops.timer_summary()
     ops.TIMERS = None
     ms_fwd = timed(fwd_only, args.steps)
-
     # ---- end to end: inputs from pinned host memory, a scalar back, every step ----
     hosts = [{"cam": {k: v.pin_memory() for k, v in wlk["cam"].items()},
               "motion": {k: v.cpu().pin_memory() for k, v in motion.items()},
@@ -342,12 +341,33 @@ def run_ours(args):
 
     pairs = list_pairs(scene)
     pairs_last = last_pairs(scene)
+
+    # the same step with upstream gradients on the auxiliary channels too (normal and distortion losses switched on):
+    # the compositing backward then carries 21 instead of 15 gradient components per splat
+    gen = torch.Generator().manual_seed(300 + rank)
+    g_nrm, g_dist = torch.randn(3, H, W, generator=gen).to(dev), (0.1 * torch.randn(1, H, W, generator=gen)).to(dev)
+    g_aux = [{"normals": sgn * g_nrm, "distortion": sgn * g_dist} for sgn in (1.0, -1.0)]
+
+    def step_aux():
+        gi, go = g_sets[tick[0] & 1]
+        ga = g_aux[tick[0] & 1]
+        tick[0] += 1
+        scene.train_step(cam, (W, H), motion, gi, go, distributed=distributed, g_aux=ga)
+
+    for _ in range(3):
+        step_aux()
+    ms_step_aux = timed(step_aux, args.steps)
+    pairs_aux = last_pairs(scene)
+
     line = None
     if rank == 0:
         peak, peak_kind = peaks()
         n_bwd, ms_bwd = per_kernel.get("blend_backward", (0, float("nan")))
         HW = W * H
-        bwd_bytes = pairs * (72 + 4) + HW * 4 * (3 + 1 + 8 + 1 + 2 + 2) + 4 * 21 * pairs
+        # compositing backward without auxiliary gradients, algorithmic bytes per launch: per list entry its id (4 B),
+        # its 112-byte record and one reduction per gradient component (15 x 4 B); per pixel the upstream colour and
+        # opacity gradients, the forward opacity and the last contributor (24 B)
+        bwd_bytes = pairs * (4 + 112 + 4 * 15) + HW * 24
         achieved = bwd_bytes / (ms_bwd * 1e-3) / 1e9
         # algorithmic HBM bytes per launch of the bandwidth-bound stages (P Gaussians, V visible, 4-byte floats):
         #   adam: 58 floats x (param, grad, 2 moments read; param, 2 moments written) per visible Gaussian + the mask
@@ -375,6 +395,7 @@ def run_ours(args):
                        "l2": "per-step working set (parameters, Adam state, gradients, records, images: > 400 MB) "
                              "exceeds the 126 MB L2; no explicit flush"},
             "fwd_frames_per_s": world * 1e3 / ms_fwd, "ms_per_fwd_frame": ms_fwd,
+            "ms_per_step_with_aux_gradients": ms_step_aux, "pairs_after_aux_phase": pairs_aux,
             "e2e": {"value": world * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4 + 32},
             "gpu_launches": int(round(launches_per_step * args.steps)),

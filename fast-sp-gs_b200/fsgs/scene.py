@@ -57,10 +57,11 @@ class DynamicScene:
                                  cam["Tv2s"], cam["campos"], sh_degree=3, sh_features=self.sh_dc,
                                  sh_features_rest=self.sh_rest, lbs=lbs, only_image=only_image, grad_out=grad_out)
 
-    def train_step(self, cam, size, motion, g_images, g_opacity, group=None, distributed=False):
-        """One iteration: forward, backward with the given upstream gradients on images [3,H,W] and opacity [H,W],
-        (all-reduce of the gradients and of the visibility mask when ``distributed``), fused masked Adam.
-        Returns the render dictionary."""
+    def train_step(self, cam, size, motion, g_images, g_opacity, group=None, distributed=False, g_aux=None):
+        """One iteration: forward, backward with the given upstream gradients on images [3,H,W] and opacity [H,W]
+        (and, with ``g_aux = {"normals": [3,H,W], "distortion": [1,H,W], ...}``, on those entries of the render
+        dictionary), (all-reduce of the gradients and of the visibility mask when ``distributed``), fused masked
+        Adam.  Returns the render dictionary."""
         grad_out = None
         if distributed:
             if self.bucket is None:
@@ -72,7 +73,11 @@ class DynamicScene:
                                 xyz=b.view_of(self.xyz), scaling_raw=b.view_of(self.scaling),
                                 rotation_raw=b.view_of(self.rotation))
         out = self.render(cam, size, motion, grad_out=grad_out)
-        torch.autograd.backward([out["images"], out["opacity"]], [g_images, g_opacity])
+        heads, grads = [out["images"], out["opacity"]], [g_images, g_opacity]
+        for name, g in (g_aux or {}).items():
+            heads.append(out[name])
+            grads.append(g)
+        torch.autograd.backward(heads, grads)
         visible = out["visibility_filter"]
         if distributed:
             # one collective: the gradient sum, with the visibility masks (0/1) riding in the bucket's tail
