@@ -314,7 +314,7 @@ __device__ __forceinline__ float warp_transpose_reduce(float (&v)[32], int lane,
 }
 
 template <bool AUX, bool FLOW>
-__global__ void __launch_bounds__(256, 3) blend_backward_kernel(BwdDev a) {
+__global__ void __launch_bounds__(256, AUX ? 3 : 4) blend_backward_kernel(BwdDev a) {
   // dynamic shared memory: two record buffers, two gradient buffers, a ring of four id batches (+ flow matrices)
   extern __shared__ float4 s_dyn[];
   float4 *const s_recs = s_dyn;                                               // [2][kStage * kQ]

@@ -100,6 +100,13 @@ __global__ void __launch_bounds__(256) lbs_warp_forward_kernel(int P, LbsDev l, 
   rots[i] = q;
 }
 
+__device__ __forceinline__ void red_add_v4(float *p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void red_add_v2(float *p, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(a), "f"(b) : "memory");
+}
+
 // Superpoint gradient table row: q(4) t(3) dr(4) ds(2) = 13 floats.
 constexpr int kSpRow = 13;
 constexpr int kLbsCluster = 8;  // blocks per cluster in the backward (portable maximum)
@@ -164,14 +171,12 @@ __global__ void __launch_bounds__(256) lbs_warp_backward_kernel(int P, LbsDev l,
 #pragma unroll
         for (int c = 0; c < kSpRow; ++c) atomicAdd(table + m * kSpRow + c, row[c]);
       } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) atomicAdd(g_sp_q + 4 * m + c, row[c]);
+        // vector reductions in L2: the [M,4] and [M,2] rows are 16- and 8-byte aligned
+        red_add_v4(g_sp_q + 4 * m, row[0], row[1], row[2], row[3]);
 #pragma unroll
         for (int c = 0; c < 3; ++c) atomicAdd(g_sp_t + 3 * m + c, row[4 + c]);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) atomicAdd(g_sp_dr + 4 * m + c, row[7 + c]);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) atomicAdd(g_sp_ds + 2 * m + c, row[11 + c]);
+        red_add_v4(g_sp_dr + 4 * m, row[7], row[8], row[9], row[10]);
+        red_add_v2(g_sp_ds + 2 * m, row[11], row[12]);
       }
     }
     g_xyz[3 * i] = gx.x, g_xyz[3 * i + 1] = gx.y, g_xyz[3 * i + 2] = gx.z;

@@ -22,10 +22,11 @@ def _lbs_inputs(s, M=64, K=3, seed=0):
                 sp_q=q, sp_t=t, sp_dr=sp["sp_dr"].cuda(), sp_ds=sp["sp_ds"].cuda())
 
 
-def test_lbs_warp_forward_backward_vs_torch():
+@pytest.mark.parametrize("M", [64, 1024])   # 1024: the superpoint table no longer fits shared memory
+def test_lbs_warp_forward_backward_vs_torch(M):
     from fsgs.renderer import lbs_warp
     s, cam = make_scene(5000, 64, 64, seed=3)
-    L = _lbs_inputs(s)
+    L = _lbs_inputs(s, M=M)
     names = ["xyz", "scaling_raw", "rotation_raw", "knn_w", "sp_q", "sp_t", "sp_dr", "sp_ds"]
     a = {k: (v.clone().requires_grad_() if k in names else v) for k, v in L.items()}
     b = {k: (v.clone().requires_grad_() if k in names else v) for k, v in L.items()}
