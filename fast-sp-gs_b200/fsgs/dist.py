@@ -13,20 +13,27 @@ def shard_views(n_views, rank, world_size):
 
 
 class GradBucket:
-    """A flat fp32 buffer holding the gradients of ``params`` back to back, plus ``extra`` trailing floats that ride
-    in the same collective (the visibility mask as 0/1).  ``reduce()`` copies in only the ``.grad`` tensors that do
-    not already live in their slice (``view_of(p)`` handed to the backward kernels as the destination makes the copy
-    unnecessary), all-reduces the buffer once and re-points every ``.grad`` at its slice."""
+    """A flat fp32 buffer holding the gradients of ``params`` back to back, plus ``extra`` floats that ride in the
+    same collectives (the visibility mask as 0/1), placed after parameter number ``extra_after`` (default: at the
+    end).  The buffer is a sequence of segments -- one per parameter, one for the extra block -- and collectives act
+    on runs of segments.  ``reduce()`` copies in only the ``.grad`` tensors that do not already live in their slice
+    (``view_of(p)`` handed to the backward kernels as the destination makes the copy unnecessary), all-reduces the
+    whole buffer and re-points every ``.grad`` at its slice."""
 
-    def __init__(self, params, extra=0):
+    def __init__(self, params, extra=0, extra_after=None):
         self.params = list(params)
         self.sizes = [p.numel() for p in self.params]
-        self.flat = torch.zeros(sum(self.sizes) + extra, dtype=torch.float32, device=self.params[0].device)
-        self.views, off = [], 0
-        for p, n in zip(self.params, self.sizes):
-            self.views.append(self.flat[off:off + n].view(p.shape))
+        k = len(self.params) if extra_after is None else extra_after + 1
+        seg_sizes = self.sizes[:k] + [extra] + self.sizes[k:]
+        self.extra_segment = k
+        self.flat = torch.zeros(sum(seg_sizes), dtype=torch.float32, device=self.params[0].device)
+        self.bounds, off = [], 0
+        for n in seg_sizes:
+            self.bounds.append((off, off + n))
             off += n
-        self.extra = self.flat[off:off + extra]
+        seg_views = [self.flat[lo:hi] for lo, hi in self.bounds]
+        self.extra = seg_views[k]
+        self.views = [v.view(p.shape) for v, p in zip(seg_views[:k] + seg_views[k + 1:], self.params)]
         self.copied = 0  # gradients that had to be copied in by the last pack()
 
     def nbytes(self):
@@ -50,14 +57,29 @@ class GradBucket:
         if src:
             torch._foreach_copy_(dst, src)
 
+    def adopt(self):
+        """Point every ``.grad`` at its slice of the buffer."""
+        for p, v in zip(self.params, self.views):
+            p.grad = v
+
     def reduce(self, group=None, async_op=False):
         self.pack()
         work = None
         if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
             work = dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
-        for p, v in zip(self.params, self.views):
-            p.grad = v
+        self.adopt()
         return work
+
+    def span(self, first, last):
+        """Flat slice covering segments ``first`` .. ``last`` (inclusive)."""
+        return self.flat[self.bounds[first][0]:self.bounds[last][1]]
+
+    def reduce_span(self, first, last, group=None):
+        """Asynchronous all-reduce of a run of segments (their contents must already be in place); returns the work
+        handle, or None when there is nobody to talk to.  ``.wait()`` orders the current stream after it."""
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            return dist.all_reduce(self.span(first, last), op=dist.ReduceOp.SUM, group=group, async_op=True)
+        return None
 
 
 def reduce_visibility(visible, group=None):

@@ -24,11 +24,16 @@ class SparseGaussianAdam(torch.optim.Adam):
         self.visibility, self.N = visibility, N
 
     @torch.no_grad()
-    def step(self):
+    def step(self, only=None):
+        """``only``: an iterable of parameters; the step is then applied to those groups alone (each parameter keeps
+        its own step count, so a step may be split to overlap with communication)."""
         batch = []
+        only = None if only is None else {id(p) for p in only}
         for group in self.param_groups:
             assert len(group["params"]) == 1, "more than one tensor in group"
             param = group["params"][0]
+            if only is not None and id(param) not in only:
+                continue
             if param.grad is None or param.grad.numel() == 0:
                 continue
             state = self.state[param]

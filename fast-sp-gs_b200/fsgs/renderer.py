@@ -249,6 +249,8 @@ class _FastRender(torch.autograd.Function):
         a.grad_shs, a.grad_sh_rest = p(gsh), p(grest)
         with ops._timed("preprocess_backward"):
             check(lib().fsgs_preprocess_backward(ctypes.byref(a), ops._stream()), "fsgs_preprocess_backward")
+        if grad_out.get("on_sh_ready") is not None:
+            grad_out["on_sh_ready"]()  # the SH gradients are final in stream order: their exchange may start
         if sh_degree < 0:
             gsh = g_col  # colours were an input: their gradient is the compositing gradient itself
         grads = [gm, gs, gr, go, gsh, grest, None, None, None, None, None, None, None, None, None, None, g_m2d]
@@ -347,7 +349,8 @@ def GS_2D_fast_render(points, scales, rotations, opacity, size, Tw2v, Tv2c, Tv2s
     ``grad_out={name: tensor}`` (names ``sh_features``, ``sh_features_rest`` and, with ``lbs``, ``xyz``,
     ``scaling_raw``, ``rotation_raw``) makes the backward kernels write those gradients straight into the caller's
     tensors (slices of a communication bucket, say) instead of fresh allocations; the tensors returned to autograd
-    alias them.  Only valid while the corresponding leaves have no ``.grad`` yet.
+    alias them.  Only valid while the corresponding leaves have no ``.grad`` yet.  An entry ``on_sh_ready`` (a
+    callable) is invoked in the backward as soon as the SH gradients have been queued, before the LBS adjoint.
     """
     P = opacity.shape[0]
     means2D = torch.zeros(P, 2, device=opacity.device, dtype=torch.float32, requires_grad=True)

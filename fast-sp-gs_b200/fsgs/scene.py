@@ -62,32 +62,64 @@ class DynamicScene:
         (and, with ``g_aux = {"normals": [3,H,W], "distortion": [1,H,W], ...}``, on those entries of the render
         dictionary), (all-reduce of the gradients and of the visibility mask when ``distributed``), fused masked
         Adam.  Returns the render dictionary."""
+        if not distributed:
+            out = self.render(cam, size, motion)
+            self._backward(out, g_images, g_opacity, g_aux)
+            self.optimizer.set_before_step(out["visibility_filter"], self.num_points)
+            self.optimizer.step()
+            self.optimizer.zero_grad(set_to_none=True)
+            return out
+        # Multi-GPU.  Bucket segments: SH DC, SH rest, visibility mask | position, opacity, scale, rotation.
+        # The backward kernels write into the bucket.  The first three segments (49 of the 59 floats per Gaussian)
+        # are all-reduced as soon as the preprocess adjoint has been queued, beside the LBS adjoint; the rest follows;
+        # Adam runs on the SH tensors while the second exchange is in flight.
+        if self.bucket is None:
+            self.bucket = GradBucket([self.sh_dc, self.sh_rest, self.xyz, self.opacity, self.scaling, self.rotation],
+                                     extra=self.num_points, extra_after=1)
+        b = self.bucket
+        early = []
         grad_out = None
-        if distributed:
-            if self.bucket is None:
-                self.bucket = GradBucket(self.params, extra=self.num_points)
-            if all(p.grad is None for p in self.params):
-                # the backward kernels write these gradients straight into the communication bucket
-                b = self.bucket
-                grad_out = dict(sh_features=b.view_of(self.sh_dc), sh_features_rest=b.view_of(self.sh_rest),
-                                xyz=b.view_of(self.xyz), scaling_raw=b.view_of(self.scaling),
-                                rotation_raw=b.view_of(self.rotation))
+        if all(p.grad is None for p in self.params):
+            grad_out = dict(sh_features=b.view_of(self.sh_dc), sh_features_rest=b.view_of(self.sh_rest),
+                            xyz=b.view_of(self.xyz), scaling_raw=b.view_of(self.scaling),
+                            rotation_raw=b.view_of(self.rotation),
+                            on_sh_ready=lambda: early.append(b.reduce_span(0, 2, group)))
         out = self.render(cam, size, motion, grad_out=grad_out)
+        b.extra.copy_(out["visibility_filter"])  # known after the forward: travels with the first exchange
+        self._backward(out, g_images, g_opacity, g_aux)
+        sh_in_place = all(p.grad is not None and p.grad.data_ptr() == b.view_of(p).data_ptr()
+                          for p in (self.sh_dc, self.sh_rest))
+        b.pack()  # copies in what the kernels did not write in place (the opacity gradient)
+        if early and not sh_in_place:
+            # autograd did not adopt the in-place SH gradients (it made copies, which pack() has just moved in): the
+            # early exchange summed stale data; let it finish, then exchange those segments again from fresh contents
+            if early[0] is not None:
+                early[0].wait()
+            b.extra.copy_(out["visibility_filter"])
+            early = [b.reduce_span(0, 2, group)]
+        if early:
+            late = b.reduce_span(3, 6, group)
+        else:  # gradients were not produced in place: one exchange for everything
+            early.append(b.reduce_span(0, 6, group))
+            late = None
+        b.adopt()
+        if early[0] is not None:
+            early[0].wait()
+        visible = b.extra > 0
+        self.optimizer.set_before_step(visible, self.num_points)
+        self.optimizer.step(only=[self.sh_dc, self.sh_rest])
+        if late is not None:
+            late.wait()
+        self.optimizer.step(only=[self.xyz, self.opacity, self.scaling, self.rotation])
+        self.optimizer.zero_grad(set_to_none=True)
+        return out
+
+    def _backward(self, out, g_images, g_opacity, g_aux):
         heads, grads = [out["images"], out["opacity"]], [g_images, g_opacity]
         for name, g in (g_aux or {}).items():
             heads.append(out[name])
             grads.append(g)
         torch.autograd.backward(heads, grads)
-        visible = out["visibility_filter"]
-        if distributed:
-            # one collective: the gradient sum, with the visibility masks (0/1) riding in the bucket's tail
-            self.bucket.extra.copy_(visible)
-            self.bucket.reduce(group)
-            visible = self.bucket.extra > 0
-        self.optimizer.set_before_step(visible, self.num_points)
-        self.optimizer.step()
-        self.optimizer.zero_grad(set_to_none=True)
-        return out
 
     def check(self):
         list_capacity(self.xyz.device).check_overflow()

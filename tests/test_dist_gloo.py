@@ -45,6 +45,23 @@ def _worker(rank, world, port, out):
     vis[rank::3] = True
     vis = reduce_visibility(vis)
     ok &= vis.tolist() == [True, True, False, True, True, False, True]
+    # the split exchange of the training step: mask placed after the first parameter, two runs of segments
+    split = GradBucket(params, extra=7, extra_after=0)
+    for p in params:
+        p.grad = None
+    for p, v in zip(params, split.views):
+        v.copy_(float(rank + 1) * p.detach())
+        p.grad = v.detach()
+    split.extra.copy_(mask)
+    first = split.reduce_span(0, 1)
+    split.pack()
+    second = split.reduce_span(2, 3)
+    first.wait()
+    second.wait()
+    split.adopt()
+    ok &= split.copied == 0 and all(torch.allclose(p.grad, 3.0 * p.detach()) for p in params)
+    ok &= (split.extra > 0).tolist() == [True, True, False, True, True, False, True]
+    ok &= split.span(0, 1).numel() == 7 * 3 + 7 and split.span(2, 3).numel() == 7 * 45 + 7
     radii = torch.tensor([rank, 5 - rank, 2], dtype=torch.int32)
     ok &= reduce_max_(radii).tolist() == [1, 5, 2]
     out[rank] = (bool(ok), views)
