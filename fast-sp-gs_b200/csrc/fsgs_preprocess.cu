@@ -248,7 +248,7 @@ __device__ __forceinline__ void store_rows(float *__restrict__ dst, const float 
   for (int e = threadIdx.x; e < n; e += kPreBlock) dst[e] = src[e];
 }
 
-template <bool LBS>
+template <bool LBS, bool HIGH_SH>
 __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a, LbsDev lbs) {
   // the SH slice is dead once the colours are known; the output staging reuses its space
   __shared__ __align__(128) float s_mem[kStageFloats > kPreBlock * kWideMax ? kStageFloats : kPreBlock * kWideMax];
@@ -370,6 +370,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
           rgb.x += c[0] * b[k], rgb.y += c[1] * b[k], rgb.z += c[2] * b[k];
         }
       }
+      if (HIGH_SH) sh_high_colour(a.sh_degree, x, y, z, cw, rgb);
       rgb = make_float3(fmaxf(rgb.x + 0.5f, 0.0f), fmaxf(rgb.y + 0.5f, 0.0f), fmaxf(rgb.z + 0.5f, 0.0f));
     } else {
       rgb = make_float3(a.shs[3 * i], a.shs[3 * i + 1], a.shs[3 * i + 2]);
@@ -553,6 +554,7 @@ __device__ __forceinline__ bool bulk_ok(const void *g, uint32_t bytes) {
   return ((uintptr_t) g & 15) == 0 && (bytes & 15u) == 0 && bytes > 0;
 }
 
+template <bool HIGH_SH>
 __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDev a) {
   __shared__ __align__(128) float s_mem[kBwdFloats];
   __shared__ __align__(8) uint64_t s_bar;
@@ -705,6 +707,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
           else if (g_g) g_g[o] = grgb.x * b[k], g_g[o + 1] = grgb.y * b[k], g_g[o + 2] = grgb.z * b[k];
         }
       }
+      if (HIGH_SH) sh_high_adjoint(a.sh_degree, x, y, z, c_g - 3 * first, g_g ? g_g - 3 * first : nullptr, grgb, dx, dy, dz);
       // coefficients beyond the active degree get no gradient
       if (staged) {
         for (int o = 3 * (nb - first); o < wide; ++o) w_row[o] = 0.0f;
@@ -856,8 +859,12 @@ extern "C" int fsgs_preprocess_forward(const fsgs_preprocess_args *a, fsgs_strea
   cudaMemsetAsync(a->tile_counts, 0, sizeof(int32_t) * (size_t) d.gx * d.gy, st);
   cudaMemsetAsync(a->counters, 0, sizeof(int64_t) * FSGS_NUM_COUNTERS, st);
   if (a->P == 0) return FSGS_OK;
-  if (a->lbs) preprocess_forward_kernel<true><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, st>>>(d, to_dev(a->lbs));
-  else preprocess_forward_kernel<false><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, st>>>(d, LbsDev());
+  const int blocks = ceil_div(a->P, kPreBlock);
+  const bool high = a->sh_degree > 3;  // degrees 4..7: rare, kept out of the common instantiation
+  if (a->lbs && high) preprocess_forward_kernel<true, true><<<blocks, kPreBlock, 0, st>>>(d, to_dev(a->lbs));
+  else if (a->lbs) preprocess_forward_kernel<true, false><<<blocks, kPreBlock, 0, st>>>(d, to_dev(a->lbs));
+  else if (high) preprocess_forward_kernel<false, true><<<blocks, kPreBlock, 0, st>>>(d, LbsDev());
+  else preprocess_forward_kernel<false, false><<<blocks, kPreBlock, 0, st>>>(d, LbsDev());
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }
@@ -913,7 +920,8 @@ extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_
   d.g_normal_opacity = (const float4 *) a->grad_normal_opacity;
   d.g_means = a->grad_means, d.g_scales = (float2 *) a->grad_scales, d.g_rots = (float4 *) a->grad_rots;
   d.g_opac = a->grad_opac, d.g_shs = a->grad_shs, d.g_sh_rest = d.sh_rest ? a->grad_sh_rest : nullptr;
-  preprocess_backward_kernel<<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
+  if (a->sh_degree > 3) preprocess_backward_kernel<true><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
+  else preprocess_backward_kernel<false><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

@@ -1,8 +1,9 @@
-// Real spherical-harmonic colour, degrees 0..3, forward and adjoint.
+// Real spherical-harmonic colour, forward and adjoint: degrees 0..3 here, 4..7 in the generated fsgs_sh_high.h.
 // Basis and sign convention of the reference (fast_2d_gs/_C/include/spherical_harmonic.h:18-202, 204-677):
 // colour = max(0, 0.5 + sum_k c_k * Y_k(dir)),  dir = normalize(position - camera position).
 #pragma once
 #include "fsgs_common.cuh"
+#include "fsgs_sh_high.h"
 
 namespace fsgs {
 
@@ -66,6 +67,49 @@ __device__ __forceinline__ float3 sh_basis_grad(int k, float x, float y, float z
     case 15: return make_float3(kSH3a * (-3.0f * x2 + 3.0f * y2), kSH3a * 6.0f * x * y, 0);
     default: return make_float3(0, 0, 0);
   }
+}
+
+// Degrees 4..deg of the colour: rgb += sum_k c_k * Y_k, coefficient k at coef + 3 * k.
+__device__ __forceinline__ void sh_high_colour(int deg, float x, float y, float z, const float *coef, float3 &rgb) {
+  float bb[15];
+#define FSGS_SH_BAND(L)                                                                  \
+  if (deg >= L) {                                                                        \
+    fsgs_sh_band##L(x, y, z, bb);                                                        \
+    _Pragma("unroll") for (int m = 0; m < 2 * L + 1; ++m) {                              \
+      const float *c = coef + 3 * (L * L + m);                                           \
+      rgb.x += c[0] * bb[m], rgb.y += c[1] * bb[m], rgb.z += c[2] * bb[m];               \
+    }                                                                                    \
+  }
+  FSGS_SH_BAND(4)
+  FSGS_SH_BAND(5)
+  FSGS_SH_BAND(6)
+  FSGS_SH_BAND(7)
+#undef FSGS_SH_BAND
+}
+
+// Adjoint of the above for degrees 4..deg: writes g_coef[k] = grgb * Y_k (when g_coef is not null) and accumulates
+// (dx, dy, dz) += sum_k (grgb . c_k) dY_k / d(x, y, z).
+__device__ __forceinline__ void sh_high_adjoint(int deg, float x, float y, float z, const float *coef, float *g_coef,
+    float3 grgb, float &dx, float &dy, float &dz) {
+  float bb[15], t[15];
+#define FSGS_SH_BAND(L)                                                                  \
+  if (deg >= L) {                                                                        \
+    fsgs_sh_band##L(x, y, z, bb);                                                        \
+    _Pragma("unroll") for (int m = 0; m < 2 * L + 1; ++m) {                              \
+      const float *c = coef + 3 * (L * L + m);                                           \
+      t[m] = grgb.x * c[0] + grgb.y * c[1] + grgb.z * c[2];                              \
+      if (g_coef) {                                                                      \
+        float *g = g_coef + 3 * (L * L + m);                                             \
+        g[0] = grgb.x * bb[m], g[1] = grgb.y * bb[m], g[2] = grgb.z * bb[m];             \
+      }                                                                                  \
+    }                                                                                    \
+    fsgs_sh_band##L##_adjoint(x, y, z, t, &dx, &dy, &dz);                                \
+  }
+  FSGS_SH_BAND(4)
+  FSGS_SH_BAND(5)
+  FSGS_SH_BAND(6)
+  FSGS_SH_BAND(7)
+#undef FSGS_SH_BAND
 }
 
 }  // namespace fsgs

@@ -203,7 +203,7 @@ def gs_2d_fast_preprocess_forward(W, H, sh_degree, is_opengl, means3D, scales, r
         _check_input(culling, "culling", (P,), torch.bool)
     if trans_precomp is not None:
         _check_input(trans_precomp, "trans_precomp", (P, 3, 3))
-    _need(sh_degree <= 3, "SH degree above 3 is not built")
+    _need(sh_degree <= 7, "SH degree above 7 is not supported (neither by the reference)")
     o = preprocess_launch(W, H, sh_degree, means3D, scales, rotations, opacities, shs, sh_rest, Tw2v, Tv2s, cam_pos,
                           trans_precomp, means2D, culling)
     n_slots = int(o["counters"][0].item()) if P > 0 else 0  # the reference blocks here too (:729)

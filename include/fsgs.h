@@ -34,7 +34,7 @@ typedef enum fsgs_status {
 
 #define FSGS_TILE 16           /* tiles are 16 x 16 pixels (include/gaussian_render.h:27-31) */
 #define FSGS_RECORD_FLOATS 32  /* one packed per-Gaussian render record = 128 bytes */
-#define FSGS_MAX_SH_DEGREE 3
+#define FSGS_MAX_SH_DEGREE 7
 #define FSGS_KNN_MAX_K 16
 
 /* counters[] written by fsgs_preprocess_forward / fsgs_bin_tiles (int64 each) */

@@ -125,6 +125,57 @@ void orc_transmat(int P, const float *means, const float *scales, const float *q
 #define SH_C3D 0.3731763325901154f
 #define SH_C3E 1.4453057213202769f
 
+/* Degrees 4..7 by the general definition the reference states (utils/ops_3d/spherical_harmonics.py:16-67; its CUDA
+ * header tabulates the same functions as polynomials, include/spherical_harmonic.h:81-202): associated Legendre
+ * functions by the upward recurrence, Condon-Shortley phase included, in double precision. */
+#define SH_MAX 64
+
+static double sh_legendre(int l, int m, double x) {
+  double pmm = 1.0;
+  if (m > 0) {
+    const double somx2 = sqrt((1.0 - x) * (1.0 + x));
+    double fact = 1.0;
+    for (int i = 1; i <= m; ++i) {
+      pmm *= -fact * somx2;
+      fact += 2.0;
+    }
+  }
+  if (l == m) return pmm;
+  double pmmp1 = x * (2.0 * m + 1.0) * pmm;
+  if (l == m + 1) return pmmp1;
+  double pll = 0.0;
+  for (int ll = m + 2; ll <= l; ++ll) {
+    pll = ((2.0 * ll - 1.0) * x * pmmp1 - (ll + m - 1.0) * pmm) / (ll - m);
+    pmm = pmmp1;
+    pmmp1 = pll;
+  }
+  return pll;
+}
+
+static double sh_norm(int l, int m) {
+  double f = 1.0; /* (l-m)! / (l+m)! */
+  for (int i = l - m + 1; i <= l + m; ++i) f /= (double) i;
+  return sqrt((2.0 * l + 1.0) * f / (4.0 * 3.14159265358979323846));
+}
+
+/* Y_l^m at the unit vector (x, y, z) */
+static double sh_general(int l, int m, double x, double y, double z) {
+  const double phi = atan2(y, x);
+  const double ct = z > 1.0 ? 1.0 : (z < -1.0 ? -1.0 : z);
+  if (m == 0) return sh_norm(l, 0) * sh_legendre(l, 0, ct);
+  if (m > 0) return 1.4142135623730951 * sh_norm(l, m) * sh_legendre(l, m, ct) * cos(m * phi);
+  return 1.4142135623730951 * sh_norm(l, -m) * sh_legendre(l, -m, ct) * sin(-m * phi);
+}
+
+/* sum over the coefficients of degrees 4..deg of t[k] * Y_k(normalize(p)), for the adjoint by differences */
+static double sh_high_sum(int deg, const float *t, double px, double py, double pz) {
+  const double n = 1.0 / sqrt(px * px + py * py + pz * pz + 1e-12);
+  double acc = 0.0;
+  for (int l = 4; l <= deg; ++l)
+    for (int m = -l; m <= l; ++m) acc += (double) t[l * l + l + m] * sh_general(l, m, px * n, py * n, pz * n);
+  return acc;
+}
+
 static void sh_basis(int deg, float x, float y, float z, float *b) {
   const float x2 = x * x, y2 = y * y, z2 = z * z;
   b[0] = SH_C0;
@@ -148,6 +199,17 @@ static void sh_basis(int deg, float x, float y, float z, float *b) {
     b[13] = SH_C3C * x * (1.0f - 5.0f * z2);
     b[14] = SH_C3E * z * (x2 - y2);
     b[15] = SH_C3A * x * (-x2 + 3.0f * y2);
+  }
+  for (int l = 4; l <= deg; ++l)
+    for (int m = -l; m <= l; ++m) b[l * l + l + m] = (float) sh_general(l, m, x, y, z);
+}
+
+void orc_sh_basis(int n, int deg, const float *dirs, float *out /* [n, (deg+1)^2] */) {
+  const int nb = (deg + 1) * (deg + 1);
+  for (int i = 0; i < n; ++i) {
+    float b[SH_MAX];
+    sh_basis(deg, dirs[3 * i], dirs[3 * i + 1], dirs[3 * i + 2], b);
+    for (int k = 0; k < nb; ++k) out[(size_t) i * nb + k] = b[k];
   }
 }
 
@@ -189,7 +251,7 @@ static void sh_to_rgb(int deg, const float *pos, const float *campos, const floa
   float x = pos[0] - campos[0], y = pos[1] - campos[1], z = pos[2] - campos[2];
   const float n = 1.0f / sqrtf(x * x + y * y + z * z + 1e-12f);
   x *= n, y *= n, z *= n;
-  float b[16];
+  float b[SH_MAX];
   sh_basis(deg, x, y, z, b);
   const int nb = (deg + 1) * (deg + 1);
   float r[3] = {0, 0, 0};
@@ -765,7 +827,7 @@ void orc_preprocess_bwd(int P, int W, int H, int sh_degree, int n_dc, int n_rest
       x *= n, y *= n, z *= n;
       float grgb[3];
       for (int ch = 0; ch < 3; ++ch) grgb[ch] = colors[3 * i + ch] > 0 ? g_colors[3 * i + ch] : 0.0f;
-      float b[16], bx[16], by[16], bz[16];
+      float b[SH_MAX], bx[16], by[16], bz[16], tk[SH_MAX];
       sh_basis(sh_degree, x, y, z, b);
       sh_basis_grad(sh_degree, x, y, z, bx, by, bz);
       const int nb = (sh_degree + 1) * (sh_degree + 1);
@@ -777,12 +839,24 @@ void orc_preprocess_bwd(int P, int W, int H, int sh_degree, int n_dc, int n_rest
         if (gc && !(sh_rest && k > 0 && !g_sh_rest))
           for (int ch = 0; ch < 3; ++ch) gc[ch] = grgb[ch] * b[k];
         const float tdot = grgb[0] * c[0] + grgb[1] * c[1] + grgb[2] * c[2];
-        dx += tdot * bx[k], dy += tdot * by[k], dz += tdot * bz[k];
+        tk[k] = tdot;
+        if (k < 16) dx += tdot * bx[k], dy += tdot * by[k], dz += tdot * bz[k];
       }
       const float t = -(ux * dx + uy * dy + uz * dz) * n * n * n;
       gp[0] += dx * n + t * ux;
       gp[1] += dy * n + t * uy;
       gp[2] += dz * n + t * uz;
+      if (sh_degree > 3) {
+        /* degrees 4..: central differences of the general definition with respect to the position, in double */
+        const double h = 1e-5 / (double) n;
+        const double u[3] = {ux, uy, uz};
+        for (int a = 0; a < 3; ++a) {
+          double up[3] = {u[0], u[1], u[2]}, um[3] = {u[0], u[1], u[2]};
+          up[a] += h, um[a] -= h;
+          gp[a] += (float) ((sh_high_sum(sh_degree, tk, up[0], up[1], up[2]) -
+                             sh_high_sum(sh_degree, tk, um[0], um[1], um[2])) / (2.0 * h));
+        }
+      }
     }
     for (int k = 0; k < 3; ++k) g_means[3 * i + k] = gp[k];
     g_means2D[2 * i + 0] = gT[2] * m[8] * 0.5f * (float) W;

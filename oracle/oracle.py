@@ -71,6 +71,15 @@ def transmat(means, scales, rots, Tw2v, Tv2s):
     return M, n
 
 
+def sh_basis(dirs, degree):
+    """Real SH basis at unit directions [n,3] -> [n, (degree+1)^2], degree <= 7."""
+    dirs = _f(dirs)
+    n, nb = dirs.shape[0], (degree + 1) ** 2
+    out = torch.zeros(n, nb)
+    lib().orc_sh_basis(_ci(n), _ci(degree), _p(dirs), _p(out))
+    return out
+
+
 def preprocess_forward(W, H, sh_degree, means, scales, rots, opac, shs, sh_rest, Tw2v, Tv2s, campos, culling=None,
                        with_bin=True):
     """Returns the reference's nine outputs, then tiles_touched and the number of real (non padding) pairs."""

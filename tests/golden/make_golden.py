@@ -15,6 +15,7 @@ What each fixture pins (paths inside the reference project):
                   :303/:318) incl. SH colours via utils/ops_3d/spherical_harmonics.py:242-302 (+ autograd)
   rasterize.npz   GS_2D_fast_rasterize (python)         renderer/gs_2d_fast_render.py:433-555  (+ autograd)
   cdist_top.npz   cdist_top / cdist_top_backward CPU branch  _C/src/other/cdist_top.cu:57-81,130-150
+  sh_basis_deg7.npz  real SH of degrees 0..7, general definition  utils/ops_3d/spherical_harmonics.py:16-67
 """
 import argparse
 import importlib.abc
@@ -162,6 +163,16 @@ def make_rasterize(R, get_python_function, ops_3d):
         g_means2D=ins[0].grad, g_colors=ins[1].grad, g_normal_opacity=ins[2].grad, g_trans_mat=ins[3].grad)
 
 
+def make_sh_basis():
+    """Real SH of degrees 0..7 at random unit directions by the reference's general definition."""
+    from utils.ops_3d import spherical_harmonics as S
+    g = torch.Generator().manual_seed(41)
+    d = torch.nn.functional.normalize(torch.randn(48, 3, generator=g, dtype=torch.float64), dim=-1)
+    theta, phi = torch.acos(d[:, 2].clamp(-1, 1)), torch.atan2(d[:, 1], d[:, 0])
+    Y = torch.stack([S._SH(l, m, theta, phi) for l in range(8) for m in range(-l, l + 1)], dim=-1)
+    npz("sh_basis_deg7.npz", dirs=d.float(), Y=Y.float())
+
+
 def make_cdist_top():
     ref_dir = os.path.join(ROOT, "oracle", "_ref")
     sys.path.insert(0, ref_dir)
@@ -191,10 +202,16 @@ def make_cdist_top():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--only", default=None, help="\"sh\": regenerate sh_basis_deg7.npz alone")
     args = ap.parse_args()
     torch.set_num_threads(4)
+    if args.only == "sh":
+        import_reference(args.ref)
+        make_sh_basis()
+        return
     make_cdist_top()
     R, get_python_function, ops_3d = import_reference(args.ref)
+    make_sh_basis()
     make_transmat(R, ops_3d)
     make_preprocess(R, ops_3d)
     make_rasterize(R, get_python_function, ops_3d)

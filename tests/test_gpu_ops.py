@@ -479,6 +479,66 @@ def test_preprocess_io_paths(ops, P, deg):
             assert rel_l2(ref_g[k], o[k]) < GRAD_TOL, k
 
 
+@pytest.mark.parametrize("deg", [4, 5, 7])
+def test_preprocess_high_sh_degrees(ops, ref, deg):
+    """SH degrees 4..7: colours and the SH / position gradients against the oracle (general definition by the
+    Legendre recurrence) and, when built, against the reference's kernels."""
+    P, W, H = 4000, 160, 120
+    s, cam = make_scene(P, W, H, seed=31, log_scale_mean=-2.5)
+    nb = (deg + 1) ** 2
+    g = torch.Generator().manual_seed(deg)
+    rest = (torch.randn(P, nb - 1, 3, generator=g) * 0.05).cuda()
+    fwd = ops.gs_2d_fast_preprocess_forward(W, H, deg, False, s["means"], s["scales"], s["rots"], s["opac"],
+                                            s["sh_dc"], rest, cam["Tw2v"], cam["Tv2c"], cam["Tv2s"], cam["campos"],
+                                            None, None, None, True)
+    c = lambda t: cpu(t) if t is not None else None
+    o = orc.preprocess_forward(W, H, deg, c(s["means"]), c(s["scales"]), c(s["rots"]), c(s["opac"]), c(s["sh_dc"]),
+                               c(rest), c(cam["Tw2v"]), c(cam["Tv2s"]), c(cam["campos"]))
+    vis = cpu(fwd[6]) > 0
+    assert int(vis.sum()) > P // 2
+    # degree-7 polynomials in fp32 against the recurrence in double: a few 1e-6 per term
+    err = float((cpu(fwd[1]) - o[1])[vis].abs().max())
+    assert err < 5e-5, f"colour vs oracle {err}"
+    ups = [torch.randn(P, k, generator=g).cuda() for k in (2, 9, 9, 3, 4)]
+    new = lambda *shape: torch.full(shape, float("nan"), device="cuda")
+    gm, gs, gr, go, gdc, grest = new(P, 3), new(P, 2), new(P, 4), new(P, 1), new(P, 1, 3), new(P, nb - 1, 3)
+    ops.gs_2d_fast_preprocess_backward(W, H, deg, False, s["means"], s["scales"], s["rots"], s["opac"], s["sh_dc"],
+                                       rest, cam["Tw2v"], cam["Tv2s"], cam["campos"], fwd[2], fwd[6], fwd[1], fwd[4],
+                                       ups[0].clone(), ups[1], ups[2], None, ups[3], ups[4], gm, gs, gr, go, gdc,
+                                       grest, None, None)
+    ob = orc.preprocess_backward(W, H, deg, c(s["means"]), c(s["scales"]), c(s["rots"]), c(s["sh_dc"]), c(rest),
+                                 c(cam["Tw2v"]), c(cam["Tv2s"]), c(cam["campos"]), c(fwd[2]), c(fwd[6]), c(fwd[1]),
+                                 c(ups[0]), c(ups[1]), c(ups[2]), c(ups[3]), c(ups[4]))
+    assert rel_l2(gm, ob[0]) < GRAD_TOL and rel_l2(gdc, ob[4]) < 1e-5 and rel_l2(grest, ob[5]) < 1e-5
+    # the part of the position gradient that comes through the view direction alone
+    zero = [torch.zeros_like(u) for u in ups]
+    zero[3] = ups[3]
+    gm2 = new(P, 3)
+    ops.gs_2d_fast_preprocess_backward(W, H, deg, False, s["means"], s["scales"], s["rots"], s["opac"], s["sh_dc"],
+                                       rest, cam["Tw2v"], cam["Tv2s"], cam["campos"], fwd[2], fwd[6], fwd[1], fwd[4],
+                                       zero[0].clone(), zero[1], zero[2], None, zero[3], zero[4], gm2, new(P, 2),
+                                       new(P, 4), new(P, 1), new(P, 1, 3), new(P, nb - 1, 3), None, None)
+    ob2 = orc.preprocess_backward(W, H, deg, c(s["means"]), c(s["scales"]), c(s["rots"]), c(s["sh_dc"]), c(rest),
+                                  c(cam["Tw2v"]), c(cam["Tv2s"]), c(cam["campos"]), c(fwd[2]), c(fwd[6]), c(fwd[1]),
+                                  c(zero[0]), c(zero[1]), c(zero[2]), c(zero[3]), c(zero[4]))
+    assert rel_l2(gm2, ob2[0]) < GRAD_TOL
+    if ref is not None:
+        theirs = ref.gs_2d_fast_preprocess_forward(W, H, deg, False, s["means"], s["scales"], s["rots"], s["opac"],
+                                                   s["sh_dc"], rest, cam["Tw2v"], cam["Tv2c"], cam["Tv2s"],
+                                                   cam["campos"], None, None, None, False)
+        torch.cuda.synchronize()
+        err = float((fwd[1] - theirs[1]).abs().max())
+        assert err < 5e-5, f"colour vs reference kernel {err}; oracle vs reference {float((o[1].cuda() - theirs[1]).abs().max())}"
+        rgm, rgs, rgr, rgo = (torch.zeros(P, k, device="cuda") for k in (3, 2, 4, 1))
+        rdc, rrest = torch.zeros(P, 1, 3, device="cuda"), torch.zeros(P, nb - 1, 3, device="cuda")
+        ref.gs_2d_fast_preprocess_backward(W, H, deg, False, s["means"], s["scales"], s["rots"], s["opac"],
+                                           s["sh_dc"], rest, cam["Tw2v"], cam["Tv2s"], cam["campos"], theirs[2],
+                                           theirs[6], theirs[1], theirs[4], zero[0].clone(), zero[1], zero[2], None,
+                                           zero[3], zero[4], rgm, rgs, rgr, rgo, rdc, rrest, None, None)
+        torch.cuda.synchronize()
+        assert rel_l2(gm2, rgm) < GRAD_TOL and rel_l2(grest, rrest) < 1e-5
+
+
 def test_preprocess_forward_golden(ops):
     g = load_golden("preprocess_deg3.npz", "cuda")
     W, H = int(g["W"]), int(g["H"])

@@ -3,6 +3,7 @@ synthetic workloads are reproducible, and the oracle's k-NN / Adam restatements 
 import ctypes
 import os
 import re
+import sys
 
 import pytest
 import torch
@@ -94,3 +95,50 @@ def test_oracle_adam_against_torch():
     p_ref = p0 - 1e-2 * m_ref / (v_ref.sqrt() + 1e-8)
     assert torch.allclose(p[vis], p_ref[vis], rtol=1e-5, atol=1e-6) and torch.equal(p[~vis], p0[~vis])
     assert torch.allclose(m[vis], m_ref[vis], rtol=1e-5, atol=1e-8) and bool((m[~vis] == 0).all())
+
+
+def test_generated_sh_polynomials_match_the_golden_basis_and_their_generator(tmp_path):
+    """csrc/fsgs_sh_high.h (degrees 4..7 as Cartesian polynomials) is plain C: compile it for the host, compare the
+    bands with the reference's general definition (golden fixture) and the adjoint with central differences."""
+    import ctypes
+    import subprocess
+    import numpy as np
+    from util import load_golden
+    csrc = os.path.join(ROOT, "fast-sp-gs_b200", "csrc")
+    src = tmp_path / "sh.c"
+    src.write_text('#include "fsgs_sh_high.h"\n' + "".join(
+        f"void band{l}(float x, float y, float z, float *b) {{ fsgs_sh_band{l}(x, y, z, b); }}\n"
+        f"void adj{l}(float x, float y, float z, const float *t, float *g) "
+        f"{{ fsgs_sh_band{l}_adjoint(x, y, z, t, g, g + 1, g + 2); }}\n" for l in range(4, 8)))
+    so = tmp_path / "sh.so"
+    subprocess.check_call(["gcc", "-O1", "-std=c99", "-ffp-contract=off", "-shared", "-fPIC", "-I", csrc, str(src),
+                           "-o", str(so)])
+    lib = ctypes.CDLL(str(so))
+    g = load_golden("sh_basis_deg7.npz")
+    dirs, Y = g["dirs"].numpy(), g["Y"].numpy()
+    f = ctypes.c_float
+    rng = np.random.default_rng(0)
+    for l in range(4, 8):
+        n = 2 * l + 1
+        band, adj = getattr(lib, f"band{l}"), getattr(lib, f"adj{l}")
+        for i in range(dirs.shape[0]):
+            b = (f * n)()
+            band(f(dirs[i, 0]), f(dirs[i, 1]), f(dirs[i, 2]), b)
+            assert np.abs(np.array(b) - Y[i, l * l:l * l + n]).max() < 2e-6, (l, i)
+        # adjoint = gradient of sum_m t_m Y_l^m, the three variables taken as independent
+        t = rng.standard_normal(n).astype(np.float32)
+        x0 = dirs[0].astype(np.float64)
+
+        def value(p):
+            b = (f * n)()
+            band(f(p[0]), f(p[1]), f(p[2]), b)
+            return float(np.dot(np.array(b, dtype=np.float64), t))
+
+        grad = (f * 3)(0, 0, 0)
+        adj(f(x0[0]), f(x0[1]), f(x0[2]), (f * n)(*t), grad)
+        h = 1e-2
+        fd = [(value(x0 + h * e) - value(x0 - h * e)) / (2 * h) for e in np.eye(3)]
+        assert np.abs(np.array(grad) - np.array(fd)).max() < 2e-2 * max(1.0, np.abs(fd).max()), (l, list(grad), fd)
+    # the committed header is what the generator prints
+    out = subprocess.check_output([sys.executable, os.path.join(csrc, "gen_sh_high.py")], text=True)
+    assert out == open(os.path.join(csrc, "fsgs_sh_high.h")).read()

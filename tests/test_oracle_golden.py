@@ -128,3 +128,10 @@ def test_cdist_top_against_reference_cpu_branch():
     # exact duplicates among the control points: nearest goes to the LAST duplicate, farthest to the first
     near_hits = g["idx_near"][(g["idx_near"] == 5) | (g["idx_near"] == 17) | (g["idx_near"] == 30)]
     assert len(near_hits) > 0 and bool((near_hits == 30).all())
+
+
+def test_sh_basis_matches_reference_definition_up_to_degree_7():
+    g = _load("sh_basis_deg7.npz")
+    for deg in (0, 3, 4, 7):
+        nb = (deg + 1) ** 2
+        assert float((orc.sh_basis(g["dirs"], deg) - g["Y"][:, :nb]).abs().max()) < 1e-6
