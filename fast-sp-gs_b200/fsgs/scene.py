@@ -15,6 +15,31 @@ from .renderer import GS_2D_fast_render, list_capacity
 LRS = dict(xyz=1.6e-4, sh_dc=2.5e-3, sh_rest=1.25e-4, opacity=0.05, scaling=5e-3, rotation=1e-3)
 
 
+def lbs_weights(d2, idx, mode="dist", temperature=1.0, radius=None, weight=None, table=None):
+    """Blend weights [N,K] of each Gaussian's K nearest superpoints from the squared distances ``d2`` [N,K] and
+    indices ``idx`` [N,K] of the k-NN search; the three forms of the reference's ``calc_LBS_weight``
+    (fast_2d_gs/network.py:506-518):
+
+    * ``"dist"``: softmax(-d2 / temperature);
+    * ``"kernel"``: exp(-d2 / (2 r^2)) with the per-superpoint ``radius`` [M], times the per-superpoint ``weight`` [M]
+      when given, plus 1e-7, normalised to sum 1 (the shipped configuration's 'weighted_kernel');
+    * ``"table"``: softmax over the K gathered entries of a learned ``table`` [N,M].
+
+    Plain torch operations on [N,K] tensors, differentiable in ``radius``, ``weight`` and ``table``."""
+    if mode == "dist":
+        return torch.softmax(-d2 / temperature, dim=-1)
+    if mode == "kernel":
+        r = radius[idx]
+        w = torch.exp(-d2 / (2 * r ** 2))
+        if weight is not None:
+            w = w * weight[idx]
+        w = w + 1e-7
+        return w / w.sum(dim=-1, keepdim=True)
+    if mode == "table":
+        return torch.gather(table, dim=1, index=idx).softmax(dim=-1)
+    raise ValueError(f"unknown LBS weighting {mode!r}")
+
+
 class DynamicScene:
     def __init__(self, surfels, centres, K=3, eps=1e-15, device="cuda", lrs=None):
         P = lambda t: torch.nn.Parameter(t.to(device).contiguous())
@@ -43,11 +68,11 @@ class DynamicScene:
         return self.xyz.shape[0]
 
     @torch.no_grad()
-    def refresh_knn(self):
-        """K nearest superpoints of every Gaussian and softmax(-d^2) blend weights."""
+    def refresh_knn(self, mode="dist", **weighting):
+        """K nearest superpoints of every Gaussian and their blend weights (``lbs_weights``; default softmax(-d^2))."""
         d2, idx = ops.knn(self.xyz.detach(), self.centres, self.K)
         self.knn_idx = idx
-        self.knn_w = torch.softmax(-d2, dim=-1).contiguous()
+        self.knn_w = lbs_weights(d2, idx, mode, **weighting).contiguous()
 
     def render(self, cam, size, motion, only_image=False, grad_out=None):
         """``motion``: dict sp_q [M,4] unit quaternions, sp_t [M,3], sp_dr [M,4], sp_ds [M,2] for this time step."""

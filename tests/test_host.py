@@ -142,3 +142,27 @@ def test_generated_sh_polynomials_match_the_golden_basis_and_their_generator(tmp
     # the committed header is what the generator prints
     out = subprocess.check_output([sys.executable, os.path.join(csrc, "gen_sh_high.py")], text=True)
     assert out == open(os.path.join(csrc, "fsgs_sh_high.h")).read()
+
+
+def test_lbs_weight_forms():
+    """The three weightings of the reference's calc_LBS_weight (network.py:506-518), element by element."""
+    import math
+    from fsgs.scene import lbs_weights
+    g = torch.Generator().manual_seed(3)
+    N, K, M = 50, 3, 7
+    d2 = torch.rand(N, K, generator=g)
+    idx = torch.randint(0, M, (N, K), generator=g)
+    radius, weight, table = torch.rand(M, generator=g) + 0.2, torch.rand(M, generator=g), torch.randn(N, M, generator=g)
+    w_dist = lbs_weights(d2, idx, "dist", temperature=0.5)
+    w_kern = lbs_weights(d2, idx, "kernel", radius=radius, weight=weight)
+    w_tab = lbs_weights(d2, idx, "table", table=table)
+    for n in (0, 17, 49):
+        e = [math.exp(-float(d2[n, k]) / 0.5) for k in range(K)]
+        assert all(abs(float(w_dist[n, k]) - e[k] / sum(e)) < 1e-6 for k in range(K))
+        e = [math.exp(-float(d2[n, k]) / (2 * float(radius[idx[n, k]]) ** 2)) * float(weight[idx[n, k]]) + 1e-7
+             for k in range(K)]
+        assert all(abs(float(w_kern[n, k]) - e[k] / sum(e)) < 1e-6 for k in range(K))
+        e = [math.exp(float(table[n, idx[n, k]])) for k in range(K)]
+        assert all(abs(float(w_tab[n, k]) - e[k] / sum(e)) < 1e-6 for k in range(K))
+    with pytest.raises(ValueError):
+        lbs_weights(d2, idx, "nearest")
