@@ -359,6 +359,22 @@ def run_ours(args):
     ms_step_aux = timed(step_aux, args.steps)
     pairs_aux = last_pairs(scene)
 
+    # the step as a trainer runs it: target image in HBM, fused L1 + SSIM loss kernels produce the image gradient
+    target = torch.rand(3, H, W, generator=torch.Generator().manual_seed(400 + rank)).to(dev)
+    scene_l = DynamicScene(wlk["surf"], wlk["centres"], K=wlk["K"], device=dev,
+                           lrs=dict(xyz=lr, sh_dc=lr, sh_rest=lr, opacity=lr, scaling=lr, rotation=lr))
+
+    def step_loss():
+        scene_l.train_step_with_loss(cam, (W, H), motion, target, distributed=distributed)
+
+    for _ in range(3):
+        step_loss()
+    ops.TIMERS = {}
+    ms_step_loss = timed(step_loss, args.steps)
+    loss_kernels = ops.timer_summary()
+    ops.TIMERS = None
+    del scene_l
+
     line = None
     if rank == 0:
         peak, peak_kind = peaks()
@@ -396,6 +412,8 @@ def run_ours(args):
                              "exceeds the 126 MB L2; no explicit flush"},
             "fwd_frames_per_s": world * 1e3 / ms_fwd, "ms_per_fwd_frame": ms_fwd,
             "ms_per_step_with_aux_gradients": ms_step_aux, "pairs_after_aux_phase": pairs_aux,
+            "ms_per_step_with_l1_ssim_loss": ms_step_loss,
+            "loss_kernels_ms": {k: round(v[1], 4) for k, v in sorted(loss_kernels.items()) if k.startswith("ssim")},
             "e2e": {"value": world * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4 + 32},
             "gpu_launches": int(round(launches_per_step * args.steps)),

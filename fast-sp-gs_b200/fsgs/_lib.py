@@ -93,6 +93,9 @@ SYMBOLS = {
     "fsgs_render_forward": (c_int, [POINTER(RenderArgs), _vp]),
     "fsgs_render_backward": (c_int, [POINTER(RenderBwdArgs), _vp]),
     "fsgs_preprocess_backward": (c_int, [POINTER(PreprocessBwdArgs), _vp]),
+    "fsgs_ssim_forward": (c_int, [c_int, c_int, c_int, c_int, c_float, c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_ssim_backward": (c_int, [c_int, c_int, c_int, c_int, c_float, c_float, _vp, _vp, _vp, c_float, c_float,
+                                   _vp, _vp, _vp, _vp, _vp]),
     "fsgs_epilogue_forward": (c_int, [c_int, c_int, c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_epilogue_backward": (c_int, [c_int, c_int, c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
 }

@@ -485,8 +485,45 @@ def knn(x, c, K):
     return d2, idx
 
 
-# the nine names the reference looks up with get_C_function(...) (fast_2d_gs/_C/__init__.py:41-42)
+def _ssim_check(img1, img2):
+    _need(img1.dim() == 4 and img1.shape == img2.shape, "fusedssim: images must be [B,C,H,W] of equal shape")
+    for t, n in ((img1, "img1"), (img2, "img2")):
+        _need(t.is_cuda and t.dtype == torch.float32, f"{n} must be a float32 CUDA tensor")
+
+
+def fusedssim(C1, C2, img1, img2, train=True):
+    """``fusedssim`` (src/other/structural_similarity.cu:340-361) -> ``(ssim_map, dm_dmu1, dm_dsigma1_sq,
+    dm_dsigma12)``; the three derivative maps are empty tensors when ``train`` is false."""
+    _ssim_check(img1, img2)
+    img1, img2 = img1.contiguous(), img2.contiguous()
+    B, C, H, W = img1.shape
+    ssim_map = torch.empty_like(img1)
+    d = [torch.empty_like(img1) for _ in range(3)] if train else [None] * 3
+    with _timed("ssim_forward"):
+        check(lib().fsgs_ssim_forward(B, C, H, W, float(C1), float(C2), _ptr(img1), _ptr(img2), _ptr(ssim_map),
+                                      _ptr(d[0]), _ptr(d[1]), _ptr(d[2]), None, _stream()), "fsgs_ssim_forward")
+    if not train:
+        d = [torch.empty(0) for _ in range(3)]
+    return ssim_map, d[0], d[1], d[2]
+
+
+def fusedssim_backward(C1, C2, img1, img2, dL_dmap, dm_dmu1, dm_dsigma1_sq, dm_dsigma12):
+    """``fusedssim_backward`` (structural_similarity.cu:363-381) -> ``dL_dimg1``."""
+    _ssim_check(img1, img2)
+    img1, img2, dL_dmap = img1.contiguous(), img2.contiguous(), dL_dmap.contiguous()
+    _need(dL_dmap.shape == img1.shape and dm_dmu1.shape == img1.shape, "fusedssim_backward: shape mismatch")
+    B, C, H, W = img1.shape
+    out = torch.empty_like(img1)
+    with _timed("ssim_backward"):
+        check(lib().fsgs_ssim_backward(B, C, H, W, float(C1), float(C2), _ptr(img1), _ptr(img2), _ptr(dL_dmap), 0.0,
+                                       0.0, _ptr(dm_dmu1.contiguous()), _ptr(dm_dsigma1_sq.contiguous()),
+                                       _ptr(dm_dsigma12.contiguous()), _ptr(out), _stream()), "fsgs_ssim_backward")
+    return out
+
+
+# the names the reference looks up with get_C_function(...) (fast_2d_gs/_C/__init__.py:41-42): the nine operators
+# of the rendering path and the two of the SSIM loss
 REFERENCE_OPS = {f.__name__: _Op(f) for f in (
     gs_2d_fast_preprocess_forward, gs_2d_fast_preprocess_backward, GS_2D_fast_render_forward,
     GS_2D_fast_render_backward, gs_2d_fast_compute_transmat_forward, gs_2d_fast_compute_trans_mat_backward,
-    cdist_top, cdist_top_backward, AdamMasksedUpdated)}
+    cdist_top, cdist_top_backward, AdamMasksedUpdated, fusedssim, fusedssim_backward)}

@@ -139,7 +139,26 @@ class DynamicScene:
         self.optimizer.zero_grad(set_to_none=True)
         return out
 
+    def train_step_with_loss(self, cam, size, motion, target, lambda_l1=0.8, lambda_ssim=0.2, group=None,
+                             distributed=False):
+        """One iteration against a target image [3,H,W]: forward, fused L1 + SSIM loss and its image gradient
+        (``fsgs.loss``), backward, optimiser.  Returns (render dictionary, loss as a device scalar)."""
+        from .loss import l1_ssim_value_and_grad
+        holder = {}
+
+        def upstream(out):
+            holder["loss"], g = l1_ssim_value_and_grad(out["images"], target, lambda_l1, lambda_ssim)
+            return g
+
+        out = self.train_step(cam, size, motion, upstream, None, group=group, distributed=distributed)
+        return out, holder["loss"]
+
     def _backward(self, out, g_images, g_opacity, g_aux):
+        if callable(g_images):  # the upstream image gradient is a function of the rendered result (a loss)
+            g_images = g_images(out)
+        if g_opacity is None:
+            torch.autograd.backward([out["images"]], [g_images])
+            return
         heads, grads = [out["images"], out["opacity"]], [g_images, g_opacity]
         for name, g in (g_aux or {}).items():
             heads.append(out[name])

@@ -266,6 +266,23 @@ typedef struct fsgs_render_bwd_args {
 int fsgs_render_backward(const fsgs_render_bwd_args *args /* host */, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Structural similarity, 11x11 Gaussian window (sigma 1.5, zero padding), forward and adjoint.
+ * Replaces fusedssim / fusedssim_backward   (src/other/structural_similarity.cu:340-381; callers
+ * fast_2d_gs/losses/ssim.py:24-45; the map is that of _ssim, ssim.py:48-67).
+ * Images are [B,C,H,W] contiguous.  Forward: ssim_map and, when the three dm_* pointers are given, the
+ * partial derivatives of the map with respect to mu1, w*x^2 and w*xy.  `sums` (optional, [2], zeroed by
+ * the caller) receives the sum of the map and the sum of |img1 - img2| (for mean reductions without
+ * another pass).  Backward: dL_dimg1 from dL_dmap, or from the constant dL_dmap_uniform when dL_dmap is
+ * NULL; l1_weight * sign(img1 - img2) is added (0 to leave it out).  B*C <= 65535.
+ * ---------------------------------------------------------------------------------------------- */
+int fsgs_ssim_forward(int B, int C, int H, int W, float C1, float C2, const float *img1, const float *img2,
+                      float *ssim_map, float *dm_dmu1, float *dm_dsigma1_sq, float *dm_dsigma12, float *sums,
+                      fsgs_stream_t stream);
+int fsgs_ssim_backward(int B, int C, int H, int W, float C1, float C2, const float *img1, const float *img2,
+                       const float *dL_dmap, float dL_dmap_uniform, float l1_weight, const float *dm_dmu1,
+                       const float *dm_dsigma1_sq, const float *dm_dsigma12, float *dL_dimg1, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Preprocess backward.
  * Replaces gs_2d_fast_preprocess_backward   (gs_2d_fast_preprocess.cu:536-609, 784-859).
  * grad_means2D is consumed and then overwritten with the densification proxy, as in the reference.

@@ -12,6 +12,7 @@ reference's own optimisation level (``-O3``, ``fast_2d_gs/_C/setup.py:36-41``):
   src/gaussian_splatting/gaussian_prepare.cu        getHigherMsb (host helper the preprocess TU links to)
   src/other/cdist_top.cu                            top-1 neighbour (CUDA + CPU branch)
   src/other/adam_masked_update.cu                   masked Adam
+  src/other/structural_similarity.cu                fused SSIM forward / backward
 
 The reference passes ``-rdc=true`` without a device-link step, which makes the
 stock extension un-importable; no TU above calls a device function of another
@@ -38,6 +39,7 @@ UNITS = [
     "src/gaussian_splatting/gaussian_prepare.cu",
     "src/other/cdist_top.cu",
     "src/other/adam_masked_update.cu",
+    "src/other/structural_similarity.cu",
 ]
 
 

@@ -967,3 +967,83 @@ void orc_adam(float *param, const float *grad, float *exp_avg, float *exp_avg_sq
     }
   }
 }
+
+/* ------------------------------------------------------------------------- */
+/* SSIM map and its adjoint: fast_2d_gs/losses/ssim.py:12-22 (window), 48-67   */
+/* (_ssim: five zero-padded 11x11 convolutions); derivative maps and adjoint   */
+/* as bound by FusedSSIM (ssim.py:24-45; src/other/structural_similarity.cu)   */
+/* ------------------------------------------------------------------------- */
+
+static void ssim_window(float *w2 /* [11*11] */) {
+  float g[11], sum = 0.0f;
+  for (int i = 0; i < 11; ++i) {
+    g[i] = (float) exp(-(double) ((i - 5) * (i - 5)) / (2.0 * 1.5 * 1.5));
+    sum += g[i];
+  }
+  for (int i = 0; i < 11; ++i) g[i] /= sum;
+  for (int i = 0; i < 11; ++i)
+    for (int j = 0; j < 11; ++j) w2[i * 11 + j] = g[i] * g[j];
+}
+
+/* images [planes, H, W]; outputs the map and d map / d(mu1, w*x^2, w*xy) */
+void orc_ssim_forward(int planes, int H, int W, float C1, float C2, const float *x, const float *y, float *map,
+    float *d_mu1, float *d_s11, float *d_s12) {
+  float w2[121];
+  ssim_window(w2);
+#pragma omp parallel for schedule(static)
+  for (int p = 0; p < planes * H; ++p) {
+    const int pl = p / H, r = p % H;
+    const float *xp = x + (size_t) pl * H * W, *yp = y + (size_t) pl * H * W;
+    for (int c = 0; c < W; ++c) {
+      float mu1 = 0, mu2 = 0, q11 = 0, q22 = 0, q12 = 0;
+      for (int i = 0; i < 11; ++i) {
+        const int rr = r + i - 5;
+        if (rr < 0 || rr >= H) continue;
+        for (int j = 0; j < 11; ++j) {
+          const int cc = c + j - 5;
+          if (cc < 0 || cc >= W) continue;
+          const float w = w2[i * 11 + j], u = xp[(size_t) rr * W + cc], v = yp[(size_t) rr * W + cc];
+          mu1 += w * u, mu2 += w * v, q11 += w * (u * u), q22 += w * (v * v), q12 += w * (u * v);
+        }
+      }
+      const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2, mu12 = mu1 * mu2;
+      const float s11 = q11 - mu1_sq, s22 = q22 - mu2_sq, s12 = q12 - mu12;
+      const float A = mu1_sq + mu2_sq + C1, B = s11 + s22 + C2, Cn = 2 * mu12 + C1, D = 2 * s12 + C2;
+      const size_t o = (size_t) pl * H * W + (size_t) r * W + c;
+      map[o] = (Cn * D) / (A * B);
+      if (d_mu1) {
+        d_mu1[o] = 2 * mu2 * (D - Cn) / (A * B) - 2 * mu1 * Cn * D / (A * A * B) + 2 * mu1 * Cn * D / (A * B * B);
+        d_s11[o] = -Cn * D / (A * B * B);
+        d_s12[o] = 2 * Cn / (A * B);
+      }
+    }
+  }
+}
+
+/* dL/dx = w * (g d_mu1) + 2 x (w * (g d_s11)) + y (w * (g d_s12)) */
+void orc_ssim_backward(int planes, int H, int W, const float *x, const float *y, const float *g_map,
+    const float *d_mu1, const float *d_s11, const float *d_s12, float *g_x) {
+  float w2[121];
+  ssim_window(w2);
+#pragma omp parallel for schedule(static)
+  for (int p = 0; p < planes * H; ++p) {
+    const int pl = p / H, r = p % H;
+    const size_t base = (size_t) pl * H * W;
+    for (int c = 0; c < W; ++c) {
+      float t0 = 0, t1 = 0, t2 = 0;
+      for (int i = 0; i < 11; ++i) {
+        const int rr = r + i - 5;
+        if (rr < 0 || rr >= H) continue;
+        for (int j = 0; j < 11; ++j) {
+          const int cc = c + j - 5;
+          if (cc < 0 || cc >= W) continue;
+          const size_t q = base + (size_t) rr * W + cc;
+          const float w = w2[i * 11 + j] * g_map[q];
+          t0 += w * d_mu1[q], t1 += w * d_s11[q], t2 += w * d_s12[q];
+        }
+      }
+      const size_t o = base + (size_t) r * W + c;
+      g_x[o] = t0 + 2 * x[o] * t1 + y[o] * t2;
+    }
+  }
+}

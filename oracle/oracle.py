@@ -255,3 +255,34 @@ def lbs_warp(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, 
     scales = torch.exp(scaling_raw) + d_scale
     rots = torch.nn.functional.normalize(rotation_raw + d_rot, dim=-1)
     return means, scales, rots
+
+
+def ssim_forward(img1, img2, C1=0.01 ** 2, C2=0.03 ** 2):
+    """[..., H, W] images -> (ssim_map, dm_dmu1, dm_dsigma1_sq, dm_dsigma12), 11x11 Gaussian window, zero padding."""
+    x, y = _f(img1), _f(img2)
+    H, W = x.shape[-2:]
+    planes = x.numel() // (H * W)
+    outs = [torch.zeros_like(x) for _ in range(4)]
+    lib().orc_ssim_forward(_ci(planes), _ci(H), _ci(W), ctypes.c_float(C1), ctypes.c_float(C2), _p(x), _p(y),
+                           _p(outs[0]), _p(outs[1]), _p(outs[2]), _p(outs[3]))
+    return tuple(outs)
+
+
+def ssim_backward(img1, img2, g_map, d_mu1, d_s11, d_s12):
+    x, y = _f(img1), _f(img2)
+    H, W = x.shape[-2:]
+    planes = x.numel() // (H * W)
+    out = torch.zeros_like(x)
+    lib().orc_ssim_backward(_ci(planes), _ci(H), _ci(W), _p(x), _p(y), _p(_f(g_map)), _p(_f(d_mu1)), _p(_f(d_s11)),
+                            _p(_f(d_s12)), _p(out))
+    return out
+
+
+def l1_ssim_loss(image, target, lambda_l1=0.8, lambda_ssim=0.2):
+    """-> (loss, dL/dimage) of lambda_l1 * mean|image - target| + lambda_ssim * (1 - mean ssim)."""
+    m, d1, d2, d3 = ssim_forward(image, target)
+    n = image.numel()
+    loss = lambda_l1 * (image - target).abs().mean() + lambda_ssim * (1 - m.mean())
+    g = ssim_backward(image, target, torch.full_like(m, -lambda_ssim / n), d1, d2, d3)
+    g = g + lambda_l1 / n * torch.sign(image - target)
+    return loss, g

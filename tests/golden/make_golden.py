@@ -16,6 +16,7 @@ What each fixture pins (paths inside the reference project):
   rasterize.npz   GS_2D_fast_rasterize (python)         renderer/gs_2d_fast_render.py:433-555  (+ autograd)
   cdist_top.npz   cdist_top / cdist_top_backward CPU branch  _C/src/other/cdist_top.cu:57-81,130-150
   sh_basis_deg7.npz  real SH of degrees 0..7, general definition  utils/ops_3d/spherical_harmonics.py:16-67
+  ssim.npz        _ssim (python, five padded convolutions)  fast_2d_gs/losses/ssim.py:48-67  (+ autograd)
 """
 import argparse
 import importlib.abc
@@ -173,6 +174,20 @@ def make_sh_basis():
     npz("sh_basis_deg7.npz", dirs=d.float(), Y=Y.float())
 
 
+def make_ssim(get_python_function):
+    """SSIM map of the reference's python ``_ssim`` (losses/ssim.py:48-67) and its autograd gradient."""
+    from fast_2d_gs.losses import ssim as S
+    g = torch.Generator().manual_seed(51)
+    a = torch.rand(2, 3, 37, 45, generator=g)
+    b = (a + 0.2 * torch.randn(2, 3, 37, 45, generator=g)).clamp(0, 1)
+    a.requires_grad_()
+    window = S.create_window(11, 3)
+    m = S._ssim(a, b, window)  # the python twin: the compiled operators are absent in this container
+    up = torch.randn(m.shape, generator=g)
+    m.backward(up)
+    npz("ssim.npz", img1=a, img2=b, ssim_map=m, up=up, g_img1=a.grad)
+
+
 def make_cdist_top():
     ref_dir = os.path.join(ROOT, "oracle", "_ref")
     sys.path.insert(0, ref_dir)
@@ -202,12 +217,15 @@ def make_cdist_top():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
-    ap.add_argument("--only", default=None, help="\"sh\": regenerate sh_basis_deg7.npz alone")
+    ap.add_argument("--only", default=None, help="\"sh\" / \"ssim\": regenerate that fixture alone")
     args = ap.parse_args()
     torch.set_num_threads(4)
     if args.only == "sh":
         import_reference(args.ref)
         make_sh_basis()
+        return
+    if args.only == "ssim":
+        make_ssim(import_reference(args.ref)[1])
         return
     make_cdist_top()
     R, get_python_function, ops_3d = import_reference(args.ref)
@@ -215,6 +233,7 @@ def main():
     make_transmat(R, ops_3d)
     make_preprocess(R, ops_3d)
     make_rasterize(R, get_python_function, ops_3d)
+    make_ssim(get_python_function)
 
 
 if __name__ == "__main__":

@@ -133,12 +133,13 @@ def test_sparse_adam_fused_equals_per_tensor():
     assert opt.state[params[0]]["step"].item() == 3.0
 
 
-def test_install_exposes_the_nine_operator_names():
+def test_install_exposes_the_reference_operator_names():
     import fsgs
     mod = fsgs.install("fast_2d_gs_test._C._C")
     names = ["gs_2d_fast_preprocess_forward", "gs_2d_fast_preprocess_backward", "GS_2D_fast_render_forward",
              "GS_2D_fast_render_backward", "gs_2d_fast_compute_transmat_forward",
-             "gs_2d_fast_compute_trans_mat_backward", "cdist_top", "cdist_top_backward", "AdamMasksedUpdated"]
+             "gs_2d_fast_compute_trans_mat_backward", "cdist_top", "cdist_top_backward", "AdamMasksedUpdated",
+             "fusedssim", "fusedssim_backward"]
     assert all(callable(getattr(mod, n)) for n in names)
     assert sys.modules["fast_2d_gs_test._C._C"] is mod
 

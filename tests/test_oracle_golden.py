@@ -135,3 +135,11 @@ def test_sh_basis_matches_reference_definition_up_to_degree_7():
     for deg in (0, 3, 4, 7):
         nb = (deg + 1) ** 2
         assert float((orc.sh_basis(g["dirs"], deg) - g["Y"][:, :nb]).abs().max()) < 1e-6
+
+
+def test_ssim_map_and_adjoint_against_reference_python():
+    g = _load("ssim.npz")
+    m, d1, d2, d3 = orc.ssim_forward(g["img1"], g["img2"])
+    assert float((m - g["ssim_map"]).abs().max()) < 1e-5
+    gx = orc.ssim_backward(g["img1"], g["img2"], g["up"], d1, d2, d3)
+    assert _rel_l2(gx, g["g_img1"]) < 1e-5
