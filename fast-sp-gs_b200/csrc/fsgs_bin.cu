@@ -13,10 +13,11 @@ namespace fsgs {
 constexpr int kOrderBins = 4096;     // tile_order buckets: list length >> 4, saturating
 constexpr int kSortSmall = 4096;     // keys sorted in static shared memory
 constexpr int kSortLarge = 16384;    // keys sorted in opt-in dynamic shared memory
+constexpr int kCursorStride = 32;    // ints between the slot cursors of consecutive tiles: one 128-byte line each
 
 struct BinWorkspace {
   unsigned long long *keys;  // [capacity]
-  int32_t *cursors;          // [T]
+  int32_t *cursors;          // [T * kCursorStride]
   long long *starts;         // [T]
   int32_t *eff_counts;       // [T]
 };
@@ -29,7 +30,7 @@ static BinWorkspace carve(void *ws, int T, int64_t capacity) {
   w.keys = (unsigned long long *) p;
   p += align_up(sizeof(unsigned long long) * (size_t) (capacity > 0 ? capacity : 1));
   w.cursors = (int32_t *) p;
-  p += align_up(sizeof(int32_t) * (size_t) T);
+  p += align_up(sizeof(int32_t) * (size_t) T * kCursorStride);
   w.starts = (long long *) p;
   p += align_up(sizeof(long long) * (size_t) T);
   w.eff_counts = (int32_t *) p;
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(1024) tile_scan_kernel(int T, const int32_t *_
     dropped += c - eff;
     starts[t] = s_clip;
     eff_counts[t] = eff;
-    cursors[t] = 0;
+    cursors[(size_t) t * kCursorStride] = 0;
     ranges[2 * t] = eff > 0 ? s_clip : 0;
     ranges[2 * t + 1] = eff > 0 ? e_clip : 0;
     atomicAdd(&s_hist[min(eff >> 4, kOrderBins - 1)], 1);
@@ -122,24 +123,36 @@ __global__ void __launch_bounds__(256) emit_pairs_kernel(int P, int gx, int gy, 
     int32_t *__restrict__ cursors, unsigned long long *__restrict__ keys, int32_t *__restrict__ point_list,
     long long capacity, const unsigned long long *__restrict__ counters) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  bool has = false;
+  int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
+  Conic cn = {};
+  unsigned long long key = 0;
   if (i < P) {
     const int r = radii[i];
     if (r > 0) {
-      int x0, y0, x1, y1;
       const float2 c = means2D[i];
       tile_rect(c.x, c.y, r, gx, gy, x0, y0, x1, y1);
       float IM[9];
 #pragma unroll
       for (int k = 0; k < 9; ++k) IM[k] = inverse_m[(size_t) 9 * i + k];
-      const Conic cn = make_conic(IM, opac[i]);
-      const unsigned long long key = ((unsigned long long) __float_as_uint(depths[i]) << 32) | (unsigned int) i;
-      for_each_covered_tile(cn, x0, y0, x1, y1, [&](int x, int y) {
-        const int t = y * gx + x;
-        const int slot = atomicAdd(cursors + t, 1);
-        if (slot < eff_counts[t]) keys[starts[t] + slot] = key;
-      });
+      cn = make_conic(IM, opac[i]);
+      key = ((unsigned long long) __float_as_uint(depths[i]) << 32) | (unsigned int) i;
+      has = true;
     }
   }
+  // the warp walks the tiles of its 32 splats together; a slot claimed in one round is filled in the next, so the
+  // atomic's round trip overlaps the next round's corner tests
+  long long pend_at = -1;
+  unsigned long long pend_key = 0;
+  warp_for_each_covered_tile(cn, x0, y0, x1, y1, has, (unsigned) (key >> 32), (unsigned) key,
+      [&](int x, int y, unsigned k_hi, unsigned k_lo) {
+        if (pend_at >= 0) keys[pend_at] = pend_key;
+        const int t = y * gx + x;
+        const int slot = atomicAdd(cursors + (size_t) t * kCursorStride, 1);
+        pend_at = slot < eff_counts[t] ? starts[t] + slot : -1;
+        pend_key = ((unsigned long long) k_hi << 32) | k_lo;
+      });
+  if (pend_at >= 0) keys[pend_at] = pend_key;
   // padding entries of the reference's list: point_list[R* .. min(R, capacity)) = -1
   const long long n_pairs = (long long) counters[FSGS_CNT_PAIRS];
   const long long n_slots = (long long) counters[FSGS_CNT_SLOTS];
@@ -157,6 +170,9 @@ __device__ __forceinline__ void smem_bitonic(unsigned long long *s, int n, const
   while (np2 < n) np2 <<= 1;
   for (int k = threadIdx.x; k < np2; k += blockDim.x) s[k] = k < n ? src[k] : ~0ull;
   __syncthreads();
+  // Comparator t of a step with stride j works on elements i and i + j of the 2j-block that holds i; for j <= 32 the
+  // 32 comparators of a warp stay inside 64 consecutive elements that no other warp touches, whatever j is, so runs
+  // of such steps need only a warp barrier.  A block barrier is paid only around steps with j >= 64 (and at the end).
   for (int k = 2; k <= np2; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
       for (int t = threadIdx.x; t < (np2 >> 1); t += blockDim.x) {
@@ -166,7 +182,9 @@ __device__ __forceinline__ void smem_bitonic(unsigned long long *s, int n, const
         const bool asc = (i & k) == 0;
         if ((a > b) == asc) s[i] = b, s[l] = a;
       }
-      __syncthreads();
+      const int next_j = j > 1 ? (j >> 1) : k;  // first stride of the next stage is k
+      if (j > 32 || next_j > 32 || (j == 1 && k == np2)) __syncthreads();
+      else __syncwarp();
     }
   }
   for (int k = threadIdx.x; k < n; k += blockDim.x) dst[k] = (int32_t) (unsigned int) (s[k] & 0xffffffffull);
@@ -217,7 +235,7 @@ using namespace fsgs;
 extern "C" size_t fsgs_bin_workspace_bytes(int W, int H, int64_t capacity) {
   const int T = ((W + kTile - 1) / kTile) * ((H + kTile - 1) / kTile);
   return align_up(sizeof(unsigned long long) * (size_t) (capacity > 0 ? capacity : 1)) +
-         align_up(sizeof(int32_t) * (size_t) T) + align_up(sizeof(long long) * (size_t) T) +
+         align_up(sizeof(int32_t) * (size_t) T * kCursorStride) + align_up(sizeof(long long) * (size_t) T) +
          align_up(sizeof(int32_t) * (size_t) T);
 }
 
@@ -260,7 +278,8 @@ extern "C" int fsgs_bin_tiles(const fsgs_bin_args *a, fsgs_stream_t stream) {
 
 namespace fsgs {
 constexpr size_t kNoallocKeysBytes = sizeof(unsigned long long) * (size_t) FSGS_NOALLOC_MAX_PAIRS;
-constexpr size_t kNoallocTileBytes = (sizeof(int32_t) + sizeof(long long) + sizeof(int32_t)) * (size_t) FSGS_NOALLOC_MAX_TILES;
+constexpr size_t kNoallocTileBytes =
+    (sizeof(int32_t) * kCursorStride + sizeof(long long) + sizeof(int32_t)) * (size_t) FSGS_NOALLOC_MAX_TILES;
 constexpr size_t kNoallocBytes = kNoallocKeysBytes + kNoallocTileBytes + 3 * 256;
 // Held by every device that loads the library.  In host code this name is only a handle: the device address
 // comes from cudaGetSymbolAddress, once per device.
@@ -290,7 +309,7 @@ extern "C" int fsgs_bin_tiles_noalloc(const fsgs_bin_args *a, fsgs_stream_t stre
   w.keys = (unsigned long long *) p;
   p += align_up(kNoallocKeysBytes);
   w.cursors = (int32_t *) p;
-  p += align_up(sizeof(int32_t) * (size_t) FSGS_NOALLOC_MAX_TILES);
+  p += align_up(sizeof(int32_t) * (size_t) FSGS_NOALLOC_MAX_TILES * kCursorStride);
   w.starts = (long long *) p;
   p += align_up(sizeof(long long) * (size_t) FSGS_NOALLOC_MAX_TILES);
   w.eff_counts = (int32_t *) p;

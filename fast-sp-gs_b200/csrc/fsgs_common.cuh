@@ -205,6 +205,55 @@ __device__ __forceinline__ void for_each_covered_tile(const Conic &c, int x0, in
   }
 }
 
+// The same enumeration for the 32 splats held by the lanes of a warp, with the work spread evenly: the tiles of all
+// 32 rectangles are numbered consecutively (prefix sum of the areas) and handed out 32 per round, so that every lane
+// tests one tile per round whatever the shapes of the individual rectangles (one thread walking its own rectangle
+// leaves three quarters of the warp idle: rectangle areas range from 1 to over 100).  Lane L passes its conic and
+// rectangle (`has` false: none) and two payload words; f(tile_x, tile_y, payload0, payload1) runs on the lane that
+// tested the tile, with the payload of the splat the tile belongs to.  The corner test is Conic::inside on the same
+// values as above, so the set of (splat, tile) pairs is identical.  Must be called by all 32 lanes.
+template <typename F>
+__device__ __forceinline__ void warp_for_each_covered_tile(const Conic &c, int x0, int y0, int x1, int y1, bool has,
+    unsigned p0, unsigned p1, F f) {
+  const unsigned full = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  const int w = has ? x1 - x0 : 0, h = has ? y1 - y0 : 0;
+  const int area = w * h;
+  int incl = area;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(full, incl, o);
+    if (lane >= o) incl += n;
+  }
+  const int excl = incl - area;
+  const int total = __shfl_sync(full, incl, 31);
+  for (int base = 0; base < total; base += 32) {
+    const bool valid = base + lane < total;
+    const int item = valid ? base + lane : total - 1;
+    int s = 0;  // first lane whose inclusive prefix exceeds item
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1) {
+      const int v = __shfl_sync(full, incl, s + step - 1);
+      if (v <= item) s += step;
+    }
+    const int local = item - __shfl_sync(full, excl, s);
+    const int sw = __shfl_sync(full, w, s);
+    const int sx0 = __shfl_sync(full, x0, s), sy0 = __shfl_sync(full, y0, s);
+    Conic cs;
+    cs.xx = __shfl_sync(full, c.xx, s), cs.yy = __shfl_sync(full, c.yy, s), cs.xy = __shfl_sync(full, c.xy, s);
+    cs.x_ = __shfl_sync(full, c.x_, s), cs.y_ = __shfl_sync(full, c.y_, s), cs.__ = __shfl_sync(full, c.__, s);
+    const unsigned q0 = __shfl_sync(full, p0, s), q1 = __shfl_sync(full, p1, s);
+    const int ly = local / sw, lx = local - ly * sw;
+    const int tx = sx0 + lx, ty = sy0 + ly;
+    bool covered = false;
+    if (valid) {
+      const float u0 = (float) tx, u1 = (float) (tx + 1), v0 = (float) ty, v1 = (float) (ty + 1);
+      covered = cs.inside(u0, v0) || cs.inside(u1, v0) || cs.inside(u0, v1) || cs.inside(u1, v1);
+    }
+    if (covered) f(tx, ty, q0, q1);
+  }
+}
+
 // Conservative pixel box of {alpha >= 1/255} for one splat: the projected disc u^2+v^2 <= tau plus the
 // low-pass disc around the 3-sigma box centre, padded against rounding.  An empty box (xmin > xmax)
 // means the splat can never pass the alpha cut; an infinite box means "cannot bound" (the disc crosses

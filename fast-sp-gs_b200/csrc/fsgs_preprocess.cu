@@ -289,6 +289,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
   float2 ctr = make_float2(0, 0);
   float vz = 0, opacity = 0, radius = 0;
   int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
+  Conic cn = {};
   if (i < a.P) {
     if (LBS) lbs_warp_one(lbs, i, p, s, q);
     else p = make_float3(a.means[3 * i], a.means[3 * i + 1], a.means[3 * i + 2]);
@@ -324,14 +325,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
     if (vis) {
       adjugate(M, IM);
       area = (y1 - y0) * (x1 - x0);
-      // count (and histogram) the tiles with a corner inside the alpha >= 1/255 conic
-      const Conic cn = make_conic(IM, opacity);
-      const int gx = a.gx;
-      int32_t *tc = a.tile_counts;
-      for_each_covered_tile(cn, x0, y0, x1, y1, [&](int x, int y) {
-        atomicAdd(tc + y * gx + x, 1);
-        ++real;
-      });
+      cn = make_conic(IM, opacity);
     } else {
 #pragma unroll
       for (int k = 0; k < 9; ++k) M[k] = 0.0f, IM[k] = 0.0f;
@@ -339,6 +333,16 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
       ctr = make_float2(0, 0);
       vz = 0, opacity = 0, radius = 0;
     }
+  }
+
+  // count (and histogram) the tiles with a corner inside the alpha >= 1/255 conic, the warp's 32 splats together
+  {
+    const int gx = a.gx;
+    int32_t *tc = a.tile_counts;
+    warp_for_each_covered_tile(cn, x0, y0, x1, y1, vis, 0u, 0u, [&](int x, int y, unsigned, unsigned) {
+      atomicAdd(tc + y * gx + x, 1);
+      ++real;
+    });
   }
 
   // the SH slice must have landed before the colours are evaluated

