@@ -78,6 +78,56 @@ __device__ __forceinline__ void issue_stage(const float4 *__restrict__ records, 
   }
 }
 
+// Can the splat of this record reach alpha >= 1/255 on any pixel of the rectangle [bx0,bx1] x [by0,by1]?
+// Conservative (never false when some pixel passes), much tighter than the box for elongated, slanted footprints.
+//   alpha >= 1/255  <=>  min(rho3d, rho2d) <= tau  (tau' padded), with
+//   rho2d = 2 |x - centre|^2  -> distance from the centre to the rectangle;
+//   rho3d = (p0^2 + p1^2) / p2^2, p = IM (x, y, 1)  ->  Q(x, y) = p0^2 + p1^2 - tau' p2^2 <= 0, a quadratic whose
+//   minimum over the rectangle is at its unconstrained minimiser if that lies inside, else on one of the four edges.
+// If Q is not convex (the splat's disc crosses the camera plane) the answer is "maybe".  A tolerance proportional to
+// the cancelling terms covers rounding.
+__device__ __forceinline__ bool subtile_may_hit(const float4 q0, const float4 q1, const float4 q2, const float4 q3,
+    float bx0, float bx1, float by0, float by1) {
+  const float tau = q0.w;
+  if (!(tau > 0.0f)) return false;
+  // low-pass disc
+  const float ddx = fmaxf(fmaxf(bx0 - q0.x, q0.x - bx1), 0.0f), ddy = fmaxf(fmaxf(by0 - q0.y, q0.y - by1), 0.0f);
+  if (2.0f * (ddx * ddx + ddy * ddy) <= tau) return true;
+  const float xc = 0.5f * (bx0 + bx1), yc = 0.5f * (by0 + by1);
+  const float hx = 0.5f * (bx1 - bx0) + 0.01f, hy = 0.5f * (by1 - by0) + 0.01f;
+  const float a0 = q1.x, b0 = q1.y, a1 = q1.w, b1 = q2.x, a2 = q2.z, b2 = q2.w;
+  const float P0 = a0 * xc + b0 * yc + q1.z, P1 = a1 * xc + b1 * yc + q2.y, P2 = a2 * xc + b2 * yc + q3.x;
+  const float tP2 = tau * P2, ta2 = tau * a2, tb2 = tau * b2;
+  const float Q0 = P0 * P0 + P1 * P1 - tP2 * P2;
+  const float gx = 2.0f * (P0 * a0 + P1 * a1 - tP2 * a2), gy = 2.0f * (P0 * b0 + P1 * b1 - tP2 * b2);
+  const float Axx = a0 * a0 + a1 * a1 - ta2 * a2, Ayy = b0 * b0 + b1 * b1 - tb2 * b2;
+  const float Axy = 2.0f * (a0 * b0 + a1 * b1 - ta2 * b2);
+  const float det = 4.0f * Axx * Ayy - Axy * Axy;
+  if (!(Axx > 0.0f && Ayy > 0.0f && det > 1e-6f * (4.0f * Axx * Ayy))) return true;
+  const float tol = 1e-4f * (P0 * P0 + P1 * P1 + tP2 * P2);
+  const float inv_det = __fdividef(1.0f, det);
+  const float ux = (Axy * gy - 2.0f * Ayy * gx) * inv_det, uy = (Axy * gx - 2.0f * Axx * gy) * inv_det;
+  float qmin;
+  if (fabsf(ux) <= hx && fabsf(uy) <= hy) {
+    qmin = Q0 + 0.5f * (gx * ux + gy * uy);
+  } else {
+    const float inv_2ayy = __fdividef(0.5f, Ayy), inv_2axx = __fdividef(0.5f, Axx);
+    qmin = 3.0e38f;
+#pragma unroll
+    for (int sgn = -1; sgn <= 1; sgn += 2) {
+      const float ex = sgn * hx;  // edge x = ex: quadratic in y
+      const float ly = gy + Axy * ex, cy = Q0 + ex * (gx + Axx * ex);
+      const float ty = fminf(fmaxf(-ly * inv_2ayy, -hy), hy);
+      qmin = fminf(qmin, cy + ty * (ly + Ayy * ty));
+      const float ey = sgn * hy;  // edge y = ey: quadratic in x
+      const float lx = gx + Axy * ey, cx = Q0 + ey * (gy + Ayy * ey);
+      const float tx = fminf(fmaxf(-lx * inv_2axx, -hx), hx);
+      qmin = fminf(qmin, cx + tx * (lx + Axx * tx));
+    }
+  }
+  return !(qmin > tol);  // also true when anything went NaN
+}
+
 struct Hit {
   float sx, sy, pz, rho3d, rho2d, depth, G, alpha, dx, dy;
 };
@@ -175,6 +225,9 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
       if (rr < cnt) {
         const float4 box = s_rec[rr * kQ + 4];
         hit = box.x <= bx1 && box.y >= bx0 && box.z <= by1 && box.w >= by0;
+        if (hit)
+          hit = subtile_may_hit(s_rec[rr * kQ], s_rec[rr * kQ + 1], s_rec[rr * kQ + 2], s_rec[rr * kQ + 3], bx0, bx1,
+              by0, by1);
       }
       unsigned mask = __ballot_sync(kFull, hit);
 #ifdef FSGS_STATS
@@ -439,6 +492,9 @@ __global__ void __launch_bounds__(256, AUX ? 3 : 4) blend_backward_kernel(BwdDev
         if (rr < cnt) {
           const float4 box = s_rec[rr * kQ + 4];
           hit = box.x <= bx1 && box.y >= bx0 && box.z <= by1 && box.w >= by0;
+          if (hit)
+            hit = subtile_may_hit(s_rec[rr * kQ], s_rec[rr * kQ + 1], s_rec[rr * kQ + 2], s_rec[rr * kQ + 3], bx0,
+                bx1, by0, by1);
         }
         unsigned mask = __ballot_sync(kFull, hit);
         while (mask) {

@@ -24,7 +24,7 @@ constexpr int kRecFloats = FSGS_RECORD_FLOATS;
 static inline int ceil_div(int64_t a, int64_t b) { return (int) ((a + b - 1) / b); }
 
 // Render record, 8 float4 per Gaussian (128 B, one cache line):
-//  q0: mean2D.x, mean2D.y, opacity, unused
+//  q0: mean2D.x, mean2D.y, opacity, tau' (the padded bound on rho inside which alpha can reach 1/255; 0: never)
 //  q1: A.x A.y A.z B.x        rows A, B, C of inverse_m (the adjugate of the splat->screen matrix)
 //  q2: B.y B.z C.x C.y
 //  q3: C.z Tw.x Tw.y Tw.z     Tw = row 2 of the splat->screen matrix (depth row)
@@ -258,12 +258,14 @@ __device__ __forceinline__ void warp_for_each_covered_tile(const Conic &c, int x
 // low-pass disc around the 3-sigma box centre, padded against rounding.  An empty box (xmin > xmax)
 // means the splat can never pass the alpha cut; an infinite box means "cannot bound" (the disc crosses
 // the camera plane).  M is the splat->screen matrix, ctr the low-pass centre (means2D).
-__device__ __forceinline__ float4 alpha_box(const float *M, float2 ctr, float opacity) {
+__device__ __forceinline__ float4 alpha_box(const float *M, float2 ctr, float opacity, float &tau_padded) {
   const float inf = __int_as_float(0x7f800000);
+  tau_padded = 0.0f;
   float tau = 2.0f * __logf(255.0f * opacity);  // alpha >= 1/255  <=>  rho <= tau
   if (!(opacity > 0.0f) || !(tau == tau)) return make_float4(1.0f, -1.0f, 1.0f, -1.0f);
   tau = tau * 1.002f + 0.02f;
   if (tau <= 0.0f) return make_float4(1.0f, -1.0f, 1.0f, -1.0f);
+  tau_padded = tau;
   const float r2d = sqrtf(0.5f * tau) + 0.5f;
   float4 box = make_float4(ctr.x - r2d, ctr.x + r2d, ctr.y - r2d, ctr.y + r2d);
   const float d = tau * (M[6] * M[6] + M[7] * M[7]) - M[8] * M[8];
@@ -284,8 +286,8 @@ __device__ __forceinline__ float4 alpha_box(const float *M, float2 ctr, float op
 }
 
 __device__ __forceinline__ void write_record(float4 *rec, float2 xy, float opacity, const float *im, const float *M,
-    float4 box, float3 rgb, float3 nrm) {
-  rec[0] = make_float4(xy.x, xy.y, opacity, 0.0f);
+    float4 box, float tau_padded, float3 rgb, float3 nrm) {
+  rec[0] = make_float4(xy.x, xy.y, opacity, tau_padded);
   rec[1] = make_float4(im[0], im[1], im[2], im[3]);
   rec[2] = make_float4(im[4], im[5], im[6], im[7]);
   rec[3] = make_float4(im[8], M[6], M[7], M[8]);

@@ -389,9 +389,10 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
     s_stage[kStageCol + 3 * t] = rgb.x, s_stage[kStageCol + 3 * t + 1] = rgb.y, s_stage[kStageCol + 3 * t + 2] = rgb.z;
     if (LBS) s_stage[kStageWm + 3 * t] = p.x, s_stage[kStageWm + 3 * t + 1] = p.y, s_stage[kStageWm + 3 * t + 2] = p.z;
     if (a.records) {
-      const float4 box = vis ? alpha_box(M, ctr, opacity) : make_float4(1.0f, -1.0f, 1.0f, -1.0f);
+      float tau = 0.0f;
+      const float4 box = vis ? alpha_box(M, ctr, opacity, tau) : make_float4(1.0f, -1.0f, 1.0f, -1.0f);
       float4 *rec = reinterpret_cast<float4 *>(s_stage + kStageRec) + t * (kRecFloats / 4);
-      write_record(rec, ctr, opacity, IM, M, box, rgb, nrm);
+      write_record(rec, ctr, opacity, IM, M, box, tau, rgb, nrm);
       rec[7] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     a.means2D[i] = ctr;
@@ -444,7 +445,9 @@ __global__ void __launch_bounds__(256) pack_records_kernel(int P, const float2 *
   const float4 no = normal_opacity[i];
   const float2 ctr = means2D[i];
   const float3 rgb = make_float3(colors[3 * i], colors[3 * i + 1], colors[3 * i + 2]);
-  write_record(records + (size_t) i * (kRecFloats / 4), ctr, no.w, IM, M, alpha_box(M, ctr, no.w), rgb,
+  float tau = 0.0f;
+  const float4 box = alpha_box(M, ctr, no.w, tau);
+  write_record(records + (size_t) i * (kRecFloats / 4), ctr, no.w, IM, M, box, tau, rgb,
       make_float3(no.x, no.y, no.z));
 }
 
