@@ -56,63 +56,83 @@ def peaks():
     return 6650.0, "fallback"
 
 
+_SAMPLER_CHILD = r"""
+import sys, time
+import pynvml as nv
+nv.nvmlInit()
+uuid, index = sys.argv[1], int(sys.argv[2])
+try:
+    h = nv.nvmlDeviceGetHandleByUUID(uuid) if uuid else nv.nvmlDeviceGetHandleByIndex(index)
+except Exception:
+    h = nv.nvmlDeviceGetHandleByIndex(index)
+try:
+    print("max", nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM), flush=True)
+except Exception:
+    print("max", -1, flush=True)
+while True:
+    try:
+        mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+        try:
+            bits = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+        except AttributeError:
+            bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+        print(repr(time.time()), mhz, bits, flush=True)
+    except Exception:
+        pass
+    time.sleep(0.002)
+"""
+
+
 class ClockSampler:
     """SM clock and clock-event (throttle) reasons sampled through NVML while the timed region runs: read-only
-    queries from a thread of this process, one every few milliseconds (a timed region lasts tens of milliseconds, too
-    short for an external nvidia-smi loop to see)."""
+    queries every 2 ms from a child process (a thread of this process competes with the launching thread for the
+    interpreter lock and may get a single sample in a 40 ms region).  The child is started before the warm-up;
+    ``mark_start`` / ``mark_stop`` bracket the timed region and only the samples between them are reported."""
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
                0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, gpu_index, period=0.004):
-        self.samples, self.period, self.handle, self.nv = [], period, None, None
-        self.running = False
+    def __init__(self, gpu_index):
+        self.proc, self.lines, self.t0, self.t1 = None, [], None, None
         try:
-            import pynvml as nv
-            nv.nvmlInit()
-            try:
-                uuid = "GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid)
-                self.handle = nv.nvmlDeviceGetHandleByUUID(uuid)
-            except Exception:
-                self.handle = nv.nvmlDeviceGetHandleByIndex(gpu_index)
-            self.nv = nv
-        except Exception as e:  # no NVML: reported, not fatal
-            self.error = f"NVML unavailable: {e}"
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid)
+        except Exception:
+            uuid = ""
+        try:
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, uuid, str(gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError as e:
+            self.error = f"sampler not started: {e}"
 
-    def _loop(self):
-        nv = self.nv
-        while self.running:
-            try:
-                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
-                try:
-                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
-                except AttributeError:
-                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
-                self.samples.append((mhz, bits))
-            except Exception:
-                pass
-            time.sleep(self.period)
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.split())
 
-    def start(self):
-        if self.nv is None:
-            return
-        self.running = True
-        self.thread = threading.Thread(target=self._loop, daemon=True)
-        self.thread.start()
+    def mark_start(self):
+        deadline = time.time() + 5.0  # the child needs a moment to import and initialise NVML
+        while self.proc is not None and len(self.lines) < 2 and time.time() < deadline:
+            time.sleep(0.005)
+        self.t0 = time.time()
+
+    def mark_stop(self):
+        self.t1 = time.time()
 
     def stop(self):
-        if self.nv is None:
+        if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error], "samples": 0}
-        self.running = False
+        time.sleep(0.01)
+        self.proc.terminate()
         self.thread.join(timeout=2)
-        sm = sorted(m for m, _ in self.samples)
+        mx = next((int(l[1]) for l in self.lines if l and l[0] == "max"), None)
+        rows = [(float(l[0]), int(l[1]), int(l[2])) for l in self.lines if len(l) == 3 and l[0] != "max"]
+        inside = [r for r in rows if self.t0 is not None and self.t0 <= r[0] <= self.t1]
+        sm = sorted(r[1] for r in inside)
         bits = 0
-        for _, b in self.samples:
-            bits |= b
-        try:
-            mx = self.nv.nvmlDeviceGetMaxClockInfo(self.handle, self.nv.NVML_CLOCK_SM)
-        except Exception:
-            mx = None
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None, "sm_max_mhz": mx,
+        for r in inside:
+            bits |= r[2]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
+                "sm_max_mhz": mx if mx and mx > 0 else None,
                 "reasons": sorted(n for b, n in self.REASONS.items() if bits & b), "samples": len(sm)}
 
 
@@ -294,14 +314,16 @@ def run_ours(args):
         with torch.no_grad():
             scene.render(cam, (W, H), motion)
 
+    sampler = ClockSampler(local) if rank == 0 else None  # its child process starts while the warm-up runs
     for _ in range(max(args.warmup, 3)):
         step()
     scene.check()
     pairs_first = last_pairs(scene)
-    sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.mark_start()
     ms_step = timed(step, args.steps)
+    if rank == 0:
+        sampler.mark_stop()
     clocks = sampler.stop() if rank == 0 else None
     scene.check()
     # the same K steps once more with every launch of this library bracketed by CUDA events (per-kernel times)
