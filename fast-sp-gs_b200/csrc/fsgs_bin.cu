@@ -1,4 +1,5 @@
-// Tile binning: per-tile list offsets, pair emission, per-tile depth sort.
+// Tile binning: per-tile list offsets, pair emission, per-tile depth sort (bucket / radix pass on the depth bits
+// plus in-bucket ranking; bitonic network for lists beyond 2048 entries).
 //
 // The reference builds one global list of 64-bit keys (tile << 32 | depth bits), pads every Gaussian's
 // slot range up to its rectangle area, and radix-sorts all slots.  Here the tile histogram is already known
@@ -190,15 +191,97 @@ __device__ __forceinline__ void smem_bitonic(unsigned long long *s, int n, const
   for (int k = threadIdx.x; k < n; k += blockDim.x) dst[k] = (int32_t) (unsigned int) (s[k] & 0xffffffffull);
 }
 
+// Bucket sort of n <= kBucketKeys unique 64-bit keys (depth bits << 32 | index) in shared memory, 256 threads:
+// a radix pass on the depth bits scaled to the tile's own depth range (kBuckets buckets, monotone in the key), then
+// every key finds its rank among the few keys of its bucket by direct comparison of the full key.  About a tenth of
+// the instructions of a bitonic network at the list lengths that matter (a few hundred keys).
+constexpr int kBuckets = 1024;
+constexpr int kBucketKeys = kSortSmall / 2;  // the scattered copy lives in the second half of the key buffer
+
+__device__ __forceinline__ int depth_bucket(unsigned long long key, unsigned lo, float scale) {
+  const float d = (float) ((unsigned) (key >> 32) - lo);  // conversions and the product round monotonically
+  return min(kBuckets - 1, (int) (d * scale));
+}
+
+__device__ __forceinline__ void smem_bucket_sort(unsigned long long *s, int *s_start, int *s_cursor, unsigned *s_red,
+    int n, const unsigned long long *__restrict__ src, int32_t *__restrict__ dst) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned lo = 0xffffffffu, hi = 0u;
+  for (int k = tid; k < n; k += 256) {
+    const unsigned long long key = src[k];
+    s[k] = key;
+    const unsigned d = (unsigned) (key >> 32);
+    lo = min(lo, d), hi = max(hi, d);
+  }
+  for (int k = tid; k < kBuckets; k += 256) s_cursor[k] = 0;
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if (lane == 0) s_red[warp] = lo, s_red[8 + warp] = hi;
+  __syncthreads();
+  lo = s_red[0], hi = s_red[8];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) lo = min(lo, s_red[w]), hi = max(hi, s_red[8 + w]);
+  const float scale = (float) kBuckets / ((float) (hi - lo) + 1.0f);
+  // histogram
+  for (int k = tid; k < n; k += 256) atomicAdd(&s_cursor[depth_bucket(s[k], lo, scale)], 1);
+  __syncthreads();
+  // exclusive scan of the kBuckets counts: four per thread, warp scan, then the eight warp totals
+  {
+    int c[kBuckets / 256], sum = 0;
+#pragma unroll
+    for (int k = 0; k < kBuckets / 256; ++k) c[k] = s_cursor[tid * (kBuckets / 256) + k], sum += c[k];
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    __syncthreads();  // s_red was read above
+    if (lane == 31) s_red[warp] = (unsigned) inc;
+    __syncthreads();
+    int base = inc - sum;
+    for (int w = 0; w < warp; ++w) base += (int) s_red[w];
+#pragma unroll
+    for (int k = 0; k < kBuckets / 256; ++k) {
+      s_start[tid * (kBuckets / 256) + k] = base;
+      s_cursor[tid * (kBuckets / 256) + k] = base;
+      base += c[k];
+    }
+    if (tid == 255) s_start[kBuckets] = base;
+  }
+  __syncthreads();
+  // scatter into bucket order (any order inside a bucket)
+  unsigned long long *t = s + kBucketKeys;
+  for (int k = tid; k < n; k += 256) {
+    const unsigned long long key = s[k];
+    t[atomicAdd(&s_cursor[depth_bucket(key, lo, scale)], 1)] = key;
+  }
+  __syncthreads();
+  // rank inside the bucket by the full key (keys are unique)
+  for (int k = tid; k < n; k += 256) {
+    const unsigned long long key = t[k];
+    const int b = depth_bucket(key, lo, scale);
+    const int b0 = s_start[b], b1 = s_start[b + 1];
+    int rank = 0;
+    for (int e = b0; e < b1; ++e) rank += t[e] < key;
+    dst[b0 + rank] = (int32_t) (unsigned int) (key & 0xffffffffull);
+  }
+}
+
 __global__ void __launch_bounds__(256) tile_sort_small_kernel(int T, const int32_t *__restrict__ tile_order,
     const long long *__restrict__ starts, const int32_t *__restrict__ eff_counts,
     const unsigned long long *__restrict__ keys, int32_t *__restrict__ point_list) {
   __shared__ unsigned long long s[kSortSmall];
+  __shared__ int s_start[kBuckets + 1], s_cursor[kBuckets];
+  __shared__ unsigned s_red[16];
   const int tile = tile_order[blockIdx.x];
   const int n = eff_counts[tile];
   if (n == 0 || n > kSortSmall) return;
   const long long st = starts[tile];
-  smem_bitonic<kSortSmall>(s, n, keys + st, point_list + st);
+  if (n <= kBucketKeys) smem_bucket_sort(s, s_start, s_cursor, s_red, n, keys + st, point_list + st);
+  else smem_bitonic<kSortSmall>(s, n, keys + st, point_list + st);
 }
 
 // Lists longer than kSortSmall sit at the front of tile_order.  Up to kSortLarge keys: shared-memory sort;
