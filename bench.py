@@ -444,7 +444,7 @@ def run_ours(args):
             "roofline": {"kernel": "blend_backward", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                          "algorithmic_bytes": bwd_bytes,
-                         "note": "compositing is FP32-issue bound, not HBM bound: see DESIGN.md"},
+                         "note": "compositing is bound by instruction issue, not by HBM: the fraction is small by construction"},
             "hbm_stages": hbm_stages,
             "clocks": clocks,
         }

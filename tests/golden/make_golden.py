@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference checkout>] [--only sh|ssim]
 
 It imports the reference's PyTorch twins of the hot path (third-party packages the reference imports
 but this image lacks are replaced by inert stand-ins) and, when ``oracle/_ref`` holds the compiled
