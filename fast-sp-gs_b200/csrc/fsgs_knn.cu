@@ -9,19 +9,25 @@ namespace fsgs {
 
 constexpr int kChunk = 1024;  // control points per shared-memory chunk (3-D path)
 
-template <int D>
-__global__ void __launch_bounds__(128) cdist_top_kernel(int N, int M, const float *__restrict__ x1,
-    const float *__restrict__ x2, int largest, float *__restrict__ dist, int64_t *__restrict__ index) {
-  __shared__ float s_c[kChunk * D];
+// sum + t * t with the product and the sum rounded separately (no FMA contraction), float and double
+__device__ __forceinline__ float add_sq(float sum, float t) { return __fadd_rn(sum, __fmul_rn(t, t)); }
+__device__ __forceinline__ double add_sq(double sum, double t) { return __dadd_rn(sum, __dmul_rn(t, t)); }
+__device__ __forceinline__ float root(float v) { return sqrtf(v); }
+__device__ __forceinline__ double root(double v) { return sqrt(v); }
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128) cdist_top_kernel(int N, int M, const T *__restrict__ x1,
+    const T *__restrict__ x2, int largest, T *__restrict__ dist, int64_t *__restrict__ index) {
+  __shared__ T s_c[kChunk * D];
   const int b = blockIdx.y;
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  const float *c = x2 + (size_t) b * M * D;
-  float p[D];
+  const T *c = x2 + (size_t) b * M * D;
+  T p[D];
   if (n < N) {
 #pragma unroll
     for (int k = 0; k < D; ++k) p[k] = x1[((size_t) b * N + n) * D + k];
   }
-  float best = 0;
+  T best = 0;
   int besti = 0;
   for (int m0 = 0; m0 < M; m0 += kChunk) {
     const int cnt = min(kChunk, M - m0);
@@ -30,56 +36,52 @@ __global__ void __launch_bounds__(128) cdist_top_kernel(int N, int M, const floa
     __syncthreads();
     if (n < N) {
       for (int m = 0; m < cnt; ++m) {
-        float sum = 0;
+        T sum = 0;
 #pragma unroll
-        for (int k = 0; k < D; ++k) {
-          const float t = p[k] - s_c[m * D + k];
-          sum = __fadd_rn(sum, __fmul_rn(t, t));
-        }
+        for (int k = 0; k < D; ++k) sum = add_sq(sum, p[k] - s_c[m * D + k]);
         // replace when (sum > best) == largest: exact ties go to the last index when searching the nearest
         if ((m0 + m) == 0 || (int) (sum > best) == largest) best = sum, besti = m0 + m;
       }
     }
   }
   if (n < N) {
-    dist[(size_t) b * N + n] = sqrtf(best);
+    dist[(size_t) b * N + n] = root(best);
     index[(size_t) b * N + n] = besti;
   }
 }
 
 // any dimension: control points read through the cache
-__global__ void __launch_bounds__(128) cdist_top_generic_kernel(int N, int M, int D, const float *__restrict__ x1,
-    const float *__restrict__ x2, int largest, float *__restrict__ dist, int64_t *__restrict__ index) {
+template <typename T>
+__global__ void __launch_bounds__(128) cdist_top_generic_kernel(int N, int M, int D, const T *__restrict__ x1,
+    const T *__restrict__ x2, int largest, T *__restrict__ dist, int64_t *__restrict__ index) {
   const int b = blockIdx.y;
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
-  const float *p = x1 + ((size_t) b * N + n) * D;
-  const float *c = x2 + (size_t) b * M * D;
-  float best = 0;
+  const T *p = x1 + ((size_t) b * N + n) * D;
+  const T *c = x2 + (size_t) b * M * D;
+  T best = 0;
   int besti = 0;
   for (int m = 0; m < M; ++m) {
-    float sum = 0;
-    for (int k = 0; k < D; ++k) {
-      const float t = p[k] - __ldg(c + (size_t) m * D + k);
-      sum = __fadd_rn(sum, __fmul_rn(t, t));
-    }
+    T sum = 0;
+    for (int k = 0; k < D; ++k) sum = add_sq(sum, p[k] - __ldg(c + (size_t) m * D + k));
     if (m == 0 || (int) (sum > best) == largest) best = sum, besti = m;
   }
-  dist[(size_t) b * N + n] = sqrtf(best);
+  dist[(size_t) b * N + n] = root(best);
   index[(size_t) b * N + n] = besti;
 }
 
 // (reference src/other/cdist_top.cu:86-105)
-__global__ void __launch_bounds__(256) cdist_top_backward_kernel(int B, int N, int M, int D, const float *__restrict__ x1,
-    const float *__restrict__ x2, const float *__restrict__ dist, const int64_t *__restrict__ index,
-    const float *__restrict__ grad_dist, float *__restrict__ g1, float *__restrict__ g2) {
+template <typename T>
+__global__ void __launch_bounds__(256) cdist_top_backward_kernel(int B, int N, int M, int D, const T *__restrict__ x1,
+    const T *__restrict__ x2, const T *__restrict__ dist, const int64_t *__restrict__ index,
+    const T *__restrict__ grad_dist, T *__restrict__ g1, T *__restrict__ g2) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= B * N) return;
   const int b = i / N;
   const size_t j = (size_t) b * M + (size_t) index[i];
-  const float g = grad_dist[i] / dist[i];
+  const T g = grad_dist[i] / dist[i];
   for (int k = 0; k < D; ++k) {
-    const float t = g * (x1[(size_t) i * D + k] - x2[j * D + k]);
+    const T t = g * (x1[(size_t) i * D + k] - x2[j * D + k]);
     g1[(size_t) i * D + k] = t;
     atomicAdd(g2 + j * D + k, -t);
   }
@@ -235,31 +237,53 @@ extern "C" const char *fsgs_status_string(int status) {
 
 extern "C" int fsgs_version(void) { return 100; }
 
-extern "C" int fsgs_cdist_top(int B, int N, int M, int D, const float *x1, const float *x2, int largest, float *dist,
-    int64_t *index, fsgs_stream_t stream) {
+template <typename T>
+static int cdist_top_impl(int B, int N, int M, int D, const T *x1, const T *x2, int largest, T *dist, int64_t *index,
+    fsgs_stream_t stream) {
   FSGS_REQUIRE(B >= 0 && N >= 0 && M > 0 && D > 0);
   if (B == 0 || N == 0) return FSGS_OK;
   FSGS_REQUIRE(x1 && x2 && dist && index);
   cudaStream_t st = (cudaStream_t) stream;
   const dim3 grid(ceil_div(N, 128), B);
   largest = largest ? 1 : 0;
-  if (D == 3) cdist_top_kernel<3><<<grid, 128, 0, st>>>(N, M, x1, x2, largest, dist, index);
-  else if (D == 2) cdist_top_kernel<2><<<grid, 128, 0, st>>>(N, M, x1, x2, largest, dist, index);
-  else cdist_top_generic_kernel<<<grid, 128, 0, st>>>(N, M, D, x1, x2, largest, dist, index);
+  if (D == 3) cdist_top_kernel<T, 3><<<grid, 128, 0, st>>>(N, M, x1, x2, largest, dist, index);
+  else if (D == 2) cdist_top_kernel<T, 2><<<grid, 128, 0, st>>>(N, M, x1, x2, largest, dist, index);
+  else cdist_top_generic_kernel<T><<<grid, 128, 0, st>>>(N, M, D, x1, x2, largest, dist, index);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }
 
-extern "C" int fsgs_cdist_top_backward(int B, int N, int M, int D, const float *x1, const float *x2,
-    const float *dist, const int64_t *index, const float *grad_dist, float *g1, float *g2, fsgs_stream_t stream) {
+template <typename T>
+static int cdist_top_backward_impl(int B, int N, int M, int D, const T *x1, const T *x2, const T *dist,
+    const int64_t *index, const T *grad_dist, T *g1, T *g2, fsgs_stream_t stream) {
   FSGS_REQUIRE(B >= 0 && N >= 0 && M > 0 && D > 0 && x1 && x2 && dist && index && grad_dist && g1 && g2);
   cudaStream_t st = (cudaStream_t) stream;
-  cudaMemsetAsync(g2, 0, sizeof(float) * (size_t) B * M * D, st);
+  cudaMemsetAsync(g2, 0, sizeof(T) * (size_t) B * M * D, st);
   if (B == 0 || N == 0) return FSGS_OK;
-  cdist_top_backward_kernel<<<ceil_div((int64_t) B * N, 256), 256, 0, st>>>(B, N, M, D, x1, x2, dist, index, grad_dist,
-      g1, g2);
+  cdist_top_backward_kernel<T><<<ceil_div((int64_t) B * N, 256), 256, 0, st>>>(B, N, M, D, x1, x2, dist, index,
+      grad_dist, g1, g2);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
+}
+
+extern "C" int fsgs_cdist_top(int B, int N, int M, int D, const float *x1, const float *x2, int largest, float *dist,
+    int64_t *index, fsgs_stream_t stream) {
+  return cdist_top_impl<float>(B, N, M, D, x1, x2, largest, dist, index, stream);
+}
+
+extern "C" int fsgs_cdist_top_f64(int B, int N, int M, int D, const double *x1, const double *x2, int largest,
+    double *dist, int64_t *index, fsgs_stream_t stream) {
+  return cdist_top_impl<double>(B, N, M, D, x1, x2, largest, dist, index, stream);
+}
+
+extern "C" int fsgs_cdist_top_backward(int B, int N, int M, int D, const float *x1, const float *x2,
+    const float *dist, const int64_t *index, const float *grad_dist, float *g1, float *g2, fsgs_stream_t stream) {
+  return cdist_top_backward_impl<float>(B, N, M, D, x1, x2, dist, index, grad_dist, g1, g2, stream);
+}
+
+extern "C" int fsgs_cdist_top_backward_f64(int B, int N, int M, int D, const double *x1, const double *x2,
+    const double *dist, const int64_t *index, const double *grad_dist, double *g1, double *g2, fsgs_stream_t stream) {
+  return cdist_top_backward_impl<double>(B, N, M, D, x1, x2, dist, index, grad_dist, g1, g2, stream);
 }
 
 extern "C" int fsgs_knn(int N, int M, int K, const float *x, const float *c, float *d2, int64_t *index,

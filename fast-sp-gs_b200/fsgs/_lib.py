@@ -78,6 +78,8 @@ SYMBOLS = {
     "fsgs_version": (c_int, []),
     "fsgs_cdist_top": (c_int, [c_int, c_int, c_int, c_int, _vp, _vp, c_int, _vp, _vp, _vp]),
     "fsgs_cdist_top_backward": (c_int, [c_int, c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_cdist_top_f64": (c_int, [c_int, c_int, c_int, c_int, _vp, _vp, c_int, _vp, _vp, _vp]),
+    "fsgs_cdist_top_backward_f64": (c_int, [c_int, c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_knn": (c_int, [c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_adam_masked": (c_int, [_vp, _vp, _vp, _vp, _vp, c_float, c_float, c_float, c_float, c_int64, c_int64, _vp]),
     "fsgs_adam_masked_multi": (c_int, [c_int, POINTER(AdamTensor), _vp, c_int64, c_float, c_float, _vp]),

@@ -425,7 +425,8 @@ def gs_2d_fast_compute_trans_mat_backward(means3D, scales, rotations, Tw2v, Tv2s
 def _batch_dims(x1, x2):
     _need(x1.is_cuda and x2.is_cuda, "cdist_top: this library has no CPU path; pass CUDA tensors")
     _need(x1.device == x2.device, "x1 and x2 must be same device")
-    _need(x1.dtype == torch.float32 and x2.dtype == torch.float32, "cdist_top: float32 only")
+    _need(x1.dtype in (torch.float32, torch.float64) and x2.dtype == x1.dtype,
+          "cdist_top: float32 or float64, the same for both inputs")
     N, D, M = x1.shape[-2], x1.shape[-1], x2.shape[-2]
     _need(x2.shape[-1] == D, f"The dimenstion of point must be {D}")
     B = 1
@@ -440,12 +441,12 @@ def cdist_top(x1, x2, largest=False):
     ``x1`` the nearest (or farthest) row of ``x2``, Euclidean distance.  Exact ties: nearest -> last index."""
     B, N, M, D = _batch_dims(x1, x2)
     x1, x2 = x1.contiguous(), x2.contiguous()
-    dist = torch.empty(x1.shape[:-1], device=x1.device, dtype=torch.float32)
+    dist = torch.empty(x1.shape[:-1], device=x1.device, dtype=x1.dtype)
     index = torch.empty(x1.shape[:-1], device=x1.device, dtype=torch.int64)
     if dist.numel() == 0:
         return [dist, index]
-    check(lib().fsgs_cdist_top(B, N, M, D, _ptr(x1), _ptr(x2), int(bool(largest)), _ptr(dist), _ptr(index), _stream()),
-          "fsgs_cdist_top")
+    fn = lib().fsgs_cdist_top_f64 if x1.dtype == torch.float64 else lib().fsgs_cdist_top
+    check(fn(B, N, M, D, _ptr(x1), _ptr(x2), int(bool(largest)), _ptr(dist), _ptr(index), _stream()), "fsgs_cdist_top")
     return [dist, index]
 
 
@@ -454,9 +455,9 @@ def cdist_top_backward(x1, x2, distance, index, grad_dist):
     B, N, M, D = _batch_dims(x1, x2)
     x1, x2 = x1.contiguous(), x2.contiguous()
     g1, g2 = torch.empty_like(x1), torch.empty_like(x2)
-    check(lib().fsgs_cdist_top_backward(B, N, M, D, _ptr(x1), _ptr(x2), _ptr(distance.contiguous()),
-                                        _ptr(index.contiguous()), _ptr(grad_dist.contiguous()), _ptr(g1), _ptr(g2),
-                                        _stream()), "fsgs_cdist_top_backward")
+    fn = lib().fsgs_cdist_top_backward_f64 if x1.dtype == torch.float64 else lib().fsgs_cdist_top_backward
+    check(fn(B, N, M, D, _ptr(x1), _ptr(x2), _ptr(distance.to(x1.dtype).contiguous()), _ptr(index.contiguous()),
+             _ptr(grad_dist.to(x1.dtype).contiguous()), _ptr(g1), _ptr(g2), _stream()), "fsgs_cdist_top_backward")
     return [g1, g2]
 
 

@@ -58,6 +58,11 @@ int fsgs_cdist_top(int B, int N, int M, int D, const float *x1, const float *x2,
     int64_t *index, fsgs_stream_t stream);
 int fsgs_cdist_top_backward(int B, int N, int M, int D, const float *x1, const float *x2, const float *dist,
     const int64_t *index, const float *grad_dist, float *g1, float *g2, fsgs_stream_t stream);
+/* The same two in double precision (the reference dispatches on the dtype, cdist_top.cu:48,116). */
+int fsgs_cdist_top_f64(int B, int N, int M, int D, const double *x1, const double *x2, int largest, double *dist,
+    int64_t *index, fsgs_stream_t stream);
+int fsgs_cdist_top_backward_f64(int B, int N, int M, int D, const double *x1, const double *x2, const double *dist,
+    const int64_t *index, const double *grad_dist, double *g1, double *g2, fsgs_stream_t stream);
 
 /* Exact K nearest control points (3-D), squared L2 by direct differences, ascending by (distance, index):
  * ties go to the lower index.  x [N,3], c [M,3] -> d2 [N,K], index [N,K] int64.  K <= FSGS_KNN_MAX_K.

@@ -911,6 +911,50 @@ void orc_cdist_top_bwd(int B, int N, int M, int D, const float *x1, const float 
     }
 }
 
+/* the same two functions in double precision (the reference dispatches on the dtype, cdist_top.cu:48,116) */
+void orc_cdist_top_f64(int B, int N, int M, int D, const double *x1, const double *x2, int largest, double *dist,
+    int64_t *index) {
+  for (int b = 0; b < B; ++b) {
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n) {
+      const double *p = x1 + ((size_t) b * N + n) * D;
+      double best = 0;
+      int besti = 0;
+      for (int m = 0; m < M; ++m) {
+        const double *c = x2 + ((size_t) b * M + m) * D;
+        double sum = 0;
+        for (int k = 0; k < D; ++k) {
+          const double t = p[k] - c[k];
+          sum += t * t;
+        }
+        /* replace when (sum > best) == largest: exact ties go to the LAST index for largest == 0 */
+        if (m == 0 || ((sum > best) ? 1 : 0) == (largest ? 1 : 0)) {
+          best = sum;
+          besti = m;
+        }
+      }
+      dist[(size_t) b * N + n] = sqrt(best);
+      index[(size_t) b * N + n] = besti;
+    }
+  }
+}
+
+/* src/other/cdist_top.cu:86-105, 130-150 */
+void orc_cdist_top_bwd_f64(int B, int N, int M, int D, const double *x1, const double *x2, const double *dist,
+    const int64_t *index, const double *grad_dist, double *g1, double *g2) {
+  for (int b = 0; b < B; ++b)
+    for (int n = 0; n < N; ++n) {
+      const size_t i = (size_t) b * N + n;
+      const int64_t j = index[i];
+      const double g = grad_dist[i] / dist[i];
+      for (int k = 0; k < D; ++k) {
+        const double t = g * (x1[i * D + k] - x2[((size_t) b * M + j) * D + k]);
+        g1[i * D + k] = t;
+        g2[((size_t) b * M + j) * D + k] -= t;
+      }
+    }
+}
+
 /* Exact K nearest control points by squared L2 (direct differences, accumulation order of
  * cdist_top.cu:19-23), ascending by (distance, index): ties go to the LOWER index.
  * This is the contract of the K-NN used for LBS weights (fast_2d_gs/network.py:504), whose

@@ -186,25 +186,36 @@ def fold_inverse_grad(trans_mat, g_inverse_m, g_trans_mat):
     return out
 
 
+def _same_float(t, like):
+    return t.detach().to(like.dtype).contiguous()
+
+
 def cdist_top(x1, x2, largest=False):
-    x1, x2 = _f(x1), _f(x2)
+    """float32 or float64 (the dtype of ``x1`` decides, as in the reference's dispatch)."""
+    dbl = x1.dtype == torch.float64
+    x1 = x1.detach().contiguous() if dbl else _f(x1)
+    x2 = _same_float(x2, x1)
     N, D = x1.shape[-2], x1.shape[-1]
     M = x2.shape[-2]
     B = x1.numel() // (N * D)
-    dist = torch.zeros(x1.shape[:-1])
+    dist = torch.zeros(x1.shape[:-1], dtype=x1.dtype)
     idx = torch.zeros(x1.shape[:-1], dtype=torch.int64)
-    lib().orc_cdist_top(_ci(B), _ci(N), _ci(M), _ci(D), _p(x1), _p(x2), _ci(int(largest)), _p(dist), _p(idx))
+    fn = lib().orc_cdist_top_f64 if dbl else lib().orc_cdist_top
+    fn(_ci(B), _ci(N), _ci(M), _ci(D), _p(x1), _p(x2), _ci(int(largest)), _p(dist), _p(idx))
     return dist, idx
 
 
 def cdist_top_backward(x1, x2, dist, index, grad_dist):
-    x1, x2 = _f(x1), _f(x2)
+    dbl = x1.dtype == torch.float64
+    x1 = x1.detach().contiguous() if dbl else _f(x1)
+    x2 = _same_float(x2, x1)
     N, D = x1.shape[-2], x1.shape[-1]
     M = x2.shape[-2]
     B = x1.numel() // (N * D)
     g1, g2 = torch.zeros_like(x1), torch.zeros_like(x2)
-    lib().orc_cdist_top_bwd(_ci(B), _ci(N), _ci(M), _ci(D), _p(x1), _p(x2), _p(_f(dist)), _p(index.contiguous()),
-                            _p(_f(grad_dist)), _p(g1), _p(g2))
+    fn = lib().orc_cdist_top_bwd_f64 if dbl else lib().orc_cdist_top_bwd
+    fn(_ci(B), _ci(N), _ci(M), _ci(D), _p(x1), _p(x2), _p(_same_float(dist, x1)), _p(index.contiguous()),
+       _p(_same_float(grad_dist, x1)), _p(g1), _p(g2))
     return g1, g2
 
 

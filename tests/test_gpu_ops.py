@@ -56,6 +56,24 @@ def test_cdist_top_oracle(ops, N, M):
         assert torch.equal(cpu(d), do)
 
 
+@pytest.mark.parametrize("N,M,D", [(20_000, 300, 3), (513, 70, 5), (4, 2, 2)])
+def test_cdist_top_double(ops, N, M, D):
+    """float64 inputs take the double-precision kernels (the reference dispatches on the dtype): indices and distances
+    bit-exact against the oracle, gradients to rounding."""
+    g = torch.Generator().manual_seed(N)
+    x, c = torch.rand(2, N, D, generator=g, dtype=torch.float64), torch.rand(2, M, D, generator=g, dtype=torch.float64)
+    for largest in (False, True):
+        d, i = ops.cdist_top(x.cuda(), c.cuda(), largest)
+        do, io = orc.cdist_top(x, c, largest)
+        assert d.dtype == torch.float64 and torch.equal(cpu(i), io) and torch.equal(cpu(d), do)
+    up = torch.randn(2, N, generator=g, dtype=torch.float64)
+    g1, g2 = ops.cdist_top_backward(x.cuda(), c.cuda(), d, i, up.cuda())
+    o1, o2 = orc.cdist_top_backward(x, c, do, io, up)
+    assert g1.dtype == torch.float64 and torch.equal(cpu(g1), o1) and rel_l2(g2, o2) < 1e-12
+    with pytest.raises(RuntimeError):
+        ops.cdist_top(x.cuda(), c.cuda().float())
+
+
 def test_cdist_top_empty_and_errors(ops):
     d, i = ops.cdist_top(torch.zeros(0, 3, device="cuda"), torch.zeros(4, 3, device="cuda"))
     assert d.shape == (0,) and i.dtype == torch.int64
