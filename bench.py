@@ -314,6 +314,16 @@ def run_ours(args):
         with torch.no_grad():
             scene.render(cam, (W, H), motion)
 
+    if distributed:
+        # communicator set-up: NCCL builds its channels lazily at the first collectives of each size class, which
+        # would otherwise land in the first timed steps; these exchanges carry zeros and touch no training state
+        P = wlk["P"]
+        for n in (49 * P, 10 * P):
+            z = torch.zeros(n, device=dev)
+            for _ in range(5):
+                dist.all_reduce(z)
+        del z
+        torch.cuda.synchronize()
     sampler = ClockSampler(local) if rank == 0 else None  # its child process starts while the warm-up runs
     for _ in range(max(args.warmup, 3)):
         step()

@@ -30,7 +30,14 @@ class _Op:
         return self._fn(*args, **kwargs)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """Handle of torch's current stream on the current device (the raw getter costs a fraction of a microsecond; the
+    Stream object route costs several, ten times per frame)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -19,6 +19,15 @@ class SparseGaussianAdam(torch.optim.Adam):
         super().__init__(params=params, lr=lr, eps=eps)
         self.N = None
         self.visibility = None
+        self._bias_cache = (None, None, None)
+
+    def _bias_terms(self, step):
+        """((1 - 0.999^t)^0.5, 1 - 0.9^t) as float32 tensors, computed once per distinct step count (all groups of a
+        step share it) exactly as the reference's expression computes them."""
+        t = float(step)
+        if self._bias_cache[0] != t:
+            self._bias_cache = (t, (1 - 0.999 ** step) ** 0.5, 1 - 0.9 ** step)
+        return self._bias_cache[1], self._bias_cache[2]
 
     def set_before_step(self, visibility, N):
         self.visibility, self.N = visibility, N
@@ -27,6 +36,11 @@ class SparseGaussianAdam(torch.optim.Adam):
     def step(self, only=None):
         """``only``: an iterable of parameters; the step is then applied to those groups alone (each parameter keeps
         its own step count, so a step may be split to overlap with communication)."""
+        self.step_visible(only)
+
+    def step_visible(self, only=None):
+        """The body of ``step`` as a plain method: ``torch.optim.Optimizer`` wraps ``step`` itself in profiling and
+        hook layers that cost more host time than the launch; a training loop that has no use for them calls this."""
         batch = []
         only = None if only is None else {id(p) for p in only}
         for group in self.param_groups:
@@ -42,13 +56,16 @@ class SparseGaussianAdam(torch.optim.Adam):
                 state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
                 state["exp_avg_sq"] = torch.zeros_like(param, memory_format=torch.preserve_format)
             state["step"] += 1
-            step = state["step"]
-            lr_eff = group["lr"] * (1 - 0.999 ** step) ** 0.5 / (1 - 0.9 ** step)
-            batch.append((param, param.grad, state["exp_avg"], state["exp_avg_sq"], float(lr_eff), group["eps"]))
+            s, b = self._bias_terms(state["step"])
+            lr_eff = group["lr"] * s / b  # the reference's float32 tensor arithmetic, in its order
+            batch.append((param, param.grad.detach(), state["exp_avg"], state["exp_avg_sq"], float(lr_eff),
+                          group["eps"]))
         if not batch:
             return
         assert self.N is not None, "call set_before_step(visibility, N) before step()"
         masked_adam_step(batch, self.visibility, self.N)
+
+
 
 
 def masked_adam_step(batch, visibility, N, b1=0.9, b2=0.999):

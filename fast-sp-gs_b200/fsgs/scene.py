@@ -91,8 +91,8 @@ class DynamicScene:
             out = self.render(cam, size, motion)
             self._backward(out, g_images, g_opacity, g_aux)
             self.optimizer.set_before_step(out["visibility_filter"], self.num_points)
-            self.optimizer.step()
-            self.optimizer.zero_grad(set_to_none=True)
+            self.optimizer.step_visible()
+            self._drop_grads()
             return out
         # Multi-GPU.  Bucket segments: SH DC, SH rest, visibility mask | position, opacity, scale, rotation.
         # The backward kernels write into the bucket.  The first three segments (49 of the 59 floats per Gaussian)
@@ -132,11 +132,11 @@ class DynamicScene:
             early[0].wait()
         visible = b.extra > 0
         self.optimizer.set_before_step(visible, self.num_points)
-        self.optimizer.step(only=[self.sh_dc, self.sh_rest])
+        self.optimizer.step_visible(only=[self.sh_dc, self.sh_rest])
         if late is not None:
             late.wait()
-        self.optimizer.step(only=[self.xyz, self.opacity, self.scaling, self.rotation])
-        self.optimizer.zero_grad(set_to_none=True)
+        self.optimizer.step_visible(only=[self.xyz, self.opacity, self.scaling, self.rotation])
+        self._drop_grads()
         return out
 
     def train_step_with_loss(self, cam, size, motion, target, lambda_l1=0.8, lambda_ssim=0.2, group=None,
@@ -152,6 +152,10 @@ class DynamicScene:
 
         out = self.train_step(cam, size, motion, upstream, None, group=group, distributed=distributed)
         return out, holder["loss"]
+
+    def _drop_grads(self):
+        for p in self.params:  # zero_grad(set_to_none=True) without the optimizer's hook and profiling layers
+            p.grad = None
 
     def _backward(self, out, g_images, g_opacity, g_aux):
         if callable(g_images):  # the upstream image gradient is a function of the rendered result (a loss)
