@@ -291,12 +291,16 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_ms = {}
+
     def timed(fn, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        h0 = time.perf_counter()
         for _ in range(steps):
             fn()
+        host_ms[fn.__name__] = (time.perf_counter() - h0) * 1e3 / steps  # time the host needs to queue one step
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -314,16 +318,27 @@ def run_ours(args):
         with torch.no_grad():
             scene.render(cam, (W, H), motion)
 
+    allreduce_ms = None
     if distributed:
         # communicator set-up: NCCL builds its channels lazily at the first collectives of each size class, which
-        # would otherwise land in the first timed steps; these exchanges carry zeros and touch no training state
+        # would otherwise land in the first timed steps; these exchanges carry zeros and touch no training state.
+        # The same buffers then time the two exchanges of a step in isolation (reported beside the step time).
         P = wlk["P"]
+        allreduce_ms = []
         for n in (49 * P, 10 * P):
             z = torch.zeros(n, device=dev)
             for _ in range(5):
                 dist.all_reduce(z)
-        del z
-        torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                dist.all_reduce(z)
+            e1.record()
+            torch.cuda.synchronize()
+            allreduce_ms.append(round(e0.elapsed_time(e1) / 10, 4))
+            del z
     sampler = ClockSampler(local) if rank == 0 else None  # its child process starts while the warm-up runs
     for _ in range(max(args.warmup, 3)):
         step()
@@ -456,6 +471,8 @@ def run_ours(args):
                          "algorithmic_bytes": bwd_bytes,
                          "note": "compositing is bound by instruction issue, not by HBM: the fraction is small by construction"},
             "hbm_stages": hbm_stages,
+            "host_ms_per_step": {k: round(v, 4) for k, v in host_ms.items()},
+            "allreduce_ms_49P_10P_floats": allreduce_ms,
             "clocks": clocks,
         }
         if world == 1 and not args.no_baselines:
