@@ -23,23 +23,62 @@ class HostFeed:
         self.queue = collections.deque()
         self.next_slot = 0
 
+    SMALL = 1 << 16  # bytes: float32 tensors below this size travel together in one packed copy
+
     def stage(self, host_tensors):
-        """Start copying ``host_tensors`` (dict name -> pinned CPU tensor, or nested dicts of them)."""
+        """Start copying ``host_tensors`` (dict name -> pinned CPU tensor, or nested dicts of them).  Small float32
+        tensors (camera matrices, superpoint motion) are packed into one pinned staging buffer on the host and cross
+        in a single copy; the device tensors handed out are views into its device twin."""
         if len(self.queue) == len(self.slots):
             raise RuntimeError("HostFeed: every slot is staged; call take() first")
         slot = self.slots[self.next_slot]
         self.next_slot = (self.next_slot + 1) % len(self.slots)
         if slot["released"] is not None:
             self.copy_stream.wait_event(slot["released"])  # the step that last used these buffers has finished
+        small = []
+        self._collect_small(host_tensors, small)
+        n_small = sum(self._padded(t.numel()) for t in small)
+        if n_small and (slot.get("pack_host") is None or slot["pack_host"].numel() != n_small):
+            slot["pack_host"] = torch.empty(n_small, dtype=torch.float32).pin_memory()
+            slot["pack_dev"] = torch.empty(n_small, dtype=torch.float32, device=self.device)
+        if slot.get("copied") is not None:
+            slot["copied"].synchronize()  # the previous copy out of this slot's staging buffer has left the host
+        off = 0
+        for t in small:
+            slot["pack_host"][off:off + t.numel()].copy_(t.reshape(-1))
+            off += self._padded(t.numel())
         with torch.cuda.stream(self.copy_stream):
-            slot["buffers"] = self._copy(host_tensors, slot["buffers"])
+            if n_small:
+                slot["pack_dev"].copy_(slot["pack_host"], non_blocking=True)
+                slot["copied"] = torch.cuda.Event()
+                slot["copied"].record(self.copy_stream)
+            cursor = [0]
+            slot["buffers"] = self._copy(host_tensors, slot["buffers"], slot.get("pack_dev"), cursor)
             slot["ready"].record(self.copy_stream)
         self.queue.append(slot)
 
-    def _copy(self, src, dst):
+    @staticmethod
+    def _padded(n):
+        return (n + 63) & ~63  # every packed tensor starts on a 256-byte boundary, like a fresh allocation
+
+    def _is_small(self, t):
+        return t.dtype == torch.float32 and t.numel() * 4 < self.SMALL
+
+    def _collect_small(self, src, out):
+        if isinstance(src, dict):
+            for v in src.values():
+                self._collect_small(v, out)
+        elif self._is_small(src):
+            out.append(src)
+
+    def _copy(self, src, dst, pack_dev, cursor):
         if isinstance(src, dict):
             dst = dst if isinstance(dst, dict) else {}
-            return {k: self._copy(v, dst.get(k)) for k, v in src.items()}
+            return {k: self._copy(v, dst.get(k), pack_dev, cursor) for k, v in src.items()}
+        if self._is_small(src):
+            view = pack_dev[cursor[0]:cursor[0] + src.numel()].view(src.shape)
+            cursor[0] += self._padded(src.numel())
+            return view
         if not src.is_pinned():
             raise RuntimeError("HostFeed: inputs must live in pinned host memory")
         if dst is None or dst.shape != src.shape or dst.dtype != src.dtype:

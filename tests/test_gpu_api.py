@@ -218,6 +218,7 @@ def test_host_feed_and_scalar_reader():
         if i + 1 < 6:
             feed.stage(batches[i + 1])
         x = feed.take()
+        assert x["n"]["b"].data_ptr() % 256 == 0                # packed small tensors keep allocation alignment
         y = x["a"].sum() / x["a"].numel() + x["n"]["b"][0]      # consumes the buffers on the compute stream
         feed.release()
         reader.push(y)
@@ -227,7 +228,7 @@ def test_host_feed_and_scalar_reader():
     got += [float(v) for v in reader.drain()]
     assert got == [2.0 * i for i in range(6)]
     with pytest.raises(RuntimeError):
-        feed.stage({"a": torch.zeros(4)})                       # not pinned
+        feed.stage({"a": torch.zeros(1 << 20)})                 # large and not pinned
     feed2 = HostFeed("cuda")
     feed2.stage(batches[0]); feed2.stage(batches[1])
     with pytest.raises(RuntimeError):
