@@ -63,6 +63,9 @@ __device__ __forceinline__ float4 quat_adjoint(const float4 q, const float *dR) 
 
 __device__ __forceinline__ void lbs_warp_one(const LbsDev &l, int i, float3 &mean, float2 &scale, float4 &rot) {
   const float3 p = make_float3(l.xyz[3 * i], l.xyz[3 * i + 1], l.xyz[3 * i + 2]);
+  // issued before the gathers below so that their latency overlaps
+  const float ls0 = __ldg(l.scaling_raw + 2 * i), ls1 = __ldg(l.scaling_raw + 2 * i + 1);
+  const float4 r0 = __ldg(reinterpret_cast<const float4 *>(l.rotation_raw) + i);
   float3 acc = make_float3(0, 0, 0);
   float4 dr = make_float4(0, 0, 0, 0);
   float2 ds = make_float2(0, 0);
@@ -80,8 +83,7 @@ __device__ __forceinline__ void lbs_warp_one(const LbsDev &l, int i, float3 &mea
     ds.x += b.x * w, ds.y += b.y * w;
   }
   mean = make_float3(p.x + (acc.x - p.x), p.y + (acc.y - p.y), p.z + (acc.z - p.z));
-  scale = make_float2(expf(l.scaling_raw[2 * i]) + ds.x, expf(l.scaling_raw[2 * i + 1]) + ds.y);
-  const float4 r0 = reinterpret_cast<const float4 *>(l.rotation_raw)[i];
+  scale = make_float2(expf(ls0) + ds.x, expf(ls1) + ds.y);
   const float4 r = make_float4(r0.x + dr.x, r0.y + dr.y, r0.z + dr.z, r0.w + dr.w);
   const float inv = 1.0f / fmaxf(sqrtf(r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w), 1e-12f);
   rot = make_float4(r.x * inv, r.y * inv, r.z * inv, r.w * inv);
@@ -290,6 +292,15 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
   float vz = 0, opacity = 0, radius = 0;
   int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
   Conic cn = {};
+  // loads that the culled path would not need are issued up front all the same: one round trip instead of a chain
+  float opac_in = 0.0f, dc0 = 0.0f, dc1 = 0.0f, dc2 = 0.0f;
+  if (i < a.P) {
+    opac_in = __ldg(a.opac + i);
+    if (a.sh_degree >= 0) {
+      const float *c0 = a.shs + (size_t) i * (a.sh_degree >= 0 ? a.n_dc : 1) * 3;
+      dc0 = __ldg(c0), dc1 = __ldg(c0 + 1), dc2 = __ldg(c0 + 2);
+    }
+  }
   if (i < a.P) {
     if (LBS) lbs_warp_one(lbs, i, p, s, q);
     else p = make_float3(a.means[3 * i], a.means[3 * i + 1], a.means[3 * i + 2]);
@@ -299,7 +310,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
       vz = pv.z;
       vis = !(vz <= 0.2f);
       if (vis) {
-        opacity = a.opac[i];
+        opacity = opac_in;
         if (a.trans_precomp == nullptr) {
           if (!LBS) s = a.scales[i], q = a.rots[i];
           splat_matrix(p, s, q, Tw2v, Tv2s, M, nrm);
@@ -366,7 +377,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
       const float *c0 = a.shs + (size_t) i * a.n_dc * 3;          // coefficient 0
       const float *cw = staged ? s_wide + t * wide : (a.sh_rest ? a.sh_rest + (size_t) i * wide : c0);
       if (a.sh_rest) cw -= 3;                                     // the rest array starts at coefficient 1
-      rgb.x += c0[0] * b[0], rgb.y += c0[1] * b[0], rgb.z += c0[2] * b[0];
+      rgb.x += dc0 * b[0], rgb.y += dc1 * b[0], rgb.z += dc2 * b[0];
 #pragma unroll
       for (int k = 1; k < 16; ++k) {
         if (k < nb) {
