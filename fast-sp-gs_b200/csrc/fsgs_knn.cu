@@ -166,8 +166,21 @@ struct AdamMulti {
   fsgs_adam_tensor t[FSGS_ADAM_MAX_TENSORS];
   long long chunk_start[FSGS_ADAM_MAX_TENSORS + 1];  // prefix sums of ceil(N * M / 4)
   int vec[FSGS_ADAM_MAX_TENSORS];                     // all four arrays 16-byte aligned
+  unsigned magic[FSGS_ADAM_MAX_TENSORS];              // floor(2^32 / M), or 0: divide the slow way
   int n;
 };
+
+// e / M and e % M for e < 2^32 with magic = floor(2^32 / M): the high product is the quotient or one less.
+__device__ __forceinline__ void divmod(long long e, int M, unsigned magic, long long &q, int &r) {
+  if (magic != 0 && e < (1ll << 32)) {
+    unsigned qq = __umulhi((unsigned) e, magic);
+    unsigned rr = (unsigned) e - qq * (unsigned) M;
+    if (rr >= (unsigned) M) ++qq, rr -= (unsigned) M;
+    q = qq, r = (int) rr;
+  } else {
+    q = e / M, r = (int) (e - q * M);
+  }
+}
 
 // One launch for all tensors.  Each tensor is walked as a flat array in chunks of four consecutive floats (one
 // 16-byte access per array), consecutive threads taking consecutive chunks, so every access is fully coalesced
@@ -184,8 +197,9 @@ __global__ void __launch_bounds__(256) adam_masked_multi_kernel(AdamMulti a, con
     const long long e0 = (chunk - a.chunk_start[k]) * 4;
     const long long n_el = N * t.M;
     const int cnt = (int) (n_el - e0 < 4 ? n_el - e0 : 4);
-    long long row = e0 / t.M;
-    int col = (int) (e0 - row * t.M);
+    long long row;
+    int col;
+    divmod(e0, t.M, a.magic[k], row, col);
     bool vis[4];
     bool any = false;
 #pragma unroll
@@ -339,6 +353,7 @@ extern "C" int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *ten
     a.t[k] = t;
     a.chunk_start[k + 1] = a.chunk_start[k] + (N * t.M + 3) / 4;
     a.vec[k] = ((((uintptr_t) t.param) | ((uintptr_t) t.grad) | ((uintptr_t) t.exp_avg) | ((uintptr_t) t.exp_avg_sq)) & 15) == 0;
+    a.magic[k] = t.M > 1 ? (unsigned) ((1ull << 32) / (unsigned long long) t.M) : 0u;
   }
   if (N == 0) return FSGS_OK;
   const long long total = a.chunk_start[n_tensors];
