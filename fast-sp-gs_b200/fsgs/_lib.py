@@ -26,6 +26,10 @@ class AdamTensor(Structure):
                 ("lr", c_float), ("eps", c_float)]
 
 
+class RowTensor(Structure):
+    _fields_ = [("src", _vp), ("dst", _vp), ("row_words", c_int32)]
+
+
 class PreprocessArgs(Structure):
     _fields_ = [("P", c_int32), ("W", c_int32), ("H", c_int32), ("sh_degree", c_int32), ("n_dc", c_int32),
                 ("n_rest", c_int32),
@@ -95,6 +99,9 @@ SYMBOLS = {
     "fsgs_render_forward": (c_int, [POINTER(RenderArgs), _vp]),
     "fsgs_render_backward": (c_int, [POINTER(RenderBwdArgs), _vp]),
     "fsgs_preprocess_backward": (c_int, [POINTER(PreprocessBwdArgs), _vp]),
+    "fsgs_compact_workspace_bytes": (c_size_t, [c_int64]),
+    "fsgs_compact_plan": (c_int, [c_int64, _vp, _vp, c_size_t, _vp, _vp]),
+    "fsgs_compact_rows": (c_int, [c_int, POINTER(RowTensor), c_int64, _vp, _vp, _vp]),
     "fsgs_ssim_forward": (c_int, [c_int, c_int, c_int, c_int, c_float, c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_ssim_backward": (c_int, [c_int, c_int, c_int, c_int, c_float, c_float, _vp, _vp, _vp, c_float, c_float,
                                    _vp, _vp, _vp, _vp, _vp]),

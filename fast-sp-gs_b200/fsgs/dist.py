@@ -26,11 +26,14 @@ class GradBucket:
         k = len(self.params) if extra_after is None else extra_after + 1
         seg_sizes = self.sizes[:k] + [extra] + self.sizes[k:]
         self.extra_segment = k
-        self.flat = torch.zeros(sum(seg_sizes), dtype=torch.float32, device=self.params[0].device)
+        # every segment starts on a 256-byte boundary whatever the row count: kernels store float2 / float4 rows into
+        # these views; the padding between segments stays zero and rides along in the collectives
+        pad = lambda n: (n + 63) & ~63
+        self.flat = torch.zeros(sum(pad(n) for n in seg_sizes), dtype=torch.float32, device=self.params[0].device)
         self.bounds, off = [], 0
         for n in seg_sizes:
             self.bounds.append((off, off + n))
-            off += n
+            off += pad(n)
         seg_views = [self.flat[lo:hi] for lo, hi in self.bounds]
         self.extra = seg_views[k]
         self.views = [v.view(p.shape) for v, p in zip(seg_views[:k] + seg_views[k + 1:], self.params)]

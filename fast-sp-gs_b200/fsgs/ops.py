@@ -303,13 +303,15 @@ def GS_2D_fast_render_forward(width, height, near_n, far_n, only_image, means2D,
 def render_backward_launch(W, H, near_n, far_n, P, records, point_list, ranges, tile_order, trans_mat_t2,
                            out_opacity, out_extras, n_contrib, dL_dcolor, dL_dopacity, dL_dextras, dL_dflow):
     dev = ranges.device
-    # one allocation, five views: colours 3, mean2D 2, trans_mat 9, inverse_m 9, normal+opacity 4
-    buf = torch.empty(P * 27, device=dev, dtype=torch.float32)
+    # one allocation, five views: colours 3, mean2D 2, trans_mat 9, inverse_m 9, normal+opacity 4.  Every view starts
+    # on a 256-byte boundary whatever P is: the preprocess adjoint reads them with float2 / float4 loads
+    Pp = (P + 63) & ~63
+    buf = torch.empty(Pp * 27, device=dev, dtype=torch.float32)
     g_col = buf[:3 * P].view(P, 3)
-    g_m2d = buf[3 * P:5 * P].view(P, 2)
-    g_tm = buf[5 * P:14 * P].view(P, 3, 3)
-    g_im = buf[14 * P:23 * P].view(P, 3, 3)
-    g_no = buf[23 * P:].view(P, 4)
+    g_m2d = buf[3 * Pp:3 * Pp + 2 * P].view(P, 2)
+    g_tm = buf[5 * Pp:5 * Pp + 9 * P].view(P, 3, 3)
+    g_im = buf[14 * Pp:14 * Pp + 9 * P].view(P, 3, 3)
+    g_no = buf[23 * Pp:23 * Pp + 4 * P].view(P, 4)
     a = _lib.RenderBwdArgs()
     a.P, a.W, a.H, a.near_n, a.far_n = P, W, H, near_n, far_n
     a.records, a.point_list, a.ranges, a.tile_order = _ptr(records), _ptr(point_list), _ptr(ranges), _ptr(tile_order)
@@ -491,6 +493,33 @@ def knn(x, c, K):
     idx = torch.empty(N, K, device=x.device, dtype=torch.int64)
     check(lib().fsgs_knn(N, M, int(K), _ptr(x), _ptr(c), _ptr(d2), _ptr(idx), _stream()), "fsgs_knn")
     return d2, idx
+
+
+def compact_rows(tensors, keep):
+    """Keep the rows (dim 0) of every tensor in ``tensors`` whose entry in ``keep`` (bool [N]) is set, in order:
+    the result of ``[t[keep] for t in tensors]`` with one plan, one host read of the row count and one gather launch
+    per 24 tensors (the reference indexes each parameter and Adam moment separately,
+    fast_2d_gs/gaussian_splatting.py:495-548)."""
+    N = keep.shape[0]
+    _need(keep.is_cuda and keep.dtype in (torch.bool, torch.uint8) and keep.dim() == 1, "keep must be a CUDA bool [N]")
+    for t in tensors:
+        _need(t.is_cuda and t.shape[0] == N and t.element_size() in (4, 8), "rows of 4- or 8-byte elements, N each")
+    keep8 = keep.contiguous().view(torch.uint8)
+    ws = torch.empty(int(lib().fsgs_compact_workspace_bytes(N)), dtype=torch.uint8, device=keep.device)
+    count = torch.empty(1, dtype=torch.int64, device=keep.device)
+    check(lib().fsgs_compact_plan(N, _ptr(keep8), _ptr(ws), ws.numel(), _ptr(count), _stream()), "fsgs_compact_plan")
+    n = int(count)  # the one synchronisation: the outputs are sized by it
+    src = [t.contiguous() for t in tensors]
+    out = [torch.empty((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device) for t in src]
+    for i in range(0, len(src), 24):
+        chunk = list(zip(src[i:i + 24], out[i:i + 24]))
+        arr = (_lib.RowTensor * len(chunk))()
+        for k, (a, b) in enumerate(chunk):
+            arr[k].src, arr[k].dst = a.data_ptr(), b.data_ptr()
+            arr[k].row_words = (a.numel() // max(N, 1)) * (a.element_size() // 4)
+        if n > 0 and N > 0:
+            check(lib().fsgs_compact_rows(len(chunk), arr, N, _ptr(keep8), _ptr(ws), _stream()), "fsgs_compact_rows")
+    return out
 
 
 def _ssim_check(img1, img2):

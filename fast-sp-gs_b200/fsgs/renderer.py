@@ -222,12 +222,13 @@ class _FastRender(torch.autograd.Function):
         gsh = dest("sh_features", shs) if want_sh else None
         grest = dest("sh_features_rest", sh_rest) if (want_sh and has_rest) else None
         width = 3 + 2 + 4 + 1 + (n_sh if want_sh and gsh is None else 0) + (n_rest if want_sh and grest is None else 0)
-        block = torch.empty(P * width, device=dev, dtype=torch.float32)
+        Pp = (P + 63) & ~63  # every view starts on a 256-byte boundary: the kernels store float2 / float4 rows
+        block = torch.empty(Pp * width, device=dev, dtype=torch.float32)
         off = 0
 
         def take(n, shape):
             nonlocal off
-            v = block[off * P:(off + n) * P].view(shape)
+            v = block[off * Pp:off * Pp + n * P].view(shape)
             off += n
             return v
 

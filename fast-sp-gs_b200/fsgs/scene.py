@@ -153,6 +153,33 @@ class DynamicScene:
         out = self.train_step(cam, size, motion, upstream, None, group=group, distributed=distributed)
         return out, holder["loss"]
 
+    @torch.no_grad()
+    def prune(self, remove):
+        """Drop the Gaussians whose entry in ``remove`` (bool [P]) is set: all six parameter tensors, both Adam moments
+        of each and the superpoint neighbours are compacted together (``ops.compact_rows``); what the reference's
+        ``prune_points`` does tensor by tensor (fast_2d_gs/gaussian_splatting.py:557-568).  Returns the new count."""
+        keep = ~remove
+        params = self.params
+        moments = []
+        for p in params:
+            st = self.optimizer.state.get(p, {})
+            moments += [st.get("exp_avg"), st.get("exp_avg_sq")]
+        extra = [self.knn_idx, self.knn_w]
+        rows = [p.data for p in params] + [m for m in moments if m is not None] + extra
+        out = ops.compact_rows(rows, keep)
+        new_params = [torch.nn.Parameter(t) for t in out[:len(params)]]
+        rest = out[len(params):]
+        for group, old, new in zip(self.optimizer.param_groups, params, new_params):
+            st = self.optimizer.state.pop(old, None)
+            group["params"][0] = new
+            if st:
+                st["exp_avg"], st["exp_avg_sq"] = rest.pop(0), rest.pop(0)
+                self.optimizer.state[new] = st
+        self.xyz, self.sh_dc, self.sh_rest, self.opacity, self.scaling, self.rotation = new_params
+        self.knn_idx, self.knn_w = rest
+        self.bucket = None
+        return self.num_points
+
     def _drop_grads(self):
         for p in self.params:  # zero_grad(set_to_none=True) without the optimizer's hook and profiling layers
             p.grad = None

@@ -271,6 +271,28 @@ typedef struct fsgs_render_bwd_args {
 int fsgs_render_backward(const fsgs_render_bwd_args *args /* host */, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Row compaction of up to FSGS_COMPACT_MAX_TENSORS tensors by one keep mask (rows in order).
+ * Replaces the per-tensor boolean indexing of change_optimizer(op='prune') / prune_points
+ * (fast_2d_gs/gaussian_splatting.py:495-548, 557-568): parameters and both Adam moments in one launch.
+ * fsgs_compact_plan: keep [N] bytes -> workspace (fsgs_compact_workspace_bytes(N)), *count (device,
+ * optional) = number of kept rows.  fsgs_compact_rows: dst[k] = src[i_k] for every tensor; rows are
+ * row_words 4-byte words wide (any 4-byte type, or 8-byte types counted as two words); dst must hold
+ * count rows.  N < 2^31.
+ * ---------------------------------------------------------------------------------------------- */
+#define FSGS_COMPACT_MAX_TENSORS 24
+typedef struct fsgs_row_tensor {
+  const void *src;
+  void *dst;
+  int32_t row_words;
+} fsgs_row_tensor;
+
+size_t fsgs_compact_workspace_bytes(int64_t N);
+int fsgs_compact_plan(int64_t N, const uint8_t *keep, void *workspace, size_t workspace_bytes, int64_t *count,
+                      fsgs_stream_t stream);
+int fsgs_compact_rows(int n_tensors, const fsgs_row_tensor *tensors, int64_t N, const uint8_t *keep,
+                      const void *workspace, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Structural similarity, 11x11 Gaussian window (sigma 1.5, zero padding), forward and adjoint.
  * Replaces fusedssim / fusedssim_backward   (src/other/structural_similarity.cu:340-381; callers
  * fast_2d_gs/losses/ssim.py:24-45; the map is that of _ssim, ssim.py:48-67).

@@ -61,7 +61,8 @@ def _worker(rank, world, port, out):
     split.adopt()
     ok &= split.copied == 0 and all(torch.allclose(p.grad, 3.0 * p.detach()) for p in params)
     ok &= (split.extra > 0).tolist() == [True, True, False, True, True, False, True]
-    ok &= split.span(0, 1).numel() == 7 * 3 + 7 and split.span(2, 3).numel() == 7 * 45 + 7
+    ok &= split.span(0, 1).numel() >= 7 * 3 + 7 and split.span(2, 3).numel() >= 7 * 45 + 7
+    ok &= all(v.data_ptr() % 256 == split.flat.data_ptr() % 256 for v in split.views)   # segments keep alignment
     radii = torch.tensor([rank, 5 - rank, 2], dtype=torch.int32)
     ok &= reduce_max_(radii).tolist() == [1, 5, 2]
     out[rank] = (bool(ok), views)
@@ -85,6 +86,6 @@ def test_single_process_bucket_is_a_noop_reduce():
     p = torch.nn.Parameter(torch.ones(4, 2))
     p.grad = torch.full((4, 2), 3.0)
     b = GradBucket([p])
-    assert b.reduce() is None and torch.equal(p.grad, torch.full((4, 2), 3.0)) and b.nbytes() == 32
+    assert b.reduce() is None and torch.equal(p.grad, torch.full((4, 2), 3.0)) and b.nbytes() >= 32
     v = torch.tensor([True, False])
     assert reduce_visibility(v) is v

@@ -256,3 +256,27 @@ def test_train_step_writes_gradients_into_the_bucket():
     for a, b in zip(scenes[0].params, scenes[1].params):
         # not bit-equal: the compositing backward sums a Gaussian's tiles with float atomics in arrival order
         assert float((a - b).abs().max()) < 2e-5
+
+
+@pytest.mark.parametrize("P", [3613, 4001, 130])
+def test_training_step_with_odd_gaussian_counts(P):
+    """Gaussian counts that are no multiple of 2 or 4: every per-Gaussian view of the flat gradient blocks (and of
+    the communication bucket) must still start on an aligned address, since the kernels use float2 / float4 rows."""
+    from fsgs import workloads as wl
+    from fsgs.scene import DynamicScene, motion_at
+    W, H = 160, 120
+    surf = wl.surfels(P, seed=7, log_scale_mean=-2.5)
+    sp = wl.superpoints(surf["means"], M=64, seed=1)
+    cam = {k: v.cuda() for k, v in wl.camera(W, H).items()}
+    motion = motion_at(sp, sp["centres"], "cuda")
+    g = torch.Generator().manual_seed(3)
+    g_img, g_op = torch.randn(3, H, W, generator=g).cuda(), torch.randn(H, W, generator=g).cuda()
+    a, b = (DynamicScene(surf, sp["centres"], K=3, device="cuda") for _ in range(2))
+    for _ in range(2):
+        out = a.train_step(cam, (W, H), motion, g_img, g_op, distributed=False)
+        b.train_step(cam, (W, H), motion, g_img, g_op, distributed=True)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(out["images"]).all())
+    for x, y in zip(a.params, b.params):
+        d = (x - y).abs()
+        assert float(d.mean()) < 1e-6 and float(d.max()) < 5e-4
