@@ -204,7 +204,7 @@ int fsgs_bin_tiles(const fsgs_bin_args *args /* host */, fsgs_stream_t stream);
  * device-synchronising cudaMalloc/cudaFree per frame.  args->workspace and args->workspace_bytes are ignored.
  *
  * Limits: capacity <= FSGS_NOALLOC_MAX_PAIRS and tiles <= FSGS_NOALLOC_MAX_TILES, else FSGS_ERR_LIMIT and
- * nothing is launched.  The array (about 8.6 MB) is held by every GPU that loads the library until the process
+ * nothing is launched.  The array (about 10.7 MB) is held by every GPU that loads the library until the process
  * exits.  The first call on each device looks up the array's device address (with that device current); make
  * that first call before any stream capture.  All calls on a device share the array: calls that overlap on the
  * GPU (different streams) race; calls on one stream are safe.  Nothing has to be cleared between calls. */
