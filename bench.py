@@ -436,11 +436,11 @@ def run_ours(args):
         #   adam: 58 floats x (param, grad, 2 moments read; param, 2 moments written) per visible Gaussian + the mask
         #   preprocess forward (LBS fused): 256 B of parameters in, 284 B of per-Gaussian outputs out (128 B record)
         #   preprocess backward: 376 B in (matrices, their gradients, SH), 240 B of parameter gradients out
-        #   LBS backward: 96 B in, 48 B out
+        #   LBS backward: 96 B in, 48 B out per Gaussian, plus 56 B gathered per (Gaussian, neighbour) pair
         with torch.no_grad():
             V = int(scene.render(cam, (W, H), motion)["visibility_filter"].sum())
         stage_bytes = {"adam_masked_multi": V * 58 * 28 + P, "preprocess_forward": P * 540,
-                       "preprocess_backward": P * 616, "lbs_warp_backward": P * 144}
+                       "preprocess_backward": P * 616, "lbs_warp_backward": P * (144 + 56 * wlk["K"])}
         hbm_stages = {}
         for k, b in stage_bytes.items():
             if k in per_kernel:

@@ -22,6 +22,7 @@ struct LbsDev {
   const float *sp_t;
   const float4 *sp_dr;
   const float2 *sp_ds;
+  const int32_t *pair_offsets, *pairs;  // optional: pairs grouped by superpoint
 };
 
 static LbsDev to_dev(const fsgs_lbs *l) {
@@ -31,6 +32,7 @@ static LbsDev to_dev(const fsgs_lbs *l) {
   d.knn_idx = l->knn_idx, d.knn_w = l->knn_w;
   d.sp_q = (const float4 *) l->sp_q, d.sp_t = l->sp_t;
   d.sp_dr = (const float4 *) l->sp_dr, d.sp_ds = (const float2 *) l->sp_ds;
+  d.pair_offsets = l->sp_pair_offsets, d.pairs = l->sp_pairs;
   return d;
 }
 
@@ -201,6 +203,107 @@ __global__ void __launch_bounds__(256) lbs_warp_backward_kernel(int P, LbsDev l,
       else atomicAdd(g_sp_ds + 2 * m + (c - 11), v);
     }
     cluster.sync();  // no block leaves while its table may still be read
+  }
+}
+
+// The same adjoint without atomics, for callers that supply the (Gaussian, neighbour) pairs grouped by superpoint
+// (offsets [M+1] and pair ids i*K + k, built once per k-NN refresh).  Pass 1: one thread per Gaussian writes the
+// per-Gaussian gradients.  Pass 2: one block per superpoint walks its pairs, every thread sums its share of
+//   S_R = sum w (g_mean (x) p)   S_t = sum w g_mean   S_dr = sum w g_rot_raw   S_ds = sum w g_scale
+// (the quaternion adjoint is linear in dL/dR, so it is applied once to S_R), the block adds the partial sums up and
+// writes the superpoint's row: every output written exactly once, in a fixed order -- bit-reproducible.
+__global__ void __launch_bounds__(256) lbs_backward_points_kernel(int P, LbsDev l, const float *__restrict__ g_means,
+    const float2 *__restrict__ g_scales, const float4 *__restrict__ g_rots, float *__restrict__ g_xyz,
+    float2 *__restrict__ g_scaling_raw, float4 *__restrict__ g_rotation_raw, float *__restrict__ g_knn_w) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  const float3 p = make_float3(l.xyz[3 * i], l.xyz[3 * i + 1], l.xyz[3 * i + 2]);
+  const float3 gm = make_float3(g_means[3 * i], g_means[3 * i + 1], g_means[3 * i + 2]);
+  const float2 gs = g_scales[i];
+  float4 dr = make_float4(0, 0, 0, 0);
+  for (int k = 0; k < l.K; ++k) {
+    const int m = (int) l.knn_idx[(size_t) i * l.K + k];
+    const float w = l.knn_w[(size_t) i * l.K + k];
+    const float4 a = __ldg(l.sp_dr + m);
+    dr.x += a.x * w, dr.y += a.y * w, dr.z += a.z * w, dr.w += a.w * w;
+  }
+  const float4 r0 = reinterpret_cast<const float4 *>(l.rotation_raw)[i];
+  const float4 r = make_float4(r0.x + dr.x, r0.y + dr.y, r0.z + dr.z, r0.w + dr.w);
+  const float nrm = fmaxf(sqrtf(r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w), 1e-12f);
+  const float inv = 1.0f / nrm;
+  const float4 y = make_float4(r.x * inv, r.y * inv, r.z * inv, r.w * inv);
+  const float4 gy = g_rots[i];
+  const float yd = y.x * gy.x + y.y * gy.y + y.z * gy.z + y.w * gy.w;
+  const float4 gr = make_float4((gy.x - y.x * yd) * inv, (gy.y - y.y * yd) * inv, (gy.z - y.z * yd) * inv,
+      (gy.w - y.w * yd) * inv);
+  g_rotation_raw[i] = gr;
+  g_scaling_raw[i] = make_float2(gs.x * expf(l.scaling_raw[2 * i]), gs.y * expf(l.scaling_raw[2 * i + 1]));
+  float3 gx = make_float3(0, 0, 0);
+  for (int k = 0; k < l.K; ++k) {
+    const int m = (int) l.knn_idx[(size_t) i * l.K + k];
+    const float w = l.knn_w[(size_t) i * l.K + k];
+    const float4 q = __ldg(l.sp_q + m);
+    const float3 rp = quat_rotate(q, p);
+    const float3 moved = make_float3(rp.x + __ldg(l.sp_t + 3 * m), rp.y + __ldg(l.sp_t + 3 * m + 1),
+        rp.z + __ldg(l.sp_t + 3 * m + 2));
+    const float4 a = __ldg(l.sp_dr + m);
+    const float2 b = __ldg(l.sp_ds + m);
+    g_knn_w[(size_t) i * l.K + k] = gm.x * moved.x + gm.y * moved.y + gm.z * moved.z +
+                                    (gr.x * a.x + gr.y * a.y + gr.z * a.z + gr.w * a.w) + (gs.x * b.x + gs.y * b.y);
+    const float3 back = quat_rotate_T(q, gm);
+    gx.x += w * back.x, gx.y += w * back.y, gx.z += w * back.z;
+  }
+  g_xyz[3 * i] = gx.x, g_xyz[3 * i + 1] = gx.y, g_xyz[3 * i + 2] = gx.z;
+}
+
+constexpr int kSpSums = 18;
+constexpr int kSpThreads = 128;
+
+__global__ void __launch_bounds__(kSpThreads) lbs_backward_superpoints_kernel(LbsDev l,
+    const int32_t *__restrict__ offsets, const int32_t *__restrict__ pairs, const float *__restrict__ g_means,
+    const float2 *__restrict__ g_scales, const float4 *__restrict__ g_rotation_raw, float *__restrict__ g_sp_q,
+    float *__restrict__ g_sp_t, float *__restrict__ g_sp_dr, float *__restrict__ g_sp_ds) {
+  __shared__ float s_part[kSpThreads / 32][kSpSums];
+  const int m = blockIdx.x;
+  const int lo = offsets[m], hi = offsets[m + 1];
+  float acc[kSpSums];
+#pragma unroll
+  for (int c = 0; c < kSpSums; ++c) acc[c] = 0.0f;
+  for (int e = lo + threadIdx.x; e < hi; e += kSpThreads) {
+    const int pair = pairs[e];
+    const int i = pair / l.K;
+    const float w = l.knn_w[pair];
+    const float3 p = make_float3(l.xyz[3 * i], l.xyz[3 * i + 1], l.xyz[3 * i + 2]);
+    const float3 gm = make_float3(w * g_means[3 * i], w * g_means[3 * i + 1], w * g_means[3 * i + 2]);
+    const float4 gr = g_rotation_raw[i];
+    const float2 gs = g_scales[i];
+    acc[0] += gm.x * p.x, acc[1] += gm.x * p.y, acc[2] += gm.x * p.z;
+    acc[3] += gm.y * p.x, acc[4] += gm.y * p.y, acc[5] += gm.y * p.z;
+    acc[6] += gm.z * p.x, acc[7] += gm.z * p.y, acc[8] += gm.z * p.z;
+    acc[9] += gm.x, acc[10] += gm.y, acc[11] += gm.z;
+    acc[12] += w * gr.x, acc[13] += w * gr.y, acc[14] += w * gr.z, acc[15] += w * gr.w;
+    acc[16] += w * gs.x, acc[17] += w * gs.y;
+  }
+#pragma unroll
+  for (int c = 0; c < kSpSums; ++c)
+    for (int o = 16; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int c = 0; c < kSpSums; ++c) s_part[threadIdx.x >> 5][c] = acc[c];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t[kSpSums];
+#pragma unroll
+    for (int c = 0; c < kSpSums; ++c) {
+      t[c] = 0.0f;
+      for (int w = 0; w < kSpThreads / 32; ++w) t[c] += s_part[w][c];
+    }
+    const float4 gq = quat_adjoint(l.sp_q[m], t);
+    reinterpret_cast<float4 *>(g_sp_q)[m] = gq;
+    g_sp_t[3 * m] = t[9], g_sp_t[3 * m + 1] = t[10], g_sp_t[3 * m + 2] = t[11];
+    reinterpret_cast<float4 *>(g_sp_dr)[m] = make_float4(t[12], t[13], t[14], t[15]);
+    reinterpret_cast<float2 *>(g_sp_ds)[m] = make_float2(t[16], t[17]);
   }
 }
 
@@ -811,6 +914,16 @@ extern "C" int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs, const float *g
                g->g_sp_dr && g->g_sp_ds);
   cudaStream_t st = (cudaStream_t) stream;
   const int M = lbs->M;
+  if (lbs->sp_pair_offsets && lbs->sp_pairs) {
+    const LbsDev d = to_dev(lbs);
+    if (P > 0)
+      lbs_backward_points_kernel<<<ceil_div(P, 256), 256, 0, st>>>(P, d, g_means, (const float2 *) g_scales,
+          (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw, (float4 *) g->g_rotation_raw, g->g_knn_w);
+    lbs_backward_superpoints_kernel<<<M, kSpThreads, 0, st>>>(d, lbs->sp_pair_offsets, lbs->sp_pairs, g_means,
+        (const float2 *) g_scales, (const float4 *) g->g_rotation_raw, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+    FSGS_LAUNCH_CHECK();
+    return FSGS_OK;
+  }
   cudaMemsetAsync(g->g_sp_q, 0, sizeof(float) * 4 * M, st);
   cudaMemsetAsync(g->g_sp_t, 0, sizeof(float) * 3 * M, st);
   cudaMemsetAsync(g->g_sp_dr, 0, sizeof(float) * 4 * M, st);

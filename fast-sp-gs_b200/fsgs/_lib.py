@@ -13,7 +13,8 @@ _vp = c_void_p
 
 class LBS(Structure):
     _fields_ = [("K", c_int32), ("M", c_int32), ("xyz", _vp), ("scaling_raw", _vp), ("rotation_raw", _vp),
-                ("knn_idx", _vp), ("knn_w", _vp), ("sp_q", _vp), ("sp_t", _vp), ("sp_dr", _vp), ("sp_ds", _vp)]
+                ("knn_idx", _vp), ("knn_w", _vp), ("sp_q", _vp), ("sp_t", _vp), ("sp_dr", _vp), ("sp_ds", _vp),
+                ("sp_pair_offsets", _vp), ("sp_pairs", _vp)]
 
 
 class LBSGrads(Structure):

@@ -77,8 +77,22 @@ def list_capacity(device=None):
     return _capacity[dev]
 
 
-def make_lbs(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds):
-    """ctypes view of the LBS inputs (all contiguous CUDA tensors; ``knn_idx`` int64)."""
+def group_pairs_by_superpoint(knn_idx, M):
+    """The (Gaussian, neighbour) pairs of ``knn_idx`` [P,K] grouped by superpoint, for the atomics-free LBS adjoint:
+    ``(offsets [M+1] int32, pairs [P*K] int32)`` with ``pairs`` the pair ids ``i*K + k`` in order of their superpoint.
+    Built with torch ops (a sort), once per k-NN refresh; attach the result to the index tensor with
+    ``knn_idx.superpoint_pairs = ...`` and the backward picks it up."""
+    flat = knn_idx.reshape(-1)
+    pairs = torch.argsort(flat, stable=True).to(torch.int32).contiguous()
+    counts = torch.bincount(flat, minlength=M)
+    offsets = torch.zeros(M + 1, dtype=torch.int32, device=knn_idx.device)
+    offsets[1:] = torch.cumsum(counts, 0)
+    return offsets, pairs
+
+
+def make_lbs(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds, pairs=None):
+    """ctypes view of the LBS inputs (all contiguous CUDA tensors; ``knn_idx`` int64); ``pairs`` = the result of
+    ``group_pairs_by_superpoint`` or None."""
     l = _lib.LBS()
     l.K, l.M = knn_idx.shape[1], sp_q.shape[0]
     for name, t in (("xyz", xyz), ("scaling_raw", scaling_raw), ("rotation_raw", rotation_raw), ("knn_idx", knn_idx),
@@ -86,6 +100,12 @@ def make_lbs(xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, 
         ops._need(t.is_cuda and t.is_contiguous(), f"lbs.{name} must be a contiguous CUDA tensor")
         setattr(l, name, t.data_ptr())
     ops._need(knn_idx.dtype == torch.int64, "lbs.knn_idx must be int64")
+    if pairs is not None:
+        offsets, ids = pairs
+        ops._need(offsets.is_cuda and ids.is_cuda and offsets.dtype == torch.int32 and ids.dtype == torch.int32 and
+                  offsets.numel() == sp_q.shape[0] + 1 and ids.numel() == knn_idx.numel(),
+                  "lbs pairs: offsets [M+1] and pair ids [P*K], int32 CUDA tensors")
+        l.sp_pair_offsets, l.sp_pairs = offsets.data_ptr(), ids.data_ptr()
     return l
 
 
@@ -102,21 +122,23 @@ class _LbsWarp(torch.autograd.Function):
         check(lib().fsgs_lbs_warp_forward(P, ctypes.byref(l), ops._ptr(means), ops._ptr(scales), ops._ptr(rots),
                                           ops._stream()), "fsgs_lbs_warp_forward")
         ctx.save_for_backward(*ts)
+        ctx.pairs = getattr(knn_idx, "superpoint_pairs", None)
         return means, scales, rots
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, g_means, g_scales, g_rots):
         ts = ctx.saved_tensors
-        grads = lbs_backward(ts, g_means.contiguous(), g_scales.contiguous(), g_rots.contiguous())
+        grads = lbs_backward(ts, g_means.contiguous(), g_scales.contiguous(), g_rots.contiguous(), pairs=ctx.pairs)
         return grads[0], grads[1], grads[2], None, grads[3], grads[4], grads[5], grads[6], grads[7]
 
 
-def lbs_backward(ts, g_means, g_scales, g_rots, outs=()):
-    """Gradients of the warp's eight float inputs; ``outs`` may give destinations for the first of them."""
+def lbs_backward(ts, g_means, g_scales, g_rots, outs=(), pairs=None):
+    """Gradients of the warp's eight float inputs; ``outs`` may give destinations for the first of them; ``pairs``
+    (``group_pairs_by_superpoint``) selects the atomics-free superpoint reduction."""
     xyz, scaling_raw, rotation_raw, knn_idx, knn_w, sp_q, sp_t, sp_dr, sp_ds = ts
     P = xyz.shape[0]
-    l = make_lbs(*ts)
+    l = make_lbs(*ts, pairs=pairs)
     given = list(outs) + [None] * 8
     outs = [g if g is not None else torch.empty_like(t)
             for g, t in zip(given, (xyz, scaling_raw, rotation_raw, knn_w, sp_q, sp_t, sp_dr, sp_ds))]
@@ -163,6 +185,7 @@ class _FastRender(torch.autograd.Function):
                                          accum_weights_count)
         pixel_colors, pixel_opacity, pixel_extras, pixel_flow, n_contrib = outs
         ctx.cfg = cfg
+        ctx.lbs_pairs = getattr(lbs_tensors[3], "superpoint_pairs", None) if use_lbs else None
         ctx.set_materialize_grads(False)  # outputs without an upstream gradient arrive as None, not as zeros
         ctx.use_lbs = use_lbs
         ctx.has = (sh_rest is not None, trans_mat_t2 is not None, pixel_extras is not None, pixel_flow is not None)
@@ -256,7 +279,7 @@ class _FastRender(torch.autograd.Function):
             gsh = g_col  # colours were an input: their gradient is the compositing gradient itself
         grads = [gm, gs, gr, go, gsh, grest, None, None, None, None, None, None, None, None, None, None, g_m2d]
         if ctx.use_lbs:
-            lg = lbs_backward(lbs_tensors, gm, gs, gr,
+            lg = lbs_backward(lbs_tensors, gm, gs, gr, pairs=ctx.lbs_pairs,
                               outs=(dest("xyz", lbs_tensors[0]), dest("scaling_raw", lbs_tensors[1]),
                                     dest("rotation_raw", lbs_tensors[2])))
             grads[0] = grads[1] = grads[2] = None

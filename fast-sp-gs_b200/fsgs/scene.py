@@ -9,7 +9,7 @@ import torch
 from . import ops
 from .dist import GradBucket, reduce_visibility
 from .optim import SparseGaussianAdam
-from .renderer import GS_2D_fast_render, list_capacity
+from .renderer import GS_2D_fast_render, group_pairs_by_superpoint, list_capacity
 
 # learning rates of exps/d_nerf.yaml (position lr at its initial value)
 LRS = dict(xyz=1.6e-4, sh_dc=2.5e-3, sh_rest=1.25e-4, opacity=0.05, scaling=5e-3, rotation=1e-3)
@@ -73,6 +73,8 @@ class DynamicScene:
         d2, idx = ops.knn(self.xyz.detach(), self.centres, self.K)
         self.knn_idx = idx
         self.knn_w = lbs_weights(d2, idx, mode, **weighting).contiguous()
+        # pairs grouped by superpoint: the LBS adjoint then needs no atomics
+        self.knn_idx.superpoint_pairs = group_pairs_by_superpoint(idx, self.centres.shape[0])
 
     def render(self, cam, size, motion, only_image=False, grad_out=None):
         """``motion``: dict sp_q [M,4] unit quaternions, sp_t [M,3], sp_dr [M,4], sp_ds [M,2] for this time step."""
@@ -177,6 +179,7 @@ class DynamicScene:
                 self.optimizer.state[new] = st
         self.xyz, self.sh_dc, self.sh_rest, self.opacity, self.scaling, self.rotation = new_params
         self.knn_idx, self.knn_w = rest
+        self.knn_idx.superpoint_pairs = group_pairs_by_superpoint(self.knn_idx, self.centres.shape[0])
         self.bucket = None
         return self.num_points
 

@@ -120,6 +120,12 @@ typedef struct fsgs_lbs {
   const float *sp_t;         /* [M,3] translations */
   const float *sp_dr;        /* [M,4] additive rotation deltas */
   const float *sp_ds;        /* [M,2] additive scale deltas */
+  /* Optional (both or neither): the P*K (Gaussian, neighbour) pairs grouped by superpoint, built once per
+   * k-NN refresh: sp_pairs holds the pair ids i*K + k ordered by knn_idx, sp_pair_offsets [M+1] where each
+   * superpoint's run starts.  With them the backward sums every superpoint's gradient in one block, without
+   * atomics and bit-reproducibly; without them it accumulates with floating-point atomics. */
+  const int32_t *sp_pair_offsets;
+  const int32_t *sp_pairs;
 } fsgs_lbs;
 
 int fsgs_lbs_warp_forward(int P, const fsgs_lbs *lbs /* host */, float *means, float *scales, float *rots,

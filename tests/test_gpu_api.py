@@ -280,3 +280,25 @@ def test_training_step_with_odd_gaussian_counts(P):
     for x, y in zip(a.params, b.params):
         d = (x - y).abs()
         assert float(d.mean()) < 1e-6 and float(d.max()) < 5e-4
+
+
+@pytest.mark.parametrize("M,K", [(64, 3), (1024, 3), (4096, 8)])
+def test_lbs_backward_grouped_pairs_equals_atomic_path_and_is_reproducible(M, K):
+    """With the pairs grouped by superpoint the LBS adjoint sums each superpoint's row in one block: same values as the
+    atomic path (to summation order), identical bits from run to run."""
+    from fsgs.renderer import group_pairs_by_superpoint, lbs_backward
+    s, cam = make_scene(20_000, 64, 64, seed=13)
+    L = _lbs_inputs(s, M=M, K=K)
+    order = ["xyz", "scaling_raw", "rotation_raw", "knn_idx", "knn_w", "sp_q", "sp_t", "sp_dr", "sp_ds"]
+    ts = [L[k] for k in order]
+    g = torch.Generator().manual_seed(5)
+    ups = [torch.randn(20_000, n, generator=g).cuda() for n in (3, 2, 4)]
+    pairs = group_pairs_by_superpoint(L["knn_idx"], M)
+    flat = L["knn_idx"].reshape(-1)
+    assert int(pairs[0][-1]) == flat.numel() and bool((flat[pairs[1].long()][1:] >= flat[pairs[1].long()][:-1]).all())
+    plain = lbs_backward(ts, *ups)
+    grouped = lbs_backward(ts, *ups, pairs=pairs)
+    again = lbs_backward(ts, *ups, pairs=pairs)
+    for a, b, c in zip(plain, grouped, again):
+        assert rel_l2(a, b) < 1e-5
+        assert torch.equal(b, c)
