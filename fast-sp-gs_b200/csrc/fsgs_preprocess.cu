@@ -257,8 +257,9 @@ __global__ void __launch_bounds__(256) lbs_backward_points_kernel(int P, LbsDev 
 }
 
 constexpr int kSpSums = 18;
-constexpr int kSpThreads = 128;
-
+// kSpThreads threads per superpoint: many when there are few superpoints (few blocks would leave the GPU idle), fewer
+// when there are thousands (the block reduction then weighs more than the latency it hides)
+template <int kSpThreads>
 __global__ void __launch_bounds__(kSpThreads) lbs_backward_superpoints_kernel(LbsDev l,
     const int32_t *__restrict__ offsets, const int32_t *__restrict__ pairs, const float *__restrict__ g_means,
     const float2 *__restrict__ g_scales, const float4 *__restrict__ g_rotation_raw, float *__restrict__ g_sp_q,
@@ -919,8 +920,12 @@ extern "C" int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs, const float *g
     if (P > 0)
       lbs_backward_points_kernel<<<ceil_div(P, 256), 256, 0, st>>>(P, d, g_means, (const float2 *) g_scales,
           (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw, (float4 *) g->g_rotation_raw, g->g_knn_w);
-    lbs_backward_superpoints_kernel<<<M, kSpThreads, 0, st>>>(d, lbs->sp_pair_offsets, lbs->sp_pairs, g_means,
-        (const float2 *) g_scales, (const float4 *) g->g_rotation_raw, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+    if (M < 1024)
+      lbs_backward_superpoints_kernel<512><<<M, 512, 0, st>>>(d, lbs->sp_pair_offsets, lbs->sp_pairs, g_means,
+          (const float2 *) g_scales, (const float4 *) g->g_rotation_raw, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+    else
+      lbs_backward_superpoints_kernel<128><<<M, 128, 0, st>>>(d, lbs->sp_pair_offsets, lbs->sp_pairs, g_means,
+          (const float2 *) g_scales, (const float4 *) g->g_rotation_raw, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
     FSGS_LAUNCH_CHECK();
     return FSGS_OK;
   }
