@@ -166,3 +166,19 @@ def test_lbs_weight_forms():
         assert all(abs(float(w_tab[n, k]) - e[k] / sum(e)) < 1e-6 for k in range(K))
     with pytest.raises(ValueError):
         lbs_weights(d2, idx, "nearest")
+
+
+def test_pairs_grouped_by_superpoint():
+    from fsgs.renderer import group_pairs_by_superpoint
+    g = torch.Generator().manual_seed(4)
+    P, K, M = 500, 3, 17
+    idx = torch.randint(0, M, (P, K), generator=g)
+    offsets, pairs = group_pairs_by_superpoint(idx, M)
+    assert offsets.dtype == torch.int32 and pairs.dtype == torch.int32 and offsets.shape == (M + 1,)
+    assert int(offsets[0]) == 0 and int(offsets[-1]) == P * K
+    flat = idx.reshape(-1)
+    assert sorted(pairs.tolist()) == list(range(P * K))                 # a permutation of all pairs
+    for m in range(M):
+        run = pairs[int(offsets[m]):int(offsets[m + 1])].long()
+        assert bool((flat[run] == m).all())                             # each run holds one superpoint's pairs
+        assert run.tolist() == sorted(run.tolist())                     # in ascending pair order (stable)
