@@ -272,7 +272,11 @@ def run_ours(args):
         # the step's exchanges are 59 MB and 12 MB: at these sizes NCCL's ring all-reduce measured faster on the
         # 8-GPU NVSwitch box than its default choice (in-switch NVLS reduction), 0.216 + 0.077 ms against
         # 0.257 + 0.095 ms in isolation and 1.57 against 1.70 ms for the whole step; an explicit setting wins
-        os.environ.setdefault("NCCL_ALGO", "Ring")
+        # (with two ranks NCCL's own choice was 2 % faster than the ring, so it is left alone there;
+        # FSGS_BENCH_NCCL_ALGO=default|Ring|... overrides)
+        algo = os.environ.get("FSGS_BENCH_NCCL_ALGO", "Ring" if world >= 4 else "default")
+        if algo != "default":
+            os.environ.setdefault("NCCL_ALGO", algo)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     wlk = build_workload(args.workload, rank, dev)
