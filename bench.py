@@ -454,7 +454,7 @@ def run_ours(args):
             if k in per_kernel:
                 gbs = b / (per_kernel[k][1] * 1e-3) / 1e9
                 hbm_stages[k] = {"bytes": b, "GB/s": round(gbs, 1), "frac": round(gbs / peak, 3)}
-        launches_per_step = sum(n for n, _ in per_kernel.values()) / args.steps + 3  # bin_tiles = 4 kernels
+        launches_per_step = sum(n for n, _ in per_kernel.values()) / args.steps + 4  # bin_tiles = 4 kernels, LBS adjoint = 2
         line = {
             "metric": METRIC, "value": world * 1e3 / ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
