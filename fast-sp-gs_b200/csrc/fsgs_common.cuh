@@ -156,15 +156,27 @@ __device__ __forceinline__ float lg2_approx(float x) {
 
 // The six coefficients (tile units) of the conic  alpha >= 1/255  of a splat
 // (reference gs_2d_fast_preprocess.cu:282-300) and the corner test (:301).
+//
+// The test cancels terms of about 1e10 down to a few rounding steps for a splat that grazes a tile corner, so which
+// products are fused into the following addition decides membership.  The reference build evaluates
+//   ((((xx*u*u + yy*v*v) + xy*u*v) + x_*u) + y_*v) + __ <= 0
+// with only the cross term fused -- except in the first row of a tile rectangle with an odd number of rows (the
+// iteration its compiler peels off the two-row loop over y), where the y_*v term is fused as well.  Both forms were
+// established against the reference kernels' lists: with them every list is identical on all scenes compared.
 struct Conic {
   float xx, yy, xy, x_, y_, __;
-  // ((((xx*u*u + yy*v*v) + xy*u*v) + x_*u) + y_*v) + __ <= 0; only the cross term is fused, as in the reference build
-  __device__ __forceinline__ bool inside(float u, float v) const {
+  __device__ __forceinline__ bool inside(float u, float v, bool fuse_y) const {
     float s = FADD(FMUL(FMUL(xx, u), u), FMUL(FMUL(yy, v), v));
     s = FFMA(FMUL(xy, u), v, s);
     s = FADD(s, FMUL(x_, u));
-    s = FADD(s, FMUL(y_, v));
+    s = fuse_y ? FFMA(y_, v, s) : FADD(s, FMUL(y_, v));
     return FADD(s, __) <= 0;
+  }
+  // tile (tx, ty) of a rectangle whose first row is y0 and which has `rows` rows: any of its four corners inside
+  __device__ __forceinline__ bool covers(int tx, int ty, int y0, int rows) const {
+    const bool fuse_y = (rows & 1) && ty == y0;
+    const float u0 = (float) tx, u1 = (float) (tx + 1), v0 = (float) ty, v1 = (float) (ty + 1);
+    return inside(u0, v0, fuse_y) || inside(u1, v0, fuse_y) || inside(u0, v1, fuse_y) || inside(u1, v1, fuse_y);
   }
 };
 
@@ -188,30 +200,13 @@ __device__ __forceinline__ Conic make_conic(const float *IM, float opacity) {
   return c;
 }
 
-// Calls f(tile_x, tile_y) for every tile of the rectangle with at least one corner inside the conic
-// (reference gs_2d_fast_preprocess.cu:301-318).  The value at a corner does not depend on which tile asks, so
-// each column's corners are evaluated once and carried down.
-template <typename F>
-__device__ __forceinline__ void for_each_covered_tile(const Conic &c, int x0, int y0, int x1, int y1, F f) {
-  for (int x = x0; x < x1; ++x) {
-    bool a = c.inside((float) x, (float) y0);
-    bool b = c.inside((float) (x + 1), (float) y0);
-    for (int y = y0; y < y1; ++y) {
-      const bool a2 = c.inside((float) x, (float) (y + 1));
-      const bool b2 = c.inside((float) (x + 1), (float) (y + 1));
-      if (a || b || a2 || b2) f(x, y);
-      a = a2, b = b2;
-    }
-  }
-}
-
-// The same enumeration for the 32 splats held by the lanes of a warp, with the work spread evenly: the tiles of all
-// 32 rectangles are numbered consecutively (prefix sum of the areas) and handed out 32 per round, so that every lane
+// Calls f for every tile of a splat's rectangle with at least one corner inside its conic (reference
+// gs_2d_fast_preprocess.cu:301-318), for the 32 splats held by the lanes of a warp, with the work spread evenly: the
+// tiles of all 32 rectangles are numbered consecutively (prefix sum of the areas) and handed out 32 per round, so that every lane
 // tests one tile per round whatever the shapes of the individual rectangles (one thread walking its own rectangle
 // leaves three quarters of the warp idle: rectangle areas range from 1 to over 100).  Lane L passes its conic and
 // rectangle (`has` false: none) and two payload words; f(tile_x, tile_y, payload0, payload1) runs on the lane that
-// tested the tile, with the payload of the splat the tile belongs to.  The corner test is Conic::inside on the same
-// values as above, so the set of (splat, tile) pairs is identical.  Must be called by all 32 lanes.
+// tested the tile, with the payload of the splat the tile belongs to.  Must be called by all 32 lanes.
 template <typename F>
 __device__ __forceinline__ void warp_for_each_covered_tile(const Conic &c, int x0, int y0, int x1, int y1, bool has,
     unsigned p0, unsigned p1, F f) {
@@ -237,7 +232,8 @@ __device__ __forceinline__ void warp_for_each_covered_tile(const Conic &c, int x
       if (v <= item) s += step;
     }
     const int local = item - __shfl_sync(full, excl, s);
-    const int sw = __shfl_sync(full, w, s);
+    const int swh = __shfl_sync(full, w | (h << 16), s);
+    const int sw = swh & 0xffff, sh = swh >> 16;
     const int sx0 = __shfl_sync(full, x0, s), sy0 = __shfl_sync(full, y0, s);
     Conic cs;
     cs.xx = __shfl_sync(full, c.xx, s), cs.yy = __shfl_sync(full, c.yy, s), cs.xy = __shfl_sync(full, c.xy, s);
@@ -245,11 +241,7 @@ __device__ __forceinline__ void warp_for_each_covered_tile(const Conic &c, int x
     const unsigned q0 = __shfl_sync(full, p0, s), q1 = __shfl_sync(full, p1, s);
     const int ly = local / sw, lx = local - ly * sw;
     const int tx = sx0 + lx, ty = sy0 + ly;
-    bool covered = false;
-    if (valid) {
-      const float u0 = (float) tx, u1 = (float) (tx + 1), v0 = (float) ty, v1 = (float) (ty + 1);
-      covered = cs.inside(u0, v0) || cs.inside(u1, v0) || cs.inside(u0, v1) || cs.inside(u1, v1);
-    }
+    const bool covered = valid && cs.covers(tx, ty, sy0, sh);
     if (covered) f(tx, ty, q0, q1);
   }
 }

@@ -1,17 +1,18 @@
 // Exact nearest control-point search in fp32 SIMT: top-1 (any dimension) and top-K (3-D).
 // Control points are staged through shared memory in chunks; every thread owns one query and scans the chunk
 // with broadcast reads.  Squared distances are accumulated by direct differences in dimension order
-// (reference src/other/cdist_top.cu:19-23) with the multiply and the add kept separate (no FMA), so indices
-// and distances are identical to a plain CPU loop.
+// (reference src/other/cdist_top.cu:19-23).  cdist_top fuses each square into the running sum, sum = fma(t, t, sum),
+// as the reference's CUDA build does: indices and distances equal that kernel's bit for bit.  The K-nearest search
+// (no counterpart in the reference's own code) keeps multiply and add separate and so equals a plain CPU loop.
 #include "fsgs_common.cuh"
 
 namespace fsgs {
 
 constexpr int kChunk = 1024;  // control points per shared-memory chunk (3-D path)
 
-// sum + t * t with the product and the sum rounded separately (no FMA contraction), float and double
-__device__ __forceinline__ float add_sq(float sum, float t) { return __fadd_rn(sum, __fmul_rn(t, t)); }
-__device__ __forceinline__ double add_sq(double sum, double t) { return __dadd_rn(sum, __dmul_rn(t, t)); }
+// sum + t * t as one fused multiply-add, float and double
+__device__ __forceinline__ float add_sq(float sum, float t) { return __fmaf_rn(t, t, sum); }
+__device__ __forceinline__ double add_sq(double sum, double t) { return __fma_rn(t, t, sum); }
 __device__ __forceinline__ float root(float v) { return sqrtf(v); }
 __device__ __forceinline__ double root(double v) { return sqrt(v); }
 

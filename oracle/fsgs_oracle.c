@@ -15,8 +15,10 @@
  *
  * Known, deliberate deviations from the reference CUDA arithmetic:
  *   - lg2.approx.f32 is replaced by log2f (CPU has no such instruction);
- *   - nvcc contracts a*b+c into FMA, this file does not.
- * Both only matter for conic corner tests that land within a few ulp of zero.
+ *   - nvcc contracts a*b+c into FMA; this file does not, except where a result is an index or a list membership
+ *     that a rounding step can flip (the conic corner test of the binning, cdist_top): there the fused operations of
+ *     the reference's CUDA build are written out with fmaf.
+ * The first only matters for conic corner tests that land within a few ulp of zero.
  */
 #include <math.h>
 #include <stdint.h>
@@ -347,16 +349,23 @@ void orc_preprocess_fwd(int P, int W, int H, int sh_degree, int n_dc, int n_rest
 /* ------------------------------------------------------------------------- */
 
 /* Six conic coefficients of the alpha >= 1/255 footprint, in tile units.
- * gs_2d_fast_preprocess.cu:282-300 */
+ * gs_2d_fast_preprocess.cu:282-300.  The corner test below cancels terms of about 1e10 down to a few rounding
+ * steps for a splat that grazes a tile corner, so the fused multiply-adds of the reference's CUDA build (nvcc,
+ * default -fmad) are restated with fmaf: each coefficient is fma(d*c, c', fma(a, a', b*b')). */
+static inline float dot3_cuda(float a0, float b0, float a1, float b1, float a2, float b2) {
+  return fmaf(a2, b2, fmaf(a0, b0, a1 * b1));
+}
+
 static void conic_coeffs(const float *im, float opacity, float *w6) {
   const float ln2 = 0.69314718055f;
   const float d = -2.0f * ln2 * (7.9886846867721655f + log2f(opacity));
-  float Wxx = im[0] * im[0] + im[3] * im[3] + d * im[6] * im[6];
-  float Wyy = im[1] * im[1] + im[4] * im[4] + d * im[7] * im[7];
-  float W__ = im[2] * im[2] + im[5] * im[5] + d * im[8] * im[8];
-  float Wxy = 2 * (im[0] * im[1] + im[3] * im[4] + d * im[6] * im[7]);
-  float Wx_ = 2 * (im[0] * im[2] + im[3] * im[5] + d * im[6] * im[8]);
-  float Wy_ = 2 * (im[1] * im[2] + im[4] * im[5] + d * im[7] * im[8]);
+  const float d6 = d * im[6], d7 = d * im[7], d8 = d * im[8];
+  float Wxx = dot3_cuda(im[0], im[0], im[3], im[3], d6, im[6]);
+  float Wyy = dot3_cuda(im[1], im[1], im[4], im[4], d7, im[7]);
+  float W__ = dot3_cuda(im[2], im[2], im[5], im[5], d8, im[8]);
+  float Wxy = 2 * dot3_cuda(im[0], im[1], im[3], im[4], d6, im[7]);
+  float Wx_ = 2 * dot3_cuda(im[0], im[2], im[3], im[5], d6, im[8]);
+  float Wy_ = 2 * dot3_cuda(im[1], im[2], im[4], im[5], d7, im[8]);
   w6[0] = Wxx * TILE * TILE;
   w6[1] = Wyy * TILE * TILE;
   w6[2] = Wxy * TILE * TILE;
@@ -365,8 +374,15 @@ static void conic_coeffs(const float *im, float opacity, float *w6) {
   w6[5] = W__;
 }
 
-static inline float conic_eval(const float *w, float u, float v) {
-  return w[0] * u * u + w[1] * v * v + w[2] * u * v + w[3] * u + w[4] * v + w[5];
+/* The corner test of :301 as the reference's CUDA build evaluates it: only the cross term is fused, except in the
+ * first row of a rectangle with an odd number of rows (the iteration peeled off its two-row loop over y), where the
+ * w[4]*v term is fused too. */
+static inline float conic_eval(const float *w, float u, float v, int fuse_y) {
+  float s = (w[0] * u) * u + (w[1] * v) * v;
+  s = fmaf(w[2] * u, v, s);
+  s = s + w[3] * u;
+  s = fuse_y ? fmaf(w[4], v, s) : s + w[4] * v;
+  return s + w[5];
 }
 
 void orc_conic(int P, const float *inverse_m, const float *opac, const int32_t *radii, float *w6) {
@@ -416,8 +432,9 @@ int64_t orc_bin(int P, int W, int H, const float *means2D, const float *inverse_
     memcpy(&dbits, depths + i, 4);
     for (int x = x0; x < x1; ++x)
       for (int y = y0; y < y1; ++y) {
-        if (conic_eval(w, x, y) <= 0 || conic_eval(w, x + 1, y) <= 0 || conic_eval(w, x, y + 1) <= 0 ||
-            conic_eval(w, x + 1, y + 1) <= 0) {
+        const int fy = ((y1 - y0) & 1) && y == y0;
+        if (conic_eval(w, x, y, fy) <= 0 || conic_eval(w, x + 1, y, fy) <= 0 || conic_eval(w, x, y + 1, fy) <= 0 ||
+            conic_eval(w, x + 1, y + 1, fy) <= 0) {
           pairs[off].key = ((uint64_t) (y * gx + x) << 32) | dbits;
           pairs[off].val = i;
           pairs[off].seq = off;
@@ -868,32 +885,37 @@ void orc_preprocess_bwd(int P, int W, int H, int sh_degree, int n_dc, int n_rest
 /* nearest / farthest control point: src/other/cdist_top.cu:3-32, 57-81       */
 /* ------------------------------------------------------------------------- */
 
-void orc_cdist_top(int B, int N, int M, int D, const float *x1, const float *x2, int largest, float *dist,
-    int64_t *index) {
-  for (int b = 0; b < B; ++b) {
-#pragma omp parallel for schedule(static)
-    for (int n = 0; n < N; ++n) {
-      const float *p = x1 + ((size_t) b * N + n) * D;
-      float best = 0;
-      int besti = 0;
-      for (int m = 0; m < M; ++m) {
-        const float *c = x2 + ((size_t) b * M + m) * D;
-        float sum = 0;
-        for (int k = 0; k < D; ++k) {
-          const float t = p[k] - c[k];
-          sum += t * t;
-        }
-        /* replace when (sum > best) == largest: exact ties go to the LAST index for largest == 0 */
-        if (m == 0 || ((sum > best) ? 1 : 0) == (largest ? 1 : 0)) {
-          best = sum;
-          besti = m;
-        }
-      }
-      dist[(size_t) b * N + n] = sqrtf(best);
-      index[(size_t) b * N + n] = besti;
-    }
+/* The reference has two builds of this loop.  Its CPU branch (:57-81, gcc) rounds the product and the sum
+ * separately; its CUDA kernel (:19-23, nvcc with the default -fmad) contracts them into sum = fma(t, t, sum).  The two
+ * can pick different control points on near-ties, so both forms are restated: `fused` selects the CUDA build's. */
+#define ORC_CDIST_TOP(NAME, T, FMA, SQRT)                                                                      \
+  void NAME(int B, int N, int M, int D, const T *x1, const T *x2, int largest, int fused, T *dist,             \
+      int64_t *index) {                                                                                         \
+    for (int b = 0; b < B; ++b) {                                                                               \
+      _Pragma("omp parallel for schedule(static)") for (int n = 0; n < N; ++n) {                                \
+        const T *p = x1 + ((size_t) b * N + n) * D;                                                             \
+        T best = 0;                                                                                             \
+        int besti = 0;                                                                                          \
+        for (int m = 0; m < M; ++m) {                                                                           \
+          const T *c = x2 + ((size_t) b * M + m) * D;                                                           \
+          T sum = 0;                                                                                            \
+          for (int k = 0; k < D; ++k) {                                                                         \
+            const T t = p[k] - c[k];                                                                            \
+            if (fused) sum = FMA(t, t, sum);                                                                    \
+            else sum += t * t;                                                                                  \
+          }                                                                                                     \
+          /* replace when (sum > best) == largest: exact ties go to the LAST index for largest == 0 */          \
+          if (m == 0 || ((sum > best) ? 1 : 0) == (largest ? 1 : 0)) {                                          \
+            best = sum;                                                                                         \
+            besti = m;                                                                                          \
+          }                                                                                                     \
+        }                                                                                                       \
+        dist[(size_t) b * N + n] = SQRT(best);                                                                  \
+        index[(size_t) b * N + n] = besti;                                                                      \
+      }                                                                                                         \
+    }                                                                                                           \
   }
-}
+ORC_CDIST_TOP(orc_cdist_top, float, fmaf, sqrtf)
 
 /* src/other/cdist_top.cu:86-105, 130-150 */
 void orc_cdist_top_bwd(int B, int N, int M, int D, const float *x1, const float *x2, const float *dist,
@@ -912,32 +934,7 @@ void orc_cdist_top_bwd(int B, int N, int M, int D, const float *x1, const float 
 }
 
 /* the same two functions in double precision (the reference dispatches on the dtype, cdist_top.cu:48,116) */
-void orc_cdist_top_f64(int B, int N, int M, int D, const double *x1, const double *x2, int largest, double *dist,
-    int64_t *index) {
-  for (int b = 0; b < B; ++b) {
-#pragma omp parallel for schedule(static)
-    for (int n = 0; n < N; ++n) {
-      const double *p = x1 + ((size_t) b * N + n) * D;
-      double best = 0;
-      int besti = 0;
-      for (int m = 0; m < M; ++m) {
-        const double *c = x2 + ((size_t) b * M + m) * D;
-        double sum = 0;
-        for (int k = 0; k < D; ++k) {
-          const double t = p[k] - c[k];
-          sum += t * t;
-        }
-        /* replace when (sum > best) == largest: exact ties go to the LAST index for largest == 0 */
-        if (m == 0 || ((sum > best) ? 1 : 0) == (largest ? 1 : 0)) {
-          best = sum;
-          besti = m;
-        }
-      }
-      dist[(size_t) b * N + n] = sqrt(best);
-      index[(size_t) b * N + n] = besti;
-    }
-  }
-}
+ORC_CDIST_TOP(orc_cdist_top_f64, double, fma, sqrt)
 
 /* src/other/cdist_top.cu:86-105, 130-150 */
 void orc_cdist_top_bwd_f64(int B, int N, int M, int D, const double *x1, const double *x2, const double *dist,

@@ -190,8 +190,9 @@ def _same_float(t, like):
     return t.detach().to(like.dtype).contiguous()
 
 
-def cdist_top(x1, x2, largest=False):
-    """float32 or float64 (the dtype of ``x1`` decides, as in the reference's dispatch)."""
+def cdist_top(x1, x2, largest=False, fused=True):
+    """float32 or float64 (the dtype of ``x1`` decides, as in the reference's dispatch).  ``fused`` selects the
+    arithmetic of the reference's CUDA build (sum = fma(t, t, sum)); False that of its CPU branch."""
     dbl = x1.dtype == torch.float64
     x1 = x1.detach().contiguous() if dbl else _f(x1)
     x2 = _same_float(x2, x1)
@@ -201,7 +202,7 @@ def cdist_top(x1, x2, largest=False):
     dist = torch.zeros(x1.shape[:-1], dtype=x1.dtype)
     idx = torch.zeros(x1.shape[:-1], dtype=torch.int64)
     fn = lib().orc_cdist_top_f64 if dbl else lib().orc_cdist_top
-    fn(_ci(B), _ci(N), _ci(M), _ci(D), _p(x1), _p(x2), _ci(int(largest)), _p(dist), _p(idx))
+    fn(_ci(B), _ci(N), _ci(M), _ci(D), _p(x1), _p(x2), _ci(int(largest)), _ci(int(fused)), _p(dist), _p(idx))
     return dist, idx
 
 

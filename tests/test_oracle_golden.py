@@ -117,14 +117,19 @@ def test_rasterize_backward():
 def test_cdist_top_against_reference_cpu_branch():
     g = _load("cdist_top.npz")
     for tag, largest in (("near", False), ("far", True)):
-        d, i = orc.cdist_top(g["x"], g["c"], largest)
+        d, i = orc.cdist_top(g["x"], g["c"], largest, fused=False)
         assert torch.equal(i, g[f"idx_{tag}"])
         assert torch.equal(d, g[f"dist_{tag}"])
         g1, g2 = orc.cdist_top_backward(g["x"], g["c"], d, i, g[f"gd_{tag}"])
         assert torch.equal(g1, g[f"g1_{tag}"])
         assert torch.allclose(g2, g[f"g2_{tag}"], rtol=1e-5, atol=1e-5)
-    d5, i5 = orc.cdist_top(g["x5"], g["c5"], False)
+    d5, i5 = orc.cdist_top(g["x5"], g["c5"], False, fused=False)
     assert torch.equal(i5, g["idx5"]) and torch.equal(d5, g["dist5"])
+    # the CUDA build's fused accumulation: same control points on this fixture, distances within a rounding step
+    for tag, largest in (("near", False), ("far", True)):
+        d, i = orc.cdist_top(g["x"], g["c"], largest, fused=True)
+        assert torch.equal(i, g[f"idx_{tag}"])
+        assert torch.allclose(d, g[f"dist_{tag}"], rtol=3e-7, atol=0) and not torch.equal(d, g[f"dist_{tag}"])
     # exact duplicates among the control points: nearest goes to the LAST duplicate, farthest to the first
     near_hits = g["idx_near"][(g["idx_near"] == 5) | (g["idx_near"] == 17) | (g["idx_near"] == 30)]
     assert len(near_hits) > 0 and bool((near_hits == 30).all())

@@ -42,3 +42,27 @@ def make_scene(P, W, H, seed=0, log_scale_mean=-3.0, eye=(0.3, -0.4, 4.0), devic
 
 def cpu(t):
     return None if t is None else t.detach().cpu()
+
+
+def pair_keys(ranges, point_list):
+    """(tile << 32 | Gaussian) of every listed pair, in list order."""
+    lens = ranges[:, 1] - ranges[:, 0]
+    tile = torch.repeat_interleave(torch.arange(ranges.shape[0], device=ranges.device), lens)
+    return tile * (1 << 32) + point_list[: int(lens.sum())].long()
+
+
+def assert_preprocess_equal(mine, theirs):
+    """Outputs of gs_2d_fast_preprocess_forward against the reference kernels': everything bit-equal (colours to
+    2e-6: the SH polynomial is not pinned operation by operation), tile lists included."""
+    names = ["means2D", "colors", "trans_mat", "inverse_m", "normal_opacity", "depths", "radii"]
+    for n, a, b in zip(names, mine, theirs):
+        assert a.shape == b.shape, n
+        if n == "colors":
+            assert float((a - b).abs().max()) < 2e-6, n
+        else:
+            assert torch.equal(a, b), f"{n}: {(a != b).sum().item()} of {a.numel()} elements differ"
+    assert mine[8].shape == theirs[8].shape  # numel == sum of rectangle areas
+    if not (torch.equal(mine[7], theirs[7]) and torch.equal(mine[8], theirs[8])):
+        a, b = pair_keys(mine[7], mine[8]), pair_keys(theirs[7], theirs[8])
+        _, cnt = torch.unique(torch.cat([a, b]), return_counts=True)
+        raise AssertionError(f"tile lists differ: {int((cnt == 1).sum())} of {b.numel()} pairs are in one list only")
