@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(256) emit_pairs_kernel(int P, int gx, int gy, 
     const float *__restrict__ inverse_m, const float *__restrict__ depths, const float *__restrict__ opac,
     const int32_t *__restrict__ radii, const long long *__restrict__ starts, const int32_t *__restrict__ eff_counts,
     int32_t *__restrict__ cursors, unsigned long long *__restrict__ keys, int32_t *__restrict__ point_list,
-    long long capacity, const unsigned long long *__restrict__ counters) {
+    long long capacity, const unsigned long long *__restrict__ counters, int opac_stride) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   bool has = false;
   int x0 = 0, y0 = 0, x1 = 0, y1 = 0;
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) emit_pairs_kernel(int P, int gx, int gy, 
       float IM[9];
 #pragma unroll
       for (int k = 0; k < 9; ++k) IM[k] = inverse_m[(size_t) 9 * i + k];
-      cn = make_conic(IM, opac[i]);
+      cn = make_conic(IM, opac[(size_t) i * opac_stride]);
       key = ((unsigned long long) __float_as_uint(depths[i]) << 32) | (unsigned int) i;
       has = true;
     }
@@ -322,37 +322,45 @@ extern "C" size_t fsgs_bin_workspace_bytes(int W, int H, int64_t capacity) {
          align_up(sizeof(int32_t) * (size_t) T);
 }
 
-extern "C" int fsgs_bin_tiles(const fsgs_bin_args *a, fsgs_stream_t stream) {
-  FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0 && a->capacity >= 0);
-  FSGS_REQUIRE(a->tile_counts && a->counters);
-  FSGS_REQUIRE(a->P == 0 || (a->means2D && a->inverse_m && a->depths && a->opac && a->radii));
-  FSGS_REQUIRE(a->ranges && a->tile_order && a->workspace && (a->point_list || a->capacity == 0));
-  if (a->workspace_bytes < fsgs_bin_workspace_bytes(a->W, a->H, a->capacity)) return FSGS_ERR_WORKSPACE;
-  cudaStream_t st = (cudaStream_t) stream;
+// The four launches of the binning on a carved workspace: scan, pair emission, the two per-tile sorts.
+static int launch_binning(const fsgs_bin_args *a, const BinWorkspace &w, cudaStream_t st) {
   const int gx = (a->W + kTile - 1) / kTile, gy = (a->H + kTile - 1) / kTile, T = gx * gy;
-  BinWorkspace w = carve(a->workspace, T, a->capacity);
   tile_scan_kernel<<<1, 1024, 0, st>>>(T, a->tile_counts, (long long) a->capacity, (long long *) a->ranges, w.starts,
       w.eff_counts, w.cursors, a->tile_order, (unsigned long long *) a->counters);
   FSGS_LAUNCH_CHECK();
   const int blocks = max(1, ceil_div(a->P, 256));
   emit_pairs_kernel<<<blocks, 256, 0, st>>>(a->P, gx, gy, (const float2 *) a->means2D, a->inverse_m, a->depths, a->opac,
       a->radii, w.starts, w.eff_counts, w.cursors, w.keys, a->point_list, (long long) a->capacity,
-      (const unsigned long long *) a->counters);
+      (const unsigned long long *) a->counters, a->opac_stride > 0 ? a->opac_stride : 1);
   FSGS_LAUNCH_CHECK();
   tile_sort_small_kernel<<<T, 256, 0, st>>>(T, a->tile_order, w.starts, w.eff_counts, w.keys, a->point_list);
   FSGS_LAUNCH_CHECK();
-  static bool attr_set = false;  // per process; the attribute is per device function and idempotent
+  // the opt-in to 128 KB of dynamic shared memory is a per-device attribute of the kernel
+  constexpr int kMaxDev = 64;
+  static bool attr_set[kMaxDev] = {false};
   const size_t dyn = sizeof(unsigned long long) * kSortLarge;
-  if (!attr_set) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return FSGS_ERR_LAUNCH;
+  if (dev < 0 || dev >= kMaxDev || !attr_set[dev]) {
     if (cudaFuncSetAttribute(tile_sort_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) dyn) !=
         cudaSuccess)
       return FSGS_ERR_LAUNCH;
-    attr_set = true;
+    if (dev >= 0 && dev < kMaxDev) attr_set[dev] = true;
   }
   tile_sort_large_kernel<<<min(T, 148), 1024, dyn, st>>>(T, a->tile_order, w.starts, w.eff_counts, w.keys,
       a->point_list);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
+}
+
+extern "C" int fsgs_bin_tiles(const fsgs_bin_args *a, fsgs_stream_t stream) {
+  FSGS_REQUIRE(a && a->P >= 0 && a->W > 0 && a->H > 0 && a->capacity >= 0);
+  FSGS_REQUIRE(a->tile_counts && a->counters);
+  FSGS_REQUIRE(a->P == 0 || (a->means2D && a->inverse_m && a->depths && a->opac && a->radii));
+  FSGS_REQUIRE(a->ranges && a->tile_order && a->workspace && (a->point_list || a->capacity == 0));
+  if (a->workspace_bytes < fsgs_bin_workspace_bytes(a->W, a->H, a->capacity)) return FSGS_ERR_WORKSPACE;
+  const int T = ((a->W + kTile - 1) / kTile) * ((a->H + kTile - 1) / kTile);
+  return launch_binning(a, carve(a->workspace, T, a->capacity), (cudaStream_t) stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -376,7 +384,7 @@ extern "C" int fsgs_bin_tiles_noalloc(const fsgs_bin_args *a, fsgs_stream_t stre
   FSGS_REQUIRE(a->tile_counts && a->counters);
   FSGS_REQUIRE(a->P == 0 || (a->means2D && a->inverse_m && a->depths && a->opac && a->radii));
   FSGS_REQUIRE(a->ranges && a->tile_order && (a->point_list || a->capacity == 0));
-  const int gx = (a->W + kTile - 1) / kTile, gy = (a->H + kTile - 1) / kTile, T = gx * gy;
+  const int T = ((a->W + kTile - 1) / kTile) * ((a->H + kTile - 1) / kTile);
   if (a->capacity > FSGS_NOALLOC_MAX_PAIRS || T > FSGS_NOALLOC_MAX_TILES) return FSGS_ERR_LIMIT;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FSGS_ERR_LAUNCH;
@@ -398,22 +406,5 @@ extern "C" int fsgs_bin_tiles_noalloc(const fsgs_bin_args *a, fsgs_stream_t stre
   w.eff_counts = (int32_t *) p;
   // every scratch word that is read is written first: the scan kernel fills cursors / starts / counts for all
   // tiles, the emit kernel fills exactly the key slots the sort kernels read
-  tile_scan_kernel<<<1, 1024, 0, st>>>(T, a->tile_counts, (long long) a->capacity, (long long *) a->ranges, w.starts,
-      w.eff_counts, w.cursors, a->tile_order, (unsigned long long *) a->counters);
-  FSGS_LAUNCH_CHECK();
-  const int blocks = max(1, ceil_div(a->P, 256));
-  emit_pairs_kernel<<<blocks, 256, 0, st>>>(a->P, gx, gy, (const float2 *) a->means2D, a->inverse_m, a->depths, a->opac,
-      a->radii, w.starts, w.eff_counts, w.cursors, w.keys, a->point_list, (long long) a->capacity,
-      (const unsigned long long *) a->counters);
-  FSGS_LAUNCH_CHECK();
-  tile_sort_small_kernel<<<T, 256, 0, st>>>(T, a->tile_order, w.starts, w.eff_counts, w.keys, a->point_list);
-  FSGS_LAUNCH_CHECK();
-  const size_t dyn = sizeof(unsigned long long) * kSortLarge;
-  if (cudaFuncSetAttribute(tile_sort_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) dyn) !=
-      cudaSuccess)
-    return FSGS_ERR_LAUNCH;
-  tile_sort_large_kernel<<<min(T, 148), 1024, dyn, st>>>(T, a->tile_order, w.starts, w.eff_counts, w.keys,
-      a->point_list);
-  FSGS_LAUNCH_CHECK();
-  return FSGS_OK;
+  return launch_binning(a, w, st);
 }

@@ -31,9 +31,6 @@ struct GradMap {
 constexpr unsigned kFull = 0xffffffffu;
 
 struct FwdDev {
-#ifdef FSGS_STATS
-  unsigned long long *stats;  // [0] warp-entries visited, [1] box hits, [2] hits with >= 1 blending lane, [3] blending lanes
-#endif
   int P, W, H, gx;
   float near_n, far_n;
   const float4 *records;
@@ -230,20 +227,9 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
               by0, by1);
       }
       unsigned mask = __ballot_sync(kFull, hit);
-#ifdef FSGS_STATS
-      if (lane == 0) atomicAdd(a.stats + 0, (unsigned long long) min(32, cnt - c)), atomicAdd(a.stats + 1, (unsigned long long) __popc(mask));
-#endif
       while (mask) {
         const int j = __ffs(mask) - 1;
         mask &= mask - 1;
-#ifdef FSGS_STATS
-        {
-          Hit h2; float o2; float3 t2;
-          const bool bl = !done && eval_pair<false>(s_rec + (c + j) * kQ, px, py, a.near_n, h2, o2, t2);
-          const unsigned bm = __ballot_sync(kFull, bl);
-          if (lane == 0 && bm) atomicAdd(a.stats + 2, 1ull), atomicAdd(a.stats + 3, (unsigned long long) __popc(bm));
-        }
-#endif
         if (done) continue;
         const int r = c + j;
         const float4 *rec = s_rec + r * kQ;
@@ -316,6 +302,52 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
     } else {
       a.n_contrib[HW + pix] = 0;
     }
+  }
+}
+
+// Work counter for roofline arithmetic (a diagnostic, not part of a frame): replays every pixel's walk over its
+// tile's list with the forward pass's own tests and counts
+//   [0] traversed pairs: (pixel, list entry) visited before the pixel's exit (transmittance exhausted or list end),
+//   [1] contributing pairs: those that pass the depth, power and alpha cuts and are blended,
+//   [2] pairs the backward pass walks: entries up to each pixel's last contributor.
+// One thread per pixel, records read straight from global memory.
+__global__ void __launch_bounds__(256) pair_count_kernel(FwdDev a, unsigned long long *__restrict__ counts) {
+  __shared__ unsigned long long s_sum[3][8];
+  const int tile = blockIdx.x;
+  const int tx = tile % a.gx, ty = tile / a.gx;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ix = tx * kTile + (warp & 1) * 8 + (lane & 7), iy = ty * kTile + (warp >> 1) * 4 + (lane >> 3);
+  const bool inside = ix < a.W && iy < a.H;
+  const float px = (float) ix, py = (float) iy;
+  const long long r0 = a.ranges[2 * tile], r1 = a.ranges[2 * tile + 1];
+  unsigned long long traversed = 0, blended = 0, last = 0;
+  if (inside) {
+    float T = 1.0f;
+    for (long long e = r0; e < r1; ++e) {
+      ++traversed;
+      const float4 *rec = a.records + (size_t) a.point_list[e] * (kRecFloats / 4);
+      Hit h;
+      float opa;
+      float3 Tw;
+      if (!eval_pair<false>(rec, px, py, a.near_n, h, opa, Tw)) continue;
+      const float test_T = T * (1 - h.alpha);
+      if (test_T < 0.0001f) break;
+      T = test_T;
+      ++blended;
+      last = (unsigned long long) (e - r0 + 1);
+    }
+  }
+  unsigned long long v[3] = {traversed, blended, last};
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    for (int o = 16; o > 0; o >>= 1) v[k] += __shfl_xor_sync(kFull, v[k], o);
+    if (lane == 0) s_sum[k][warp] = v[k];
+  }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    unsigned long long t = 0;
+    for (int w = 0; w < 8; ++w) t += s_sum[threadIdx.x][w];
+    atomicAdd(counts + threadIdx.x, t);
   }
 }
 
@@ -609,14 +641,26 @@ extern "C" int fsgs_render_forward(const fsgs_render_args *a, fsgs_stream_t stre
   d.out_flow = (float2 *) a->out_flow, d.n_contrib = a->n_contrib;
   d.accum_max_count = a->accum_max_count, d.accum_weights_p = a->accum_weights_p;
   d.accum_weights_count = a->accum_weights_count;
-#ifdef FSGS_STATS
-  d.stats = (unsigned long long *) a->counters;
-#endif
   const int T = d.gx * ((a->H + kTile - 1) / kTile);
   cudaStream_t st = (cudaStream_t) stream;
   if (a->only_image) blend_forward_kernel<false, false><<<T, 256, 0, st>>>(d);
   else if (a->trans_mat_t2) blend_forward_kernel<true, true><<<T, 256, 0, st>>>(d);
   else blend_forward_kernel<true, false><<<T, 256, 0, st>>>(d);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_render_pair_counts(const fsgs_render_args *a, int64_t *counts, fsgs_stream_t stream) {
+  FSGS_REQUIRE(a && counts && a->P >= 0 && a->W > 0 && a->H > 0 && a->ranges);
+  FSGS_REQUIRE(a->P == 0 || (a->records && a->point_list));
+  cudaStream_t st = (cudaStream_t) stream;
+  cudaMemsetAsync(counts, 0, sizeof(int64_t) * 3, st);
+  FwdDev d = {};
+  d.P = a->P, d.W = a->W, d.H = a->H, d.gx = (a->W + kTile - 1) / kTile;
+  d.near_n = a->near_n, d.far_n = a->far_n;
+  d.records = (const float4 *) a->records, d.point_list = a->point_list, d.ranges = (const long long *) a->ranges;
+  const int T = d.gx * ((a->H + kTile - 1) / kTile);
+  pair_count_kernel<<<T, 256, 0, st>>>(d, (unsigned long long *) counts);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

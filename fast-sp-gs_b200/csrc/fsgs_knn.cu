@@ -171,6 +171,10 @@ struct AdamMulti {
   int n;
 };
 
+// the visibility mask as bytes (non-zero: visible) or as floats (> 0: visible)
+__device__ __forceinline__ bool is_visible(const uint8_t *m, long long row) { return m[row] != 0; }
+__device__ __forceinline__ bool is_visible(const float *m, long long row) { return m[row] > 0.0f; }
+
 // e / M and e % M for e < 2^32 with magic = floor(2^32 / M): the high product is the quotient or one less.
 __device__ __forceinline__ void divmod(long long e, int M, unsigned magic, long long &q, int &r) {
   if (magic != 0 && e < (1ll << 32)) {
@@ -187,7 +191,8 @@ __device__ __forceinline__ void divmod(long long e, int M, unsigned magic, long 
 // 16-byte access per array), consecutive threads taking consecutive chunks, so every access is fully coalesced
 // whatever the row length.  A chunk may straddle two Gaussians: elements of an invisible one keep their bits.
 // Chunks without a visible element touch nothing but the mask.
-__global__ void __launch_bounds__(256) adam_masked_multi_kernel(AdamMulti a, const uint8_t *__restrict__ visible,
+template <typename MaskT>
+__global__ void __launch_bounds__(256) adam_masked_multi_kernel(AdamMulti a, const MaskT *__restrict__ visible,
     long long N, float b1, float b2) {
   const long long total = a.chunk_start[a.n];
   for (long long chunk = (long long) blockIdx.x * blockDim.x + threadIdx.x; chunk < total;
@@ -205,7 +210,7 @@ __global__ void __launch_bounds__(256) adam_masked_multi_kernel(AdamMulti a, con
     bool any = false;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      vis[u] = u < cnt && visible[row] != 0;
+      vis[u] = u < cnt && is_visible(visible, row);
       any |= vis[u];
       if (++col == t.M) col = 0, ++row;
     }
@@ -341,8 +346,9 @@ extern "C" int fsgs_adam_masked(float *param, const float *grad, float *exp_avg,
   return FSGS_OK;
 }
 
-extern "C" int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *tensors, const uint8_t *visible,
-    int64_t N, float b1, float b2, fsgs_stream_t stream) {
+template <typename MaskT>
+static int adam_multi_impl(int n_tensors, const fsgs_adam_tensor *tensors, const MaskT *visible, int64_t N, float b1,
+    float b2, fsgs_stream_t stream) {
   FSGS_REQUIRE(n_tensors > 0 && tensors && visible && N >= 0);
   if (n_tensors > FSGS_ADAM_MAX_TENSORS) return FSGS_ERR_LIMIT;
   AdamMulti a;
@@ -359,7 +365,17 @@ extern "C" int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *ten
   if (N == 0) return FSGS_OK;
   const long long total = a.chunk_start[n_tensors];
   const int blocks = (int) ((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-  adam_masked_multi_kernel<<<blocks, 256, 0, (cudaStream_t) stream>>>(a, visible, (long long) N, b1, b2);
+  adam_masked_multi_kernel<MaskT><<<blocks, 256, 0, (cudaStream_t) stream>>>(a, visible, (long long) N, b1, b2);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
+}
+
+extern "C" int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *tensors, const uint8_t *visible,
+    int64_t N, float b1, float b2, fsgs_stream_t stream) {
+  return adam_multi_impl<uint8_t>(n_tensors, tensors, visible, N, b1, b2, stream);
+}
+
+extern "C" int fsgs_adam_masked_multi_fmask(int n_tensors, const fsgs_adam_tensor *tensors, const float *visible,
+    int64_t N, float b1, float b2, fsgs_stream_t stream) {
+  return adam_multi_impl<float>(n_tensors, tensors, visible, N, b1, b2, stream);
 }

@@ -212,9 +212,13 @@ __global__ void __launch_bounds__(256) lbs_warp_backward_kernel(int P, LbsDev l,
 //   S_R = sum w (g_mean (x) p)   S_t = sum w g_mean   S_dr = sum w g_rot_raw   S_ds = sum w g_scale
 // (the quaternion adjoint is linear in dL/dR, so it is applied once to S_R), the block adds the partial sums up and
 // writes the superpoint's row: every output written exactly once, in a fixed order -- bit-reproducible.
+// With `scratch_rot` the rotation gradient of this view goes there (pass 2 reads it) and, like the other per-Gaussian
+// outputs, is ADDED to what g_* already hold (several views accumulated into one gradient).
+template <bool ACC>
 __global__ void __launch_bounds__(256) lbs_backward_points_kernel(int P, LbsDev l, const float *__restrict__ g_means,
     const float2 *__restrict__ g_scales, const float4 *__restrict__ g_rots, float *__restrict__ g_xyz,
-    float2 *__restrict__ g_scaling_raw, float4 *__restrict__ g_rotation_raw, float *__restrict__ g_knn_w) {
+    float2 *__restrict__ g_scaling_raw, float4 *__restrict__ g_rotation_raw, float *__restrict__ g_knn_w,
+    float4 *__restrict__ scratch_rot) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= P) return;
   const float3 p = make_float3(l.xyz[3 * i], l.xyz[3 * i + 1], l.xyz[3 * i + 2]);
@@ -236,8 +240,17 @@ __global__ void __launch_bounds__(256) lbs_backward_points_kernel(int P, LbsDev 
   const float yd = y.x * gy.x + y.y * gy.y + y.z * gy.z + y.w * gy.w;
   const float4 gr = make_float4((gy.x - y.x * yd) * inv, (gy.y - y.y * yd) * inv, (gy.z - y.z * yd) * inv,
       (gy.w - y.w * yd) * inv);
-  g_rotation_raw[i] = gr;
-  g_scaling_raw[i] = make_float2(gs.x * expf(l.scaling_raw[2 * i]), gs.y * expf(l.scaling_raw[2 * i + 1]));
+  const float2 gsr = make_float2(gs.x * expf(l.scaling_raw[2 * i]), gs.y * expf(l.scaling_raw[2 * i + 1]));
+  if (ACC) {
+    scratch_rot[i] = gr;
+    const float4 o = g_rotation_raw[i];
+    g_rotation_raw[i] = make_float4(o.x + gr.x, o.y + gr.y, o.z + gr.z, o.w + gr.w);
+    const float2 os = g_scaling_raw[i];
+    g_scaling_raw[i] = make_float2(os.x + gsr.x, os.y + gsr.y);
+  } else {
+    g_rotation_raw[i] = gr;
+    g_scaling_raw[i] = gsr;
+  }
   float3 gx = make_float3(0, 0, 0);
   for (int k = 0; k < l.K; ++k) {
     const int m = (int) l.knn_idx[(size_t) i * l.K + k];
@@ -248,18 +261,21 @@ __global__ void __launch_bounds__(256) lbs_backward_points_kernel(int P, LbsDev 
         rp.z + __ldg(l.sp_t + 3 * m + 2));
     const float4 a = __ldg(l.sp_dr + m);
     const float2 b = __ldg(l.sp_ds + m);
-    g_knn_w[(size_t) i * l.K + k] = gm.x * moved.x + gm.y * moved.y + gm.z * moved.z +
-                                    (gr.x * a.x + gr.y * a.y + gr.z * a.z + gr.w * a.w) + (gs.x * b.x + gs.y * b.y);
+    const float gw = gm.x * moved.x + gm.y * moved.y + gm.z * moved.z +
+                     (gr.x * a.x + gr.y * a.y + gr.z * a.z + gr.w * a.w) + (gs.x * b.x + gs.y * b.y);
+    if (ACC) g_knn_w[(size_t) i * l.K + k] += gw;
+    else g_knn_w[(size_t) i * l.K + k] = gw;
     const float3 back = quat_rotate_T(q, gm);
     gx.x += w * back.x, gx.y += w * back.y, gx.z += w * back.z;
   }
-  g_xyz[3 * i] = gx.x, g_xyz[3 * i + 1] = gx.y, g_xyz[3 * i + 2] = gx.z;
+  if (ACC) g_xyz[3 * i] += gx.x, g_xyz[3 * i + 1] += gx.y, g_xyz[3 * i + 2] += gx.z;
+  else g_xyz[3 * i] = gx.x, g_xyz[3 * i + 1] = gx.y, g_xyz[3 * i + 2] = gx.z;
 }
 
 constexpr int kSpSums = 18;
 // kSpThreads threads per superpoint: many when there are few superpoints (few blocks would leave the GPU idle), fewer
 // when there are thousands (the block reduction then weighs more than the latency it hides)
-template <int kSpThreads>
+template <int kSpThreads, bool ACC>
 __global__ void __launch_bounds__(kSpThreads) lbs_backward_superpoints_kernel(LbsDev l,
     const int32_t *__restrict__ offsets, const int32_t *__restrict__ pairs, const float *__restrict__ g_means,
     const float2 *__restrict__ g_scales, const float4 *__restrict__ g_rotation_raw, float *__restrict__ g_sp_q,
@@ -300,7 +316,15 @@ __global__ void __launch_bounds__(kSpThreads) lbs_backward_superpoints_kernel(Lb
       t[c] = 0.0f;
       for (int w = 0; w < kSpThreads / 32; ++w) t[c] += s_part[w][c];
     }
-    const float4 gq = quat_adjoint(l.sp_q[m], t);
+    float4 gq = quat_adjoint(l.sp_q[m], t);
+    if (ACC) {  // this block is the only writer of row m: a plain read-modify-write
+      const float4 oq = reinterpret_cast<float4 *>(g_sp_q)[m], od = reinterpret_cast<float4 *>(g_sp_dr)[m];
+      const float2 os = reinterpret_cast<float2 *>(g_sp_ds)[m];
+      gq = make_float4(gq.x + oq.x, gq.y + oq.y, gq.z + oq.z, gq.w + oq.w);
+      t[9] += g_sp_t[3 * m], t[10] += g_sp_t[3 * m + 1], t[11] += g_sp_t[3 * m + 2];
+      t[12] += od.x, t[13] += od.y, t[14] += od.z, t[15] += od.w;
+      t[16] += os.x, t[17] += os.y;
+    }
     reinterpret_cast<float4 *>(g_sp_q)[m] = gq;
     g_sp_t[3 * m] = t[9], g_sp_t[3 * m + 1] = t[10], g_sp_t[3 * m + 2] = t[11];
     reinterpret_cast<float4 *>(g_sp_dr)[m] = make_float4(t[12], t[13], t[14], t[15]);
@@ -330,7 +354,11 @@ struct PreDev {
   float4 *records;
   int32_t *tile_counts;
   unsigned long long *counters;
+  int opacity_is_logit;
 };
+
+// sigmoid in the operation order of the framework's own CUDA kernel (1 / (1 + exp(-x)) in float)
+__device__ __forceinline__ float sigmoid_f32(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 
 __device__ __forceinline__ const float *sh_coef(const PreDev &a, int i, int k) {
   if (a.sh_rest == nullptr) return a.shs + ((size_t) i * a.n_dc + k) * 3;
@@ -352,6 +380,11 @@ template <int N>
 __device__ __forceinline__ void store_rows(float *__restrict__ dst, const float *src, int rows) {
   const int n = rows * N;
   for (int e = threadIdx.x; e < n; e += kPreBlock) dst[e] = src[e];
+}
+template <int N>
+__device__ __forceinline__ void add_rows(float *__restrict__ dst, const float *src, int rows) {
+  const int n = rows * N;
+  for (int e = threadIdx.x; e < n; e += kPreBlock) dst[e] += src[e];
 }
 
 template <bool LBS, bool HIGH_SH>
@@ -414,7 +447,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_forward_kernel(PreDev a,
       vz = pv.z;
       vis = !(vz <= 0.2f);
       if (vis) {
-        opacity = opac_in;
+        opacity = a.opacity_is_logit ? sigmoid_f32(opac_in) : opac_in;
         if (a.trans_precomp == nullptr) {
           if (!LBS) s = a.scales[i], q = a.rots[i];
           splat_matrix(p, s, q, Tw2v, Tv2s, M, nrm);
@@ -656,6 +689,9 @@ struct PreBwdDev {
   float2 *g_scales;
   float4 *g_rots;
   float *g_opac, *g_shs, *g_sh_rest;
+  const float4 *normal_opacity;  // with it, g_opac is the gradient of the opacity LOGIT: g * o * (1 - o)
+  float *visible;                // optional [P] 0/1 mask of the Gaussians with radii > 0
+  int accumulate;                // add to g_opac / g_shs / g_sh_rest / visible instead of writing them
 };
 
 __device__ __forceinline__ float3 cross3(const float3 a, const float3 b) {
@@ -848,14 +884,25 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
   } else if (i < a.P && want_sh) {
     if (staged) {
       for (int o = 0; o < wide; ++o) w_row[o] = 0.0f;
-    } else {
+    } else if (!a.accumulate) {
       float *g_g = a.sh_rest ? a.g_sh_rest : a.g_shs;
       if (g_g)
         for (int o = 0; o < wide; ++o) g_g[(size_t) i * wide + o] = 0.0f;
     }
   }
   if (i < a.P) {
-    a.g_opac[i] = gno.w;
+    float g_o = gno.w;
+    if (a.normal_opacity) {
+      const float o = a.normal_opacity[i].w;
+      g_o = g_o * (1.0f - o) * o;
+    }
+    if (a.accumulate) {
+      if (live) a.g_opac[i] += g_o;
+      if (live && a.visible) a.visible[i] = 1.0f;
+    } else {
+      a.g_opac[i] = g_o;
+      if (a.visible) a.visible[i] = live ? 1.0f : 0.0f;
+    }
     a.g_scales[i] = gs;
     a.g_rots[i] = gq;
     s_mem[kBwdMeans + 3 * t] = gm.x, s_mem[kBwdMeans + 3 * t + 1] = gm.y, s_mem[kBwdMeans + 3 * t + 2] = gm.z;
@@ -871,7 +918,12 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
       const uint32_t bytes = (uint32_t) rows * wide * 4u;
       out_bulk = bulk_ok(g_wide, bytes);
       if (out_bulk) {
-        if (t == 0) bulk_store(g_wide, s_mem + kBwdWide, bytes);
+        if (t == 0) {
+          if (a.accumulate) bulk_reduce_add_f32(g_wide, s_mem + kBwdWide, bytes);
+          else bulk_store(g_wide, s_mem + kBwdWide, bytes);
+        }
+      } else if (a.accumulate) {
+        for (int e = t; e < rows * wide; e += kPreBlock) g_wide[e] += s_mem[kBwdWide + e];
       } else {
         for (int e = t; e < rows * wide; e += kPreBlock) g_wide[e] = s_mem[kBwdWide + e];
       }
@@ -880,7 +932,8 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
   store_rows<3>(a.g_means + (size_t) base * 3, s_mem + kBwdMeans, rows);
   if (want_sh && a.sh_rest && a.g_shs) {
     // the DC gradient; n_dc is 1 in this layout
-    if (a.n_dc == 1) store_rows<3>(a.g_shs + (size_t) base * 3, s_mem + kBwdCol, rows);
+    if (a.n_dc == 1 && a.accumulate) add_rows<3>(a.g_shs + (size_t) base * 3, s_mem + kBwdCol, rows);
+    else if (a.n_dc == 1) store_rows<3>(a.g_shs + (size_t) base * 3, s_mem + kBwdCol, rows);
     else if (i < a.P) {
       float *g = a.g_shs + (size_t) i * a.n_dc * 3;
       g[0] = s_mem[kBwdCol + 3 * t], g[1] = s_mem[kBwdCol + 3 * t + 1], g[2] = s_mem[kBwdCol + 3 * t + 2];
@@ -915,17 +968,28 @@ extern "C" int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs, const float *g
                g->g_sp_dr && g->g_sp_ds);
   cudaStream_t st = (cudaStream_t) stream;
   const int M = lbs->M;
+  const bool acc = g->accumulate != 0;
+  if (acc) FSGS_REQUIRE(lbs->sp_pair_offsets && lbs->sp_pairs && g->scratch_rot);  // grouped pairs only
   if (lbs->sp_pair_offsets && lbs->sp_pairs) {
     const LbsDev d = to_dev(lbs);
-    if (P > 0)
-      lbs_backward_points_kernel<<<ceil_div(P, 256), 256, 0, st>>>(P, d, g_means, (const float2 *) g_scales,
-          (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw, (float4 *) g->g_rotation_raw, g->g_knn_w);
-    if (M < 1024)
-      lbs_backward_superpoints_kernel<512><<<M, 512, 0, st>>>(d, lbs->sp_pair_offsets, lbs->sp_pairs, g_means,
-          (const float2 *) g_scales, (const float4 *) g->g_rotation_raw, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
-    else
-      lbs_backward_superpoints_kernel<128><<<M, 128, 0, st>>>(d, lbs->sp_pair_offsets, lbs->sp_pairs, g_means,
-          (const float2 *) g_scales, (const float4 *) g->g_rotation_raw, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds);
+    float4 *view_rot = acc ? (float4 *) g->scratch_rot : (float4 *) g->g_rotation_raw;  // this view's, read by pass 2
+    if (P > 0) {
+      if (acc)
+        lbs_backward_points_kernel<true><<<ceil_div(P, 256), 256, 0, st>>>(P, d, g_means, (const float2 *) g_scales,
+            (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw, (float4 *) g->g_rotation_raw, g->g_knn_w,
+            view_rot);
+      else
+        lbs_backward_points_kernel<false><<<ceil_div(P, 256), 256, 0, st>>>(P, d, g_means, (const float2 *) g_scales,
+            (const float4 *) g_rots, g->g_xyz, (float2 *) g->g_scaling_raw, (float4 *) g->g_rotation_raw, g->g_knn_w,
+            nullptr);
+    }
+#define FSGS_SP_LAUNCH(T, A)                                                                                       \
+  lbs_backward_superpoints_kernel<T, A><<<M, T, 0, st>>>(d, lbs->sp_pair_offsets, lbs->sp_pairs, g_means,         \
+      (const float2 *) g_scales, view_rot, g->g_sp_q, g->g_sp_t, g->g_sp_dr, g->g_sp_ds)
+    // the superpoint rows are written, never accumulated: every view has its own motion, hence its own gradient
+    if (M < 1024) FSGS_SP_LAUNCH(512, false);
+    else FSGS_SP_LAUNCH(128, false);
+#undef FSGS_SP_LAUNCH
     FSGS_LAUNCH_CHECK();
     return FSGS_OK;
   }
@@ -992,6 +1056,7 @@ extern "C" int fsgs_preprocess_forward(const fsgs_preprocess_args *a, fsgs_strea
   d.normal_opacity = (float4 *) a->normal_opacity, d.depths = a->depths, d.radii = a->radii;
   d.tiles_touched = a->tiles_touched, d.records = (float4 *) a->records, d.tile_counts = a->tile_counts;
   d.counters = (unsigned long long *) a->counters;
+  d.opacity_is_logit = a->opacity_is_logit;
   cudaMemsetAsync(a->tile_counts, 0, sizeof(int32_t) * (size_t) d.gx * d.gy, st);
   cudaMemsetAsync(a->counters, 0, sizeof(int64_t) * FSGS_NUM_COUNTERS, st);
   if (a->P == 0) return FSGS_OK;
@@ -1056,6 +1121,13 @@ extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_
   d.g_normal_opacity = (const float4 *) a->grad_normal_opacity;
   d.g_means = a->grad_means, d.g_scales = (float2 *) a->grad_scales, d.g_rots = (float4 *) a->grad_rots;
   d.g_opac = a->grad_opac, d.g_shs = a->grad_shs, d.g_sh_rest = d.sh_rest ? a->grad_sh_rest : nullptr;
+  d.normal_opacity = (const float4 *) a->normal_opacity, d.visible = a->visible, d.accumulate = a->accumulate;
+  if (a->accumulate && a->sh_degree >= 0) {
+    // only the layouts whose SH rows are staged through shared memory accumulate: degree 1..3, rows of at most 48
+    // floats, the DC coefficient either inside those rows or alone in shs
+    const int wide = d.sh_rest ? a->n_rest * 3 : a->n_dc * 3;
+    if (a->sh_degree < 1 || a->sh_degree > 3 || wide > kWideMax || (d.sh_rest && a->n_dc != 1)) return FSGS_ERR_UNSUPPORTED;
+  }
   if (a->sh_degree > 3) preprocess_backward_kernel<true><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
   else preprocess_backward_kernel<false><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
   FSGS_LAUNCH_CHECK();

@@ -56,6 +56,15 @@ __device__ __forceinline__ void bulk_store(void *dst_gmem, const void *src_smem,
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+// shared -> global with element-wise float addition at the destination (the copy engine's reduction form); same
+// issue and wait rules as bulk_store().
+__device__ __forceinline__ void bulk_reduce_add_f32(void *dst_gmem, const void *src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst_gmem),
+               "r"(smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 __device__ __forceinline__ void bulk_store_wait() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 }  // namespace fsgs

@@ -19,7 +19,7 @@ class LBS(Structure):
 
 class LBSGrads(Structure):
     _fields_ = [("g_xyz", _vp), ("g_scaling_raw", _vp), ("g_rotation_raw", _vp), ("g_knn_w", _vp), ("g_sp_q", _vp),
-                ("g_sp_t", _vp), ("g_sp_dr", _vp), ("g_sp_ds", _vp)]
+                ("g_sp_t", _vp), ("g_sp_dr", _vp), ("g_sp_ds", _vp), ("accumulate", c_int32), ("scratch_rot", _vp)]
 
 
 class AdamTensor(Structure):
@@ -39,14 +39,14 @@ class PreprocessArgs(Structure):
                 ("lbs", POINTER(LBS)), ("warped_means", _vp), ("warped_scales", _vp), ("warped_rots", _vp),
                 ("means2D", _vp), ("colors", _vp), ("trans_mat", _vp), ("inverse_m", _vp), ("normal_opacity", _vp),
                 ("depths", _vp), ("radii", _vp), ("tiles_touched", _vp), ("records", _vp), ("tile_counts", _vp),
-                ("counters", _vp)]
+                ("counters", _vp), ("opacity_is_logit", c_int32)]
 
 
 class BinArgs(Structure):
     _fields_ = [("P", c_int32), ("W", c_int32), ("H", c_int32),
                 ("means2D", _vp), ("inverse_m", _vp), ("depths", _vp), ("opac", _vp), ("radii", _vp),
                 ("tile_counts", _vp), ("counters", _vp), ("capacity", c_int64), ("point_list", _vp), ("ranges", _vp),
-                ("tile_order", _vp), ("workspace", _vp), ("workspace_bytes", c_size_t)]
+                ("tile_order", _vp), ("workspace", _vp), ("workspace_bytes", c_size_t), ("opac_stride", c_int32)]
 
 
 class RenderArgs(Structure):
@@ -74,7 +74,22 @@ class PreprocessBwdArgs(Structure):
                 ("grad_means2D", _vp), ("grad_trans_mat", _vp), ("grad_inverse_m", _vp), ("grad_colors", _vp),
                 ("grad_normal_opacity", _vp),
                 ("grad_means", _vp), ("grad_scales", _vp), ("grad_rots", _vp), ("grad_opac", _vp), ("grad_shs", _vp),
-                ("grad_sh_rest", _vp)]
+                ("grad_sh_rest", _vp), ("normal_opacity", _vp), ("visible", _vp), ("accumulate", c_int32)]
+
+
+class ViewArgs(Structure):
+    _fields_ = [("P", c_int32), ("W", c_int32), ("H", c_int32), ("sh_degree", c_int32), ("n_dc", c_int32),
+                ("n_rest", c_int32), ("near_n", c_float), ("far_n", c_float),
+                ("opacity_raw", _vp), ("sh_dc", _vp), ("sh_rest", _vp), ("lbs", POINTER(LBS)),
+                ("Tw2v", _vp), ("Tv2s", _vp), ("campos", _vp),
+                ("out_color", _vp), ("out_opacity", _vp), ("out_extras", _vp), ("n_contrib", _vp), ("radii", _vp),
+                ("counters", _vp),
+                ("dL_dcolor", _vp), ("dL_dopacity", _vp), ("dL_dextras", _vp),
+                ("g_xyz", _vp), ("g_scaling_raw", _vp), ("g_rotation_raw", _vp), ("g_opacity_raw", _vp),
+                ("g_sh_dc", _vp), ("g_sh_rest", _vp),
+                ("g_knn_w", _vp), ("g_sp_q", _vp), ("g_sp_t", _vp), ("g_sp_dr", _vp), ("g_sp_ds", _vp),
+                ("visible", _vp), ("viewspace_grad", _vp), ("accumulate", c_int32), ("phase", c_int32),
+                ("list_capacity", c_int64), ("workspace", _vp), ("workspace_bytes", c_size_t)]
 
 
 # every symbol include/fsgs.h declares: name -> (restype, argtypes)
@@ -88,6 +103,14 @@ SYMBOLS = {
     "fsgs_knn": (c_int, [c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_adam_masked": (c_int, [_vp, _vp, _vp, _vp, _vp, c_float, c_float, c_float, c_float, c_int64, c_int64, _vp]),
     "fsgs_adam_masked_multi": (c_int, [c_int, POINTER(AdamTensor), _vp, c_int64, c_float, c_float, _vp]),
+    "fsgs_adam_masked_multi_fmask": (c_int, [c_int, POINTER(AdamTensor), _vp, c_int64, c_float, c_float, _vp]),
+    "fsgs_view_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int64, c_int, c_int]),
+    "fsgs_view_pair_counts": (c_int, [POINTER(ViewArgs), _vp, _vp]),
+    "fsgs_stage_timing": (c_int, [c_int]),
+    "fsgs_stage_times": (c_int, [POINTER(c_float), POINTER(c_int32)]),
+    "fsgs_render_pair_counts": (c_int, [POINTER(RenderArgs), _vp, _vp]),
+    "fsgs_view_forward": (c_int, [POINTER(ViewArgs), _vp]),
+    "fsgs_view_backward": (c_int, [POINTER(ViewArgs), _vp]),
     "fsgs_transmat_forward": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_transmat_backward": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_lbs_warp_forward": (c_int, [c_int, POINTER(LBS), _vp, _vp, _vp, _vp]),

@@ -20,9 +20,8 @@ class _L1SSIM(torch.autograd.Function):
         maps = torch.empty(4, C, H, W, device=image.device, dtype=torch.float32)
         sums = torch.zeros(2, device=image.device, dtype=torch.float32)
         p = ops._ptr
-        with ops._timed("ssim_forward"):
-            check(lib().fsgs_ssim_forward(1, C, H, W, C1, C2, p(image), p(target), p(maps[0]), p(maps[1]), p(maps[2]),
-                                          p(maps[3]), p(sums), ops._stream()), "fsgs_ssim_forward")
+        check(lib().fsgs_ssim_forward(1, C, H, W, C1, C2, p(image), p(target), p(maps[0]), p(maps[1]), p(maps[2]),
+                                      p(maps[3]), p(sums), ops._stream()), "fsgs_ssim_forward")
         n = float(C * H * W)
         ctx.save_for_backward(image, target, maps)
         ctx.weights = (lambda_l1 / n, lambda_ssim / n)
@@ -39,15 +38,13 @@ class _L1SSIM(torch.autograd.Function):
         p = ops._ptr
         if g is None:
             # upstream scale lives on the device: keep it there (no synchronisation), scale afterwards
-            with ops._timed("ssim_backward"):
-                check(lib().fsgs_ssim_backward(1, C, H, W, C1, C2, p(image), p(target), None, -w_ssim, w_l1, p(maps[1]),
-                                               p(maps[2]), p(maps[3]), p(out), ops._stream()), "fsgs_ssim_backward")
+            check(lib().fsgs_ssim_backward(1, C, H, W, C1, C2, p(image), p(target), None, -w_ssim, w_l1, p(maps[1]),
+                                           p(maps[2]), p(maps[3]), p(out), ops._stream()), "fsgs_ssim_backward")
             out = out * g_loss
         else:
-            with ops._timed("ssim_backward"):
-                check(lib().fsgs_ssim_backward(1, C, H, W, C1, C2, p(image), p(target), None, -w_ssim * g, w_l1 * g,
-                                               p(maps[1]), p(maps[2]), p(maps[3]), p(out), ops._stream()),
-                      "fsgs_ssim_backward")
+            check(lib().fsgs_ssim_backward(1, C, H, W, C1, C2, p(image), p(target), None, -w_ssim * g, w_l1 * g,
+                                           p(maps[1]), p(maps[2]), p(maps[3]), p(out), ops._stream()),
+                  "fsgs_ssim_backward")
         return out, None, None, None
 
 
@@ -66,11 +63,9 @@ def l1_ssim_value_and_grad(image, target, lambda_l1=0.8, lambda_ssim=0.2):
     grad = torch.empty_like(image)
     n = float(C * H * W)
     p = ops._ptr
-    with ops._timed("ssim_forward"):
-        check(lib().fsgs_ssim_forward(1, C, H, W, C1, C2, p(image), p(target), p(maps[0]), p(maps[1]), p(maps[2]),
-                                      p(maps[3]), p(sums), ops._stream()), "fsgs_ssim_forward")
-    with ops._timed("ssim_backward"):
-        check(lib().fsgs_ssim_backward(1, C, H, W, C1, C2, p(image), p(target), None, -lambda_ssim / n, lambda_l1 / n,
-                                       p(maps[1]), p(maps[2]), p(maps[3]), p(grad), ops._stream()),
-              "fsgs_ssim_backward")
+    check(lib().fsgs_ssim_forward(1, C, H, W, C1, C2, p(image), p(target), p(maps[0]), p(maps[1]), p(maps[2]),
+                                  p(maps[3]), p(sums), ops._stream()), "fsgs_ssim_forward")
+    check(lib().fsgs_ssim_backward(1, C, H, W, C1, C2, p(image), p(target), None, -lambda_ssim / n, lambda_l1 / n,
+                                   p(maps[1]), p(maps[2]), p(maps[3]), p(grad), ops._stream()),
+          "fsgs_ssim_backward")
     return lambda_l1 * (sums[1] / n) + lambda_ssim * (1.0 - sums[0] / n), grad

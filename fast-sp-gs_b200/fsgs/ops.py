@@ -41,32 +41,6 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-# Optional per-launch timing: set TIMERS = {} and every C-ABI launch below is bracketed by a pair of CUDA events
-# recorded on the launching stream; read them back with timer_summary() after a synchronize.
-TIMERS = None
-
-
-class _timed:
-    def __init__(self, name):
-        self.name = name
-
-    def __enter__(self):
-        if TIMERS is not None:
-            self.ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-            self.ev[0].record()
-
-    def __exit__(self, *exc):
-        if TIMERS is not None:
-            self.ev[1].record()
-            TIMERS.setdefault(self.name, []).append(self.ev)
-
-
-def timer_summary():
-    """{name: (launches, mean ms)} of everything recorded since TIMERS was set (synchronises)."""
-    torch.cuda.synchronize()
-    return {k: (len(v), sum(a.elapsed_time(b) for a, b in v) / len(v)) for k, v in (TIMERS or {}).items()}
-
-
 def _ptr(t):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
@@ -146,8 +120,7 @@ def preprocess_launch(W, H, sh_degree, means3D, scales, rotations, opacities, sh
     a.inverse_m, a.normal_opacity, a.depths = _ptr(o["inverse_m"]), _ptr(o["normal_opacity"]), _ptr(o["depths"])
     a.radii, a.tiles_touched, a.records = _ptr(o["radii"]), _ptr(o["tiles_touched"]), _ptr(o["records"])
     a.tile_counts, a.counters = _ptr(o["tile_counts"]), _ptr(o["counters"])
-    with _timed("preprocess_forward"):
-        check(lib().fsgs_preprocess_forward(ctypes.byref(a), _stream()), "fsgs_preprocess_forward")
+    check(lib().fsgs_preprocess_forward(ctypes.byref(a), _stream()), "fsgs_preprocess_forward")
     return o
 
 
@@ -167,8 +140,7 @@ def bin_launch(W, H, o, opacities, capacity):
     b.radii, b.tile_counts, b.counters = _ptr(o["radii"]), _ptr(o["tile_counts"]), _ptr(o["counters"])
     b.capacity, b.point_list, b.ranges, b.tile_order = capacity, _ptr(point_list), _ptr(ranges), _ptr(tile_order)
     b.workspace, b.workspace_bytes = _ptr(ws), ws_bytes
-    with _timed("bin_tiles"):
-        check(lib().fsgs_bin_tiles(ctypes.byref(b), _stream()), "fsgs_bin_tiles")
+    check(lib().fsgs_bin_tiles(ctypes.byref(b), _stream()), "fsgs_bin_tiles")
     return ranges, point_list, tile_order
 
 
@@ -251,8 +223,7 @@ def render_forward_launch(W, H, near_n, far_n, only_image, P, records, point_lis
     a.out_flow, a.n_contrib = _ptr(pixel_flow), _ptr(n_contrib)
     a.accum_max_count, a.accum_weights_p = _ptr(accum_max_count), _ptr(accum_weights_p)
     a.accum_weights_count = _ptr(accum_weights_count)
-    with _timed("blend_forward"):
-        check(lib().fsgs_render_forward(ctypes.byref(a), _stream()), "fsgs_render_forward")
+    check(lib().fsgs_render_forward(ctypes.byref(a), _stream()), "fsgs_render_forward")
     return pixel_colors, pixel_opacity, pixel_extras, pixel_flow, n_contrib
 
 
@@ -320,8 +291,7 @@ def render_backward_launch(W, H, near_n, far_n, P, records, point_list, ranges, 
     a.dL_dcolor, a.dL_dopacity, a.dL_dextras, a.dL_dflow = _ptr(dL_dcolor), _ptr(dL_dopacity), _ptr(dL_dextras), _ptr(dL_dflow)
     a.dL_dcolors, a.dL_dmeans2D, a.dL_dtrans_mat = _ptr(g_col), _ptr(g_m2d), _ptr(g_tm)
     a.dL_dinverse_m, a.dL_dnormal_opacity = _ptr(g_im), _ptr(g_no)
-    with _timed("blend_backward"):
-        check(lib().fsgs_render_backward(ctypes.byref(a), _stream()), "fsgs_render_backward")
+    check(lib().fsgs_render_backward(ctypes.byref(a), _stream()), "fsgs_render_backward")
     return g_col, g_m2d, g_tm, g_im, g_no
 
 
@@ -536,9 +506,8 @@ def fusedssim(C1, C2, img1, img2, train=True):
     B, C, H, W = img1.shape
     ssim_map = torch.empty_like(img1)
     d = [torch.empty_like(img1) for _ in range(3)] if train else [None] * 3
-    with _timed("ssim_forward"):
-        check(lib().fsgs_ssim_forward(B, C, H, W, float(C1), float(C2), _ptr(img1), _ptr(img2), _ptr(ssim_map),
-                                      _ptr(d[0]), _ptr(d[1]), _ptr(d[2]), None, _stream()), "fsgs_ssim_forward")
+    check(lib().fsgs_ssim_forward(B, C, H, W, float(C1), float(C2), _ptr(img1), _ptr(img2), _ptr(ssim_map),
+                                  _ptr(d[0]), _ptr(d[1]), _ptr(d[2]), None, _stream()), "fsgs_ssim_forward")
     if not train:
         d = [torch.empty(0) for _ in range(3)]
     return ssim_map, d[0], d[1], d[2]
@@ -551,10 +520,9 @@ def fusedssim_backward(C1, C2, img1, img2, dL_dmap, dm_dmu1, dm_dsigma1_sq, dm_d
     _need(dL_dmap.shape == img1.shape and dm_dmu1.shape == img1.shape, "fusedssim_backward: shape mismatch")
     B, C, H, W = img1.shape
     out = torch.empty_like(img1)
-    with _timed("ssim_backward"):
-        check(lib().fsgs_ssim_backward(B, C, H, W, float(C1), float(C2), _ptr(img1), _ptr(img2), _ptr(dL_dmap), 0.0,
-                                       0.0, _ptr(dm_dmu1.contiguous()), _ptr(dm_dsigma1_sq.contiguous()),
-                                       _ptr(dm_dsigma12.contiguous()), _ptr(out), _stream()), "fsgs_ssim_backward")
+    check(lib().fsgs_ssim_backward(B, C, H, W, float(C1), float(C2), _ptr(img1), _ptr(img2), _ptr(dL_dmap), 0.0,
+                                   0.0, _ptr(dm_dmu1.contiguous()), _ptr(dm_dsigma1_sq.contiguous()),
+                                   _ptr(dm_dsigma12.contiguous()), _ptr(out), _stream()), "fsgs_ssim_backward")
     return out
 
 

@@ -6,7 +6,7 @@ import torch
 
 from . import _lib
 from ._lib import lib, check
-from .ops import _ptr, _stream, _timed
+from .ops import _ptr, _stream
 
 
 class SparseGaussianAdam(torch.optim.Adam):
@@ -72,6 +72,10 @@ def masked_adam_step(batch, visibility, N, b1=0.9, b2=0.999):
     """``batch``: list of (param, grad, exp_avg, exp_avg_sq, lr_eff, eps) with ``param.numel() % N == 0``.
     Launches ``fsgs_adam_masked_multi`` once per eight tensors."""
     vis = visibility.contiguous()
+    # a float mask (visible where > 0) is the form in which the mask comes out of the gradient all-reduce
+    launch = lib().fsgs_adam_masked_multi_fmask if vis.dtype == torch.float32 else lib().fsgs_adam_masked_multi
+    if vis.dtype != torch.float32 and vis.dtype != torch.uint8:
+        vis = vis.to(torch.uint8) if vis.dtype != torch.bool else vis
     for i in range(0, len(batch), 8):
         chunk = batch[i:i + 8]
         arr = (_lib.AdamTensor * len(chunk))()
@@ -82,6 +86,4 @@ def masked_adam_step(batch, visibility, N, b1=0.9, b2=0.999):
             keep.append(g)
             arr[k].param, arr[k].grad, arr[k].exp_avg, arr[k].exp_avg_sq = p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr()
             arr[k].M, arr[k].lr, arr[k].eps = p.numel() // N, lr, eps
-        with _timed("adam_masked_multi"):
-            check(lib().fsgs_adam_masked_multi(len(chunk), arr, _ptr(vis), int(N), b1, b2, _stream()),
-                  "fsgs_adam_masked_multi")
+        check(launch(len(chunk), arr, _ptr(vis), int(N), b1, b2, _stream()), "fsgs_adam_masked_multi")

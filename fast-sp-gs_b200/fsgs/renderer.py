@@ -3,9 +3,10 @@
 
 Differences from routing the reference's own ``_Fast_Render`` through ``fsgs.install``:
   * the packed render records made by the preprocess kernel go straight to the compositing kernels;
-  * no device-to-host read sizes the tile lists: they are written into a buffer whose capacity follows the
-    pair count seen on earlier frames (``ListCapacity``); the counters come back asynchronously and an
-    overflow raises on the next call or on ``check_overflow()``;
+  * no device-to-host read sizes the tile lists (after a device's first frame, which is sized exactly from a
+    blocking read as the reference sizes every frame): they are written into a buffer whose capacity follows the
+    pair count seen on earlier frames (``ListCapacity``); the counters come back asynchronously, and a frame whose
+    pairs did not fit makes the next render call on that device -- or ``check_overflow()`` -- raise;
   * optionally the superpoint LBS warp is evaluated inside the preprocess kernel (``lbs=...``).
 Results are the same tensors, bit for bit, as through the operator-by-operator path.
 """
@@ -29,9 +30,15 @@ class ListCapacity:
         self._pending = []  # (event, pinned counters, capacity)
         self.overflowed = 0
 
-    def capacity(self, P):
-        self.poll()
+    def capacity(self, P, counters=None):
+        """Entries to provide for the next frame.  Raises if an earlier frame overflowed (its results, and anything
+        computed from them, are invalid).  Without history the pair count of this frame is read from ``counters``
+        (device, written by the preprocess launch already queued): one blocking read, once per device."""
+        self.check_overflow(wait=False)
         if self.high_water == 0:
+            if counters is not None:
+                self.high_water = int(counters[1])
+                return max(self.floor, self.high_water)
             return max(self.floor, 8 * P)
         return max(self.floor, int(self.high_water * self.growth))
 
@@ -146,9 +153,8 @@ def lbs_backward(ts, g_means, g_scales, g_rots, outs=(), pairs=None):
     for name, t in zip(("g_xyz", "g_scaling_raw", "g_rotation_raw", "g_knn_w", "g_sp_q", "g_sp_t", "g_sp_dr",
                         "g_sp_ds"), outs):
         setattr(g, name, t.data_ptr())
-    with ops._timed("lbs_warp_backward"):
-        check(lib().fsgs_lbs_warp_backward(P, ctypes.byref(l), ops._ptr(g_means), ops._ptr(g_scales),
-                                           ops._ptr(g_rots), ctypes.byref(g), ops._stream()), "fsgs_lbs_warp_backward")
+    check(lib().fsgs_lbs_warp_backward(P, ctypes.byref(l), ops._ptr(g_means), ops._ptr(g_scales),
+                                       ops._ptr(g_rots), ctypes.byref(g), ops._stream()), "fsgs_lbs_warp_backward")
     return outs
 
 
@@ -177,7 +183,7 @@ class _FastRender(torch.autograd.Function):
         o = ops.preprocess_launch(W, H, sh_degree, means3D, scales, rotations, opacities, shs, sh_rest, Tw2v, Tv2s,
                                   campos, None, means2D, culling, lbs, warped)
         cap_policy = list_capacity(opacities.device)
-        capacity = cap_policy.capacity(P)
+        capacity = cap_policy.capacity(P, o["counters"])
         ranges, point_list, tile_order = ops.bin_launch(W, H, o, opacities, capacity)
         cap_policy.submit(o["counters"], capacity)
         outs = ops.render_forward_launch(W, H, near_n, far_n, only_image, P, o["records"], point_list, ranges,
@@ -271,8 +277,7 @@ class _FastRender(torch.autograd.Function):
         a.grad_colors, a.grad_normal_opacity = p(g_col), p(g_no)
         a.grad_means, a.grad_scales, a.grad_rots, a.grad_opac = p(gm), p(gs), p(gr), p(go)
         a.grad_shs, a.grad_sh_rest = p(gsh), p(grest)
-        with ops._timed("preprocess_backward"):
-            check(lib().fsgs_preprocess_backward(ctypes.byref(a), ops._stream()), "fsgs_preprocess_backward")
+        check(lib().fsgs_preprocess_backward(ctypes.byref(a), ops._stream()), "fsgs_preprocess_backward")
         if grad_out.get("on_sh_ready") is not None:
             grad_out["on_sh_ready"]()  # the SH gradients are final in stream order: their exchange may start
         if sh_degree < 0:
@@ -333,10 +338,9 @@ class _SurfaceEpilogue(torch.autograd.Function):
         f32 = dict(device=out_extras.device, dtype=torch.float32)
         normals, surf_depth, surf_normal = torch.empty(3, H, W, **f32), torch.empty(1, H, W, **f32), torch.empty(3, H, W, **f32)
         p = ops._ptr
-        with ops._timed("epilogue_forward"):
-            check(lib().fsgs_epilogue_forward(W, H, float(depth_ratio), p(Tw2v), p(Tv2c), p(out_extras), p(opacities),
-                                              p(normals), p(surf_depth), p(surf_normal), ops._stream()),
-                  "fsgs_epilogue_forward")
+        check(lib().fsgs_epilogue_forward(W, H, float(depth_ratio), p(Tw2v), p(Tv2c), p(out_extras), p(opacities),
+                                          p(normals), p(surf_depth), p(surf_normal), ops._stream()),
+              "fsgs_epilogue_forward")
         ctx.save_for_backward(out_extras, opacities, Tw2v, Tv2c)
         ctx.ratio = float(depth_ratio)
         return normals, surf_depth, surf_normal
@@ -350,10 +354,9 @@ class _SurfaceEpilogue(torch.autograd.Function):
         p = ops._ptr
         c = lambda t: None if t is None else t.contiguous()
         g_normals, g_depth, g_surf_normal = c(g_normals), c(g_depth), c(g_surf_normal)
-        with ops._timed("epilogue_backward"):
-            check(lib().fsgs_epilogue_backward(W, H, ctx.ratio, p(Tw2v), p(Tv2c), p(out_extras), p(opacities),
-                                               p(g_normals), p(g_depth), p(g_surf_normal), p(g_extras), ops._stream()),
-                  "fsgs_epilogue_backward")
+        check(lib().fsgs_epilogue_backward(W, H, ctx.ratio, p(Tw2v), p(Tv2c), p(out_extras), p(opacities),
+                                           p(g_normals), p(g_depth), p(g_surf_normal), p(g_extras), ops._stream()),
+              "fsgs_epilogue_backward")
         return g_extras, None, None, None, None
 
 

@@ -1,13 +1,15 @@
 """A minimal dynamic surfel scene: the parameters the reference model owns (``fast_2d_gs/network.py:357``:
 positions, 2 log-scales, rotation, opacity logit, SH DC + 15 rest coefficients = 58 floats per Gaussian), the
 superpoint k-NN / LBS weights (``network.py:498-521``, 'dist' weighting) and one training step
-(warp -> render -> backward -> visibility-masked Adam) as ``train.py:343-412`` runs it, minus losses: the
-upstream image gradient is an input.
+(warp -> render -> backward -> visibility-masked Adam) as ``train.py:343-412`` runs it; the upstream image
+gradient is an input or comes from the fused L1 + SSIM loss.  Training runs on ``fsgs.engine.ViewEngine`` (two C
+calls per view, gradients of several views summed in place, one exchange per step); ``render`` is the autograd
+operator ``GS_2D_fast_render`` for everything else.
 """
 import torch
 
 from . import ops
-from .dist import GradBucket, reduce_visibility
+from .dist import GradBucket
 from .optim import SparseGaussianAdam
 from .renderer import GS_2D_fast_render, group_pairs_by_superpoint, list_capacity
 
@@ -58,6 +60,7 @@ class DynamicScene:
                   dict(params=[self.scaling], lr=LRS["scaling"]), dict(params=[self.rotation], lr=LRS["rotation"])]
         self.optimizer = SparseGaussianAdam(groups, lr=0.0, eps=eps)
         self.bucket = None
+        self.engine = None
 
     @property
     def params(self):
@@ -84,62 +87,106 @@ class DynamicScene:
                                  cam["Tv2s"], cam["campos"], sh_degree=3, sh_features=self.sh_dc,
                                  sh_features_rest=self.sh_rest, lbs=lbs, only_image=only_image, grad_out=grad_out)
 
-    def train_step(self, cam, size, motion, g_images, g_opacity, group=None, distributed=False, g_aux=None):
-        """One iteration: forward, backward with the given upstream gradients on images [3,H,W] and opacity [H,W]
-        (and, with ``g_aux = {"normals": [3,H,W], "distortion": [1,H,W], ...}``, on those entries of the render
-        dictionary), (all-reduce of the gradients and of the visibility mask when ``distributed``), fused masked
-        Adam.  Returns the render dictionary."""
-        if not distributed:
-            out = self.render(cam, size, motion)
-            self._backward(out, g_images, g_opacity, g_aux)
-            self.optimizer.set_before_step(out["visibility_filter"], self.num_points)
-            self.optimizer.step_visible()
-            self._drop_grads()
-            return out
-        # Multi-GPU.  Bucket segments: SH DC, SH rest, visibility mask | position, opacity, scale, rotation.
-        # The backward kernels write into the bucket.  The first three segments (49 of the 59 floats per Gaussian)
-        # are all-reduced as soon as the preprocess adjoint has been queued, beside the LBS adjoint; the rest follows;
-        # Adam runs on the SH tensors while the second exchange is in flight.
+    # ---- training ---------------------------------------------------------------------------------------------
+    def _engine(self, size):
+        from .engine import ViewEngine
+        W, H = (int(v) for v in size)
+        e = self.engine
+        if e is None or (e.W, e.H, e.P) != (W, H, self.num_points):
+            e = self.engine = ViewEngine(self.num_points, W, H, self.K, self.centres.shape[0], self.xyz.device)
+        return e
+
+    def _grad_bucket(self):
+        """One flat buffer for all leaf gradients and the visibility mask (as floats): the backward kernels write and
+        accumulate straight into it, and it is what the ranks exchange.  Segments: SH DC, SH rest, mask | position,
+        opacity, scale, rotation -- the first three are final as soon as the preprocess adjoint has run."""
         if self.bucket is None:
             self.bucket = GradBucket([self.sh_dc, self.sh_rest, self.xyz, self.opacity, self.scaling, self.rotation],
                                      extra=self.num_points, extra_after=1)
-        b = self.bucket
-        early = []
-        grad_out = None
-        if all(p.grad is None for p in self.params):
-            grad_out = dict(sh_features=b.view_of(self.sh_dc), sh_features_rest=b.view_of(self.sh_rest),
-                            xyz=b.view_of(self.xyz), scaling_raw=b.view_of(self.scaling),
-                            rotation_raw=b.view_of(self.rotation),
-                            on_sh_ready=lambda: early.append(b.reduce_span(0, 2, group)))
-        out = self.render(cam, size, motion, grad_out=grad_out)
-        b.extra.copy_(out["visibility_filter"])  # known after the forward: travels with the first exchange
-        self._backward(out, g_images, g_opacity, g_aux)
-        sh_in_place = all(p.grad is not None and p.grad.data_ptr() == b.view_of(p).data_ptr()
-                          for p in (self.sh_dc, self.sh_rest))
-        b.pack()  # copies in what the kernels did not write in place (the opacity gradient)
-        if early and not sh_in_place:
-            # autograd did not adopt the in-place SH gradients (it made copies, which pack() has just moved in): the
-            # early exchange summed stale data; let it finish, then exchange those segments again from fresh contents
-            if early[0] is not None:
-                early[0].wait()
-            b.extra.copy_(out["visibility_filter"])
-            early = [b.reduce_span(0, 2, group)]
-        if early:
-            late = b.reduce_span(3, 6, group)
-        else:  # gradients were not produced in place: one exchange for everything
-            early.append(b.reduce_span(0, 6, group))
-            late = None
+            self.g_knn_w = torch.zeros_like(self.knn_w)
+            M = self.centres.shape[0]
+            z = lambda k: torch.zeros(M, k, device=self.xyz.device)
+            self.motion_grads = dict(sp_q=z(4), sp_t=z(3), sp_dr=z(4), sp_ds=z(2))
+        return self.bucket
+
+    def train_views(self, views, size, group=None, distributed=False):
+        """One iteration over the views this rank owns: for each view forward and backward (``libfsgs`` launches only,
+        two C calls per view), the per-Gaussian gradients of the views summed in place in call order; then -- when
+        ``distributed`` -- ONE exchange of the summed gradients and the visibility mask with the other ranks
+        (split in two all-reduces so that the first overlaps the last view's LBS adjoint and the second the SH part
+        of the optimiser); then the fused visibility-masked Adam.  The reference's serial loop over a batch of views,
+        ``fast_2d_gs/network.py:683-745``, followed by ``train.py:402-405``.
+
+        ``views``: list of dicts with ``cam`` (``Tw2v, Tv2s, campos``), ``motion`` (``sp_q, sp_t, sp_dr, sp_ds``),
+        ``g_images`` -- a [3,H,W] tensor, or a callable ``engine -> [3,H,W]`` evaluated after the view's forward (a
+        loss) --, and optionally ``g_opacity [H,W]``, ``g_extras [8,H,W]``, ``on_motion_grads`` (a callable run after the
+        view's backward has been queued, while ``self.motion_grads`` hold this view's superpoint-motion gradients).
+        Returns the engine, whose ``images / opacity / extras / radii`` are those of the last view."""
+        eng, b = self._engine(size), self._grad_bucket()
+        dst = dict(xyz=b.view_of(self.xyz), scaling=b.view_of(self.scaling), rotation=b.view_of(self.rotation),
+                   opacity=b.view_of(self.opacity), sh_dc=b.view_of(self.sh_dc), sh_rest=b.view_of(self.sh_rest),
+                   visible=b.extra, knn_w=self.g_knn_w, **self.motion_grads)
+        early = late = None
+        for j, v in enumerate(views):
+            eng.forward(self, v["cam"], v["motion"])
+            g_images = v["g_images"]
+            if callable(g_images):
+                g_images = g_images(eng)
+            args = (g_images, v.get("g_opacity"), v.get("g_extras"), dst)
+            if distributed and j == len(views) - 1:
+                eng.backward(*args, accumulate=j > 0, phase=1)
+                early = b.reduce_span(0, 2, group)   # SH gradients and the mask leave while the LBS adjoint runs
+                eng.backward(*args, accumulate=j > 0, phase=2)
+                late = b.reduce_span(3, 6, group)
+            else:
+                eng.backward(*args, accumulate=j > 0)
+            if v.get("on_motion_grads") is not None:
+                v["on_motion_grads"](self.motion_grads)
+        if not views:  # a rank without a view this step still takes part in the exchange, with zeros
+            b.flat.zero_()
+            if distributed:
+                early, late = b.reduce_span(0, 2, group), b.reduce_span(3, 6, group)
         b.adopt()
-        if early[0] is not None:
-            early[0].wait()
-        visible = b.extra > 0
-        self.optimizer.set_before_step(visible, self.num_points)
+        self.optimizer.set_before_step(b.extra, self.num_points)  # float mask: visible where > 0
+        if early is not None:
+            early.wait()
         self.optimizer.step_visible(only=[self.sh_dc, self.sh_rest])
         if late is not None:
             late.wait()
         self.optimizer.step_visible(only=[self.xyz, self.opacity, self.scaling, self.rotation])
         self._drop_grads()
-        return out
+        return eng
+
+    def train_step(self, cam, size, motion, g_images, g_opacity, group=None, distributed=False, g_aux=None):
+        """One iteration on one view with the given upstream gradients on images [3,H,W] and opacity [H,W] (and, with
+        ``g_aux = {"normals": [3,H,W] (world space), "distortion": [1,H,W], "surf_depth": ..., "surf_normal": ...}``,
+        on those entries of the render dictionary).  Returns a dictionary with the view's ``images``, ``opacity``,
+        ``extras``, ``radii`` and ``visibility_filter`` (buffers of the engine: valid until the next view)."""
+        view = dict(cam=cam, motion=motion, g_images=g_images, g_opacity=g_opacity)
+        if g_aux:
+            def with_aux(eng):  # the auxiliary gradient needs the forward's extras: both are evaluated after the forward
+                view["g_extras"] = self._extras_gradient(eng, cam, g_aux)
+                return g_images(eng) if callable(g_images) else g_images
+            view["g_images"] = with_aux
+        eng = self.train_views([view], size, group=group, distributed=distributed)
+        return dict(images=eng.images, opacity=eng.opacity, extras=eng.extras, radii=eng.radii,
+                    visibility_filter=eng.radii > 0)
+
+    def _extras_gradient(self, eng, cam, g_aux, depth_ratio=1.0):
+        """Upstream gradients on the entries of the render dictionary derived from the auxiliary channels -> the
+        gradient of the [8,H,W] channels themselves (adjoint of the epilogue kernel; distortion is channel 5)."""
+        from ._lib import check, lib
+        p = ops._ptr
+        g_extras = torch.empty_like(eng.extras)
+        c = lambda t: None if t is None else t.contiguous()
+        check(lib().fsgs_epilogue_backward(eng.W, eng.H, float(depth_ratio), p(cam["Tw2v"].contiguous()),
+                                           p(cam["Tv2c"].contiguous()), p(eng.extras), p(eng.opacity),
+                                           p(c(g_aux.get("normals"))), p(c(g_aux.get("surf_depth"))),
+                                           p(c(g_aux.get("surf_normal"))), p(g_extras), ops._stream()),
+              "fsgs_epilogue_backward")
+        if g_aux.get("distortion") is not None:
+            g_extras[5:6] += g_aux["distortion"]
+        return g_extras
 
     def train_step_with_loss(self, cam, size, motion, target, lambda_l1=0.8, lambda_ssim=0.2, group=None,
                              distributed=False):
@@ -148,8 +195,8 @@ class DynamicScene:
         from .loss import l1_ssim_value_and_grad
         holder = {}
 
-        def upstream(out):
-            holder["loss"], g = l1_ssim_value_and_grad(out["images"], target, lambda_l1, lambda_ssim)
+        def upstream(eng):
+            holder["loss"], g = l1_ssim_value_and_grad(eng.images, target, lambda_l1, lambda_ssim)
             return g
 
         out = self.train_step(cam, size, motion, upstream, None, group=group, distributed=distributed)
@@ -181,26 +228,18 @@ class DynamicScene:
         self.knn_idx, self.knn_w = rest
         self.knn_idx.superpoint_pairs = group_pairs_by_superpoint(self.knn_idx, self.centres.shape[0])
         self.bucket = None
+        self.engine = None
         return self.num_points
 
     def _drop_grads(self):
         for p in self.params:  # zero_grad(set_to_none=True) without the optimizer's hook and profiling layers
             p.grad = None
 
-    def _backward(self, out, g_images, g_opacity, g_aux):
-        if callable(g_images):  # the upstream image gradient is a function of the rendered result (a loss)
-            g_images = g_images(out)
-        if g_opacity is None:
-            torch.autograd.backward([out["images"]], [g_images])
-            return
-        heads, grads = [out["images"], out["opacity"]], [g_images, g_opacity]
-        for name, g in (g_aux or {}).items():
-            heads.append(out[name])
-            grads.append(g)
-        torch.autograd.backward(heads, grads)
-
     def check(self):
+        """Raise if a tile list overflowed on an earlier view (``render`` path or training views)."""
         list_capacity(self.xyz.device).check_overflow()
+        if self.engine is not None:
+            self.engine.check()
 
 
 def motion_at(sp, centres, device="cuda"):

@@ -91,6 +91,10 @@ typedef struct fsgs_adam_tensor {
 #define FSGS_ADAM_MAX_TENSORS 8
 int fsgs_adam_masked_multi(int n_tensors, const fsgs_adam_tensor *tensors /* host */, const uint8_t *visible,
     int64_t N, float b1, float b2, fsgs_stream_t stream);
+/* The same with the mask as floats (visible where > 0): the form in which the mask travels with the gradients
+ * through one all-reduce (the sum over ranks of 0/1 masks is > 0 exactly where any rank saw the Gaussian). */
+int fsgs_adam_masked_multi_fmask(int n_tensors, const fsgs_adam_tensor *tensors /* host */, const float *visible,
+    int64_t N, float b1, float b2, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Splat -> screen matrix, standalone.
@@ -135,6 +139,12 @@ typedef struct fsgs_lbs_grads {
   float *g_xyz, *g_scaling_raw, *g_rotation_raw; /* [P,3] [P,2] [P,4]  written */
   float *g_knn_w;                                /* [P,K]              written */
   float *g_sp_q, *g_sp_t, *g_sp_dr, *g_sp_ds;    /* [M,*]              zeroed then accumulated */
+  /* accumulate != 0: the per-Gaussian outputs (g_xyz, g_scaling_raw, g_rotation_raw, g_knn_w) are ADDED to instead
+   * of written (the gradients of several views summed in place, views in call order); the superpoint rows g_sp_* are
+   * written as always, because every view has its own motion.  Needs the grouped pairs of fsgs_lbs and scratch_rot
+   * [P,4], which receives this view's rotation gradient. */
+  int32_t accumulate;
+  float *scratch_rot;
 } fsgs_lbs_grads;
 
 int fsgs_lbs_warp_backward(int P, const fsgs_lbs *lbs /* host */, const float *g_means, const float *g_scales,
@@ -167,6 +177,9 @@ typedef struct fsgs_preprocess_args {
   float *records;         /* [P,32] packed render records, or NULL */
   int32_t *tile_counts;   /* [T] pairs per tile; zeroed by the call */
   int64_t *counters;      /* [FSGS_NUM_COUNTERS]; zeroed by the call */
+  /* != 0: opac holds logits; the kernel applies the sigmoid the model applies before its render call
+   * (fast_2d_gs/network.py:611), in the same float operations (1 / (1 + exp(-x))) */
+  int32_t opacity_is_logit;
 } fsgs_preprocess_args;
 
 int fsgs_preprocess_forward(const fsgs_preprocess_args *args /* host */, fsgs_stream_t stream);
@@ -195,6 +208,7 @@ typedef struct fsgs_bin_args {
   int32_t *tile_order;  /* [T] */
   void *workspace;
   size_t workspace_bytes;
+  int32_t opac_stride;  /* floats between consecutive opacities; 0 means 1 (4 reads them out of normal_opacity) */
 } fsgs_bin_args;
 
 size_t fsgs_bin_workspace_bytes(int W, int H, int64_t capacity);
@@ -248,6 +262,14 @@ typedef struct fsgs_render_args {
 } fsgs_render_args;
 
 int fsgs_render_forward(const fsgs_render_args *args /* host */, fsgs_stream_t stream);
+
+/* Work counter (diagnostic; no counterpart in the reference): replays every pixel's walk over its tile's list with
+ * the forward pass's tests (gs_2d_fast_redner.cu:152-191) and writes counts[3] (device, int64):
+ *   [0] traversed (pixel, list entry) pairs: entries visited before the pixel's exit,
+ *   [1] contributing pairs: those that are blended,
+ *   [2] pairs the backward pass walks: entries up to each pixel's last contributor.
+ * Reads records, point_list and ranges of args; the output pointers are ignored. */
+int fsgs_render_pair_counts(const fsgs_render_args *args /* host */, int64_t *counts, fsgs_stream_t stream);
 
 typedef struct fsgs_render_bwd_args {
   int32_t P, W, H;
@@ -332,6 +354,19 @@ typedef struct fsgs_preprocess_bwd_args {
   float *grad_means2D;
   const float *grad_trans_mat, *grad_inverse_m, *grad_colors, *grad_normal_opacity;
   float *grad_means, *grad_scales, *grad_rots, *grad_opac, *grad_shs, *grad_sh_rest; /* last two may be NULL */
+  /* Optional extensions for a training loop that keeps everything on the device (all may stay 0 / NULL):
+   *  normal_opacity [P,4] (the forward output): grad_opac then receives the gradient of the opacity LOGIT,
+   *    g * o * (1 - o), the adjoint of the sigmoid the model applies (network.py:611);
+   *  visible [P] float: 1 for Gaussians with radii > 0, else 0 (the mask of the sparse Adam, in a form that can ride
+   *    in the same all-reduce as the gradients);
+   *  accumulate != 0: grad_opac, grad_shs, grad_sh_rest are ADDED to (rows of culled Gaussians untouched) and
+   *    visible is raised to 1 where visible, never lowered -- the gradients of several views summed in place, in
+   *    call order.  grad_means / grad_scales / grad_rots are always written (they feed the LBS adjoint, which has its
+   *    own accumulate flag).  Supported for sh_degree < 0 and for degrees 1..3 with SH rows of at most 48 floats;
+   *    otherwise FSGS_ERR_UNSUPPORTED. */
+  const float *normal_opacity;
+  float *visible;
+  int32_t accumulate;
 } fsgs_preprocess_bwd_args;
 
 int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *args /* host */, fsgs_stream_t stream);
@@ -352,6 +387,63 @@ int fsgs_epilogue_forward(int W, int H, float depth_ratio, const float *Tw2v, co
 int fsgs_epilogue_backward(int W, int H, float depth_ratio, const float *Tw2v, const float *Tv2c,
     const float *out_extras, const float *out_opacity, const float *g_normals_world, const float *g_surf_depth,
     const float *g_surf_normal, float *g_extras, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * One view of a training iteration in two calls (forward, backward), all intermediates in one workspace.
+ * Covers the body of the reference's per-view loop, fast_2d_gs/network.py:683-745 -- sigmoid of the opacity
+ * logits (:611), superpoint LBS warp (:523-573, 630-645), GS_2D_fast_render -- and the backward autograd derives
+ * from it, down to the gradients of the model's leaves (positions, log-scales, raw rotations, opacity logits,
+ * SH coefficients) and of the superpoint motion.  Launches only; nothing is allocated or synchronised.
+ *
+ * fsgs_view_forward writes out_color [3,H,W], out_opacity [H,W], out_extras [8,H,W], n_contrib [2,H,W], radii
+ * (optional, [P]) and counters.  fsgs_view_backward needs the same struct again (same workspace, untouched since
+ * the forward) plus the upstream gradients: dL_dcolor [3,H,W] is required; dL_dopacity [H,W] may be NULL (zero);
+ * dL_dextras [8,H,W] NULL selects the adjoint without auxiliary channels.  Gradients go to the g_* pointers:
+ * accumulate == 0 writes every row (zeros for culled Gaussians), accumulate != 0 adds to the per-Gaussian gradients
+ * (views summed in call order; g_knn_w must then be given); the superpoint-motion gradients g_sp_* belong to this
+ * view's motion and are always written.  visible [P] floats: 1 where radii > 0 (raised, never lowered,
+ * when accumulating).  viewspace_grad [P,2] (optional) receives the densification proxy of visible Gaussians
+ * (gs_2d_fast_preprocess.cu:605-608).  list_capacity: entries reserved for the tile lists; when
+ * counters[FSGS_CNT_OVERFLOW] comes back non-zero the view was composited from truncated lists.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fsgs_view_args {
+  int32_t P, W, H, sh_degree, n_dc, n_rest;
+  float near_n, far_n;
+  const float *opacity_raw;      /* [P,1] logits */
+  const float *sh_dc, *sh_rest;  /* [P,n_dc,3], [P,n_rest,3] or NULL */
+  const fsgs_lbs *lbs;           /* host pointer: canonical geometry, neighbours, this view's superpoint motion */
+  const float *Tw2v, *Tv2s, *campos;
+  float *out_color, *out_opacity, *out_extras;
+  int32_t *n_contrib;
+  int32_t *radii;     /* [P] or NULL */
+  int64_t *counters;  /* [FSGS_NUM_COUNTERS] */
+  const float *dL_dcolor, *dL_dopacity, *dL_dextras;
+  float *g_xyz, *g_scaling_raw, *g_rotation_raw, *g_opacity_raw, *g_sh_dc, *g_sh_rest;
+  float *g_knn_w, *g_sp_q, *g_sp_t, *g_sp_dr, *g_sp_ds; /* [P,K], [M,4], [M,3], [M,4], [M,2]; NULL: discarded */
+  float *visible;        /* [P] or NULL */
+  float *viewspace_grad; /* [P,2] or NULL */
+  int32_t accumulate;
+  /* backward only: 0 = everything; 1 = up to and including the preprocess adjoint (g_sh_*, g_opacity_raw and visible
+   * are then final in stream order: their exchange may start); 2 = the remaining LBS adjoint */
+  int32_t phase;
+  int64_t list_capacity;
+  void *workspace;
+  size_t workspace_bytes;
+} fsgs_view_args;
+
+size_t fsgs_view_workspace_bytes(int P, int W, int H, int64_t list_capacity, int K, int M);
+/* fsgs_render_pair_counts on the lists of the view last passed to fsgs_view_forward (same struct, same workspace). */
+int fsgs_view_pair_counts(const fsgs_view_args *args /* host */, int64_t *counts, fsgs_stream_t stream);
+/* Optional stage timing of the two calls below (a diagnostic): after fsgs_stage_timing(1), every stage they launch
+ * is bracketed by CUDA events recorded on the call's stream; fsgs_stage_times() waits for the recorded events and
+ * returns, per stage, the summed milliseconds and the number of launches since timing was switched on, then
+ * clears them.  Stages: 0 preprocess forward (LBS warp fused), 1 tile binning, 2 compositing forward,
+ * 3 compositing backward, 4 preprocess backward, 5 LBS backward.  Process-wide state, one thread at a time. */
+#define FSGS_NUM_STAGES 6
+int fsgs_stage_timing(int enable);
+int fsgs_stage_times(float *ms /* host [FSGS_NUM_STAGES] */, int32_t *launches /* host [FSGS_NUM_STAGES] */);
+int fsgs_view_forward(const fsgs_view_args *args /* host */, fsgs_stream_t stream);
+int fsgs_view_backward(const fsgs_view_args *args /* host */, fsgs_stream_t stream);
 
 #ifdef __cplusplus
 }

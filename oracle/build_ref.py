@@ -18,6 +18,11 @@ The reference passes ``-rdc=true`` without a device-link step, which makes the
 stock extension un-importable; no TU above calls a device function of another
 TU, so the flag is simply dropped here.
 
+Besides the kernels, the reference's own Python packages (``fast_2d_gs``, ``utils``: ``*.py`` only) are copied to
+``oracle/_ref/py`` (git-ignored like the rest of ``oracle/_ref``), so that the drop-in test can run the reference's
+unmodified ``_Fast_Render`` / ``SparseGaussianAdam`` / ``utils.cdist_top`` over this library, and the benchmark its
+PyTorch compositor, on a machine that has no reference checkout.
+
 Usage:  python oracle/build_ref.py [--ref /path/to/reference] [--jobs N]
 The output is used by the GPU parity tests (new CUDA == reference CUDA) and as
 a timed baseline; it needs the reference checkout only at build time.
@@ -31,6 +36,8 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
+sys.path.insert(0, HERE)
+from refpath import reference_root  # noqa: E402
 
 UNITS = [
     "src/pybind11.cpp",
@@ -43,15 +50,38 @@ UNITS = [
 ]
 
 
+def copy_python(ref_root):
+    """``*.py`` of the reference's ``fast_2d_gs`` and ``utils`` packages -> oracle/_ref/py (unmodified)."""
+    import shutil
+    dst_root = os.path.join(OUT, "py")
+    n = 0
+    for pkg in ("fast_2d_gs", "utils"):
+        for dirpath, _, files in os.walk(os.path.join(ref_root, pkg)):
+            for f in files:
+                if not f.endswith(".py"):
+                    continue
+                src = os.path.join(dirpath, f)
+                dst = os.path.join(dst_root, os.path.relpath(src, ref_root))
+                os.makedirs(os.path.dirname(dst), exist_ok=True)
+                if not os.path.exists(dst) or os.path.getmtime(dst) < os.path.getmtime(src):
+                    shutil.copy2(src, dst)
+                n += 1
+    print(f"reference python: {n} files under {dst_root}")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=None, help="reference checkout (default: $FSGS_REFERENCE_ROOT, else a "
+                                                "directory named 'reference' beside this repository)")
     ap.add_argument("--jobs", type=int, default=4)
     args = ap.parse_args()
-    cdir = os.path.join(args.ref, "fast_2d_gs", "_C")
-    if not os.path.isdir(cdir):
-        print(f"reference checkout not found at {args.ref}; nothing built")
+    ref_root = reference_root(args.ref)
+    if ref_root is None:
+        print("reference checkout not found; nothing built")
         return 0
+    cdir = os.path.join(ref_root, "fast_2d_gs", "_C")
+    os.makedirs(OUT, exist_ok=True)
+    copy_python(ref_root)
 
     import pybind11
     import torch

@@ -53,6 +53,15 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Threads the parallel loops below use from now on (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void) n;
+#endif
+}
+
 /* Tile rectangle of a splat.  fast_2d_gs/_C/include/gaussian_render.h:33-40
  * (C truncation toward zero, then clamp to the grid). */
 static void tile_rect(float px, float py, int radius, int gx, int gy, int *x0, int *y0, int *x1, int *y1) {

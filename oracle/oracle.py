@@ -40,6 +40,11 @@ def num_threads():
     return lib().orc_num_threads()
 
 
+def set_num_threads(n):
+    """Threads for the oracle's parallel loops from now on (overrides an inherited OMP_NUM_THREADS)."""
+    lib().orc_set_num_threads(ctypes.c_int(int(n)))
+
+
 def _p(t):
     if t is None:
         return ctypes.c_void_p(0)

@@ -19,12 +19,8 @@ What each fixture pins (paths inside the reference project):
   ssim.npz        _ssim (python, five padded convolutions)  fast_2d_gs/losses/ssim.py:48-67  (+ autograd)
 """
 import argparse
-import importlib.abc
-import importlib.machinery
 import os
 import sys
-import types
-from unittest import mock
 
 import numpy as np
 import torch
@@ -32,39 +28,11 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 
-_ABSENT = ("matplotlib", "seaborn", "torchmetrics", "imageio", "lietorch", "plyfile", "pytorch3d", "pykdtree",
-           "diff_surfel_rasterization", "diff_gaussian_rasterization", "dearpygui", "open3d", "trimesh", "lpips",
-           "tensorboard", "tensorboardX", "skimage", "kornia", "cv2", "PIL", "roma", "pycolmap", "mediapy")
-
-
-class _StubFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
-    def find_spec(self, name, path, target=None):
-        if name.split(".")[0] in _ABSENT:
-            try:
-                if name.split(".")[0] in ("cv2", "PIL"):
-                    return None  # present in this image: let the real one load
-            except Exception:
-                pass
-            return importlib.machinery.ModuleSpec(name, self, is_package=True)
-        return None
-
-    def create_module(self, spec):
-        m = mock.MagicMock(name=spec.name)
-        m.__path__ = []
-        m.__name__ = spec.name
-        m.__spec__ = spec
-        m.__loader__ = self
-        return m
-
-    def exec_module(self, module):
-        pass
-
 
 def import_reference(ref):
-    sys.meta_path.insert(0, _StubFinder())
-    sys.path.insert(0, ref)
-    import warnings
-    warnings.filterwarnings("ignore")
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import refpy
+    refpy.import_reference(native=None, root=ref)
     from fast_2d_gs.renderer import gs_2d_fast_render as R
     from fast_2d_gs._C import get_python_function
     from utils import ops_3d
@@ -216,9 +184,15 @@ def make_cdist_top():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=None, help="reference checkout (default: $FSGS_REFERENCE_ROOT, else a "
+                                                "directory named 'reference' beside this repository)")
     ap.add_argument("--only", default=None, help="\"sh\" / \"ssim\": regenerate that fixture alone")
     args = ap.parse_args()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from refpath import reference_root
+    args.ref = reference_root(args.ref)
+    if args.ref is None:
+        raise SystemExit("reference checkout not found: pass --ref or set FSGS_REFERENCE_ROOT")
     torch.set_num_threads(4)
     if args.only == "sh":
         import_reference(args.ref)

@@ -35,7 +35,8 @@ def test_ctypes_structs_match_header_field_order():
     for cname, cls in (("fsgs_preprocess_args", _lib.PreprocessArgs), ("fsgs_bin_args", _lib.BinArgs),
                        ("fsgs_render_args", _lib.RenderArgs), ("fsgs_render_bwd_args", _lib.RenderBwdArgs),
                        ("fsgs_preprocess_bwd_args", _lib.PreprocessBwdArgs), ("fsgs_lbs", _lib.LBS),
-                       ("fsgs_lbs_grads", _lib.LBSGrads), ("fsgs_adam_tensor", _lib.AdamTensor)):
+                       ("fsgs_lbs_grads", _lib.LBSGrads), ("fsgs_adam_tensor", _lib.AdamTensor),
+                       ("fsgs_view_args", _lib.ViewArgs)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
