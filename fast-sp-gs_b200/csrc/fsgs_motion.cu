@@ -1,0 +1,601 @@
+// Per-step superpoint motion: frequency encoding of the superpoint centres and of the time, the time network, the
+// deformation MLP (depth x width, one skip connection), its heads, quaternion normalisation and the re-centring of
+// the translation about each superpoint's own centre -- one kernel forward, two backward -- and the kernel-weighted
+// LBS weights with their adjoint.  Restates, in fp32 SIMT,
+//   fast_2d_gs/network.py:1670-1776  (SC_GS_DeformNetwork: encoders, timenet, linear[], heads)
+//   fast_2d_gs/_C/src/nerf/freqencoder.cu:8-32  (output order: x, then sin(2^d s x), cos(2^d s x) per degree)
+//   fast_2d_gs/network.py:545-549    (q = normalize(g_rot + (0,0,0,1)); t' = t + c - R(q) c, 'LBS_c')
+//   fast_2d_gs/network.py:506-513    (weights = exp(-d^2 / (2 r^2)) * sigma + 1e-7, normalised; r = exp(raw), sigma = sigmoid(raw))
+// The network is 0.5 GFLOP per evaluation on M = 512 rows: a latency problem, not a throughput one.  Each block owns
+// R rows and carries them through every layer with the activations in shared memory, so the eight dependent layers
+// cost no launches and no grid synchronisation; weights ([in, out] row major, so that consecutive threads read
+// consecutive floats) stream from L2.  Tensor cores are not used: the path is specified in fp32 and the whole
+// evaluation is tens of microseconds on the FP32 pipe.
+#include "fsgs_common.cuh"
+
+namespace fsgs {
+
+constexpr int kMotionRows = 8;      // rows (superpoints) per block
+constexpr int kMotionMaxWidth = 256;
+constexpr int kMotionMaxIn = 384;   // widest layer input: width + encodings
+constexpr int kHeadsMax = 16;
+
+struct MotionLayout {
+  int Ep, Et, in0, NH, depth, width, skip, Ht, To;
+  long long time0_W, time0_b, time2_W, time2_b, heads_W, heads_b, total;
+  long long lin_W[16], lin_b[16];
+  int lin_in[16];
+};
+
+static inline long long pad4(long long n) { return (n + 3) & ~3ll; }
+
+static bool motion_layout(const fsgs_motion_cfg *c, MotionLayout &L) {
+  if (!c || c->depth < 2 || c->depth > 16 || c->width < 32 || c->width > kMotionMaxWidth || (c->width & 31)) return false;
+  if (c->skip < 0 || c->skip >= c->depth - 1 || c->deg_p < 0 || c->deg_t < 0) return false;
+  L.Ep = 3 * (2 * c->deg_p + 1), L.Et = 2 * c->deg_t + 1;
+  L.Ht = c->time_out > 0 ? c->time_hidden : 0, L.To = c->time_out > 0 ? c->time_out : L.Et;
+  L.in0 = L.Ep + L.To;
+  L.NH = c->local_frame ? 14 : 10;
+  L.depth = c->depth, L.width = c->width, L.skip = c->skip;
+  if (L.in0 + L.width > kMotionMaxIn || L.in0 > 128 || L.Et > 32 || L.To > 64) return false;
+  if (c->time_out > 0 && (c->time_hidden <= 0 || c->time_hidden > 1024)) return false;
+  long long off = 0;
+  auto take = [&](long long n) {
+    const long long o = off;
+    off += pad4(n);
+    return o;
+  };
+  L.time0_W = L.time0_b = L.time2_W = L.time2_b = 0;
+  if (c->time_out > 0) {
+    L.time0_W = take((long long) L.Et * L.Ht), L.time0_b = take(L.Ht);
+    L.time2_W = take((long long) L.Ht * L.To), L.time2_b = take(L.To);
+  }
+  for (int i = 0; i < L.depth; ++i) {
+    L.lin_in[i] = i == 0 ? L.in0 : (i == L.skip + 1 ? L.width + L.in0 : L.width);
+    L.lin_W[i] = take((long long) L.lin_in[i] * L.width), L.lin_b[i] = take(L.width);
+  }
+  L.heads_W = take((long long) L.width * L.NH), L.heads_b = take(L.NH);
+  L.total = off;
+  return true;
+}
+
+struct MotionDev {
+  MotionLayout L;
+  int M, local_frame;
+  float scale_p, scale_t;
+  const float *points;  // [M,3] superpoint centres
+  const float *t;       // [1]
+  const float *params;
+  float *x0;            // [M, in0]  layer-0 input (encodings + time features)
+  float *h;             // [depth, M, width] post-ReLU activations
+  float *heads;         // [M, NH] raw head outputs: d_xyz 3 | d_scale 3 | d_rot 4 | g_rot 4
+  float *time_hidden;   // [Ht] post-ReLU hidden layer of the time network
+  float4 *sp_q;
+  float *sp_t;
+  float4 *sp_dr;
+  float2 *sp_ds;
+};
+
+// rotation by the unit quaternion q = (x, y, z, w)
+__device__ __forceinline__ float3 q_rot(const float4 q, const float3 p) {
+  const float r00 = 1 - 2 * (q.y * q.y + q.z * q.z), r01 = 2 * (q.x * q.y - q.z * q.w), r02 = 2 * (q.y * q.w + q.x * q.z);
+  const float r10 = 2 * (q.x * q.y + q.z * q.w), r11 = 1 - 2 * (q.x * q.x + q.z * q.z), r12 = 2 * (q.y * q.z - q.x * q.w);
+  const float r20 = 2 * (q.x * q.z - q.y * q.w), r21 = 2 * (q.x * q.w + q.y * q.z), r22 = 1 - 2 * (q.x * q.x + q.y * q.y);
+  return make_float3(r00 * p.x + r01 * p.y + r02 * p.z, r10 * p.x + r11 * p.y + r12 * p.z,
+      r20 * p.x + r21 * p.y + r22 * p.z);
+}
+
+// dL/dq of R(q) given dL/dR (row major)
+__device__ __forceinline__ float4 q_adjoint(const float4 q, const float *dR) {
+  float4 g;
+  g.x = 2 * (-2 * q.x * (dR[4] + dR[8]) + q.y * (dR[1] + dR[3]) + q.z * (dR[2] + dR[6]) + q.w * (dR[7] - dR[5]));
+  g.y = 2 * (q.x * (dR[1] + dR[3]) - 2 * q.y * (dR[0] + dR[8]) + q.z * (dR[5] + dR[7]) + q.w * (dR[2] - dR[6]));
+  g.z = 2 * (q.x * (dR[2] + dR[6]) + q.y * (dR[5] + dR[7]) - 2 * q.z * (dR[0] + dR[4]) + q.w * (dR[3] - dR[1]));
+  g.w = 2 * (q.x * (dR[7] - dR[5]) + q.y * (dR[2] - dR[6]) + q.z * (dR[3] - dR[1]));
+  return g;
+}
+
+// out[e] for one scalar x: x, then (sin, cos)(2^d * scale * x), interleaved with stride `dim` like the reference
+__device__ __forceinline__ void freq_encode(float x, int deg, float scale, int dim, int c, float *out) {
+  out[c] = x;
+  const float xs = x * scale;
+  for (int d = 0; d < deg; ++d) {
+    const float a = scalbnf(xs, d);
+    out[(1 + 2 * d) * dim + c] = sinf(a);
+    out[(2 + 2 * d) * dim + c] = cosf(a);
+  }
+}
+
+// One block = kMotionRows rows through the whole network.  blockDim.x == width.
+__global__ void __launch_bounds__(kMotionMaxWidth) motion_forward_kernel(MotionDev a) {
+  constexpr int R = kMotionRows;
+  __shared__ __align__(16) float s_in[kMotionMaxIn * R];   // [k][r]: the layer's input, k major
+  __shared__ __align__(16) float s_out[kMotionMaxWidth * R];
+  __shared__ float s_x0[R][128];                           // row major copy of the layer-0 input (for the skip)
+  __shared__ float s_te[32];                               // time encoding
+  __shared__ float s_th[1024];                             // time-network hidden layer
+  __shared__ float s_tf[64];                               // time features
+  __shared__ float s_heads[R][kHeadsMax];
+  const MotionLayout &L = a.L;
+  const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R;
+  const int W = L.width;
+  const float *P = a.params;
+
+  // encodings
+  if (j == 0) freq_encode(a.t[0], (L.Et - 1) / 2, a.scale_t, 1, 0, s_te);
+  for (int e = j; e < R * 3; e += nt) {
+    const int r = e / 3, c = e - 3 * r;
+    const int m = row0 + r;
+    freq_encode(m < a.M ? a.points[3 * m + c] : 0.0f, (L.Ep / 3 - 1) / 2, a.scale_p, 3, c, s_x0[r]);
+  }
+  __syncthreads();
+  // time network (the same for every row): hidden = relu(W0^T te + b0), features = W2^T hidden + b2
+  if (L.Ht > 0) {
+    for (int u = j; u < L.Ht; u += nt) {
+      float acc = P[L.time0_b + u];
+      for (int k = 0; k < L.Et; ++k) acc += s_te[k] * P[L.time0_W + (long long) k * L.Ht + u];
+      s_th[u] = fmaxf(acc, 0.0f);
+    }
+    __syncthreads();
+    for (int u = j; u < L.To; u += nt) {
+      float acc = P[L.time2_b + u];
+      for (int k = 0; k < L.Ht; ++k) acc += s_th[k] * P[L.time2_W + (long long) k * L.To + u];
+      s_tf[u] = acc;
+    }
+    if (blockIdx.x == 0)
+      for (int u = j; u < L.Ht; u += nt) a.time_hidden[u] = s_th[u];
+  } else {
+    for (int u = j; u < L.To; u += nt) s_tf[u] = s_te[u];
+  }
+  __syncthreads();
+  for (int e = j; e < R * L.To; e += nt) {
+    const int r = e / L.To, u = e - r * L.To;
+    s_x0[r][L.Ep + u] = s_tf[u];
+  }
+  __syncthreads();
+  for (int e = j; e < R * L.in0; e += nt) {
+    const int r = e / L.in0, k = e - r * L.in0;
+    s_in[k * R + r] = s_x0[r][k];
+    if (row0 + r < a.M) a.x0[(size_t) (row0 + r) * L.in0 + k] = s_x0[r][k];
+  }
+  __syncthreads();
+
+  for (int i = 0; i < L.depth; ++i) {
+    const int in = L.lin_in[i];
+    const float *Wi = P + L.lin_W[i];
+    float acc[R];
+    const float b = P[L.lin_b[i] + j];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = b;
+    for (int k = 0; k < in; ++k) {
+      const float w = __ldg(Wi + (size_t) k * W + j);
+      const float4 a0 = *reinterpret_cast<const float4 *>(s_in + k * R), a1 = *reinterpret_cast<const float4 *>(s_in + k * R + 4);
+      acc[0] += a0.x * w, acc[1] += a0.y * w, acc[2] += a0.z * w, acc[3] += a0.w * w;
+      acc[4] += a1.x * w, acc[5] += a1.y * w, acc[6] += a1.z * w, acc[7] += a1.w * w;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      acc[r] = fmaxf(acc[r], 0.0f);
+      s_out[j * R + r] = acc[r];
+      if (row0 + r < a.M) a.h[((size_t) i * a.M + row0 + r) * W + j] = acc[r];
+    }
+    __syncthreads();
+    // next layer's input: the activations, preceded by the encodings after the skip layer
+    const int lead = (i == L.skip) ? L.in0 : 0;
+    if (lead)
+      for (int e = j; e < R * lead; e += nt) {
+        const int r = e / lead, k = e - r * lead;
+        s_in[k * R + r] = s_x0[r][k];
+      }
+    for (int e = j; e < W * R; e += nt) s_in[lead * R + e] = s_out[e];
+    __syncthreads();
+  }
+
+  // heads on the last activations (s_in[0 .. W*R), k major)
+  for (int e = j; e < R * L.NH; e += nt) {
+    const int r = e / L.NH, o = e - r * L.NH;
+    float acc = P[L.heads_b + o];
+    for (int k = 0; k < W; ++k) acc += s_in[k * R + r] * P[L.heads_W + (long long) k * L.NH + o];
+    s_heads[r][o] = acc;
+    if (row0 + r < a.M) a.heads[(size_t) (row0 + r) * L.NH + o] = acc;
+  }
+  __syncthreads();
+  if (j < R && row0 + j < a.M) {
+    const int m = row0 + j;
+    const float *o = s_heads[j];
+    float4 q = make_float4(0, 0, 0, 1);
+    float3 t = make_float3(o[0], o[1], o[2]);
+    if (a.local_frame) {
+      const float4 u = make_float4(o[10], o[11], o[12], o[13] + 1.0f);
+      const float inv = 1.0f / fmaxf(sqrtf(u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w), 1e-12f);
+      q = make_float4(u.x * inv, u.y * inv, u.z * inv, u.w * inv);
+      const float3 c = make_float3(a.points[3 * m], a.points[3 * m + 1], a.points[3 * m + 2]);
+      const float3 rc = q_rot(q, c);
+      t = make_float3(t.x + c.x - rc.x, t.y + c.y - rc.y, t.z + c.z - rc.z);
+    }
+    a.sp_q[m] = q;
+    a.sp_t[3 * m] = t.x, a.sp_t[3 * m + 1] = t.y, a.sp_t[3 * m + 2] = t.z;
+    a.sp_dr[m] = make_float4(o[6], o[7], o[8], o[9]);
+    a.sp_ds[m] = make_float2(o[3], o[4]);
+  }
+}
+
+struct MotionBwdDev {
+  MotionDev f;
+  const float4 *g_sp_q;
+  const float *g_sp_t;
+  const float4 *g_sp_dr;
+  const float2 *g_sp_ds;
+  float *dpre;     // [depth, M, width] gradient of each layer's pre-activation output
+  float *dheads;   // [M, NH]
+  float *g_tf;     // [To] summed gradient of the time features (zeroed before the launch)
+  float *g_params;
+  int accumulate;
+};
+
+// Backward pass 1: one block = kMotionRows rows back through the heads and the layers; leaves dpre / dheads for the
+// weight-gradient kernel and sums the gradient of the time features.
+__global__ void __launch_bounds__(kMotionMaxWidth) motion_backward_rows_kernel(MotionBwdDev b) {
+  constexpr int R = kMotionRows;
+  __shared__ __align__(16) float s_dy[R * kMotionMaxWidth];  // [r][j]
+  __shared__ __align__(16) float s_dx[R * kMotionMaxIn];     // [r][k]
+  __shared__ float s_gh[R][kHeadsMax];
+  __shared__ float s_gtf[64];
+  const MotionDev &a = b.f;
+  const MotionLayout &L = a.L;
+  const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R, W = L.width;
+  const float *P = a.params;
+  for (int u = j; u < 64; u += nt) s_gtf[u] = 0.0f;
+
+  // adjoint of the epilogue -> gradient of the raw head outputs
+  if (j < R) {
+    float *g = s_gh[j];
+    for (int o = 0; o < kHeadsMax; ++o) g[o] = 0.0f;
+    const int m = row0 + j;
+    if (m < a.M) {
+      const float3 gt = make_float3(b.g_sp_t[3 * m], b.g_sp_t[3 * m + 1], b.g_sp_t[3 * m + 2]);
+      g[0] = gt.x, g[1] = gt.y, g[2] = gt.z;
+      const float2 gs = b.g_sp_ds[m];
+      g[3] = gs.x, g[4] = gs.y;
+      const float4 gr = b.g_sp_dr[m];
+      g[6] = gr.x, g[7] = gr.y, g[8] = gr.z, g[9] = gr.w;
+      if (a.local_frame) {
+        const float *o = a.heads + (size_t) m * L.NH;
+        const float4 u = make_float4(o[10], o[11], o[12], o[13] + 1.0f);
+        const float nrm = fmaxf(sqrtf(u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w), 1e-12f);
+        const float inv = 1.0f / nrm;
+        const float4 q = make_float4(u.x * inv, u.y * inv, u.z * inv, u.w * inv);
+        const float3 c = make_float3(a.points[3 * m], a.points[3 * m + 1], a.points[3 * m + 2]);
+        // t' = t + c - R(q) c  ->  dL/dR = -gt (outer) c
+        float dR[9] = {-gt.x * c.x, -gt.x * c.y, -gt.x * c.z, -gt.y * c.x, -gt.y * c.y, -gt.y * c.z,
+                       -gt.z * c.x, -gt.z * c.y, -gt.z * c.z};
+        float4 gq = q_adjoint(q, dR);
+        const float4 gq_in = b.g_sp_q[m];
+        gq = make_float4(gq.x + gq_in.x, gq.y + gq_in.y, gq.z + gq_in.z, gq.w + gq_in.w);
+        const float d = q.x * gq.x + q.y * gq.y + q.z * gq.z + q.w * gq.w;
+        g[10] = (gq.x - q.x * d) * inv, g[11] = (gq.y - q.y * d) * inv;
+        g[12] = (gq.z - q.z * d) * inv, g[13] = (gq.w - q.w * d) * inv;
+      }
+      for (int o = 0; o < L.NH; ++o) b.dheads[(size_t) m * L.NH + o] = g[o];
+    }
+  }
+  __syncthreads();
+  // gradient of the last activations: dh[r][k] = sum_o g[r][o] Wh[k][o]
+  {
+    float wh[kHeadsMax];
+    for (int o = 0; o < L.NH; ++o) wh[o] = P[L.heads_W + (long long) j * L.NH + o];
+    for (int r = 0; r < R; ++r) {
+      float acc = 0.0f;
+      for (int o = 0; o < L.NH; ++o) acc += s_gh[r][o] * wh[o];
+      s_dy[r * W + j] = acc;
+    }
+  }
+  __syncthreads();
+  for (int i = L.depth - 1; i >= 0; --i) {
+    // through the ReLU; keep the pre-activation gradient for the weight gradients
+    for (int r = 0; r < R; ++r) {
+      const int m = row0 + r;
+      float g = 0.0f;
+      if (m < a.M) {
+        g = a.h[((size_t) i * a.M + m) * W + j] > 0.0f ? s_dy[r * W + j] : 0.0f;
+        b.dpre[((size_t) i * a.M + m) * W + j] = g;
+      }
+      s_dy[r * W + j] = g;
+    }
+    __syncthreads();
+    // dX[r][k] = sum_j dY[r][j] W[k][j]
+    const int in = L.lin_in[i];
+    const float *Wi = P + L.lin_W[i];
+    for (int k = j; k < in; k += nt) {
+      float acc[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+      const float4 *wrow = reinterpret_cast<const float4 *>(Wi + (size_t) k * W);
+      for (int c = 0; c < W / 4; ++c) {
+        const float4 w = __ldg(wrow + c);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float4 d = *reinterpret_cast<const float4 *>(s_dy + r * W + 4 * c);
+          acc[r] += d.x * w.x + d.y * w.y + d.z * w.z + d.w * w.w;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) s_dx[r * kMotionMaxIn + k] = acc[r];
+    }
+    __syncthreads();
+    // split the input gradient: encodings (only their time features carry on) | previous activations
+    const int lead = (i == 0 || i == L.skip + 1) ? L.in0 : 0;
+    if (lead) {
+      for (int u = j; u < L.To; u += nt) {
+        float s = 0.0f;
+        for (int r = 0; r < R; ++r)
+          if (row0 + r < a.M) s += s_dx[r * kMotionMaxIn + L.Ep + u];
+        s_gtf[u] += s;
+      }
+    }
+    if (i > 0)
+      for (int r = 0; r < R; ++r) s_dy[r * W + j] = s_dx[r * kMotionMaxIn + lead + j];
+    __syncthreads();
+  }
+  for (int u = j; u < L.To; u += nt)
+    if (s_gtf[u] != 0.0f) atomicAdd(b.g_tf + u, s_gtf[u]);
+}
+
+// Backward pass 2: weight and bias gradients, one block per 16 x 64 tile of one matrix (dW = X^T dY over all M rows);
+// the last block of the grid runs the time network's backward.
+constexpr int kTileK = 16, kTileJ = 64, kTileR = 32;
+
+__device__ __forceinline__ void store_grad(float *dst, float v, int accumulate) {
+  if (accumulate) *dst += v;
+  else *dst = v;
+}
+
+__global__ void __launch_bounds__(256) motion_backward_weights_kernel(MotionBwdDev b, int tiles_per_layer_k,
+    int tiles_j, int n_layer_blocks, int n_head_blocks) {
+  __shared__ float s_x[kTileR][kTileK + 1];
+  __shared__ float s_dy[kTileR][kTileJ];
+  const MotionDev &a = b.f;
+  const MotionLayout &L = a.L;
+  const int tid = threadIdx.x, W = L.width, M = a.M;
+  int blk = blockIdx.x;
+  if (blk < n_layer_blocks + n_head_blocks) {
+    // which matrix, which tile
+    int i, kt, jt, in, out;
+    const float *dY;
+    long long offW, offb;
+    if (blk < n_layer_blocks) {
+      const int per = tiles_per_layer_k * tiles_j;
+      i = blk / per;
+      const int t = blk - i * per;
+      kt = t / tiles_j, jt = t - kt * tiles_j;
+      in = L.lin_in[i], out = W, dY = b.dpre + (size_t) i * M * W, offW = L.lin_W[i], offb = L.lin_b[i];
+    } else {
+      i = L.depth;  // heads: input = last activations
+      kt = blk - n_layer_blocks, jt = 0;
+      in = W, out = L.NH, dY = b.dheads, offW = L.heads_W, offb = L.heads_b;
+    }
+    const int k0 = kt * kTileK, j0 = jt * kTileJ;
+    if (k0 >= in) return;
+    const int tj = tid & 63, tk = tid >> 6;  // 64 columns x 4 groups of 4 rows of the tile
+    float acc[4] = {0, 0, 0, 0}, accb = 0.0f;
+    for (int r0 = 0; r0 < M; r0 += kTileR) {
+      // X tile [32 rows][16 k]: the layer's input, assembled from the saved pieces
+      for (int e = tid; e < kTileR * kTileK; e += 256) {
+        const int r = e / kTileK, kk = e - r * kTileK, m = r0 + r, k = k0 + kk;
+        float v = 0.0f;
+        if (m < M && k < in) {
+          if (i == 0) v = a.x0[(size_t) m * L.in0 + k];
+          else if (i == L.skip + 1) v = k < L.in0 ? a.x0[(size_t) m * L.in0 + k] : a.h[((size_t) (i - 1) * M + m) * W + (k - L.in0)];
+          else v = a.h[((size_t) (i - 1) * M + m) * W + k];
+        }
+        s_x[r][kk] = v;
+      }
+      for (int e = tid; e < kTileR * kTileJ; e += 256) {
+        const int r = e / kTileJ, jj = e - r * kTileJ, m = r0 + r, jcol = j0 + jj;
+        s_dy[r][jj] = (m < M && jcol < out) ? dY[(size_t) m * out + jcol] : 0.0f;
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int r = 0; r < kTileR; ++r) {
+        const float d = s_dy[r][tj];
+        acc[0] += s_x[r][4 * tk] * d, acc[1] += s_x[r][4 * tk + 1] * d;
+        acc[2] += s_x[r][4 * tk + 2] * d, acc[3] += s_x[r][4 * tk + 3] * d;
+        accb += d;
+      }
+      __syncthreads();
+    }
+    const int jcol = j0 + tj;
+    if (jcol < out) {
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + 4 * tk + u;
+        if (k < in) store_grad(b.g_params + offW + (long long) k * out + jcol, acc[u], b.accumulate);
+      }
+      if (kt == 0 && tk == 0) store_grad(b.g_params + offb + jcol, accb, b.accumulate);
+    }
+    return;
+  }
+  // time network backward (single block): features = W2^T hidden + b2, hidden = relu(W0^T te + b0)
+  if (L.Ht == 0) return;
+  __shared__ float s_te[32], s_ghid[1024];
+  if (tid == 0) freq_encode(a.t[0], (L.Et - 1) / 2, a.scale_t, 1, 0, s_te);
+  for (int u = tid; u < L.Ht; u += 256) {
+    float g = 0.0f;
+    const float hid = a.time_hidden[u];
+    for (int o = 0; o < L.To; ++o) {
+      const float go = b.g_tf[o];
+      g += go * a.params[L.time2_W + (long long) u * L.To + o];
+      store_grad(b.g_params + L.time2_W + (long long) u * L.To + o, hid * go, b.accumulate);
+    }
+    s_ghid[u] = hid > 0.0f ? g : 0.0f;
+  }
+  for (int o = tid; o < L.To; o += 256) store_grad(b.g_params + L.time2_b + o, b.g_tf[o], b.accumulate);
+  __syncthreads();
+  for (int u = tid; u < L.Ht; u += 256) {
+    store_grad(b.g_params + L.time0_b + u, s_ghid[u], b.accumulate);
+    for (int k = 0; k < L.Et; ++k)
+      store_grad(b.g_params + L.time0_W + (long long) k * L.Ht + u, s_te[k] * s_ghid[u], b.accumulate);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// kernel-weighted LBS weights
+// ------------------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256) lbs_weights_forward_kernel(int P, int K, const float *__restrict__ d2,
+    const int64_t *__restrict__ idx, const float *__restrict__ raw_radius, const float *__restrict__ raw_weight,
+    float *__restrict__ w) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  float u[FSGS_KNN_MAX_K], s = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    const int m = (int) idx[(size_t) i * K + k];
+    const float r = expf(raw_radius[m]);
+    float v = expf(-d2[(size_t) i * K + k] / (2.0f * r * r));
+    if (raw_weight) v *= 1.0f / (1.0f + expf(-raw_weight[m]));
+    u[k] = v + 1e-7f;
+    s += u[k];
+  }
+  for (int k = 0; k < K; ++k) w[(size_t) i * K + k] = u[k] / s;
+}
+
+// one block per superpoint over its grouped pairs: no atomics, fixed order
+__global__ void __launch_bounds__(256) lbs_weights_backward_kernel(int K, const float *__restrict__ d2,
+    const int64_t *__restrict__ idx, const float *__restrict__ raw_radius, const float *__restrict__ raw_weight,
+    const float *__restrict__ g_w, const int32_t *__restrict__ offsets, const int32_t *__restrict__ pairs,
+    float *__restrict__ g_radius, float *__restrict__ g_weight, int accumulate) {
+  __shared__ float s_a[8], s_b[8];
+  const int m = blockIdx.x;
+  const float r = expf(raw_radius[m]);
+  const float sg = raw_weight ? 1.0f / (1.0f + expf(-raw_weight[m])) : 1.0f;
+  float ga = 0.0f, gb = 0.0f;
+  for (int e = offsets[m] + threadIdx.x; e < offsets[m + 1]; e += blockDim.x) {
+    const int pair = pairs[e], i = pair / K, kk = pair - i * K;
+    // the row's normalisation: u_k, S, and sum_j g_j w_j
+    float S = 0.0f, gdotw = 0.0f, e_self = 0.0f;
+    for (int k = 0; k < K; ++k) {
+      const int mk = (int) idx[(size_t) i * K + k];
+      const float rk = expf(raw_radius[mk]);
+      const float ek = expf(-d2[(size_t) i * K + k] / (2.0f * rk * rk));
+      const float uk = ek * (raw_weight ? 1.0f / (1.0f + expf(-raw_weight[mk])) : 1.0f) + 1e-7f;
+      S += uk;
+      gdotw += g_w[(size_t) i * K + k] * uk;
+      if (k == kk) e_self = ek;
+    }
+    const float gu = (g_w[pair] - gdotw / S) / S;  // dL/du of this pair
+    const float d = d2[pair];
+    ga += gu * e_self * sg * d / (r * r);          // d u / d raw_radius = e * sigma * d / r^2
+    gb += gu * e_self * sg * (1.0f - sg);          // d u / d raw_weight = e * sigma (1 - sigma)
+  }
+  for (int o = 16; o > 0; o >>= 1) ga += __shfl_xor_sync(0xffffffffu, ga, o), gb += __shfl_xor_sync(0xffffffffu, gb, o);
+  if ((threadIdx.x & 31) == 0) s_a[threadIdx.x >> 5] = ga, s_b[threadIdx.x >> 5] = gb;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ta = 0.0f, tb = 0.0f;
+    for (int w = 0; w < 8; ++w) ta += s_a[w], tb += s_b[w];
+    store_grad(g_radius + m, ta, accumulate);
+    if (g_weight) store_grad(g_weight + m, raw_weight ? tb : 0.0f, accumulate);
+  }
+}
+
+static bool fill_motion(const fsgs_motion_args *a, MotionDev &d) {
+  if (!a || !motion_layout(&a->cfg, d.L)) return false;
+  d.M = a->cfg.M, d.local_frame = a->cfg.local_frame;
+  d.scale_p = a->cfg.scale_p > 0 ? a->cfg.scale_p : 1.0f, d.scale_t = a->cfg.scale_t > 0 ? a->cfg.scale_t : 1.0f;
+  d.points = a->sp_points, d.t = a->t, d.params = a->params;
+  if (d.M <= 0 || !d.points || !d.t || !d.params || !a->workspace) return false;
+  // workspace: x0 | h | heads | time_hidden | dpre | dheads | g_tf
+  float *w = (float *) a->workspace;
+  const size_t M = d.M;
+  d.x0 = w, w += pad4(M * d.L.in0);
+  d.h = w, w += pad4((size_t) d.L.depth * M * d.L.width);
+  d.heads = w, w += pad4(M * d.L.NH);
+  d.time_hidden = w, w += pad4(d.L.Ht > 0 ? d.L.Ht : 4);
+  return true;
+}
+
+static size_t motion_ws_floats(const MotionLayout &L, size_t M) {
+  return pad4(M * L.in0) + 2 * pad4((size_t) L.depth * M * L.width) + 2 * pad4(M * L.NH) + pad4(L.Ht > 0 ? L.Ht : 4) + 64;
+}
+
+}  // namespace fsgs
+
+using namespace fsgs;
+
+extern "C" int64_t fsgs_motion_param_count(const fsgs_motion_cfg *cfg) {
+  MotionLayout L;
+  return motion_layout(cfg, L) ? (int64_t) L.total : -1;
+}
+
+// offsets[0..3] time0_W, time0_b, time2_W, time2_b; then (W, b) of every linear layer; then heads W, b
+extern "C" int fsgs_motion_param_offsets(const fsgs_motion_cfg *cfg, int64_t *offsets, int32_t *inputs) {
+  MotionLayout L;
+  FSGS_REQUIRE(offsets && inputs && motion_layout(cfg, L));
+  offsets[0] = L.time0_W, offsets[1] = L.time0_b, offsets[2] = L.time2_W, offsets[3] = L.time2_b;
+  for (int i = 0; i < L.depth; ++i) offsets[4 + 2 * i] = L.lin_W[i], offsets[5 + 2 * i] = L.lin_b[i], inputs[i] = L.lin_in[i];
+  offsets[4 + 2 * L.depth] = L.heads_W, offsets[5 + 2 * L.depth] = L.heads_b;
+  return FSGS_OK;
+}
+
+extern "C" size_t fsgs_motion_workspace_bytes(const fsgs_motion_cfg *cfg) {
+  MotionLayout L;
+  if (!motion_layout(cfg, L) || cfg->M <= 0) return 0;
+  return sizeof(float) * motion_ws_floats(L, (size_t) cfg->M);
+}
+
+extern "C" int fsgs_motion_forward(const fsgs_motion_args *a, fsgs_stream_t stream) {
+  MotionDev d;
+  FSGS_REQUIRE(fill_motion(a, d));
+  FSGS_REQUIRE(a->sp_q && a->sp_t && a->sp_dr && a->sp_ds);
+  if (a->workspace_bytes < fsgs_motion_workspace_bytes(&a->cfg)) return FSGS_ERR_WORKSPACE;
+  d.sp_q = (float4 *) a->sp_q, d.sp_t = a->sp_t, d.sp_dr = (float4 *) a->sp_dr, d.sp_ds = (float2 *) a->sp_ds;
+  motion_forward_kernel<<<ceil_div(d.M, kMotionRows), d.L.width, 0, (cudaStream_t) stream>>>(d);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_motion_backward(const fsgs_motion_args *a, fsgs_stream_t stream) {
+  MotionBwdDev b;
+  FSGS_REQUIRE(fill_motion(a, b.f));
+  FSGS_REQUIRE(a->g_sp_q && a->g_sp_t && a->g_sp_dr && a->g_sp_ds && a->g_params);
+  if (a->workspace_bytes < fsgs_motion_workspace_bytes(&a->cfg)) return FSGS_ERR_WORKSPACE;
+  const MotionLayout &L = b.f.L;
+  const size_t M = b.f.M;
+  float *w = b.f.time_hidden + pad4(L.Ht > 0 ? L.Ht : 4);
+  b.dpre = w, w += pad4((size_t) L.depth * M * L.width);
+  b.dheads = w, w += pad4(M * L.NH);
+  b.g_tf = w;
+  b.g_sp_q = (const float4 *) a->g_sp_q, b.g_sp_t = a->g_sp_t, b.g_sp_dr = (const float4 *) a->g_sp_dr;
+  b.g_sp_ds = (const float2 *) a->g_sp_ds;
+  b.g_params = a->g_params, b.accumulate = a->accumulate;
+  cudaStream_t st = (cudaStream_t) stream;
+  cudaMemsetAsync(b.g_tf, 0, sizeof(float) * 64, st);
+  motion_backward_rows_kernel<<<ceil_div(b.f.M, kMotionRows), L.width, 0, st>>>(b);
+  FSGS_LAUNCH_CHECK();
+  const int tiles_k = ceil_div(L.in0 + L.width, kTileK);  // enough for the widest input; narrower layers exit early
+  const int tiles_j = ceil_div(L.width, kTileJ);
+  const int n_layer = L.depth * tiles_k * tiles_j, n_head = ceil_div(L.width, kTileK);
+  motion_backward_weights_kernel<<<n_layer + n_head + 1, 256, 0, st>>>(b, tiles_k, tiles_j, n_layer, n_head);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_lbs_weights_forward(int P, int K, const float *d2, const int64_t *idx, const float *raw_radius,
+    const float *raw_weight, float *weights, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && K > 0 && K <= FSGS_KNN_MAX_K && d2 && idx && raw_radius && weights);
+  if (P == 0) return FSGS_OK;
+  lbs_weights_forward_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, K, d2, idx, raw_radius, raw_weight,
+      weights);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_lbs_weights_backward(int P, int K, int M, const float *d2, const int64_t *idx,
+    const float *raw_radius, const float *raw_weight, const float *g_weights, const int32_t *sp_pair_offsets,
+    const int32_t *sp_pairs, float *g_raw_radius, float *g_raw_weight, int accumulate, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && K > 0 && K <= FSGS_KNN_MAX_K && M > 0 && d2 && idx && raw_radius && g_weights);
+  FSGS_REQUIRE(sp_pair_offsets && sp_pairs && g_raw_radius);
+  lbs_weights_backward_kernel<<<M, 256, 0, (cudaStream_t) stream>>>(K, d2, idx, raw_radius, raw_weight, g_weights,
+      sp_pair_offsets, sp_pairs, g_raw_radius, g_raw_weight, accumulate);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}

@@ -92,6 +92,19 @@ class ViewArgs(Structure):
                 ("list_capacity", c_int64), ("workspace", _vp), ("workspace_bytes", c_size_t)]
 
 
+class MotionCfg(Structure):
+    _fields_ = [("M", c_int32), ("depth", c_int32), ("width", c_int32), ("skip", c_int32), ("deg_p", c_int32),
+                ("deg_t", c_int32), ("time_hidden", c_int32), ("time_out", c_int32), ("local_frame", c_int32),
+                ("scale_p", c_float), ("scale_t", c_float)]
+
+
+class MotionArgs(Structure):
+    _fields_ = [("cfg", MotionCfg), ("sp_points", _vp), ("t", _vp), ("params", _vp),
+                ("sp_q", _vp), ("sp_t", _vp), ("sp_dr", _vp), ("sp_ds", _vp),
+                ("g_sp_q", _vp), ("g_sp_t", _vp), ("g_sp_dr", _vp), ("g_sp_ds", _vp), ("g_params", _vp),
+                ("accumulate", c_int32), ("workspace", _vp), ("workspace_bytes", c_size_t)]
+
+
 # every symbol include/fsgs.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "fsgs_status_string": (ctypes.c_char_p, [c_int]),
@@ -105,6 +118,14 @@ SYMBOLS = {
     "fsgs_adam_masked_multi": (c_int, [c_int, POINTER(AdamTensor), _vp, c_int64, c_float, c_float, _vp]),
     "fsgs_adam_masked_multi_fmask": (c_int, [c_int, POINTER(AdamTensor), _vp, c_int64, c_float, c_float, _vp]),
     "fsgs_view_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int64, c_int, c_int]),
+    "fsgs_motion_param_count": (c_int64, [POINTER(MotionCfg)]),
+    "fsgs_motion_param_offsets": (c_int, [POINTER(MotionCfg), POINTER(c_int64), POINTER(c_int32)]),
+    "fsgs_motion_workspace_bytes": (c_size_t, [POINTER(MotionCfg)]),
+    "fsgs_motion_forward": (c_int, [POINTER(MotionArgs), _vp]),
+    "fsgs_motion_backward": (c_int, [POINTER(MotionArgs), _vp]),
+    "fsgs_lbs_weights_forward": (c_int, [c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_lbs_weights_backward": (c_int, [c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, c_int,
+                                          _vp]),
     "fsgs_view_pair_counts": (c_int, [POINTER(ViewArgs), _vp, _vp]),
     "fsgs_stage_timing": (c_int, [c_int]),
     "fsgs_stage_times": (c_int, [POINTER(c_float), POINTER(c_int32)]),

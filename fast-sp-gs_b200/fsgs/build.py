@@ -6,7 +6,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(PKG), "csrc")
 LIB = os.path.join(os.path.dirname(PKG), "lib", "libfsgs.so")
-SOURCES = ["fsgs_preprocess.cu", "fsgs_bin.cu", "fsgs_blend.cu", "fsgs_knn.cu", "fsgs_epilogue.cu", "fsgs_loss.cu", "fsgs_compact.cu", "fsgs_step.cu"]
+SOURCES = ["fsgs_preprocess.cu", "fsgs_bin.cu", "fsgs_blend.cu", "fsgs_knn.cu", "fsgs_epilogue.cu", "fsgs_loss.cu", "fsgs_compact.cu", "fsgs_step.cu", "fsgs_motion.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-extended-lambda", "-Xcompiler", "-fPIC"]
 

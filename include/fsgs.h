@@ -389,6 +389,64 @@ int fsgs_epilogue_backward(int W, int H, float depth_ratio, const float *Tw2v, c
     const float *g_surf_normal, float *g_extras, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Per-step superpoint motion: the deformation network evaluated on the superpoint centres at one time, and the
+ * kernel-weighted LBS weights.
+ * Replaces the PyTorch module chain of SC_GS_DeformNetwork.forward (fast_2d_gs/network.py:1748-1776: frequency
+ * encodings -- fast_2d_gs/_C/src/nerf/freqencoder.cu:8-32 --, time network, `depth` linear layers of `width` units
+ * with ReLU and one skip connection after layer `skip`, heads for translation, scale, rotation and -- local_frame --
+ * the superpoint's own rotation) followed by the head of warp() (network.py:545-549: q = normalize(g_rot + (0,0,0,1)),
+ * t' = t + c - R(q) c) and the adjoint of all of it; and calc_LBS_weight's kernel form (network.py:506-513).
+ * fp32 throughout.  Parameters live in ONE flat buffer (fsgs_motion_param_count floats), every weight matrix stored
+ * [inputs, outputs] row major (the transpose of torch.nn.Linear.weight), sections starting on 16-byte boundaries at
+ * the offsets fsgs_motion_param_offsets reports; g_params has the same layout.  With time_out == 0 there is no time
+ * network and the time encoding itself is appended to the position encoding.  Outputs: sp_q [M,4] unit quaternions
+ * ((0,0,0,1) without local_frame), sp_t [M,3], sp_dr [M,4], sp_ds [M,2] -- the motion fsgs_lbs takes.  The
+ * backward reads the workspace the forward left (same args), takes the gradients of the four outputs and writes
+ * (accumulate != 0: adds to) g_params; positions and time get no gradient (the reference detaches them).
+ * Limits: 32 <= width <= 256 (multiple of 32), depth <= 16, position encoding + time features + width <= 384.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fsgs_motion_cfg {
+  int32_t M;            /* superpoints */
+  int32_t depth, width; /* linear layers, units per layer */
+  int32_t skip;         /* the input encodings are concatenated in front of the output of this layer */
+  int32_t deg_p, deg_t; /* frequency-encoding degrees of position and time */
+  int32_t time_hidden, time_out; /* time network 2*deg_t+1 -> time_hidden -> time_out; time_out == 0: none */
+  int32_t local_frame;  /* != 0: fourth head (rotation of the superpoint about its own centre) */
+  float scale_p, scale_t; /* encoder input scales (<= 0: 1) */
+} fsgs_motion_cfg;
+
+typedef struct fsgs_motion_args {
+  fsgs_motion_cfg cfg;
+  const float *sp_points; /* [M,3] */
+  const float *t;         /* [1] device */
+  const float *params;    /* flat parameter buffer */
+  float *sp_q, *sp_t, *sp_dr, *sp_ds;
+  const float *g_sp_q, *g_sp_t, *g_sp_dr, *g_sp_ds; /* backward only */
+  float *g_params;                                  /* backward only */
+  int32_t accumulate;
+  void *workspace;
+  size_t workspace_bytes;
+} fsgs_motion_args;
+
+int64_t fsgs_motion_param_count(const fsgs_motion_cfg *cfg);
+/* offsets [6 + 2*depth] (floats): time0 W, b, time2 W, b, then W, b of every linear layer, then heads W, b (heads
+ * packed column-wise: translation 3 | scale 3 | rotation 4 | local rotation 4); inputs [depth]: inputs per layer */
+int fsgs_motion_param_offsets(const fsgs_motion_cfg *cfg, int64_t *offsets, int32_t *inputs);
+size_t fsgs_motion_workspace_bytes(const fsgs_motion_cfg *cfg);
+int fsgs_motion_forward(const fsgs_motion_args *args /* host */, fsgs_stream_t stream);
+int fsgs_motion_backward(const fsgs_motion_args *args /* host */, fsgs_stream_t stream);
+
+/* weights [P,K] = normalise(exp(-d2 / (2 r^2)) * sigma + 1e-7), r = exp(raw_radius[idx]), sigma =
+ * sigmoid(raw_weight[idx]) (raw_weight NULL: 1).  Backward: g_weights [P,K] -> g_raw_radius [M], g_raw_weight [M]
+ * (written, or added to when accumulate != 0), one block per superpoint over the grouped pairs of fsgs_lbs (no
+ * atomics); the distances are treated as constants. */
+int fsgs_lbs_weights_forward(int P, int K, const float *d2, const int64_t *idx, const float *raw_radius,
+    const float *raw_weight, float *weights, fsgs_stream_t stream);
+int fsgs_lbs_weights_backward(int P, int K, int M, const float *d2, const int64_t *idx, const float *raw_radius,
+    const float *raw_weight, const float *g_weights, const int32_t *sp_pair_offsets, const int32_t *sp_pairs,
+    float *g_raw_radius, float *g_raw_weight, int accumulate, fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * One view of a training iteration in two calls (forward, backward), all intermediates in one workspace.
  * Covers the body of the reference's per-view loop, fast_2d_gs/network.py:683-745 -- sigmoid of the opacity
  * logits (:611), superpoint LBS warp (:523-573, 630-645), GS_2D_fast_render -- and the backward autograd derives

@@ -17,6 +17,7 @@ What each fixture pins (paths inside the reference project):
   cdist_top.npz   cdist_top / cdist_top_backward CPU branch  _C/src/other/cdist_top.cu:57-81,130-150
   sh_basis_deg7.npz  real SH of degrees 0..7, general definition  utils/ops_3d/spherical_harmonics.py:16-67
   ssim.npz        _ssim (python, five padded convolutions)  fast_2d_gs/losses/ssim.py:48-67  (+ autograd)
+  motion_w64.npz  SC_GS_DeformNetwork (width 64) + head of warp()  fast_2d_gs/network.py:1670-1776, 545-549  (+ autograd)
 """
 import argparse
 import os
@@ -182,11 +183,56 @@ def make_cdist_top():
     npz("cdist_top.npz", x=x, c=c, x5=x5, c5=c5, dist5=d5, idx5=i5, **out)
 
 
+def quat_to_matrix(q):
+    x, y, z, w = q.unbind(-1)
+    return torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (y * w + x * z),
+                        2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w),
+                        2 * (x * z - y * w), 2 * (x * w + y * z), 1 - 2 * (x * x + y * y)], dim=-1).reshape(-1, 3, 3)
+
+
+def make_motion():
+    """The reference's deformation network (SC_GS_DeformNetwork, network.py:1670-1776) at width 64 with its fourth
+    head, evaluated on 37 superpoint centres at one time, followed by the head of warp() (network.py:545-549;
+    lietorch's SO3.act restated as a rotation matrix), and the autograd gradients of every parameter for random
+    upstream gradients on the four motion tensors.  The frequency encoder is the reference's PyTorch twin
+    (freq_encoder.py:62-110): its compiled one (freqencoder.cu) needs a GPU and produces the same layout."""
+    from fast_2d_gs import network as N
+    from fast_2d_gs.freq_encoder import FreqEncoder_torch
+    N.FreqEncoder = FreqEncoder_torch
+    torch.manual_seed(61)
+    net = N.SC_GS_DeformNetwork(D=8, W=64, pos_enc_p_cfg=dict(degree=10), pos_enc_t_cfg=dict(degree=6),
+                                is_blender=True, local_frame=True)
+    g = torch.Generator().manual_seed(62)
+    with torch.no_grad():  # heads that move something (the reference starts them at 1e-5)
+        for head, std in ((net.gaussian_warp, 0.05), (net.gaussian_scaling, 0.02), (net.gaussian_rotation, 0.05),
+                          (net.local_rotation, 0.3)):
+            head.weight.copy_(torch.randn(head.weight.shape, generator=g) * std)
+            head.bias.copy_(torch.randn(head.bias.shape, generator=g) * std)
+        for layer in net.linear:
+            layer.bias.copy_(torch.randn(layer.bias.shape, generator=g) * 0.1)
+    M = 37
+    c = torch.rand(M, 3, generator=g) * 2 - 1
+    t = torch.tensor([0.37])
+    d_xyz, rotation, scaling, local_rot = net(c, t)
+    q = torch.nn.functional.normalize(local_rot + torch.tensor([0.0, 0.0, 0.0, 1.0]), dim=-1)
+    sp_t = d_xyz + c - (quat_to_matrix(q) @ c[..., None])[..., 0]
+    outs = dict(sp_q=q, sp_t=sp_t, sp_dr=rotation, sp_ds=scaling[:, :2])
+    ups = {k: torch.randn(v.shape, generator=g) for k, v in outs.items()}
+    torch.autograd.backward([outs[k] for k in outs], [ups[k] for k in outs])
+    arrs = dict(points=c, t=t)
+    arrs.update({"out_" + k: v for k, v in outs.items()})
+    arrs.update({"up_" + k: v for k, v in ups.items()})
+    for name, p in net.named_parameters():
+        arrs["param_" + name] = p.detach()
+        arrs["grad_" + name] = p.grad
+    npz("motion_w64.npz", **arrs)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=None, help="reference checkout (default: $FSGS_REFERENCE_ROOT, else a "
                                                 "directory named 'reference' beside this repository)")
-    ap.add_argument("--only", default=None, help="\"sh\" / \"ssim\": regenerate that fixture alone")
+    ap.add_argument("--only", default=None, help="\"sh\" / \"ssim\" / \"motion\": regenerate that fixture alone")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     from refpath import reference_root
@@ -201,6 +247,10 @@ def main():
     if args.only == "ssim":
         make_ssim(import_reference(args.ref)[1])
         return
+    if args.only == "motion":
+        import_reference(args.ref)
+        make_motion()
+        return
     make_cdist_top()
     R, get_python_function, ops_3d = import_reference(args.ref)
     make_sh_basis()
@@ -208,6 +258,7 @@ def main():
     make_preprocess(R, ops_3d)
     make_rasterize(R, get_python_function, ops_3d)
     make_ssim(get_python_function)
+    make_motion()
 
 
 if __name__ == "__main__":

@@ -148,3 +148,17 @@ def test_ssim_map_and_adjoint_against_reference_python():
     assert float((m - g["ssim_map"]).abs().max()) < 1e-5
     gx = orc.ssim_backward(g["img1"], g["img2"], g["up"], d1, d2, d3)
     assert _rel_l2(gx, g["g_img1"]) < 1e-5
+
+
+def test_motion_oracle_against_reference_network():
+    """The torch restatement of the deformation network + warp head equals the reference module's outputs and
+    autograd gradients (fixture: width 64, four heads)."""
+    import motion_oracle as mo
+    g = _load("motion_w64.npz")
+    sd = {k[len("param_"):]: v.clone().requires_grad_() for k, v in g.items() if k.startswith("param_")}
+    out = mo.motion(g["points"], g["t"], sd, local_frame=True)
+    for k in ("sp_q", "sp_t", "sp_dr", "sp_ds"):
+        assert torch.allclose(out[k], g["out_" + k], rtol=1e-5, atol=5e-6), k
+    torch.autograd.backward([out[k] for k in out], [g["up_" + k] for k in out])
+    for k, p in sd.items():
+        assert _rel_l2(p.grad, g["grad_" + k]) < 1e-5, k
