@@ -31,6 +31,7 @@ struct GradMap {
 constexpr unsigned kFull = 0xffffffffu;
 
 struct FwdDev {
+  const long long *counters;  // optional: a non-zero overflow counter poisons the frame (NaN) instead of hiding it
   int P, W, H, gx;
   float near_n, far_n;
   const float4 *records;
@@ -183,6 +184,19 @@ __global__ void __launch_bounds__(256) blend_forward_kernel(FwdDev a) {
 
   const long long r0 = a.ranges[2 * tile], r1 = a.ranges[2 * tile + 1];
   const int n = (int) (r1 - r0);
+  if (a.counters && a.counters[FSGS_CNT_OVERFLOW] != 0) {
+    // the tile lists were truncated: a frame composited from them would look plausible and be wrong
+    if (inside) {
+      const float nan = __int_as_float(0x7fc00000);
+      a.out_opacity[pix] = nan;
+      a.n_contrib[pix] = 0, a.n_contrib[HW + pix] = AUX ? -1 : 0;
+      a.out_color[pix] = nan, a.out_color[HW + pix] = nan, a.out_color[2 * HW + pix] = nan;
+      if (AUX)
+        for (int c = 0; c < 8; ++c) a.out_extras[c * HW + pix] = nan;
+      if (FLOW) a.out_flow[pix] = make_float2(nan, nan);
+    }
+    return;
+  }
 
   const float far_scale = a.far_n / (a.far_n - a.near_n);
   bool done = !inside;
@@ -641,6 +655,7 @@ extern "C" int fsgs_render_forward(const fsgs_render_args *a, fsgs_stream_t stre
   d.out_flow = (float2 *) a->out_flow, d.n_contrib = a->n_contrib;
   d.accum_max_count = a->accum_max_count, d.accum_weights_p = a->accum_weights_p;
   d.accum_weights_count = a->accum_weights_count;
+  d.counters = (const long long *) a->counters;
   const int T = d.gx * ((a->H + kTile - 1) / kTile);
   cudaStream_t st = (cudaStream_t) stream;
   if (a->only_image) blend_forward_kernel<false, false><<<T, 256, 0, st>>>(d);

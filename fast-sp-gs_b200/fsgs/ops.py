@@ -207,7 +207,8 @@ def _records_for(means2D, colors, normal_opacity, trans_mat, inverse_m, point_li
 
 
 def render_forward_launch(W, H, near_n, far_n, only_image, P, records, point_list, ranges, tile_order,
-                          trans_mat_t2=None, accum_max_count=None, accum_weights_p=None, accum_weights_count=None):
+                          trans_mat_t2=None, accum_max_count=None, accum_weights_p=None, accum_weights_count=None,
+                          counters=None):
     dev = ranges.device
     f32 = dict(device=dev, dtype=torch.float32)
     pixel_colors = torch.empty(3, H, W, **f32)
@@ -223,6 +224,7 @@ def render_forward_launch(W, H, near_n, far_n, only_image, P, records, point_lis
     a.out_flow, a.n_contrib = _ptr(pixel_flow), _ptr(n_contrib)
     a.accum_max_count, a.accum_weights_p = _ptr(accum_max_count), _ptr(accum_weights_p)
     a.accum_weights_count = _ptr(accum_weights_count)
+    a.counters = _ptr(counters)  # a truncated list (overflow counter set) poisons the frame with NaN
     check(lib().fsgs_render_forward(ctypes.byref(a), _stream()), "fsgs_render_forward")
     return pixel_colors, pixel_opacity, pixel_extras, pixel_flow, n_contrib
 

@@ -5,8 +5,9 @@ Differences from routing the reference's own ``_Fast_Render`` through ``fsgs.ins
   * the packed render records made by the preprocess kernel go straight to the compositing kernels;
   * no device-to-host read sizes the tile lists (after a device's first frame, which is sized exactly from a
     blocking read as the reference sizes every frame): they are written into a buffer whose capacity follows the
-    pair count seen on earlier frames (``ListCapacity``); the counters come back asynchronously, and a frame whose
-    pairs did not fit makes the next render call on that device -- or ``check_overflow()`` -- raise;
+    pair count seen on earlier frames of the same size (``ListCapacity``); the counters come back asynchronously; a
+    frame whose pairs did not fit comes out as NaN in every pixel (never as a plausible picture of truncated lists)
+    and makes the next render call of that size on that device -- or ``check_overflow()`` -- raise;
   * optionally the superpoint LBS warp is evaluated inside the preprocess kernel (``lbs=...``).
 Results are the same tensors, bit for bit, as through the operator-by-operator path.
 """
@@ -75,13 +76,28 @@ class ListCapacity:
 
 
 _capacity = {}
+_last_shape = {}
 
 
-def list_capacity(device=None):
+def list_capacity(device=None, shape=None):
+    """The capacity policy of one device and one frame shape ``(P, W, H)``: pair counts of frames of another size say
+    nothing about this one.  ``shape=None`` gives the policy used last on the device (for ``check_overflow``)."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index
-    if dev not in _capacity:
-        _capacity[dev] = ListCapacity()
-    return _capacity[dev]
+    if shape is None:
+        shape = _last_shape.get(dev)
+    _last_shape[dev] = shape
+    key = (dev, shape)
+    if key not in _capacity:
+        _capacity[key] = ListCapacity()
+    return _capacity[key]
+
+
+def check_overflow(device=None):
+    """Raise if any earlier frame on the device was composited from truncated lists (such frames are all NaN)."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    for (d, _), cap in list(_capacity.items()):
+        if d == dev:
+            cap.check_overflow()
 
 
 def group_pairs_by_superpoint(knn_idx, M):
@@ -182,13 +198,13 @@ class _FastRender(torch.autograd.Function):
             means3D, scales, rotations = warped
         o = ops.preprocess_launch(W, H, sh_degree, means3D, scales, rotations, opacities, shs, sh_rest, Tw2v, Tv2s,
                                   campos, None, means2D, culling, lbs, warped)
-        cap_policy = list_capacity(opacities.device)
+        cap_policy = list_capacity(opacities.device, (P, W, H))
         capacity = cap_policy.capacity(P, o["counters"])
         ranges, point_list, tile_order = ops.bin_launch(W, H, o, opacities, capacity)
         cap_policy.submit(o["counters"], capacity)
         outs = ops.render_forward_launch(W, H, near_n, far_n, only_image, P, o["records"], point_list, ranges,
                                          tile_order, trans_mat_t2, accum_max_count, accum_weights_p,
-                                         accum_weights_count)
+                                         accum_weights_count, counters=o["counters"])
         pixel_colors, pixel_opacity, pixel_extras, pixel_flow, n_contrib = outs
         ctx.cfg = cfg
         ctx.lbs_pairs = getattr(lbs_tensors[3], "superpoint_pairs", None) if use_lbs else None

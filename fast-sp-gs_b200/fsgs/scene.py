@@ -11,7 +11,7 @@ import torch
 from . import ops
 from .dist import GradBucket
 from .optim import SparseGaussianAdam
-from .renderer import GS_2D_fast_render, group_pairs_by_superpoint, list_capacity
+from .renderer import GS_2D_fast_render, check_overflow, group_pairs_by_superpoint
 
 # learning rates of exps/d_nerf.yaml (position lr at its initial value)
 LRS = dict(xyz=1.6e-4, sh_dc=2.5e-3, sh_rest=1.25e-4, opacity=0.05, scaling=5e-3, rotation=1e-3)
@@ -43,7 +43,13 @@ def lbs_weights(d2, idx, mode="dist", temperature=1.0, radius=None, weight=None,
 
 
 class DynamicScene:
-    def __init__(self, surfels, centres, K=3, eps=1e-15, device="cuda", lrs=None):
+    def __init__(self, surfels, centres, K=3, eps=1e-15, device="cuda", lrs=None, motion_net=None, kernel_weights=None,
+                 lr_deform=1.6e-4):
+        """``motion_net``: a ``fsgs.motion.MotionNet``; views may then give a time ``t`` instead of a precomputed
+        ``motion`` and the network is trained with the scene.  ``kernel_weights``: ``(raw_radius [M], raw_weight [M] or
+        None)`` switches the LBS weights to the learnable kernel form of the shipped configuration
+        (network.py:506-513), re-evaluated every step and trained as well.  Both are optimised by a dense Adam at
+        ``lr_deform`` (the reference's deformation-network group, network.py:296-305)."""
         P = lambda t: torch.nn.Parameter(t.to(device).contiguous())
         self.xyz = P(surfels["means"])
         self.scaling = P(surfels["log_scales"])
@@ -53,6 +59,15 @@ class DynamicScene:
         self.sh_rest = P(surfels["sh_rest"])
         self.centres = centres.to(device).contiguous()
         self.K = K
+        self.motion_net = motion_net
+        self.sp_radius = self.sp_weight = None
+        if kernel_weights is not None:
+            self.sp_radius = P(kernel_weights[0])
+            self.sp_weight = P(kernel_weights[1]) if kernel_weights[1] is not None else None
+        self.dense_params = ([motion_net.params] if motion_net is not None else []) + \
+            [p for p in (self.sp_radius, self.sp_weight) if p is not None]
+        self.dense_optimizer = torch.optim.Adam(self.dense_params, lr=lr_deform, eps=eps, fused=True) \
+            if self.dense_params else None
         self.refresh_knn()
         LRS = dict(globals()["LRS"], **(lrs or {}))
         groups = [dict(params=[self.xyz], lr=LRS["xyz"]), dict(params=[self.sh_dc], lr=LRS["sh_dc"]),
@@ -74,8 +89,12 @@ class DynamicScene:
     def refresh_knn(self, mode="dist", **weighting):
         """K nearest superpoints of every Gaussian and their blend weights (``lbs_weights``; default softmax(-d^2))."""
         d2, idx = ops.knn(self.xyz.detach(), self.centres, self.K)
-        self.knn_idx = idx
-        self.knn_w = lbs_weights(d2, idx, mode, **weighting).contiguous()
+        self.knn_idx, self.knn_d2 = idx, d2
+        if self.sp_radius is not None:
+            from .motion import kernel_weights
+            self.knn_w = kernel_weights(d2, idx, self.sp_radius.data, None if self.sp_weight is None else self.sp_weight.data)
+        else:
+            self.knn_w = lbs_weights(d2, idx, mode, **weighting).contiguous()
         # pairs grouped by superpoint: the LBS adjoint then needs no atomics
         self.knn_idx.superpoint_pairs = group_pairs_by_superpoint(idx, self.centres.shape[0])
 
@@ -101,12 +120,13 @@ class DynamicScene:
         accumulate straight into it, and it is what the ranks exchange.  Segments: SH DC, SH rest, mask | position,
         opacity, scale, rotation -- the first three are final as soon as the preprocess adjoint has run."""
         if self.bucket is None:
-            self.bucket = GradBucket([self.sh_dc, self.sh_rest, self.xyz, self.opacity, self.scaling, self.rotation],
-                                     extra=self.num_points, extra_after=1)
+            self.bucket = GradBucket([self.sh_dc, self.sh_rest, self.xyz, self.opacity, self.scaling, self.rotation] +
+                                     self.dense_params, extra=self.num_points, extra_after=1)
             self.g_knn_w = torch.zeros_like(self.knn_w)
             M = self.centres.shape[0]
             z = lambda k: torch.zeros(M, k, device=self.xyz.device)
             self.motion_grads = dict(sp_q=z(4), sp_t=z(3), sp_dr=z(4), sp_ds=z(2))
+            self.motion_buf = dict(sp_q=z(4), sp_t=z(3), sp_dr=z(4), sp_ds=z(2))
         return self.bucket
 
     def train_views(self, views, size, group=None, distributed=False):
@@ -117,7 +137,9 @@ class DynamicScene:
         of the optimiser); then the fused visibility-masked Adam.  The reference's serial loop over a batch of views,
         ``fast_2d_gs/network.py:683-745``, followed by ``train.py:402-405``.
 
-        ``views``: list of dicts with ``cam`` (``Tw2v, Tv2s, campos``), ``motion`` (``sp_q, sp_t, sp_dr, sp_ds``),
+        ``views``: list of dicts with ``cam`` (``Tw2v, Tv2s, campos``), ``motion`` (``sp_q, sp_t, sp_dr, sp_ds``) -- or,
+        with a motion network, ``t`` (float32 CUDA tensor with one element: the motion is then evaluated by the network
+        and the network is trained; all views of a step must use the same form) --,
         ``g_images`` -- a [3,H,W] tensor, or a callable ``engine -> [3,H,W]`` evaluated after the view's forward (a
         loss) --, and optionally ``g_opacity [H,W]``, ``g_extras [8,H,W]``, ``on_motion_grads`` (a callable run after the
         view's backward has been queued, while ``self.motion_grads`` hold this view's superpoint-motion gradients).
@@ -127,8 +149,32 @@ class DynamicScene:
                    opacity=b.view_of(self.opacity), sh_dc=b.view_of(self.sh_dc), sh_rest=b.view_of(self.sh_rest),
                    visible=b.extra, knn_w=self.g_knn_w, **self.motion_grads)
         early = late = None
+        last_seg = len(b.bounds) - 1
+        net, n_timed = self.motion_net, 0
+        if self.sp_radius is not None:  # the kernel weights follow their parameters: one launch per step
+            from .motion import kernel_weights
+            kernel_weights(self.knn_d2, self.knn_idx, self.sp_radius.data,
+                           None if self.sp_weight is None else self.sp_weight.data, out=self.knn_w)
+
+        def after_view(v):
+            nonlocal n_timed
+            if "t" in v:  # this view's motion gradients -> network parameters, summed over the views
+                net.backward(self.motion_grads, b.view_of(net.params), accumulate=n_timed > 0)
+                n_timed += 1
+            if v.get("on_motion_grads") is not None:
+                v["on_motion_grads"](self.motion_grads)
+
+        def after_last_view():
+            if self.sp_radius is not None:
+                from .motion import kernel_weights_backward
+                kernel_weights_backward(self.knn_d2, self.knn_idx, self.sp_radius.data,
+                                        None if self.sp_weight is None else self.sp_weight.data, self.g_knn_w,
+                                        self.knn_idx.superpoint_pairs, b.view_of(self.sp_radius),
+                                        None if self.sp_weight is None else b.view_of(self.sp_weight))
+
         for j, v in enumerate(views):
-            eng.forward(self, v["cam"], v["motion"])
+            motion = net.forward(self.centres, v["t"], out=self.motion_buf) if "t" in v else v["motion"]
+            eng.forward(self, v["cam"], motion)
             g_images = v["g_images"]
             if callable(g_images):
                 g_images = g_images(eng)
@@ -137,15 +183,20 @@ class DynamicScene:
                 eng.backward(*args, accumulate=j > 0, phase=1)
                 early = b.reduce_span(0, 2, group)   # SH gradients and the mask leave while the LBS adjoint runs
                 eng.backward(*args, accumulate=j > 0, phase=2)
-                late = b.reduce_span(3, 6, group)
+                after_view(v)
+                after_last_view()
+                late = b.reduce_span(3, last_seg, group)
             else:
                 eng.backward(*args, accumulate=j > 0)
-            if v.get("on_motion_grads") is not None:
-                v["on_motion_grads"](self.motion_grads)
+                after_view(v)
+                if j == len(views) - 1:
+                    after_last_view()
         if not views:  # a rank without a view this step still takes part in the exchange, with zeros
             b.flat.zero_()
             if distributed:
-                early, late = b.reduce_span(0, 2, group), b.reduce_span(3, 6, group)
+                early, late = b.reduce_span(0, 2, group), b.reduce_span(3, last_seg, group)
+        elif net is not None and n_timed == 0:
+            b.view_of(net.params).zero_()
         b.adopt()
         self.optimizer.set_before_step(b.extra, self.num_points)  # float mask: visible where > 0
         if early is not None:
@@ -154,6 +205,8 @@ class DynamicScene:
         if late is not None:
             late.wait()
         self.optimizer.step_visible(only=[self.xyz, self.opacity, self.scaling, self.rotation])
+        if self.dense_optimizer is not None:
+            self.dense_optimizer.step()
         self._drop_grads()
         return eng
 
@@ -213,7 +266,7 @@ class DynamicScene:
         for p in params:
             st = self.optimizer.state.get(p, {})
             moments += [st.get("exp_avg"), st.get("exp_avg_sq")]
-        extra = [self.knn_idx, self.knn_w]
+        extra = [self.knn_idx, self.knn_w, self.knn_d2]
         rows = [p.data for p in params] + [m for m in moments if m is not None] + extra
         out = ops.compact_rows(rows, keep)
         new_params = [torch.nn.Parameter(t) for t in out[:len(params)]]
@@ -225,19 +278,19 @@ class DynamicScene:
                 st["exp_avg"], st["exp_avg_sq"] = rest.pop(0), rest.pop(0)
                 self.optimizer.state[new] = st
         self.xyz, self.sh_dc, self.sh_rest, self.opacity, self.scaling, self.rotation = new_params
-        self.knn_idx, self.knn_w = rest
+        self.knn_idx, self.knn_w, self.knn_d2 = rest
         self.knn_idx.superpoint_pairs = group_pairs_by_superpoint(self.knn_idx, self.centres.shape[0])
         self.bucket = None
         self.engine = None
         return self.num_points
 
     def _drop_grads(self):
-        for p in self.params:  # zero_grad(set_to_none=True) without the optimizer's hook and profiling layers
+        for p in self.params + self.dense_params:  # zero_grad(set_to_none=True) without the optimizer's hook layers
             p.grad = None
 
     def check(self):
         """Raise if a tile list overflowed on an earlier view (``render`` path or training views)."""
-        list_capacity(self.xyz.device).check_overflow()
+        check_overflow(self.xyz.device)
         if self.engine is not None:
             self.engine.check()
 

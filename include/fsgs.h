@@ -258,7 +258,9 @@ typedef struct fsgs_render_args {
   int32_t *accum_max_count;     /* [P] or NULL */
   float *accum_weights_p;       /* [P] or NULL */
   int32_t *accum_weights_count; /* [P] or NULL */
-  int64_t *counters;            /* or NULL */
+  /* counters of the binning that made the lists, or NULL.  When given and counters[FSGS_CNT_OVERFLOW] != 0 (the
+   * lists were truncated) every output pixel is set to NaN instead of being composited from incomplete lists. */
+  int64_t *counters;
 } fsgs_render_args;
 
 int fsgs_render_forward(const fsgs_render_args *args /* host */, fsgs_stream_t stream);

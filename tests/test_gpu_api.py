@@ -151,38 +151,58 @@ def test_install_exposes_the_reference_operator_names():
 
 
 def test_list_overflow_is_reported():
+    """A frame whose pairs do not fit the list buffer comes out as NaN (never as a plausible picture of truncated
+    lists), the next render call of that size raises, and the capacity has grown by then."""
     from fsgs import renderer
     P, W, H = 20_000, 256, 192
     s, cam = make_scene(P, W, H, seed=8)
-    dev = torch.cuda.current_device()
-    saved = renderer._capacity.get(dev)
-    renderer._capacity[dev] = renderer.ListCapacity(floor=16)
-    renderer._capacity[dev].high_water = 1  # pretend earlier frames were almost empty
+    key = (torch.cuda.current_device(), (P, W, H))
+    saved = renderer._capacity.get(key)
+
+    def starved():
+        renderer._capacity[key] = renderer.ListCapacity(floor=16)
+        renderer._capacity[key].high_water = 1  # pretend earlier frames of this size were almost empty
     try:
+        starved()
         out = _render(s, cam, W, H, only_image=True)
+        assert bool(torch.isnan(out["images"]).all()) and bool(torch.isnan(out["opacity"]).all())
         torch.cuda.synchronize()
         with pytest.raises(RuntimeError, match="overflowed"):
-            renderer._capacity[dev].check_overflow()
+            renderer.check_overflow()
         out2 = _render(s, cam, W, H, only_image=True)  # capacity has grown: this frame is whole
-        renderer._capacity[dev].check_overflow()
-        assert float(out2["opacity"].max()) > 0.5
-        # without an explicit check the NEXT render call raises
-        renderer._capacity[dev] = renderer.ListCapacity(floor=16)
-        renderer._capacity[dev].high_water = 1
+        renderer.check_overflow()
+        assert float(out2["opacity"].detach().max()) > 0.5
+        # without an explicit check the NEXT render call of this size raises
+        starved()
         _render(s, cam, W, H, only_image=True)
         torch.cuda.synchronize()
         with pytest.raises(RuntimeError, match="overflowed"):
             _render(s, cam, W, H, only_image=True)
-        # a device without history sizes its first frame exactly (one blocking read): no overflow, whole frame
-        renderer._capacity[dev] = renderer.ListCapacity(floor=16)
+        # a frame size without history is sized exactly (one blocking read): no overflow, whole frame
+        renderer._capacity[key] = renderer.ListCapacity(floor=16)
         out3 = _render(s, cam, W, H, only_image=True)
-        renderer._capacity[dev].check_overflow()
+        renderer.check_overflow()
         assert torch.equal(out3["images"], out2["images"])
+        # the training engine: same poison, same report
+        from fsgs import workloads as wl
+        from fsgs.scene import DynamicScene, motion_at
+        surf = wl.surfels(P, seed=8, log_scale_mean=-3.0)
+        sp = wl.superpoints(surf["means"], M=32, seed=1)
+        scene = DynamicScene(surf, sp["centres"], K=3, device="cuda")
+        eng = scene._engine((W, H))
+        eng._reserve(16)
+        eng.forward(scene, cam, motion_at(sp, sp["centres"], "cuda"))
+        assert bool(torch.isnan(eng.images).all())
+        with pytest.raises(RuntimeError, match="overflowed"):
+            eng.check()
+        eng.forward(scene, cam, motion_at(sp, sp["centres"], "cuda"))
+        eng.check()
+        assert bool(torch.isfinite(eng.images).all())
     finally:
         if saved is not None:
-            renderer._capacity[dev] = saved
+            renderer._capacity[key] = saved
         else:
-            del renderer._capacity[dev]
+            renderer._capacity.pop(key, None)
 
 
 def test_epilogue_kernel_vs_torch_chain():

@@ -112,3 +112,74 @@ def test_kernel_weights_vs_oracle(P, M, K, with_weight):
     assert rel_l2(g_r, rr.grad) < GRAD_TOL
     if with_weight:
         assert rel_l2(g_w, rw.grad) < GRAD_TOL
+
+
+def test_scene_trains_the_motion_network_and_kernel_weights():
+    """``train_views`` with a time per view: the network's and the kernel weights' gradients (summed over two views,
+    through LBS adjoint -> motion operator / weight kernel) and the dense Adam step against the same iteration built
+    from the torch oracle of the motion, the autograd render operator and torch's Adam."""
+    from fsgs import workloads as wl
+    from fsgs.motion import MotionNet
+    from fsgs.scene import DynamicScene
+    W, H, P, M = 160, 120, 5000, 64
+    surf = wl.surfels(P, seed=5, log_scale_mean=-3.2)
+    centres = wl.superpoints(surf["means"], M=M, seed=1)["centres"]
+    cams = [{k: v.cuda() for k, v in wl.camera(W, H, eye=e).items()} for e in ((0.0, 0.0, 4.0), (1.0, 0.5, 3.5))]
+    gen = torch.Generator().manual_seed(9)
+    ups = [(torch.randn(3, H, W, generator=gen).cuda(), torch.randn(H, W, generator=gen).cuda()) for _ in range(2)]
+    ts = [torch.tensor([0.2]).cuda(), torch.tensor([0.7]).cuda()]
+    raw_r, raw_w = torch.full((M,), -1.2), torch.randn(M, generator=gen) * 0.5
+
+    def make():
+        net = MotionNet(M, width=64, local_frame=True, seed=4)
+        g2 = torch.Generator().manual_seed(5)
+        with torch.no_grad():
+            v = net.views()
+            v["heads.weight"].copy_(torch.randn(v["heads.weight"].shape, generator=g2) * 0.02)
+        return DynamicScene(surf, centres, K=3, device="cuda", motion_net=net, kernel_weights=(raw_r, raw_w),
+                            lr_deform=1e-3), net
+
+    a, net_a = make()
+    b, net_b = make()
+    _, net_a_twin = make()   # same parameters as net_a before the step: supplies the native motion values to route b
+    views = [dict(cam=cams[k], t=ts[k], g_images=ups[k][0], g_opacity=ups[k][1]) for k in (0, 1)]
+    for _ in range(1):  # one iteration: the second already starts from parameters that differ by sign-like Adam steps
+        a.train_views(views, (W, H))
+        # the same iteration by autograd
+        flat = net_b.params
+        sd = _reference_view(net_b, flat)
+        # values of the native kernels, derivatives of the oracle: the rendering is so sensitive to the motion (a shift
+        # of 1e-7 moves splats across alpha and tile cuts) that the 1e-6 agreement of the two evaluations would
+        # otherwise show up as per-mille noise in every gradient
+        snap = lambda ref, native: ref + (native - ref).detach()
+        b.knn_w = snap(mo.kernel_weights(b.knn_d2, b.knn_idx, b.sp_radius, b.sp_weight), a.knn_w)
+        vis = None
+        for k in (0, 1):
+            native = net_a_twin.forward(b.centres, ts[k])
+            motion = {n: snap(t, native[n]).contiguous()
+                      for n, t in mo.motion(b.centres, ts[k], sd, local_frame=True).items()}
+            out = b.render(cams[k], (W, H), motion)
+            torch.autograd.backward([out["images"], out["opacity"]], list(ups[k]), retain_graph=(k == 0))
+            vis = out["visibility_filter"] if vis is None else vis | out["visibility_filter"]
+        b.optimizer.set_before_step(vis, P)
+        b.optimizer.step()
+        b.dense_optimizer.step()
+        b.optimizer.zero_grad(set_to_none=True)
+        b.dense_optimizer.zero_grad(set_to_none=True)
+    a.check()
+    from fsgs.scene import LRS
+    lrs = [LRS[k] for k in ("xyz", "sh_dc", "sh_rest", "opacity", "scaling", "rotation")]
+    for x, y, lr in zip(a.params, b.params, lrs):
+        # the two routes evaluate the motion with different kernels (agreement 1e-5), and Adam turns a gradient that
+        # is zero to rounding into a step of the full learning rate either way: a few elements may differ by up to
+        # 2 lr, the mean by a small fraction of one step
+        d = (x.detach() - y.detach()).abs()
+        assert float(d.mean()) < 0.02 * lr + 1e-6 and float(d.max()) <= 2.1 * lr, (lr, float(d.mean()), float(d.max()))
+    # dense parameters: they moved, and Adam's first moment -- linear in the gradient, unlike the parameters
+    # themselves, whose first step is sign-like -- agrees to the noise of the float atomics in the compositing adjoint
+    for x, y, x0 in ((net_a.params, net_b.params, MotionNet(M, width=64, local_frame=True, seed=4).params),
+                     (a.sp_radius, b.sp_radius, raw_r.cuda()), (a.sp_weight, b.sp_weight, raw_w.cuda())):
+        assert float((x.detach() - x0.detach().to(x.device)).abs().max()) > 1e-4
+        ma, mb = a.dense_optimizer.state[x]["exp_avg"], b.dense_optimizer.state[y]["exp_avg"]
+        assert rel_l2(ma, mb) < 1e-4, rel_l2(ma, mb)
+        assert float((x.detach() - y.detach()).abs().mean()) < 0.1 * 1e-3
