@@ -440,8 +440,8 @@ int fsgs_motion_backward(const fsgs_motion_args *args /* host */, fsgs_stream_t 
 
 /* weights [P,K] = normalise(exp(-d2 / (2 r^2)) * sigma + 1e-7), r = exp(raw_radius[idx]), sigma =
  * sigmoid(raw_weight[idx]) (raw_weight NULL: 1).  Backward: g_weights [P,K] -> g_raw_radius [M], g_raw_weight [M]
- * (written, or added to when accumulate != 0), one block per superpoint over the grouped pairs of fsgs_lbs (no
- * atomics); the distances are treated as constants. */
+ * (written, or added to when accumulate != 0), one block per superpoint over the grouped pairs (the same
+ * sp_pair_offsets / sp_pairs as in fsgs_lbs; no atomics); the distances are treated as constants. */
 int fsgs_lbs_weights_forward(int P, int K, const float *d2, const int64_t *idx, const float *raw_radius,
     const float *raw_weight, float *weights, fsgs_stream_t stream);
 int fsgs_lbs_weights_backward(int P, int K, int M, const float *d2, const int64_t *idx, const float *raw_radius,
