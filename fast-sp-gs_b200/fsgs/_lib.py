@@ -147,6 +147,10 @@ SYMBOLS = {
     "fsgs_compact_workspace_bytes": (c_size_t, [c_int64]),
     "fsgs_compact_plan": (c_int, [c_int64, _vp, _vp, c_size_t, _vp, _vp]),
     "fsgs_compact_rows": (c_int, [c_int, POINTER(RowTensor), c_int64, _vp, _vp, _vp]),
+    "fsgs_densify_stats": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_densify_select": (c_int, [c_int, _vp, _vp, _vp, c_float, c_float, _vp, _vp]),
+    "fsgs_split_children": (c_int, [c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_gather_rows": (c_int, [c_int, POINTER(RowTensor), c_int64, _vp, _vp]),
     "fsgs_ssim_forward": (c_int, [c_int, c_int, c_int, c_int, c_float, c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_ssim_backward": (c_int, [c_int, c_int, c_int, c_int, c_float, c_float, _vp, _vp, _vp, c_float, c_float,
                                    _vp, _vp, _vp, _vp, _vp]),

@@ -494,6 +494,51 @@ def compact_rows(tensors, keep):
     return out
 
 
+def gather_rows(tensors, index):
+    """``[t[index] for t in tensors]`` in one launch per 24 tensors, with ``index`` int32 [n_out] and negative entries
+    giving zero rows (fresh optimiser state for new Gaussians)."""
+    _need(index.is_cuda and index.dtype == torch.int32 and index.dim() == 1, "index must be a CUDA int32 vector")
+    n = index.shape[0]
+    src = [t.contiguous() for t in tensors]
+    for t in src:
+        _need(t.is_cuda and t.element_size() in (4, 8) and t.shape[0] > 0, "rows of 4- or 8-byte elements")
+    out = [torch.empty((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device) for t in src]
+    for i in range(0, len(src), 24):
+        chunk = list(zip(src[i:i + 24], out[i:i + 24]))
+        arr = (_lib.RowTensor * len(chunk))()
+        for k, (a, b) in enumerate(chunk):
+            arr[k].src, arr[k].dst = a.data_ptr(), b.data_ptr()
+            arr[k].row_words = (a.numel() // a.shape[0]) * (a.element_size() // 4)
+        if n > 0:
+            check(lib().fsgs_gather_rows(len(chunk), arr, n, _ptr(index), _stream()), "fsgs_gather_rows")
+    return out
+
+
+def densify_select(accum, denom, scaling_raw, grad_threshold, scale_threshold):
+    """uint8 flags [P]: 1 clone, 2 split, 0 neither (gaussian_splatting.py:581-588, 608-613)."""
+    P = scaling_raw.shape[0]
+    flags = torch.empty(P, dtype=torch.uint8, device=scaling_raw.device)
+    check(lib().fsgs_densify_select(P, _ptr(accum.contiguous()), _ptr(denom.contiguous()), _ptr(scaling_raw.contiguous()),
+                                    float(grad_threshold), float(scale_threshold), _ptr(flags), _stream()),
+          "fsgs_densify_select")
+    return flags
+
+
+def split_children(parent, z, xyz, scaling_raw, rotation_raw, N, xyz_out, scaling_out):
+    """Positions and log-scales of the split children into ``xyz_out [n,3]`` / ``scaling_out [n,2]`` (contiguous views
+    are fine); ``parent`` int32 [n], ``z`` [n,2] standard-normal draws."""
+    n = parent.shape[0]
+    _need(xyz_out.is_contiguous() and scaling_out.is_contiguous() and z.is_contiguous(), "contiguous outputs and noise")
+    check(lib().fsgs_split_children(n, int(N), _ptr(parent), _ptr(z), _ptr(xyz.contiguous()),
+                                    _ptr(scaling_raw.contiguous()), _ptr(rotation_raw.contiguous()), _ptr(xyz_out),
+                                    _ptr(scaling_out), _stream()), "fsgs_split_children")
+
+
+def densify_stats(viewspace_grad, radii, accum, denom, max_radii):
+    check(lib().fsgs_densify_stats(radii.shape[0], _ptr(viewspace_grad), _ptr(radii), _ptr(accum), _ptr(denom),
+                                   _ptr(max_radii), _stream()), "fsgs_densify_stats")
+
+
 def _ssim_check(img1, img2):
     _need(img1.dim() == 4 and img1.shape == img2.shape, "fusedssim: images must be [B,C,H,W] of equal shape")
     for t, n in ((img1, "img1"), (img2, "img2")):

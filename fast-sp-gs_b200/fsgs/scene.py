@@ -76,6 +76,7 @@ class DynamicScene:
         self.optimizer = SparseGaussianAdam(groups, lr=0.0, eps=eps)
         self.bucket = None
         self.engine = None
+        self.track_densification = False
 
     @property
     def params(self):
@@ -158,6 +159,8 @@ class DynamicScene:
 
         def after_view(v):
             nonlocal n_timed
+            if self.track_densification:
+                ops.densify_stats(eng.viewspace_grad, eng.radii, self.grad_accum, self.grad_denom, self.max_radii)
             if "t" in v:  # this view's motion gradients -> network parameters, summed over the views
                 net.backward(self.motion_grads, b.view_of(net.params), accumulate=n_timed > 0)
                 n_timed += 1
@@ -267,6 +270,8 @@ class DynamicScene:
             st = self.optimizer.state.get(p, {})
             moments += [st.get("exp_avg"), st.get("exp_avg_sq")]
         extra = [self.knn_idx, self.knn_w, self.knn_d2]
+        if self.track_densification:
+            extra += [self.grad_accum, self.grad_denom, self.max_radii]
         rows = [p.data for p in params] + [m for m in moments if m is not None] + extra
         out = ops.compact_rows(rows, keep)
         new_params = [torch.nn.Parameter(t) for t in out[:len(params)]]
@@ -278,11 +283,73 @@ class DynamicScene:
                 st["exp_avg"], st["exp_avg_sq"] = rest.pop(0), rest.pop(0)
                 self.optimizer.state[new] = st
         self.xyz, self.sh_dc, self.sh_rest, self.opacity, self.scaling, self.rotation = new_params
-        self.knn_idx, self.knn_w, self.knn_d2 = rest
+        self.knn_idx, self.knn_w, self.knn_d2 = rest[:3]
+        if self.track_densification:
+            self.grad_accum, self.grad_denom, self.max_radii = rest[3:6]
         self.knn_idx.superpoint_pairs = group_pairs_by_superpoint(self.knn_idx, self.centres.shape[0])
         self.bucket = None
         self.engine = None
         return self.num_points
+
+    @torch.no_grad()
+    def densify(self, max_grad, extent, percent_dense=0.01, N=2, noise=None, generator=None):
+        """Clone the small and split the large Gaussians whose mean screen-space gradient reached ``max_grad``
+        (``densify``, fast_2d_gs/gaussian_splatting.py:623-628, with the 2-D split of network.py:1156-1185): selection,
+        the split children's positions and scales, and the move of all six parameters and twelve Adam moments into
+        their new rows (kept originals, clones, children copy 0 .. N-1; fresh moments zero) run on the device in four
+        launches.  ``noise`` [n_split * N, 2]: the standard-normal draws to use (else drawn from ``generator``).
+        Needs ``track_densification`` to have gathered statistics.  Returns (n_clone, n_split)."""
+        P = self.num_points
+        flags = ops.densify_select(self.grad_accum, self.grad_denom, self.scaling.data, max_grad, percent_dense * extent)
+        idx = torch.arange(P, device=flags.device, dtype=torch.int32)
+        keep, clone, split = idx[flags != 2], idx[flags == 1], idx[flags == 2]   # sizes read back: one sync each
+        n_keep, n_clone, n_split = keep.numel(), clone.numel(), split.numel()
+        parents = split.repeat(N)
+        index = torch.cat([keep, clone, parents])
+        fresh = torch.full((n_clone + N * n_split,), -1, dtype=torch.int32, device=flags.device)
+        params = self.params
+        moments = []
+        for p in params:
+            st = self.optimizer.state.get(p, {})
+            moments += [st.get("exp_avg"), st.get("exp_avg_sq")]
+        have = [m for m in moments if m is not None]
+        new_params = ops.gather_rows([p.data for p in params], index)
+        new_moments = ops.gather_rows(have, torch.cat([keep, fresh])) if have else []
+        if n_split:
+            if noise is None:
+                noise = torch.randn(N * n_split, 2, device=flags.device, generator=generator)
+            names = [id(p) for p in params]
+            x_new, s_new = new_params[names.index(id(self.xyz))], new_params[names.index(id(self.scaling))]
+            ops.split_children(parents, noise.contiguous(), self.xyz.data, self.scaling.data, self.rotation.data, N,
+                               x_new[n_keep + n_clone:], s_new[n_keep + n_clone:])
+        self._install(params, [torch.nn.Parameter(t) for t in new_params], new_moments)
+        self.refresh_knn()   # the new Gaussians need neighbours
+        return n_clone, n_split
+
+    def _install(self, old_params, new_params, new_moments):
+        """Swap in resized parameter tensors and their Adam moments (``change_optimizer``, gaussian_splatting.py:498-548)
+        and reset everything that is sized by the Gaussian count."""
+        new_moments = list(new_moments)
+        for group, old, new in zip(self.optimizer.param_groups, old_params, new_params):
+            st = self.optimizer.state.pop(old, None)
+            group["params"][0] = new
+            if st:
+                st["exp_avg"], st["exp_avg_sq"] = new_moments.pop(0), new_moments.pop(0)
+                self.optimizer.state[new] = st
+        self.xyz, self.sh_dc, self.sh_rest, self.opacity, self.scaling, self.rotation = new_params
+        self.bucket = None
+        self.engine = None
+        if self.track_densification:
+            self.track_densification = False
+            self.enable_densification_stats()
+
+    def enable_densification_stats(self):
+        """Start (or restart, zeroed) gathering the statistics ``densify`` selects by: per Gaussian the summed norm of
+        the screen-space gradient, the number of views it was visible in, and its largest radius
+        (``add_densification_stats``, network.py:1143-1154); updated by one small launch per training view."""
+        z = lambda: torch.zeros(self.num_points, device=self.xyz.device)
+        self.grad_accum, self.grad_denom, self.max_radii = z(), z(), z()
+        self.track_densification = True
 
     def _drop_grads(self):
         for p in self.params + self.dense_params:  # zero_grad(set_to_none=True) without the optimizer's hook layers

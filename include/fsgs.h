@@ -323,6 +323,33 @@ int fsgs_compact_rows(int n_tensors, const fsgs_row_tensor *tensors, int64_t N, 
                       const void *workspace, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Densification: clone / split of Gaussians and the surgery on the optimiser state, on the device.
+ * Replaces the tensor-by-tensor torch.cat / boolean indexing of densify_and_clone, densify_and_split,
+ * densification_postfix and change_optimizer(op='concat' | 'prune')
+ * (fast_2d_gs/gaussian_splatting.py:498-548, 570-622; the 2-D split of fast_2d_gs/network.py:1156-1185) and the
+ * statistics of add_densification_stats (network.py:1143-1154).
+ *  fsgs_densify_stats   one view: for radii > 0, accum += |viewspace_grad[i]| (the densification proxy the
+ *                       preprocess backward leaves), denom += 1, max_radii = max(max_radii, radii).
+ *  fsgs_densify_select  flags[i] = 1 (clone) when accum/denom (NaN -> 0) >= grad_threshold and
+ *                       max(exp(scaling_raw[i])) <= scale_threshold, 2 (split) when >= and larger, else 0.
+ *  fsgs_split_children  n children (N per parent, copy-major like torch's repeat(N, 1)): position = parent position
+ *                       + R(normalised raw quaternion) (s_x z[k,0], s_y z[k,1], 0), log-scale = log(s / (0.8 N));
+ *                       z [n,2] are standard-normal draws supplied by the caller.
+ *  fsgs_gather_rows     dst[k] = src[index[k]] for up to FSGS_COMPACT_MAX_TENSORS tensors in one launch; index[k] < 0
+ *                       gives a zero row (the fresh Adam moments of new Gaussians).  Rows as in fsgs_compact_rows.
+ * The order of the result -- kept originals, clones, split children copy 0, copy 1 -- is the reference's.
+ * ---------------------------------------------------------------------------------------------- */
+int fsgs_densify_stats(int P, const float *viewspace_grad, const int32_t *radii, float *accum, float *denom,
+                       float *max_radii, fsgs_stream_t stream);
+int fsgs_densify_select(int P, const float *accum, const float *denom, const float *scaling_raw, float grad_threshold,
+                        float scale_threshold, uint8_t *flags, fsgs_stream_t stream);
+int fsgs_split_children(int n, int N, const int32_t *parent, const float *z, const float *xyz,
+                        const float *scaling_raw, const float *rotation_raw, float *xyz_out, float *scaling_out,
+                        fsgs_stream_t stream);
+int fsgs_gather_rows(int n_tensors, const fsgs_row_tensor *tensors, int64_t n_out, const int32_t *index,
+                     fsgs_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Structural similarity, 11x11 Gaussian window (sigma 1.5, zero padding), forward and adjoint.
  * Replaces fusedssim / fusedssim_backward   (src/other/structural_similarity.cu:340-381; callers
  * fast_2d_gs/losses/ssim.py:24-45; the map is that of _ssim, ssim.py:48-67).

@@ -18,6 +18,7 @@ What each fixture pins (paths inside the reference project):
   sh_basis_deg7.npz  real SH of degrees 0..7, general definition  utils/ops_3d/spherical_harmonics.py:16-67
   ssim.npz        _ssim (python, five padded convolutions)  fast_2d_gs/losses/ssim.py:48-67  (+ autograd)
   motion_w64.npz  SC_GS_DeformNetwork (width 64) + head of warp()  fast_2d_gs/network.py:1670-1776, 545-549  (+ autograd)
+  densify.npz     densify: clone, 2-D split, optimiser surgery     fast_2d_gs/gaussian_splatting.py:498-628, network.py:1156-1215
 """
 import argparse
 import os
@@ -228,6 +229,58 @@ def make_motion():
     npz("motion_w64.npz", **arrs)
 
 
+def make_densify():
+    """The reference's own ``densify`` (gaussian_splatting.py:623-628 -> densify_and_clone :608-622, the 2-D
+    densify_and_split of network.py:1156-1185, densification_postfix, prune_points, change_optimizer :498-548) run on
+    a bare instance of its model class with 300 Gaussians, an Adam optimiser that has taken steps, and gathered
+    statistics.  ``torch.normal`` is replaced for the call by mean + std * z with stored draws z, so that the split
+    children are reproducible."""
+    from fast_2d_gs import network as N
+    g = torch.Generator().manual_seed(71)
+    P = 300
+    m = object.__new__(N.FastSuperpoint2DGaussianSplatting)
+    torch.nn.Module.__init__(m)
+    vals = dict(_xyz=torch.rand(P, 3, generator=g) * 2 - 1, _features_dc=torch.randn(P, 1, 3, generator=g),
+                _features_rest=torch.randn(P, 15, 3, generator=g) * 0.1,
+                _scaling=torch.randn(P, 2, generator=g) * 0.7 - 3.0, _rotation=torch.randn(P, 4, generator=g),
+                _opacity=torch.randn(P, 1, generator=g))
+    for k, v in vals.items():
+        setattr(m, k, torch.nn.Parameter(v.clone()))
+    m._step, m.stages, m.init_same_scale = 0, {"sp_fix": (0, 0, 0)}, "none"
+    m.scaling_activation, m.scaling_activation_inverse = torch.exp, torch.log
+    m.adaptive_control_cfg, m.render_method, m.use_so3, m.p2sp = {"blur_split": False}, "2d_gs_fast", False, None
+    m._culling, m.factor_culling = torch.zeros(P, 1, dtype=torch.bool), torch.ones(P, 1)
+    m.xyz_gradient_accum = (torch.rand(P, 1, generator=g) ** 3) * 1e-3 * 40
+    m.denom = torch.randint(0, 40, (P, 1), generator=g).float()   # zeros among them: grads NaN -> 0
+    m.max_radii2D = torch.zeros(P)
+    groups = [dict(params=[getattr(m, a)], lr=1e-3, name=n) for a, n in m.param_names_map.items()]
+    opt = torch.optim.Adam(groups, lr=0.0, eps=1e-15)
+    for _ in range(2):
+        for a in m.param_names_map:
+            p = getattr(m, a)
+            p.grad = torch.randn(p.shape, generator=g)
+        opt.step()
+    before = {a: getattr(m, a).detach().clone() for a in m.param_names_map}
+    state = {a: (opt.state[getattr(m, a)]["exp_avg"].clone(), opt.state[getattr(m, a)]["exp_avg_sq"].clone())
+             for a in m.param_names_map}
+    accum, denom = m.xyz_gradient_accum.clone(), m.denom.clone()
+    z = torch.randn(4 * P, 3, generator=g)
+    real_normal = torch.normal
+    torch.normal = lambda mean, std: mean + std * z[:mean.shape[0]]
+    try:
+        with torch.no_grad():
+            m.densify(opt, 2e-4, 4.0, 0.01)
+    finally:
+        torch.normal = real_normal
+    arrs = dict(max_grad=2e-4, extent=4.0, percent_dense=0.01, accum=accum, denom=denom, z=z)
+    for a in m.param_names_map:
+        p = getattr(m, a)
+        arrs["in" + a], arrs["out" + a] = before[a], p.detach()
+        arrs["in_m" + a], arrs["in_v" + a] = state[a]
+        arrs["out_m" + a], arrs["out_v" + a] = opt.state[p]["exp_avg"], opt.state[p]["exp_avg_sq"]
+    npz("densify.npz", **arrs)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=None, help="reference checkout (default: $FSGS_REFERENCE_ROOT, else a "
@@ -247,6 +300,10 @@ def main():
     if args.only == "ssim":
         make_ssim(import_reference(args.ref)[1])
         return
+    if args.only == "densify":
+        import_reference(args.ref)
+        make_densify()
+        return
     if args.only == "motion":
         import_reference(args.ref)
         make_motion()
@@ -259,6 +316,7 @@ def main():
     make_rasterize(R, get_python_function, ops_3d)
     make_ssim(get_python_function)
     make_motion()
+    make_densify()
 
 
 if __name__ == "__main__":

@@ -162,3 +162,28 @@ def test_motion_oracle_against_reference_network():
     torch.autograd.backward([out[k] for k in out], [g["up_" + k] for k in out])
     for k, p in sd.items():
         assert _rel_l2(p.grad, g["grad_" + k]) < 1e-5, k
+
+
+DENSIFY_NAMES = {"xyz": "_xyz", "f_dc": "_features_dc", "f_rest": "_features_rest", "scaling": "_scaling",
+                 "rotation": "_rotation", "opacity": "_opacity"}
+
+
+def test_densify_oracle_against_reference_methods():
+    """Clone / 2-D split / optimiser surgery: the restatement equals what the reference's own densify produced
+    (counts, order and copied rows exactly; the split children's positions and scales to rounding)."""
+    import densify_oracle as do
+    g = _load("densify.npz")
+    params = {k: g["in" + a] for k, a in DENSIFY_NAMES.items()}
+    moments = {k: (g["in_m" + a], g["in_v" + a]) for k, a in DENSIFY_NAMES.items()}
+    out, out_m, n_clone, n_split = do.densify(params, moments, g["accum"].clone(), g["denom"], float(g["max_grad"]),
+                                              float(g["extent"]), float(g["percent_dense"]), g["z"])
+    assert n_clone > 10 and n_split > 10
+    for k, a in DENSIFY_NAMES.items():
+        assert out[k].shape == g["out" + a].shape, k
+        if k in ("xyz", "scaling"):
+            assert torch.allclose(out[k], g["out" + a], rtol=1e-6, atol=1e-7), k
+            n_old = out[k].shape[0] - 2 * n_split
+            assert torch.equal(out[k][:n_old], g["out" + a][:n_old]), k
+        else:
+            assert torch.equal(out[k], g["out" + a]), k
+        assert torch.equal(out_m[k][0], g["out_m" + a]) and torch.equal(out_m[k][1], g["out_v" + a]), k
