@@ -675,6 +675,35 @@ def run_ours(args):
         ms_step_loss, _ = timed(step_loss, args.steps, "step_loss")
         del scene_l
 
+    # the step with the superpoint motion produced by the deformation network at a time t (network trained as well,
+    # kernel-weighted LBS weights re-evaluated and trained): what the reference's iteration does before its render
+    ms_step_motion = motion_ms = None
+    if n_views:
+        from fsgs.motion import MotionNet
+        net = MotionNet(M, device=dev, local_frame=True, seed=1)
+        scene_m = DynamicScene(wlk["surf"], wlk["centres"], K=K, device=dev, motion_net=net,
+                               kernel_weights=(torch.full((M,), -1.5), torch.zeros(M)),
+                               lrs=dict(xyz=lr, sh_dc=lr, sh_rest=lr, opacity=lr, scaling=lr, rotation=lr))
+        t_views = [[dict(cam=v[k]["cam"], t=torch.tensor([0.1 + 0.8 * j / max(n_views, 1)], device=dev),
+                         g_images=v[k]["g_images"], g_opacity=v[k]["g_opacity"]) for k in (0, 1)]
+                   for j, v in enumerate(dev_views)]
+
+        def step_motion():
+            k = tick[0] & 1
+            tick[0] += 1
+            scene_m.train_views([v[k] for v in t_views], (W, H), distributed=distributed)
+
+        for _ in range(3):
+            step_motion()
+        ms_step_motion, _ = timed(step_motion, args.steps, "step_motion_net")
+        t0 = t_views[0][0]["t"]
+        gp = torch.zeros_like(net.params.data)
+        gm = {k: torch.randn_like(x) for k, x in net.forward(scene_m.centres, t0).items()}
+        motion_ms = {"forward": round(_event_ms(lambda: net.forward(scene_m.centres, t0, out=scene_m.motion_buf), 50, 5), 4),
+                     "backward": round(_event_ms(lambda: net.backward(gm, gp), 50, 5), 4),
+                     "net": f"{net.cfg.depth} x {net.cfg.width}, {M} superpoints, {net.params.numel()} parameters"}
+        del scene_m
+
     # ---- replicas must stay identical; a split batch must equal the serial one (outside every timed region) ----
     checks = None
     if distributed:
@@ -762,6 +791,7 @@ def run_ours(args):
             "fwd_frames_per_s": total_views * 1e3 / ms_fwd, "ms_per_fwd_batch": ms_fwd,
             "fwd_repeats": {"min": fwd_runs[0], "max": fwd_runs[-1]},
             "ms_per_step_with_aux_gradients": ms_step_aux, "ms_per_step_with_l1_ssim_loss": ms_step_loss,
+            "ms_per_step_with_motion_net": ms_step_motion, "motion_net_ms": motion_ms,
             "e2e": {"value": total_views * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
                     "ms_per_step_min_max": [e2e_runs[0], e2e_runs[-1]], "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4 + 32 * n_views},

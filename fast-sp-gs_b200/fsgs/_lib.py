@@ -114,6 +114,8 @@ SYMBOLS = {
     "fsgs_cdist_top_f64": (c_int, [c_int, c_int, c_int, c_int, _vp, _vp, c_int, _vp, _vp, _vp]),
     "fsgs_cdist_top_backward_f64": (c_int, [c_int, c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_knn": (c_int, [c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_knn_grid_workspace_bytes": (c_size_t, [c_int]),
+    "fsgs_knn_grid": (c_int, [c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp, c_size_t, _vp]),
     "fsgs_adam_masked": (c_int, [_vp, _vp, _vp, _vp, _vp, c_float, c_float, c_float, c_float, c_int64, c_int64, _vp]),
     "fsgs_adam_masked_multi": (c_int, [c_int, POINTER(AdamTensor), _vp, c_int64, c_float, c_float, _vp]),
     "fsgs_adam_masked_multi_fmask": (c_int, [c_int, POINTER(AdamTensor), _vp, c_int64, c_float, c_float, _vp]),

@@ -68,6 +68,13 @@ int fsgs_cdist_top_backward_f64(int B, int N, int M, int D, const double *x1, co
  * ties go to the lower index.  x [N,3], c [M,3] -> d2 [N,K], index [N,K] int64.  K <= FSGS_KNN_MAX_K.
  * Stands in for the pytorch3d.ops.knn_points call of fast_2d_gs/network.py:504 (third party; additive). */
 int fsgs_knn(int N, int M, int K, const float *x, const float *c, float *d2, int64_t *index, fsgs_stream_t stream);
+/* The same search, same results bit for bit, through a uniform grid over the control points (built by the call in
+ * the workspace: one small launch): a query evaluates only the control points of the cells around it, shell by
+ * shell, until no unvisited cell can hold anything closer than its K-th candidate.  Hundreds instead of thousands
+ * of distance evaluations per query at M = 4096. */
+size_t fsgs_knn_grid_workspace_bytes(int M);
+int fsgs_knn_grid(int N, int M, int K, const float *x, const float *c, float *d2, int64_t *index, void *workspace,
+    size_t workspace_bytes, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Visibility-masked Adam.

@@ -115,6 +115,32 @@ def test_cdist_top_empty_and_errors(ops):
         ops.cdist_top(torch.zeros(4, 3, device="cuda"), torch.zeros(4, 2, device="cuda"))
 
 
+@pytest.mark.parametrize("N,M,K,case", [(100_000, 512, 3, "c1"), (200_000, 4096, 8, "c1"), (5000, 300, 16, "far"),
+                                        (5000, 2000, 8, "dup"), (3000, 7, 3, "c1"), (2000, 1, 2, "c1"),
+                                        (4000, 5000, 4, "plane"), (4000, 600, 3, "offset")])
+def test_knn_grid_equals_brute_force(ops, N, M, K, case):
+    """The grid search returns the brute-force search's distances and indices bit for bit: clustered and uniform
+    control points, queries far outside their bounding box, duplicated control points (ties by index), fewer control
+    points than K, all control points in one plane (a degenerate grid axis), coordinates far from the origin."""
+    from fsgs import workloads as wl
+    g = torch.Generator().manual_seed(N + M)
+    x, c = wl.knn_points_c1(max(N, M), M, seed=7)
+    x = x[:N].contiguous()
+    if case == "far":
+        x = x * 5.0
+    elif case == "dup":
+        c = c[torch.randint(0, M // 4, (M,), generator=g)].contiguous()
+    elif case == "plane":
+        c = c.clone()
+        c[:, 2] = 0.25
+    elif case == "offset":
+        x, c = x + 1000.0, c + 1000.0
+    db, ib = ops.knn(x.cuda(), c.cuda(), K, method="brute")
+    dg, ig = ops.knn(x.cuda(), c.cuda(), K, method="grid")
+    assert torch.equal(ig, ib), f"{int((ig != ib).sum())} indices differ"
+    assert torch.equal(dg, db)
+
+
 @pytest.mark.parametrize("N,M,K", [(100_000, 512, 3), (3000, 4096, 8), (100, 5, 3), (64, 2000, 1), (50, 40, 16)])
 def test_knn_oracle(ops, N, M, K):
     from fsgs import workloads as wl

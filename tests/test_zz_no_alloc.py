@@ -60,6 +60,46 @@ def test_noalloc_binning_equals_workspace_binning_twice_in_a_row():
         assert int(o["counters"][2]) == 0  # nothing dropped
 
 
+def test_noalloc_binning_allocates_nothing_and_works_at_its_limits():
+    """What the entry point is for: with every input and output in place, a call changes neither the free device
+    memory nor the framework's allocation count.  Checked on a frame close to both documented maxima (16 384 tiles,
+    about 0.98 of the 2^20 pairs), compared element for element with the workspace path."""
+    from fsgs import _lib, ops
+    lib = _lib.lib()
+    P, W, H = 100_000, 2048, 2048
+    s, cam = make_scene(P, W, H, seed=23, log_scale_mean=-4.5)
+    o = ops.preprocess_launch(W, H, 3, s["means"], s["scales"], s["rots"], s["opac"], s["sh_dc"], s["sh_rest"],
+                              cam["Tw2v"], cam["Tv2s"], cam["campos"])
+    n_pairs = int(o["counters"][1])
+    capacity = 1 << 20
+    assert ((W + 15) // 16) * ((H + 15) // 16) == 16384 and 0.8 * capacity < n_pairs <= capacity
+    ref_ranges, ref_list, _ = _bin(lib.fsgs_bin_tiles, W, H, o, s["opac"], capacity, True)
+    _bin(lib.fsgs_bin_tiles_noalloc, W, H, o, s["opac"], capacity, False)      # the set-up call on this device
+    # second call with every buffer made beforehand: nothing may be allocated while it runs
+    dev = s["opac"].device
+    T = 16384
+    ranges = torch.full((T, 2), -7, device=dev, dtype=torch.int64)
+    point_list = torch.full((capacity,), -7, device=dev, dtype=torch.int32)
+    tile_order = torch.full((T,), -7, device=dev, dtype=torch.int32)
+    b = _lib.BinArgs()
+    b.P, b.W, b.H = P, W, H
+    p = ops._ptr
+    b.means2D, b.inverse_m, b.depths, b.opac = p(o["means2D"]), p(o["inverse_m"]), p(o["depths"]), p(s["opac"])
+    b.radii, b.tile_counts, b.counters = p(o["radii"]), p(o["tile_counts"]), p(o["counters"])
+    b.capacity, b.point_list, b.ranges, b.tile_order = capacity, p(point_list), p(ranges), p(tile_order)
+    stream = ops._stream()
+    torch.cuda.synchronize()
+    free_before, allocated_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    segments_before = torch.cuda.memory_stats()["segment.all.allocated"]
+    _lib.check(lib.fsgs_bin_tiles_noalloc(ctypes.byref(b), stream), "binning")
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_allocated() == allocated_before
+    assert torch.cuda.memory_stats()["segment.all.allocated"] == segments_before
+    assert torch.equal(ranges, ref_ranges) and torch.equal(point_list, ref_list)
+    assert int(o["counters"][2]) == 0
+
+
 def test_noalloc_binning_rejects_sizes_beyond_its_fixed_scratch():
     from fsgs import _lib, ops
     lib = _lib.lib()
