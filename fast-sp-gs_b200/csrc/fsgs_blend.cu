@@ -133,7 +133,8 @@ struct Hit {
 // (pixel, splat) evaluation shared by both passes; false when the pair is skipped.
 // Same operations, in the same order, as the reference kernels (gs_2d_fast_redner.cu:152-186).
 // FAST replaces the two IEEE divisions and expf by their approximate forms: used by the backward pass only, whose
-// tolerance is relative (1e-3 per tensor); the forward pass decides the alpha and transmittance cuts and stays exact.
+// tolerance is relative (1e-3 per tensor); the forward pass decides the alpha and transmittance cuts and stays exact,
+// and the backward pass falls back to the exact forms wherever an approximate value comes close to a cut.
 template <bool FAST>
 __device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py, float near_n, Hit &h, float &opa,
     float3 &Tw) {
@@ -155,12 +156,22 @@ __device__ __forceinline__ bool eval_pair(const float4 *rec, float px, float py,
   const float rho = fminf(h.rho3d, h.rho2d);
   Tw = make_float3(q3.y, q3.z, q3.w);
   h.depth = (h.sx * Tw.x + h.sy * Tw.y) + Tw.z;
-  if (h.depth < near_n) return false;
+  if (h.depth < near_n * (FAST ? 1.0f - 2e-5f : 1.0f)) return false;
   opa = q0.z;
   const float power = -0.5f * rho;
   if (power > 0.0f) return false;
   h.G = FAST ? __expf(power) : expf(power);
   h.alpha = fminf(0.99f, opa * h.G);
+  if (FAST) {
+    // The forward pass decides the depth and alpha cuts with exact division and expf.  Within a guard band around
+    // either cut the approximate forms could land on the other side -- the pair would then be blended by one pass
+    // and skipped by the other -- so there the pair is evaluated again exactly (rare: a relative band of 2e-5).
+    const float cut = 1.0f / 255.0f, raw = opa * h.G;
+    if (raw < cut * (1.0f - 2e-5f)) return false;
+    if (raw < cut * (1.0f + 2e-5f) || h.depth < near_n * (1.0f + 2e-5f))
+      return eval_pair<false>(rec, px, py, near_n, h, opa, Tw);
+    return true;
+  }
   if (h.alpha < 1.0f / 255.0f) return false;
   return true;
 }

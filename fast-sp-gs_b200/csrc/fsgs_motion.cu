@@ -7,11 +7,12 @@
 //   fast_2d_gs/network.py:545-549    (q = normalize(g_rot + (0,0,0,1)); t' = t + c - R(q) c, 'LBS_c')
 //   fast_2d_gs/network.py:506-513    (weights = exp(-d^2 / (2 r^2)) * sigma + 1e-7, normalised; r = exp(raw), sigma = sigmoid(raw))
 // The network is 0.5 GFLOP per evaluation on M = 512 rows: a latency problem, not a throughput one.  Each block owns
-// R rows and carries them through every layer with the activations in shared memory, so the eight dependent layers
-// cost no launches and no grid synchronisation; weights ([in, out] row major, so that consecutive threads read
-// consecutive floats) stream from L2.  Tensor cores are not used: the path is specified in fp32 and the whole
-// evaluation is tens of microseconds on the FP32 pipe.
+// 8 rows and carries them through every layer with the activations in shared memory, so the eight dependent layers
+// cost no launches and no grid synchronisation; the weights ([in, out] row major) stream from L2 through shared
+// memory by bulk asynchronous copies, and every thread keeps an 8 x 4 block of outputs in registers.  Tensor cores are
+// not used: the path is specified in fp32 and the whole evaluation is tens of microseconds on the FP32 pipe.
 #include "fsgs_common.cuh"
+#include "fsgs_tma.cuh"
 
 namespace fsgs {
 
@@ -106,9 +107,86 @@ __device__ __forceinline__ void freq_encode(float x, int deg, float scale, int d
   }
 }
 
-// One block = kMotionRows rows through the whole network.  blockDim.x == width.
-__global__ void __launch_bounds__(kMotionMaxWidth) motion_forward_kernel(MotionDev a) {
+// ---- the row-block GEMM both passes are built on ---------------------------------------------------------------
+// A block carries R = 8 rows.  For one matrix Wm [K, N] (row major, N a multiple of 4) it computes
+//   acc[r][c] += sum_k act[k][r] * Wm[k][4 t + c]          r < 8, c < 4, thread t < N / 4
+// with the activations in shared memory k major ([k][r]: one 16-byte broadcast load feeds four rows) and the matrix
+// streamed through two shared-memory buffers in slabs of kSlabRows rows by bulk asynchronous copies issued two slabs
+// ahead, across matrix boundaries.  32 accumulators per thread: every shared-memory load feeds 4 to 8 multiply-adds;
+// with one output column per thread the kernel was bound by the broadcast loads and five times slower.
+constexpr int kMotionThreads = 128;
+constexpr int kSlabRows = 32;
+constexpr int kSlabFloats = kSlabRows * kMotionMaxIn;   // a slab of the widest matrix
+
+struct MatSeq {  // the matrices a pass consumes, in order (shared memory)
+  const float *ptr[17];
+  int rows[17], stride[17];
+  int n;
+};
+
+struct SlabPipe {
+  float *buf;        // [2][kSlabFloats]
+  uint64_t *bar;     // [2]
+  const MatSeq *seq;
+  int issue_m, issue_k;  // next slab to fetch: matrix, first row
+  int n_used;            // slabs consumed so far
+
+  __device__ __forceinline__ void fetch_next() {  // thread 0 only; the target buffer must be free
+    if (issue_m >= seq->n) return;
+    const int rows = min(kSlabRows, seq->rows[issue_m] - issue_k), stride = seq->stride[issue_m];
+    const int b = fetched & 1;
+    const uint32_t bytes = (uint32_t) rows * stride * 4u;
+    mbar_arrive_expect_tx(&bar[b], bytes);
+    bulk_load(buf + b * kSlabFloats, seq->ptr[issue_m] + (size_t) issue_k * stride, bytes, &bar[b]);
+    ++fetched;
+    issue_k += kSlabRows;
+    if (issue_k >= seq->rows[issue_m]) ++issue_m, issue_k = 0;
+  }
+  int fetched;
+};
+
+// acc += act^T-block times matrix m of the sequence (all K rows).  Every thread of the block must call it.
+__device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float *s_act, float (&acc)[8][4]) {
+  const int K = pipe.seq->rows[m], N = pipe.seq->stride[m], t = threadIdx.x;
+  const bool mine = 4 * t < N;
+  for (int k0 = 0; k0 < K; k0 += kSlabRows, ++pipe.n_used) {
+    const int b = pipe.n_used & 1, rows = min(kSlabRows, K - k0);
+    // a wait that runs out falls back to reading the slab from global memory
+    const bool late = !mbar_wait_bounded(&pipe.bar[b], (uint32_t) ((pipe.n_used >> 1) & 1));
+    const bool direct = __syncthreads_or(late);
+    const float *w = direct ? pipe.seq->ptr[m] + (size_t) k0 * N : pipe.buf + b * kSlabFloats;
+    if (mine) {
+#pragma unroll 2
+      for (int kk = 0; kk < rows; ++kk) {
+        const float4 wv = *reinterpret_cast<const float4 *>(w + kk * N + 4 * t);
+        const float4 a0 = *reinterpret_cast<const float4 *>(s_act + (k0 + kk) * 8);
+        const float4 a1 = *reinterpret_cast<const float4 *>(s_act + (k0 + kk) * 8 + 4);
+        const float ar[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          acc[r][0] += ar[r] * wv.x, acc[r][1] += ar[r] * wv.y, acc[r][2] += ar[r] * wv.z, acc[r][3] += ar[r] * wv.w;
+      }
+    }
+    __syncthreads();  // every thread is done with buffer b
+    if (t == 0) pipe.fetch_next();
+  }
+}
+
+__device__ __forceinline__ void pipe_start(SlabPipe &pipe, float *buf, uint64_t *bar, const MatSeq *seq) {
+  pipe.buf = buf, pipe.bar = bar, pipe.seq = seq, pipe.issue_m = 0, pipe.issue_k = 0, pipe.n_used = 0, pipe.fetched = 0;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[0], 1), mbar_init(&bar[1], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) pipe.fetch_next(), pipe.fetch_next();
+}
+
+// One block = kMotionRows rows through the whole network, kMotionThreads threads.
+__global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDev a) {
   constexpr int R = kMotionRows;
+  extern __shared__ __align__(128) float s_slabs[];        // [2][kSlabFloats]
+  __shared__ __align__(8) uint64_t s_bar[2];
+  __shared__ MatSeq s_seq;
   __shared__ __align__(16) float s_in[kMotionMaxIn * R];   // [k][r]: the layer's input, k major
   __shared__ __align__(16) float s_out[kMotionMaxWidth * R];
   __shared__ float s_x0[R][128];                           // row major copy of the layer-0 input (for the skip)
@@ -120,6 +198,13 @@ __global__ void __launch_bounds__(kMotionMaxWidth) motion_forward_kernel(MotionD
   const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R;
   const int W = L.width;
   const float *P = a.params;
+  if (j == 0) {
+    s_seq.n = L.depth;
+    for (int i = 0; i < L.depth; ++i) s_seq.ptr[i] = P + L.lin_W[i], s_seq.rows[i] = L.lin_in[i], s_seq.stride[i] = W;
+  }
+  __syncthreads();
+  SlabPipe pipe;
+  pipe_start(pipe, s_slabs, s_bar, &s_seq);   // the first two slabs travel while the encodings are evaluated
 
   // encodings
   if (j == 0) freq_encode(a.t[0], (L.Et - 1) / 2, a.scale_t, 1, 0, s_te);
@@ -137,10 +222,21 @@ __global__ void __launch_bounds__(kMotionMaxWidth) motion_forward_kernel(MotionD
       s_th[u] = fmaxf(acc, 0.0f);
     }
     __syncthreads();
-    for (int u = j; u < L.To; u += nt) {
-      float acc = P[L.time2_b + u];
-      for (int k = 0; k < L.Ht; ++k) acc += s_th[k] * P[L.time2_W + (long long) k * L.To + u];
-      s_tf[u] = acc;
+    // every warp sums a quarter of the hidden units for all outputs, then the quarters are added
+    {
+      const int lane = j & 31, warp = j >> 5, nw = nt >> 5;
+      float *part = s_out;  // [nw][64] scratch (s_out is not yet in use)
+      for (int u = lane; u < L.To; u += 32) {
+        float acc = 0.0f;
+        for (int k = warp; k < L.Ht; k += nw) acc += s_th[k] * P[L.time2_W + (long long) k * L.To + u];
+        part[warp * 64 + u] = acc;
+      }
+      __syncthreads();
+      for (int u = j; u < L.To; u += nt) {
+        float acc = P[L.time2_b + u];
+        for (int w = 0; w < nw; ++w) acc += part[w * 64 + u];
+        s_tf[u] = acc;
+      }
     }
     if (blockIdx.x == 0)
       for (int u = j; u < L.Ht; u += nt) a.time_hidden[u] = s_th[u];
@@ -161,23 +257,22 @@ __global__ void __launch_bounds__(kMotionMaxWidth) motion_forward_kernel(MotionD
   __syncthreads();
 
   for (int i = 0; i < L.depth; ++i) {
-    const int in = L.lin_in[i];
-    const float *Wi = P + L.lin_W[i];
-    float acc[R];
-    const float b = P[L.lin_b[i] + j];
+    float acc[8][4];
+    const bool mine = 4 * j < W;
+    float4 bias = make_float4(0, 0, 0, 0);
+    if (mine) bias = *reinterpret_cast<const float4 *>(P + L.lin_b[i] + 4 * j);
 #pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = b;
-    for (int k = 0; k < in; ++k) {
-      const float w = __ldg(Wi + (size_t) k * W + j);
-      const float4 a0 = *reinterpret_cast<const float4 *>(s_in + k * R), a1 = *reinterpret_cast<const float4 *>(s_in + k * R + 4);
-      acc[0] += a0.x * w, acc[1] += a0.y * w, acc[2] += a0.z * w, acc[3] += a0.w * w;
-      acc[4] += a1.x * w, acc[5] += a1.y * w, acc[6] += a1.z * w, acc[7] += a1.w * w;
-    }
+    for (int r = 0; r < 8; ++r) acc[r][0] = bias.x, acc[r][1] = bias.y, acc[r][2] = bias.z, acc[r][3] = bias.w;
+    rowblock_gemm(pipe, i, s_in, acc);
+    if (mine) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      acc[r] = fmaxf(acc[r], 0.0f);
-      s_out[j * R + r] = acc[r];
-      if (row0 + r < a.M) a.h[((size_t) i * a.M + row0 + r) * W + j] = acc[r];
+      for (int r = 0; r < 8; ++r) {
+        const float4 v = make_float4(fmaxf(acc[r][0], 0.0f), fmaxf(acc[r][1], 0.0f), fmaxf(acc[r][2], 0.0f),
+            fmaxf(acc[r][3], 0.0f));
+        s_out[(4 * j) * R + r] = v.x, s_out[(4 * j + 1) * R + r] = v.y;
+        s_out[(4 * j + 2) * R + r] = v.z, s_out[(4 * j + 3) * R + r] = v.w;
+        if (row0 + r < a.M) *reinterpret_cast<float4 *>(a.h + ((size_t) i * a.M + row0 + r) * W + 4 * j) = v;
+      }
     }
     __syncthreads();
     // next layer's input: the activations, preceded by the encodings after the skip layer
@@ -229,23 +324,61 @@ struct MotionBwdDev {
   float *dpre;     // [depth, M, width] gradient of each layer's pre-activation output
   float *dheads;   // [M, NH]
   float *g_tf;     // [To] summed gradient of the time features (zeroed before the launch)
+  float *wt;       // transposed copies of the layer matrices: layer i at wt_off[i], [width][in_pad(i)]
+  long long wt_off[16];
+  int in_pad[16];
   float *g_params;
   int accumulate;
 };
 
+// Transposed copies of the layer matrices for the backward pass (the same row-block GEMM then serves dX = dY W^T):
+// wt[i][j][k] = W_i[k][j], row stride in_pad(i) (a multiple of 4, padding zero).
+__global__ void __launch_bounds__(256) motion_transpose_kernel(MotionBwdDev b) {
+  __shared__ float tile[32][33];
+  const MotionLayout &L = b.f.L;
+  const int i = blockIdx.z, W = L.width, in = L.lin_in[i], ip = b.in_pad[i];
+  const int k0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
+  if (k0 >= ip) return;
+  const float *src = b.f.params + L.lin_W[i];
+  float *dst = b.wt + b.wt_off[i];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int y = ty; y < 32; y += 8) {
+    const int k = k0 + y, jcol = j0 + tx;
+    tile[y][tx] = (k < in && jcol < W) ? src[(size_t) k * W + jcol] : 0.0f;
+  }
+  __syncthreads();
+  for (int y = ty; y < 32; y += 8) {
+    const int jrow = j0 + y, k = k0 + tx;
+    if (jrow < W && k < ip) dst[(size_t) jrow * ip + k] = tile[tx][y];
+  }
+}
+
 // Backward pass 1: one block = kMotionRows rows back through the heads and the layers; leaves dpre / dheads for the
 // weight-gradient kernel and sums the gradient of the time features.
-__global__ void __launch_bounds__(kMotionMaxWidth) motion_backward_rows_kernel(MotionBwdDev b) {
+__global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(MotionBwdDev b) {
   constexpr int R = kMotionRows;
-  __shared__ __align__(16) float s_dy[R * kMotionMaxWidth];  // [r][j]
-  __shared__ __align__(16) float s_dx[R * kMotionMaxIn];     // [r][k]
+  extern __shared__ __align__(128) float s_slabs[];          // [2][kSlabFloats]
+  __shared__ __align__(8) uint64_t s_bar[2];
+  __shared__ MatSeq s_seq;
+  __shared__ __align__(16) float s_a[kMotionMaxIn * R];      // [k][r], ping
+  __shared__ __align__(16) float s_b[kMotionMaxIn * R];      // [k][r], pong
   __shared__ float s_gh[R][kHeadsMax];
   __shared__ float s_gtf[64];
   const MotionDev &a = b.f;
   const MotionLayout &L = a.L;
   const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R, W = L.width;
   const float *P = a.params;
+  if (j == 0) {
+    s_seq.n = L.depth;
+    for (int s = 0; s < L.depth; ++s) {  // consumed from the last layer down
+      const int i = L.depth - 1 - s;
+      s_seq.ptr[s] = b.wt + b.wt_off[i], s_seq.rows[s] = W, s_seq.stride[s] = b.in_pad[i];
+    }
+  }
   for (int u = j; u < 64; u += nt) s_gtf[u] = 0.0f;
+  __syncthreads();
+  SlabPipe pipe;
+  pipe_start(pipe, s_slabs, s_bar, &s_seq);
 
   // adjoint of the epilogue -> gradient of the raw head outputs
   if (j < R) {
@@ -280,61 +413,52 @@ __global__ void __launch_bounds__(kMotionMaxWidth) motion_backward_rows_kernel(M
     }
   }
   __syncthreads();
-  // gradient of the last activations: dh[r][k] = sum_o g[r][o] Wh[k][o]
-  {
-    float wh[kHeadsMax];
-    for (int o = 0; o < L.NH; ++o) wh[o] = P[L.heads_W + (long long) j * L.NH + o];
-    for (int r = 0; r < R; ++r) {
-      float acc = 0.0f;
-      for (int o = 0; o < L.NH; ++o) acc += s_gh[r][o] * wh[o];
-      s_dy[r * W + j] = acc;
-    }
+  // gradient of the last activations: dh[k][r] = sum_o g[r][o] Wh[k][o]
+  float *s_dy = s_a, *s_dx = s_b;
+  for (int e = j; e < W * R; e += nt) {
+    const int k = e / R, r = e - k * R;
+    float acc = 0.0f;
+    for (int o = 0; o < L.NH; ++o) acc += s_gh[r][o] * P[L.heads_W + (long long) k * L.NH + o];
+    s_dy[e] = acc;
   }
   __syncthreads();
-  for (int i = L.depth - 1; i >= 0; --i) {
+  for (int i = L.depth - 1, s = 0; i >= 0; --i, ++s) {
     // through the ReLU; keep the pre-activation gradient for the weight gradients
-    for (int r = 0; r < R; ++r) {
-      const int m = row0 + r;
+    for (int e = j; e < W * R; e += nt) {
+      const int r = e / W, col = e - r * W, m = row0 + r;
       float g = 0.0f;
       if (m < a.M) {
-        g = a.h[((size_t) i * a.M + m) * W + j] > 0.0f ? s_dy[r * W + j] : 0.0f;
-        b.dpre[((size_t) i * a.M + m) * W + j] = g;
+        g = a.h[((size_t) i * a.M + m) * W + col] > 0.0f ? s_dy[col * R + r] : 0.0f;
+        b.dpre[((size_t) i * a.M + m) * W + col] = g;
       }
-      s_dy[r * W + j] = g;
+      s_dy[col * R + r] = g;
     }
     __syncthreads();
-    // dX[r][k] = sum_j dY[r][j] W[k][j]
-    const int in = L.lin_in[i];
-    const float *Wi = P + L.lin_W[i];
-    for (int k = j; k < in; k += nt) {
-      float acc[R];
+    // dX[r][k] = sum_j dY[r][j] W[k][j], as a row-block GEMM on the transposed copy
+    float acc[8][4];
 #pragma unroll
-      for (int r = 0; r < R; ++r) acc[r] = 0.0f;
-      const float4 *wrow = reinterpret_cast<const float4 *>(Wi + (size_t) k * W);
-      for (int c = 0; c < W / 4; ++c) {
-        const float4 w = __ldg(wrow + c);
+    for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+    rowblock_gemm(pipe, s, s_dy, acc);
+    const int ip = b.in_pad[i];
+    if (4 * j < ip) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const float4 d = *reinterpret_cast<const float4 *>(s_dy + r * W + 4 * c);
-          acc[r] += d.x * w.x + d.y * w.y + d.z * w.z + d.w * w.w;
-        }
-      }
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
-      for (int r = 0; r < R; ++r) s_dx[r * kMotionMaxIn + k] = acc[r];
+        for (int r = 0; r < 8; ++r) s_dx[(4 * j + c) * R + r] = acc[r][c];
     }
     __syncthreads();
     // split the input gradient: encodings (only their time features carry on) | previous activations
     const int lead = (i == 0 || i == L.skip + 1) ? L.in0 : 0;
     if (lead) {
       for (int u = j; u < L.To; u += nt) {
-        float s = 0.0f;
-        for (int r = 0; r < R; ++r)
-          if (row0 + r < a.M) s += s_dx[r * kMotionMaxIn + L.Ep + u];
-        s_gtf[u] += s;
+        float sum = 0.0f;
+        for (int r = 0; r < R; ++r) sum += s_dx[(L.Ep + u) * R + r];   // rows beyond M carry zero gradients
+        s_gtf[u] += sum;
       }
     }
-    if (i > 0)
-      for (int r = 0; r < R; ++r) s_dy[r * W + j] = s_dx[r * kMotionMaxIn + lead + j];
+    if (i > 0) {  // the previous layer's output gradient starts `lead` rows into s_dx: copy it to the front of the other buffer
+      for (int e = j; e < W * R; e += nt) s_dy[e] = s_dx[lead * R + e];
+    }
     __syncthreads();
   }
   for (int u = j; u < L.To; u += nt)
@@ -513,8 +637,29 @@ static bool fill_motion(const fsgs_motion_args *a, MotionDev &d) {
   return true;
 }
 
+static size_t motion_wt_floats(const MotionLayout &L) {
+  size_t n = 0;
+  for (int i = 0; i < L.depth; ++i) n += (size_t) L.width * pad4(L.lin_in[i]);
+  return n;
+}
+
 static size_t motion_ws_floats(const MotionLayout &L, size_t M) {
-  return pad4(M * L.in0) + 2 * pad4((size_t) L.depth * M * L.width) + 2 * pad4(M * L.NH) + pad4(L.Ht > 0 ? L.Ht : 4) + 64;
+  return pad4(M * L.in0) + 2 * pad4((size_t) L.depth * M * L.width) + 2 * pad4(M * L.NH) + pad4(L.Ht > 0 ? L.Ht : 4) + 64 +
+         motion_wt_floats(L);
+}
+
+// the opt-in above 48 KB of dynamic shared memory is a per-device attribute of each kernel
+static bool motion_configure() {
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  if (configured[dev]) return true;
+  const int dyn = (int) (sizeof(float) * 2 * kSlabFloats);
+  if (cudaFuncSetAttribute(motion_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess ||
+      cudaFuncSetAttribute(motion_backward_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess)
+    return false;
+  configured[dev] = true;
+  return true;
 }
 
 }  // namespace fsgs
@@ -548,7 +693,9 @@ extern "C" int fsgs_motion_forward(const fsgs_motion_args *a, fsgs_stream_t stre
   FSGS_REQUIRE(a->sp_q && a->sp_t && a->sp_dr && a->sp_ds);
   if (a->workspace_bytes < fsgs_motion_workspace_bytes(&a->cfg)) return FSGS_ERR_WORKSPACE;
   d.sp_q = (float4 *) a->sp_q, d.sp_t = a->sp_t, d.sp_dr = (float4 *) a->sp_dr, d.sp_ds = (float2 *) a->sp_ds;
-  motion_forward_kernel<<<ceil_div(d.M, kMotionRows), d.L.width, 0, (cudaStream_t) stream>>>(d);
+  if (!motion_configure()) return FSGS_ERR_LAUNCH;
+  motion_forward_kernel<<<ceil_div(d.M, kMotionRows), kMotionThreads, sizeof(float) * 2 * kSlabFloats,
+      (cudaStream_t) stream>>>(d);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }
@@ -563,13 +710,25 @@ extern "C" int fsgs_motion_backward(const fsgs_motion_args *a, fsgs_stream_t str
   float *w = b.f.time_hidden + pad4(L.Ht > 0 ? L.Ht : 4);
   b.dpre = w, w += pad4((size_t) L.depth * M * L.width);
   b.dheads = w, w += pad4(M * L.NH);
-  b.g_tf = w;
+  b.g_tf = w, w += 64;
+  b.wt = w;
+  {
+    long long off = 0;
+    for (int i = 0; i < L.depth; ++i) {
+      b.in_pad[i] = (int) pad4(L.lin_in[i]);
+      b.wt_off[i] = off;
+      off += (long long) L.width * b.in_pad[i];
+    }
+  }
   b.g_sp_q = (const float4 *) a->g_sp_q, b.g_sp_t = a->g_sp_t, b.g_sp_dr = (const float4 *) a->g_sp_dr;
   b.g_sp_ds = (const float2 *) a->g_sp_ds;
   b.g_params = a->g_params, b.accumulate = a->accumulate;
   cudaStream_t st = (cudaStream_t) stream;
+  if (!motion_configure()) return FSGS_ERR_LAUNCH;
   cudaMemsetAsync(b.g_tf, 0, sizeof(float) * 64, st);
-  motion_backward_rows_kernel<<<ceil_div(b.f.M, kMotionRows), L.width, 0, st>>>(b);
+  motion_transpose_kernel<<<dim3(ceil_div(L.in0 + L.width, 32), ceil_div(L.width, 32), L.depth), 256, 0, st>>>(b);
+  FSGS_LAUNCH_CHECK();
+  motion_backward_rows_kernel<<<ceil_div(b.f.M, kMotionRows), kMotionThreads, sizeof(float) * 2 * kSlabFloats, st>>>(b);
   FSGS_LAUNCH_CHECK();
   const int tiles_k = ceil_div(L.in0 + L.width, kTileK);  // enough for the widest input; narrower layers exit early
   const int tiles_j = ceil_div(L.width, kTileJ);

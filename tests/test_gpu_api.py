@@ -309,6 +309,12 @@ def test_native_training_views_equal_the_autograd_route():
             # and Adam (steps of up to the learning rate whatever the gradient's size) amplifies that for a few elements
             d = (x - y).abs()
             assert float(d.mean()) < 1e-6 and float(d.max()) < 5e-4, (n_views, distributed)
+    # a rank without a view this step (more ranks than views) steps with zero gradients and an empty mask: no change
+    a = DynamicScene(surf, centres, K=3, device="cuda")
+    a.train_views(views[:1], (W, H), distributed=True)
+    before = [p.detach().clone() for p in a.params]
+    a.train_views([], (W, H), distributed=True)
+    assert all(torch.equal(p.detach(), q) for p, q in zip(a.params, before))
     # the sigmoid inside the preprocess kernel reproduces the framework's bits: identical radii and images
     a = DynamicScene(surf, centres, K=3, device="cuda")
     eng = a._engine((W, H))
