@@ -46,8 +46,8 @@ METRIC = "train_iters_per_s"
 UNIT = "iters/s"
 STAGES = ["preprocess_forward", "bin_tiles", "blend_forward", "blend_backward", "preprocess_backward", "lbs_backward"]
 # DRAM bytes (read + write) of one compositing-backward launch, from ncu captures of this command's workload
-# (profiles/blend_backward_*.md): workload -> bytes
-NCU_TRAFFIC_BLEND_BACKWARD = {}
+# (profiles/blend_kernels_*.md): workload -> bytes
+NCU_TRAFFIC_BLEND_BACKWARD = {"train_300k_800": 53.728e6 + 1.317e6}
 
 
 def parse():
