@@ -679,12 +679,17 @@ def run_ours(args):
 
     # the step with the superpoint motion produced by the deformation network at a time t (network trained as well,
     # kernel-weighted LBS weights re-evaluated and trained): what the reference's iteration does before its render
-    ms_step_motion = motion_ms = None
+    ms_step_motion = motion_ms = motion_pairs = None
     if n_views:
         from fsgs.motion import MotionNet
         net = MotionNet(M, device=dev, local_frame=True, seed=1)
+        # The network's learning rate is 1e-6 here, not the trainer's 1.6e-4: the upstream gradient is noise whose sign
+        # alternates, and while that keeps the Gaussians in place (each parameter moves by +-lr), a step of 1.6e-4 on
+        # all 523 k weights at once moves the network's OUTPUT by a tenth of the scene and the scene then drifts
+        # (pair count x 30 within 30 steps).  Every kernel of the step runs the same at either rate;
+        # `motion_net_pairs_first_last` in the output shows that the workload stayed put.
         scene_m = DynamicScene(wlk["surf"], wlk["centres"], K=K, device=dev, motion_net=net,
-                               kernel_weights=(torch.full((M,), -1.5), torch.zeros(M)),
+                               kernel_weights=(torch.full((M,), -1.5), torch.zeros(M)), lr_deform=1e-6,
                                lrs=dict(xyz=lr, sh_dc=lr, sh_rest=lr, opacity=lr, scaling=lr, rotation=lr))
         t_views = [[dict(cam=v[k]["cam"], t=torch.tensor([0.1 + 0.8 * j / max(n_views, 1)], device=dev),
                          g_images=v[k]["g_images"], g_opacity=v[k]["g_opacity"]) for k in (0, 1)]
@@ -697,7 +702,11 @@ def run_ours(args):
 
         for _ in range(3):
             step_motion()
+        scene_m.check()
+        motion_pairs = [scene_m.engine.last_pairs]
         ms_step_motion, _ = timed(step_motion, args.steps, "step_motion_net")
+        scene_m.check()
+        motion_pairs.append(scene_m.engine.last_pairs)
         t0 = t_views[0][0]["t"]
         gp = torch.zeros_like(net.params.data)
         gm = {k: torch.randn_like(x) for k, x in net.forward(scene_m.centres, t0).items()}
@@ -793,7 +802,8 @@ def run_ours(args):
             "fwd_frames_per_s": total_views * 1e3 / ms_fwd, "ms_per_fwd_batch": ms_fwd,
             "fwd_repeats": {"min": fwd_runs[0], "max": fwd_runs[-1]},
             "ms_per_step_with_aux_gradients": ms_step_aux, "ms_per_step_with_l1_ssim_loss": ms_step_loss,
-            "ms_per_step_with_motion_net": ms_step_motion, "motion_net_ms": motion_ms,
+            "ms_per_step_with_motion_net": ms_step_motion, "motion_net_pairs_first_last": motion_pairs,
+            "motion_net_ms": motion_ms,
             "e2e": {"value": total_views * 1e3 / ms_e2e, "unit": UNIT, "ms_per_step": ms_e2e,
                     "ms_per_step_min_max": [e2e_runs[0], e2e_runs[-1]], "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4 + 32 * n_views},

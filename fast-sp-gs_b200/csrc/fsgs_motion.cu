@@ -108,57 +108,113 @@ __device__ __forceinline__ void freq_encode(float x, int deg, float scale, int d
 }
 
 // ---- the row-block GEMM both passes are built on ---------------------------------------------------------------
-// A block carries R = 8 rows.  For one matrix Wm [K, N] (row major, N a multiple of 4) it computes
-//   acc[r][c] += sum_k act[k][r] * Wm[k][4 t + c]          r < 8, c < 4, thread t < N / 4
-// with the activations in shared memory k major ([k][r]: one 16-byte broadcast load feeds four rows) and the matrix
-// streamed through two shared-memory buffers in slabs of kSlabRows rows by bulk asynchronous copies issued two slabs
-// ahead, across matrix boundaries.  32 accumulators per thread: every shared-memory load feeds 4 to 8 multiply-adds;
-// with one output column per thread the kernel was bound by the broadcast loads and five times slower.
-constexpr int kMotionThreads = 128;
-constexpr int kSlabRows = 32;
-constexpr int kSlabFloats = kSlabRows * kMotionMaxIn;   // a slab of the widest matrix
+// A block carries R = 8 rows through a chain of matrices.  For one matrix Wm [K, N] (row major, N a multiple of 4)
+//   out[r][n] = sum_k act[k][r] * Wm[k][n]                 r < 8
+// is computed by C = N / 4 column threads x G k-groups (G = 5 .. 8, the split of the block's 512 threads): thread
+// (g, c) keeps an 8 x 4 block of partial sums over the rows k = g, g + G, ... of every slab in registers -- one
+// 16-byte weight load and two broadcast activation loads feed 32 multiply-adds -- the G partial blocks meet in shared
+// memory and a second pass adds them up, lanes along n.  The matrices stream from L2 through a ring of four
+// shared-memory buffers by bulk asynchronous copies issued three slabs ahead, across matrix boundaries, so the chain
+// of eight dependent layers never waits for a cold fetch; one block barrier per slab both frees the buffer just read
+// and publishes whether the next one arrived.  With one column per thread the kernel was bound by the broadcast
+// loads; with 8 x 4 blocks but no split over k only two warps per SM had work, at one quarter of the speed.
+constexpr int kMotionThreads = 512;
+constexpr int kSlabBufs = 4;
+constexpr int kSlabFloats = 8192;             // 32 KB per buffer: 32 rows of a 256-wide matrix
+constexpr int kSplitMax = 8;
+constexpr int kPartFloats = kSplitMax * kMotionRows * (kMotionMaxWidth + 4);
+constexpr int kMotionDynFloats = kSlabBufs * kSlabFloats + kPartFloats;
+static_assert(kMotionRows == 8, "the register blocks and the [k][8] activation layout assume 8 rows per block");
+static_assert(2 * kMotionMaxIn <= 2 * kMotionThreads, "the reduction visits at most two items per thread");
 
 struct MatSeq {  // the matrices a pass consumes, in order (shared memory)
-  const float *ptr[17];
-  int rows[17], stride[17];
-  int n;
+  const float *ptr[18];
+  int rows[18], stride[18], srows[18];
+  int n, total;  // matrices, slabs
 };
 
+// slab height and slab count of every matrix (one thread, after ptr / rows / stride are filled in)
+__device__ __forceinline__ void seq_finish(MatSeq &s) {
+  s.total = 0;
+  for (int m = 0; m < s.n; ++m) {
+    s.srows[m] = max(8, (kSlabFloats / s.stride[m]) & ~7);
+    s.total += (s.rows[m] + s.srows[m] - 1) / s.srows[m];
+  }
+}
+
+__device__ __forceinline__ int gemm_split(int N) {
+  return min(kSplitMax, min(kMotionThreads / (N >> 2), kPartFloats / (kMotionRows * (N + 4))));
+}
+
 struct SlabPipe {
-  float *buf;        // [2][kSlabFloats]
-  uint64_t *bar;     // [2]
+  float *buf;        // [kSlabBufs][kSlabFloats]
+  uint64_t *bar;     // [kSlabBufs]
   const MatSeq *seq;
-  int issue_m, issue_k;  // next slab to fetch: matrix, first row
-  int n_used;            // slabs consumed so far
+  int issue_m, issue_k, fetched;  // producer state (thread 0): next slab's matrix and first row, slabs issued
+  int n_used;                     // slabs consumed (every thread, uniform)
+  bool broken;                    // a wait ran out: from then on every slab is read from global memory (uniform)
 
   __device__ __forceinline__ void fetch_next() {  // thread 0 only; the target buffer must be free
     if (issue_m >= seq->n) return;
-    const int rows = min(kSlabRows, seq->rows[issue_m] - issue_k), stride = seq->stride[issue_m];
-    const int b = fetched & 1;
+    const int stride = seq->stride[issue_m], rows = min(seq->srows[issue_m], seq->rows[issue_m] - issue_k);
+    const int b = fetched % kSlabBufs;
     const uint32_t bytes = (uint32_t) rows * stride * 4u;
     mbar_arrive_expect_tx(&bar[b], bytes);
     bulk_load(buf + b * kSlabFloats, seq->ptr[issue_m] + (size_t) issue_k * stride, bytes, &bar[b]);
     ++fetched;
-    issue_k += kSlabRows;
+    issue_k += rows;
     if (issue_k >= seq->rows[issue_m]) ++issue_m, issue_k = 0;
   }
-  int fetched;
+  // rows k0.. of matrix m, which is the slab now at the head of the ring
+  __device__ __forceinline__ const float *slab(int m, int k0) const {
+    return broken ? seq->ptr[m] + (size_t) k0 * seq->stride[m] : buf + (n_used % kSlabBufs) * kSlabFloats;
+  }
+  __device__ __forceinline__ void await(int s) {  // every thread; s = index of the slab about to be read
+    bool late = false;
+    if (!broken && s < seq->total) late = !mbar_wait_bounded(&bar[s % kSlabBufs], (uint32_t) ((s / kSlabBufs) & 1));
+    if (__syncthreads_or(late)) broken = true;
+  }
+  // every thread: done with the slab at the head; its buffer is refilled and the next slab awaited
+  __device__ __forceinline__ void advance() {
+    await(n_used + 1);
+    if (threadIdx.x == 0 && !broken) fetch_next();
+    ++n_used;
+  }
+  // after the last slab: nothing is in flight unless a wait ran out; then give the stragglers one more bounded wait
+  __device__ __forceinline__ void finish() {
+    if (broken && threadIdx.x == 0)
+      for (int s = max(0, fetched - kSlabBufs); s < fetched; ++s)
+        mbar_wait_bounded(&bar[s % kSlabBufs], (uint32_t) ((s / kSlabBufs) & 1));
+  }
 };
 
-// acc += act^T-block times matrix m of the sequence (all K rows).  Every thread of the block must call it.
-__device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float *s_act, float (&acc)[8][4]) {
-  const int K = pipe.seq->rows[m], N = pipe.seq->stride[m], t = threadIdx.x;
-  const bool mine = 4 * t < N;
-  for (int k0 = 0; k0 < K; k0 += kSlabRows, ++pipe.n_used) {
-    const int b = pipe.n_used & 1, rows = min(kSlabRows, K - k0);
-    // a wait that runs out falls back to reading the slab from global memory
-    const bool late = !mbar_wait_bounded(&pipe.bar[b], (uint32_t) ((pipe.n_used >> 1) & 1));
-    const bool direct = __syncthreads_or(late);
-    const float *w = direct ? pipe.seq->ptr[m] + (size_t) k0 * N : pipe.buf + b * kSlabFloats;
+__device__ __forceinline__ void pipe_start(SlabPipe &pipe, float *buf, uint64_t *bar, const MatSeq *seq) {
+  pipe.buf = buf, pipe.bar = bar, pipe.seq = seq, pipe.issue_m = 0, pipe.issue_k = 0, pipe.n_used = 0, pipe.fetched = 0;
+  pipe.broken = false;
+  if (threadIdx.x == 0)
+    for (int b = 0; b < kSlabBufs; ++b) mbar_init(&bar[b], 1);
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int b = 0; b < kSlabBufs; ++b) pipe.fetch_next();
+}
+
+// Partial sums of act^T-block x matrix m (all its rows) into s_part[g][r][N + 4].  Every thread of the block calls
+// it; on return the partial sums are complete and s_act is free.
+__device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float *s_act, float *s_part) {
+  const int K = pipe.seq->rows[m], N = pipe.seq->stride[m], sr = pipe.seq->srows[m], t = threadIdx.x;
+  const int C = N >> 2, G = gemm_split(N);
+  const int kg = t / C, ct = t - kg * C;
+  const bool mine = kg < G;
+  float acc[8][4];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+  for (int k0 = 0; k0 < K; k0 += sr) {
+    const int rows = min(sr, K - k0);
+    const float *w = pipe.slab(m, k0) + 4 * ct;
     if (mine) {
-#pragma unroll 2
-      for (int kk = 0; kk < rows; ++kk) {
-        const float4 wv = *reinterpret_cast<const float4 *>(w + kk * N + 4 * t);
+#pragma unroll 4
+      for (int kk = kg; kk < rows; kk += G) {
+        const float4 wv = *reinterpret_cast<const float4 *>(w + kk * N);
         const float4 a0 = *reinterpret_cast<const float4 *>(s_act + (k0 + kk) * 8);
         const float4 a1 = *reinterpret_cast<const float4 *>(s_act + (k0 + kk) * 8 + 4);
         const float ar[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
@@ -167,44 +223,60 @@ __device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float
           acc[r][0] += ar[r] * wv.x, acc[r][1] += ar[r] * wv.y, acc[r][2] += ar[r] * wv.z, acc[r][3] += ar[r] * wv.w;
       }
     }
-    __syncthreads();  // every thread is done with buffer b
-    if (t == 0) pipe.fetch_next();
+    pipe.advance();
   }
-}
-
-__device__ __forceinline__ void pipe_start(SlabPipe &pipe, float *buf, uint64_t *bar, const MatSeq *seq) {
-  pipe.buf = buf, pipe.bar = bar, pipe.seq = seq, pipe.issue_m = 0, pipe.issue_k = 0, pipe.n_used = 0, pipe.fetched = 0;
-  if (threadIdx.x == 0) {
-    mbar_init(&bar[0], 1), mbar_init(&bar[1], 1);
+  if (mine) {
+    const int Np = N + 4;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      *reinterpret_cast<float4 *>(s_part + (kg * 8 + r) * Np + 4 * ct) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
   }
   __syncthreads();
-  if (threadIdx.x == 0) pipe.fetch_next(), pipe.fetch_next();
+}
+
+// Adds the G partial blocks: item (n, half) -- column n, rows 4 half .. 4 half + 3 -- goes to epi(slot, n, half, sums)
+// with slot = 0 or 1 counting the items of this thread (so that the caller can pair them with values it fetched ahead).
+template <class F>
+__device__ __forceinline__ void rowblock_reduce(const float *s_part, int N, F epi) {
+  const int G = gemm_split(N), Np = N + 4;
+#pragma unroll
+  for (int slot = 0; slot < 2; ++slot) {
+    const int e = threadIdx.x + slot * kMotionThreads;
+    if (e >= 2 * N) break;
+    const int half = e >= N ? 1 : 0, n = e - half * N;
+    float4 s = make_float4(0, 0, 0, 0);
+    const float *p = s_part + (4 * half) * Np + n;
+    for (int g = 0; g < G; ++g, p += 8 * Np) s.x += p[0], s.y += p[Np], s.z += p[2 * Np], s.w += p[3 * Np];
+    epi(slot, n, half, s);
+  }
 }
 
 // One block = kMotionRows rows through the whole network, kMotionThreads threads.
 __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDev a) {
   constexpr int R = kMotionRows;
-  extern __shared__ __align__(128) float s_slabs[];        // [2][kSlabFloats]
-  __shared__ __align__(8) uint64_t s_bar[2];
+  extern __shared__ __align__(128) float s_dyn[];            // slabs [kSlabBufs][kSlabFloats] | partial sums
+  float *s_part = s_dyn + kSlabBufs * kSlabFloats;
+  __shared__ __align__(8) uint64_t s_bar[kSlabBufs];
   __shared__ MatSeq s_seq;
-  __shared__ __align__(16) float s_in[kMotionMaxIn * R];   // [k][r]: the layer's input, k major
-  __shared__ __align__(16) float s_out[kMotionMaxWidth * R];
-  __shared__ float s_x0[R][128];                           // row major copy of the layer-0 input (for the skip)
-  __shared__ float s_te[32];                               // time encoding
-  __shared__ float s_th[1024];                             // time-network hidden layer
-  __shared__ float s_tf[64];                               // time features
+  __shared__ __align__(16) float s_in[kMotionMaxIn * R];     // [k][r]: the layer's input, k major
+  __shared__ float s_x0[R][128];                             // row major copy of the layer-0 input (for the skip)
+  __shared__ float s_te[32];                                 // time encoding
+  __shared__ float s_th[1024];                               // time-network hidden layer
+  __shared__ float s_tf[64];                                 // time features
   __shared__ float s_heads[R][kHeadsMax];
   const MotionLayout &L = a.L;
   const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R;
   const int W = L.width;
   const float *P = a.params;
   if (j == 0) {
-    s_seq.n = L.depth;
+    s_seq.n = L.depth + 1;
     for (int i = 0; i < L.depth; ++i) s_seq.ptr[i] = P + L.lin_W[i], s_seq.rows[i] = L.lin_in[i], s_seq.stride[i] = W;
+    s_seq.ptr[L.depth] = P + L.heads_W, s_seq.rows[L.depth] = W, s_seq.stride[L.depth] = L.NH;
+    seq_finish(s_seq);
   }
   __syncthreads();
   SlabPipe pipe;
-  pipe_start(pipe, s_slabs, s_bar, &s_seq);   // the first two slabs travel while the encodings are evaluated
+  pipe_start(pipe, s_dyn, s_bar, &s_seq);   // the first slabs travel while the encodings are evaluated
 
   // encodings
   if (j == 0) freq_encode(a.t[0], (L.Et - 1) / 2, a.scale_t, 1, 0, s_te);
@@ -222,10 +294,10 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
       s_th[u] = fmaxf(acc, 0.0f);
     }
     __syncthreads();
-    // every warp sums a quarter of the hidden units for all outputs, then the quarters are added
+    // every warp sums its share of the hidden units for all outputs, then the shares are added
     {
       const int lane = j & 31, warp = j >> 5, nw = nt >> 5;
-      float *part = s_out;  // [nw][64] scratch (s_out is not yet in use)
+      float *part = s_part;  // [nw][64] scratch
       for (int u = lane; u < L.To; u += 32) {
         float acc = 0.0f;
         for (int k = warp; k < L.Ht; k += nw) acc += s_th[k] * P[L.time2_W + (long long) k * L.To + u];
@@ -254,46 +326,55 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
     s_in[k * R + r] = s_x0[r][k];
     if (row0 + r < a.M) a.x0[(size_t) (row0 + r) * L.in0 + k] = s_x0[r][k];
   }
-  __syncthreads();
+  pipe.await(0);  // block barrier: s_in is complete and slab 0 has landed
 
   for (int i = 0; i < L.depth; ++i) {
-    float acc[8][4];
-    const bool mine = 4 * j < W;
-    float4 bias = make_float4(0, 0, 0, 0);
-    if (mine) bias = *reinterpret_cast<const float4 *>(P + L.lin_b[i] + 4 * j);
-#pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r][0] = bias.x, acc[r][1] = bias.y, acc[r][2] = bias.z, acc[r][3] = bias.w;
-    rowblock_gemm(pipe, i, s_in, acc);
-    if (mine) {
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float4 v = make_float4(fmaxf(acc[r][0], 0.0f), fmaxf(acc[r][1], 0.0f), fmaxf(acc[r][2], 0.0f),
-            fmaxf(acc[r][3], 0.0f));
-        s_out[(4 * j) * R + r] = v.x, s_out[(4 * j + 1) * R + r] = v.y;
-        s_out[(4 * j + 2) * R + r] = v.z, s_out[(4 * j + 3) * R + r] = v.w;
-        if (row0 + r < a.M) *reinterpret_cast<float4 *>(a.h + ((size_t) i * a.M + row0 + r) * W + 4 * j) = v;
-      }
-    }
-    __syncthreads();
-    // next layer's input: the activations, preceded by the encodings after the skip layer
+    rowblock_gemm(pipe, i, s_in, s_part);
+    // bias, ReLU; the activations become the next layer's input, preceded by the encodings after the skip layer
     const int lead = (i == L.skip) ? L.in0 : 0;
+    rowblock_reduce(s_part, W, [&](int, int n, int half, float4 s) {
+      const float bias = P[L.lin_b[i] + n];
+      const float4 v = make_float4(fmaxf(s.x + bias, 0.0f), fmaxf(s.y + bias, 0.0f), fmaxf(s.z + bias, 0.0f),
+          fmaxf(s.w + bias, 0.0f));
+      *reinterpret_cast<float4 *>(s_in + (lead + n) * R + 4 * half) = v;
+      const int m = row0 + 4 * half;
+      float *h = a.h + ((size_t) i * a.M + m) * W + n;
+      if (m < a.M) h[0] = v.x;
+      if (m + 1 < a.M) h[W] = v.y;
+      if (m + 2 < a.M) h[2 * W] = v.z;
+      if (m + 3 < a.M) h[3 * W] = v.w;
+    });
     if (lead)
       for (int e = j; e < R * lead; e += nt) {
         const int r = e / lead, k = e - r * lead;
         s_in[k * R + r] = s_x0[r][k];
       }
-    for (int e = j; e < W * R; e += nt) s_in[lead * R + e] = s_out[e];
     __syncthreads();
   }
 
-  // heads on the last activations (s_in[0 .. W*R), k major)
-  for (int e = j; e < R * L.NH; e += nt) {
-    const int r = e / L.NH, o = e - r * L.NH;
-    float acc = P[L.heads_b + o];
-    for (int k = 0; k < W; ++k) acc += s_in[k * R + r] * P[L.heads_W + (long long) k * L.NH + o];
-    s_heads[r][o] = acc;
-    if (row0 + r < a.M) a.heads[(size_t) (row0 + r) * L.NH + o] = acc;
+  // heads on the last activations (s_in[0 .. W*R), k major): 4 k-groups x (row, output) pairs, matrix from the ring
+  {
+    const int NH = L.NH, E = R * NH, kg = j >> 7, e = j & 127;
+    const int r = e / NH, o = e - r * NH;
+    const bool mine = e < E;
+    const int sr = s_seq.srows[L.depth];
+    float acc = 0.0f;
+    for (int k0 = 0; k0 < W; k0 += sr) {
+      const int rows = min(sr, W - k0);
+      const float *w = pipe.slab(L.depth, k0);
+      if (mine)
+        for (int kk = kg; kk < rows; kk += 4) acc += s_in[(k0 + kk) * R + r] * w[kk * NH + o];
+      pipe.advance();
+    }
+    s_part[kg * 128 + e] = acc;
+    __syncthreads();
+    if (j < E) {
+      const float v = P[L.heads_b + o] + ((s_part[e] + s_part[128 + e]) + (s_part[256 + e] + s_part[384 + e]));
+      s_heads[r][o] = v;
+      if (row0 + r < a.M) a.heads[(size_t) (row0 + r) * NH + o] = v;
+    }
   }
+  pipe.finish();
   __syncthreads();
   if (j < R && row0 + j < a.M) {
     const int m = row0 + j;
@@ -357,16 +438,16 @@ __global__ void __launch_bounds__(256) motion_transpose_kernel(MotionBwdDev b) {
 // weight-gradient kernel and sums the gradient of the time features.
 __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(MotionBwdDev b) {
   constexpr int R = kMotionRows;
-  extern __shared__ __align__(128) float s_slabs[];          // [2][kSlabFloats]
-  __shared__ __align__(8) uint64_t s_bar[2];
+  extern __shared__ __align__(128) float s_dyn[];            // slabs [kSlabBufs][kSlabFloats] | partial sums
+  float *s_part = s_dyn + kSlabBufs * kSlabFloats;
+  __shared__ __align__(8) uint64_t s_bar[kSlabBufs];
   __shared__ MatSeq s_seq;
-  __shared__ __align__(16) float s_a[kMotionMaxIn * R];      // [k][r], ping
-  __shared__ __align__(16) float s_b[kMotionMaxIn * R];      // [k][r], pong
+  __shared__ __align__(16) float s_dy[kMotionMaxIn * R];     // [k][r]: gradient of the current layer's pre-activation
   __shared__ float s_gh[R][kHeadsMax];
   __shared__ float s_gtf[64];
   const MotionDev &a = b.f;
   const MotionLayout &L = a.L;
-  const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R, W = L.width;
+  const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R, W = L.width, M = a.M;
   const float *P = a.params;
   if (j == 0) {
     s_seq.n = L.depth;
@@ -374,18 +455,23 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
       const int i = L.depth - 1 - s;
       s_seq.ptr[s] = b.wt + b.wt_off[i], s_seq.rows[s] = W, s_seq.stride[s] = b.in_pad[i];
     }
+    seq_finish(s_seq);
   }
   for (int u = j; u < 64; u += nt) s_gtf[u] = 0.0f;
   __syncthreads();
   SlabPipe pipe;
-  pipe_start(pipe, s_slabs, s_bar, &s_seq);
+  pipe_start(pipe, s_dyn, s_bar, &s_seq);
 
+  // the heads' matrix [W][NH] into shared memory (the partial-sum area is idle until the first layer)
+  float *s_wh = s_part;
+  for (int e = j; e < W * L.NH / 4; e += nt)
+    reinterpret_cast<float4 *>(s_wh)[e] = reinterpret_cast<const float4 *>(P + L.heads_W)[e];
   // adjoint of the epilogue -> gradient of the raw head outputs
   if (j < R) {
     float *g = s_gh[j];
     for (int o = 0; o < kHeadsMax; ++o) g[o] = 0.0f;
     const int m = row0 + j;
-    if (m < a.M) {
+    if (m < M) {
       const float3 gt = make_float3(b.g_sp_t[3 * m], b.g_sp_t[3 * m + 1], b.g_sp_t[3 * m + 2]);
       g[0] = gt.x, g[1] = gt.y, g[2] = gt.z;
       const float2 gs = b.g_sp_ds[m];
@@ -413,54 +499,69 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
     }
   }
   __syncthreads();
-  // gradient of the last activations: dh[k][r] = sum_o g[r][o] Wh[k][o]
-  float *s_dy = s_a, *s_dx = s_b;
-  for (int e = j; e < W * R; e += nt) {
-    const int k = e / R, r = e - k * R;
-    float acc = 0.0f;
-    for (int o = 0; o < L.NH; ++o) acc += s_gh[r][o] * P[L.heads_W + (long long) k * L.NH + o];
-    s_dy[e] = acc;
+
+  // Through a ReLU: item (column n of layer i, rows 4 half ..) of the gradient dh of layer i's activations becomes the
+  // gradient of its pre-activations, kept in global memory for the weight gradients and in s_dy for the next product.
+  // hv = the four activations, fetched by the caller ahead of the arithmetic that produced dh.
+  auto through_relu = [&](int i, int n, int half, float4 dh, const float (&hv)[4]) {
+    const float4 g = make_float4(hv[0] > 0.0f ? dh.x : 0.0f, hv[1] > 0.0f ? dh.y : 0.0f, hv[2] > 0.0f ? dh.z : 0.0f,
+        hv[3] > 0.0f ? dh.w : 0.0f);
+    *reinterpret_cast<float4 *>(s_dy + n * R + 4 * half) = g;
+    const int m = row0 + 4 * half;
+    float *d = b.dpre + ((size_t) i * M + m) * W + n;
+    if (m < M) d[0] = g.x;
+    if (m + 1 < M) d[W] = g.y;
+    if (m + 2 < M) d[2 * W] = g.z;
+    if (m + 3 < M) d[3 * W] = g.w;
+  };
+  // the four activations of item (n, half) of layer i; rows beyond M read as 0 (their gradient stays 0)
+  auto fetch_h = [&](int i, int n, int half, float (&hv)[4]) {
+    const int m = row0 + 4 * half;
+    const float *h = a.h + ((size_t) i * M + m) * W + n;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) hv[q] = (m + q < M) ? h[(size_t) q * W] : 0.0f;
+  };
+
+  // gradient of the last activations: dh[n][r] = sum_o g[r][o] Wh[n][o]
+  {
+    const int e = j;  // 2 W <= 512 items
+    if (e < 2 * W) {
+      const int half = e >= W ? 1 : 0, n = e - half * W;
+      float hv[4];
+      fetch_h(L.depth - 1, n, half, hv);
+      float4 dh = make_float4(0, 0, 0, 0);
+      for (int o = 0; o < L.NH; ++o) {
+        const float w = s_wh[n * L.NH + o];
+        dh.x += s_gh[4 * half][o] * w, dh.y += s_gh[4 * half + 1][o] * w;
+        dh.z += s_gh[4 * half + 2][o] * w, dh.w += s_gh[4 * half + 3][o] * w;
+      }
+      through_relu(L.depth - 1, n, half, dh, hv);
+    }
   }
-  __syncthreads();
+  pipe.await(0);  // block barrier: s_dy complete, s_wh no longer needed, slab 0 landed
+
   for (int i = L.depth - 1, s = 0; i >= 0; --i, ++s) {
-    // through the ReLU; keep the pre-activation gradient for the weight gradients
-    for (int e = j; e < W * R; e += nt) {
-      const int r = e / W, col = e - r * W, m = row0 + r;
-      float g = 0.0f;
-      if (m < a.M) {
-        g = a.h[((size_t) i * a.M + m) * W + col] > 0.0f ? s_dy[col * R + r] : 0.0f;
-        b.dpre[((size_t) i * a.M + m) * W + col] = g;
-      }
-      s_dy[col * R + r] = g;
-    }
-    __syncthreads();
-    // dX[r][k] = sum_j dY[r][j] W[k][j], as a row-block GEMM on the transposed copy
-    float acc[8][4];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
-    rowblock_gemm(pipe, s, s_dy, acc);
+    // dX[r][k] = sum_j dY[r][j] W[k][j], as a row-block GEMM on the transposed copy.  Its columns: the encodings
+    // first where the layer has them (only their time features carry a gradient on), then the previous activations.
     const int ip = b.in_pad[i];
-    if (4 * j < ip) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int r = 0; r < 8; ++r) s_dx[(4 * j + c) * R + r] = acc[r][c];
-    }
-    __syncthreads();
-    // split the input gradient: encodings (only their time features carry on) | previous activations
     const int lead = (i == 0 || i == L.skip + 1) ? L.in0 : 0;
-    if (lead) {
-      for (int u = j; u < L.To; u += nt) {
-        float sum = 0.0f;
-        for (int r = 0; r < R; ++r) sum += s_dx[(L.Ep + u) * R + r];   // rows beyond M carry zero gradients
-        s_gtf[u] += sum;
-      }
+    float hv[2][4];
+#pragma unroll
+    for (int slot = 0; slot < 2; ++slot) {  // the previous layer's activations for this thread's items, fetched early
+      const int e = j + slot * kMotionThreads;
+      const int half = e >= ip ? 1 : 0, n = e - half * ip - lead;
+      if (i > 0 && e < 2 * ip && n >= 0 && n < W) fetch_h(i - 1, n, half, hv[slot]);
+      else hv[slot][0] = hv[slot][1] = hv[slot][2] = hv[slot][3] = 0.0f;
     }
-    if (i > 0) {  // the previous layer's output gradient starts `lead` rows into s_dx: copy it to the front of the other buffer
-      for (int e = j; e < W * R; e += nt) s_dy[e] = s_dx[lead * R + e];
-    }
+    rowblock_gemm(pipe, s, s_dy, s_part);
+    rowblock_reduce(s_part, ip, [&](int slot, int k, int half, float4 dx) {
+      if (lead && k >= L.Ep && k < L.in0) atomicAdd(&s_gtf[k - L.Ep], (dx.x + dx.y) + (dx.z + dx.w));
+      const int n = k - lead;
+      if (i > 0 && n >= 0 && n < W) through_relu(i - 1, n, half, dx, hv[slot]);
+    });
     __syncthreads();
   }
+  pipe.finish();
   for (int u = j; u < L.To; u += nt)
     if (s_gtf[u] != 0.0f) atomicAdd(b.g_tf + u, s_gtf[u]);
 }
@@ -654,7 +755,7 @@ static bool motion_configure() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
   if (configured[dev]) return true;
-  const int dyn = (int) (sizeof(float) * 2 * kSlabFloats);
+  const int dyn = (int) (sizeof(float) * kMotionDynFloats);
   if (cudaFuncSetAttribute(motion_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess ||
       cudaFuncSetAttribute(motion_backward_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess)
     return false;
@@ -694,7 +795,7 @@ extern "C" int fsgs_motion_forward(const fsgs_motion_args *a, fsgs_stream_t stre
   if (a->workspace_bytes < fsgs_motion_workspace_bytes(&a->cfg)) return FSGS_ERR_WORKSPACE;
   d.sp_q = (float4 *) a->sp_q, d.sp_t = a->sp_t, d.sp_dr = (float4 *) a->sp_dr, d.sp_ds = (float2 *) a->sp_ds;
   if (!motion_configure()) return FSGS_ERR_LAUNCH;
-  motion_forward_kernel<<<ceil_div(d.M, kMotionRows), kMotionThreads, sizeof(float) * 2 * kSlabFloats,
+  motion_forward_kernel<<<ceil_div(d.M, kMotionRows), kMotionThreads, sizeof(float) * kMotionDynFloats,
       (cudaStream_t) stream>>>(d);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
@@ -728,7 +829,7 @@ extern "C" int fsgs_motion_backward(const fsgs_motion_args *a, fsgs_stream_t str
   cudaMemsetAsync(b.g_tf, 0, sizeof(float) * 64, st);
   motion_transpose_kernel<<<dim3(ceil_div(L.in0 + L.width, 32), ceil_div(L.width, 32), L.depth), 256, 0, st>>>(b);
   FSGS_LAUNCH_CHECK();
-  motion_backward_rows_kernel<<<ceil_div(b.f.M, kMotionRows), kMotionThreads, sizeof(float) * 2 * kSlabFloats, st>>>(b);
+  motion_backward_rows_kernel<<<ceil_div(b.f.M, kMotionRows), kMotionThreads, sizeof(float) * kMotionDynFloats, st>>>(b);
   FSGS_LAUNCH_CHECK();
   const int tiles_k = ceil_div(L.in0 + L.width, kTileK);  // enough for the widest input; narrower layers exit early
   const int tiles_j = ceil_div(L.width, kTileJ);
