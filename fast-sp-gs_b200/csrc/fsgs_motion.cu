@@ -110,22 +110,46 @@ __device__ __forceinline__ void freq_encode(float x, int deg, float scale, int d
 // ---- the row-block GEMM both passes are built on ---------------------------------------------------------------
 // A block carries R = 8 rows through a chain of matrices.  For one matrix Wm [K, N] (row major, N a multiple of 4)
 //   out[r][n] = sum_k act[k][r] * Wm[k][n]                 r < 8
-// is computed by C = N / 4 column threads x G k-groups (G = 5 .. 8, the split of the block's 512 threads): thread
-// (g, c) keeps an 8 x 4 block of partial sums over the rows k = g, g + G, ... of every slab in registers -- one
+// is computed by C = N / 4 column threads x G k-groups (G = 5 .. 8, the split of the block's 512 worker threads):
+// thread (g, c) keeps an 8 x 4 block of partial sums over the rows k = g, g + G, ... of every slab in registers -- one
 // 16-byte weight load and two broadcast activation loads feed 32 multiply-adds -- the G partial blocks meet in shared
-// memory and a second pass adds them up, lanes along n.  The matrices stream from L2 through a ring of four
-// shared-memory buffers by bulk asynchronous copies issued three slabs ahead, across matrix boundaries, so the chain
-// of eight dependent layers never waits for a cold fetch; one block barrier per slab both frees the buffer just read
-// and publishes whether the next one arrived.  With one column per thread the kernel was bound by the broadcast
-// loads; with 8 x 4 blocks but no split over k only two warps per SM had work, at one quarter of the speed.
-constexpr int kMotionThreads = 512;
+// memory and a second pass adds them up, lanes along n.
+// The matrices stream from L2 through a ring of four shared-memory buffers by bulk asynchronous copies.  A seventeenth
+// warp is the producer: one thread that waits until all sixteen worker warps have released a buffer and refills it,
+// running up to four slabs ahead of the slowest worker, across matrix boundaries.  The workers never meet at a block
+// barrier for a slab: a warp waits for the slab's "full" barrier, multiplies, arrives on its "empty" barrier and
+// goes on, so that the chain of eight dependent layers is covered by copies already in flight and the warps absorb
+// each other's jitter; they meet (a named barrier over the 512 workers) only where a layer's partial sums are added.
+// Every wait is bounded: a worker whose slab does not arrive reads it from global memory instead, a producer whose
+// buffer is never released stops producing and says so, and the workers then read everything from global memory.
+// History: one column per thread was bound by the broadcast loads (0.15 ms forward at 512 rows); 8 x 4 register
+// blocks without a split over k left two warps per SM with work (same time); with the split and a block barrier
+// per slab 0.080 ms.
+constexpr int kWorkers = 512;                  // 16 warps
+constexpr int kMotionThreads = kWorkers + 32;  // + the producer warp
 constexpr int kSlabBufs = 4;
-constexpr int kSlabFloats = 8192;             // 32 KB per buffer: 32 rows of a 256-wide matrix
+constexpr int kSlabFloats = 8192;              // 32 KB per buffer: 32 rows of a 256-wide matrix
 constexpr int kSplitMax = 8;
 constexpr int kPartFloats = kSplitMax * kMotionRows * (kMotionMaxWidth + 4);
 constexpr int kMotionDynFloats = kSlabBufs * kSlabFloats + kPartFloats;
 static_assert(kMotionRows == 8, "the register blocks and the [k][8] activation layout assume 8 rows per block");
-static_assert(2 * kMotionMaxIn <= 2 * kMotionThreads, "the reduction visits at most two items per thread");
+static_assert(2 * kMotionMaxIn <= 2 * kWorkers, "the reduction visits at most two items per thread");
+
+// barrier over the worker warps only (the producer warp never joins)
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(smem_u32(bar)), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
 
 struct MatSeq {  // the matrices a pass consumes, in order (shared memory)
   const float *ptr[18];
@@ -143,65 +167,85 @@ __device__ __forceinline__ void seq_finish(MatSeq &s) {
 }
 
 __device__ __forceinline__ int gemm_split(int N) {
-  return min(kSplitMax, min(kMotionThreads / (N >> 2), kPartFloats / (kMotionRows * (N + 4))));
+  return min(kSplitMax, min(kWorkers / (N >> 2), kPartFloats / (kMotionRows * (N + 4))));
 }
 
-struct SlabPipe {
-  float *buf;        // [kSlabBufs][kSlabFloats]
-  uint64_t *bar;     // [kSlabBufs]
+struct SlabRing {
+  float *buf;            // [kSlabBufs][kSlabFloats]
+  uint64_t *full;        // [kSlabBufs] one arrival (the producer) + the copy's bytes
+  uint64_t *empty;       // [kSlabBufs] sixteen arrivals (one per worker warp)
   const MatSeq *seq;
-  int issue_m, issue_k, fetched;  // producer state (thread 0): next slab's matrix and first row, slabs issued
-  int n_used;                     // slabs consumed (every thread, uniform)
-  bool broken;                    // a wait ran out: from then on every slab is read from global memory (uniform)
+  volatile int *dead;    // set by the producer when it gives up
+  int next;              // worker: index of the next slab to consume
 
-  __device__ __forceinline__ void fetch_next() {  // thread 0 only; the target buffer must be free
-    if (issue_m >= seq->n) return;
-    const int stride = seq->stride[issue_m], rows = min(seq->srows[issue_m], seq->rows[issue_m] - issue_k);
-    const int b = fetched % kSlabBufs;
-    const uint32_t bytes = (uint32_t) rows * stride * 4u;
-    mbar_arrive_expect_tx(&bar[b], bytes);
-    bulk_load(buf + b * kSlabFloats, seq->ptr[issue_m] + (size_t) issue_k * stride, bytes, &bar[b]);
-    ++fetched;
-    issue_k += rows;
-    if (issue_k >= seq->rows[issue_m]) ++issue_m, issue_k = 0;
+  // Worker: the slab `next` of the sequence -- rows k0.. of matrix m.  Returns where to read it: the ring buffer, or
+  // global memory when the slab did not arrive.  Lane 0 polls; the others test once after it (already complete).
+  __device__ __forceinline__ const float *acquire(int m, int k0) {
+    uint64_t *bar = &full[next % kSlabBufs];
+    const uint32_t parity = (uint32_t) ((next / kSlabBufs) & 1);
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+      ok = false;
+      for (int i = 0; i < (1 << 20) && !ok && !*dead; ++i) ok = mbar_test(bar, parity);
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) ok = mbar_test(bar, parity);
+    return ok ? buf + (next % kSlabBufs) * kSlabFloats : seq->ptr[m] + (size_t) k0 * seq->stride[m];
   }
-  // rows k0.. of matrix m, which is the slab now at the head of the ring
-  __device__ __forceinline__ const float *slab(int m, int k0) const {
-    return broken ? seq->ptr[m] + (size_t) k0 * seq->stride[m] : buf + (n_used % kSlabBufs) * kSlabFloats;
-  }
-  __device__ __forceinline__ void await(int s) {  // every thread; s = index of the slab about to be read
-    bool late = false;
-    if (!broken && s < seq->total) late = !mbar_wait_bounded(&bar[s % kSlabBufs], (uint32_t) ((s / kSlabBufs) & 1));
-    if (__syncthreads_or(late)) broken = true;
-  }
-  // every thread: done with the slab at the head; its buffer is refilled and the next slab awaited
-  __device__ __forceinline__ void advance() {
-    await(n_used + 1);
-    if (threadIdx.x == 0 && !broken) fetch_next();
-    ++n_used;
-  }
-  // after the last slab: nothing is in flight unless a wait ran out; then give the stragglers one more bounded wait
-  __device__ __forceinline__ void finish() {
-    if (broken && threadIdx.x == 0)
-      for (int s = max(0, fetched - kSlabBufs); s < fetched; ++s)
-        mbar_wait_bounded(&bar[s % kSlabBufs], (uint32_t) ((s / kSlabBufs) & 1));
+  // Worker: this warp is done with the slab `next`
+  __device__ __forceinline__ void release() {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(&empty[next % kSlabBufs]);
+    ++next;
   }
 };
 
-__device__ __forceinline__ void pipe_start(SlabPipe &pipe, float *buf, uint64_t *bar, const MatSeq *seq) {
-  pipe.buf = buf, pipe.bar = bar, pipe.seq = seq, pipe.issue_m = 0, pipe.issue_k = 0, pipe.n_used = 0, pipe.fetched = 0;
-  pipe.broken = false;
-  if (threadIdx.x == 0)
-    for (int b = 0; b < kSlabBufs; ++b) mbar_init(&bar[b], 1);
-  __syncthreads();
-  if (threadIdx.x == 0)
-    for (int b = 0; b < kSlabBufs; ++b) pipe.fetch_next();
+// Producer (one thread): issues every slab of the sequence in order, each as soon as its buffer has been released.
+__device__ __forceinline__ void slab_producer(float *buf, uint64_t *full, uint64_t *empty, const MatSeq *seq,
+    volatile int *dead) {
+  int m = 0, k = 0, s = 0;
+  for (; s < seq->total; ++s) {
+    const int b = s % kSlabBufs;
+    if (s >= kSlabBufs) {
+      // the previous occupant: released by every worker warp, and its own copy complete (a worker that gave up
+      // waiting releases early)
+      const uint32_t parity = (uint32_t) (((s / kSlabBufs) - 1) & 1);
+      if (!mbar_wait_bounded(&empty[b], parity) || !mbar_wait_bounded(&full[b], parity)) break;
+    }
+    const int stride = seq->stride[m], rows = min(seq->srows[m], seq->rows[m] - k);
+    const uint32_t bytes = (uint32_t) rows * stride * 4u;
+    mbar_arrive_expect_tx(&full[b], bytes);
+    bulk_load(buf + b * kSlabFloats, seq->ptr[m] + (size_t) k * stride, bytes, &full[b]);
+    k += rows;
+    if (k >= seq->rows[m]) ++m, k = 0;
+  }
+  if (s < seq->total) {  // gave up: tell the workers, and give the copies still in flight one more bounded wait
+    *dead = 1;
+    for (int q = max(0, s - kSlabBufs); q < s; ++q) mbar_wait_bounded(&full[q % kSlabBufs], (uint32_t) ((q / kSlabBufs) & 1));
+  }
 }
 
-// Partial sums of act^T-block x matrix m (all its rows) into s_part[g][r][N + 4].  Every thread of the block calls
-// it; on return the partial sums are complete and s_act is free.
-__device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float *s_act, float *s_part) {
-  const int K = pipe.seq->rows[m], N = pipe.seq->stride[m], sr = pipe.seq->srows[m], t = threadIdx.x;
+// Every thread of the block calls this once, after s_seq is complete (it contains the block's only full barrier).
+// The producer warp does its whole job inside and returns true: the caller returns from the kernel.
+__device__ __forceinline__ bool ring_start(SlabRing &ring, float *buf, uint64_t *full, uint64_t *empty,
+    const MatSeq *seq, int *dead) {
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < kSlabBufs; ++b) mbar_init(&full[b], 1), mbar_init(&empty[b], kWorkers / 32);
+    *dead = 0;
+  }
+  __syncthreads();
+  ring.buf = buf, ring.full = full, ring.empty = empty, ring.seq = seq, ring.dead = dead, ring.next = 0;
+  if (threadIdx.x >= kWorkers) {
+    if (threadIdx.x == kWorkers) slab_producer(buf, full, empty, seq, dead);
+    return true;
+  }
+  return false;
+}
+
+// Partial sums of act^T-block x matrix m (all its rows) into s_part[g][r][N + 4].  Every worker thread calls it; on
+// return the partial sums are complete and s_act is free.
+__device__ __forceinline__ void rowblock_gemm(SlabRing &ring, int m, const float *s_act, float *s_part) {
+  const int K = ring.seq->rows[m], N = ring.seq->stride[m], sr = ring.seq->srows[m], t = threadIdx.x;
   const int C = N >> 2, G = gemm_split(N);
   const int kg = t / C, ct = t - kg * C;
   const bool mine = kg < G;
@@ -210,7 +254,7 @@ __device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float
   for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
   for (int k0 = 0; k0 < K; k0 += sr) {
     const int rows = min(sr, K - k0);
-    const float *w = pipe.slab(m, k0) + 4 * ct;
+    const float *w = ring.acquire(m, k0) + 4 * ct;
     if (mine) {
 #pragma unroll 4
       for (int kk = kg; kk < rows; kk += G) {
@@ -223,7 +267,7 @@ __device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float
           acc[r][0] += ar[r] * wv.x, acc[r][1] += ar[r] * wv.y, acc[r][2] += ar[r] * wv.z, acc[r][3] += ar[r] * wv.w;
       }
     }
-    pipe.advance();
+    ring.release();
   }
   if (mine) {
     const int Np = N + 4;
@@ -231,7 +275,7 @@ __device__ __forceinline__ void rowblock_gemm(SlabPipe &pipe, int m, const float
     for (int r = 0; r < 8; ++r)
       *reinterpret_cast<float4 *>(s_part + (kg * 8 + r) * Np + 4 * ct) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
   }
-  __syncthreads();
+  workers_sync();
 }
 
 // Adds the G partial blocks: item (n, half) -- column n, rows 4 half .. 4 half + 3 -- goes to epi(slot, n, half, sums)
@@ -241,7 +285,7 @@ __device__ __forceinline__ void rowblock_reduce(const float *s_part, int N, F ep
   const int G = gemm_split(N), Np = N + 4;
 #pragma unroll
   for (int slot = 0; slot < 2; ++slot) {
-    const int e = threadIdx.x + slot * kMotionThreads;
+    const int e = threadIdx.x + slot * kWorkers;
     if (e >= 2 * N) break;
     const int half = e >= N ? 1 : 0, n = e - half * N;
     float4 s = make_float4(0, 0, 0, 0);
@@ -256,7 +300,8 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
   constexpr int R = kMotionRows;
   extern __shared__ __align__(128) float s_dyn[];            // slabs [kSlabBufs][kSlabFloats] | partial sums
   float *s_part = s_dyn + kSlabBufs * kSlabFloats;
-  __shared__ __align__(8) uint64_t s_bar[kSlabBufs];
+  __shared__ __align__(8) uint64_t s_full[kSlabBufs], s_empty[kSlabBufs];
+  __shared__ int s_dead;
   __shared__ MatSeq s_seq;
   __shared__ __align__(16) float s_in[kMotionMaxIn * R];     // [k][r]: the layer's input, k major
   __shared__ float s_x0[R][128];                             // row major copy of the layer-0 input (for the skip)
@@ -265,7 +310,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
   __shared__ float s_tf[64];                                 // time features
   __shared__ float s_heads[R][kHeadsMax];
   const MotionLayout &L = a.L;
-  const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R;
+  const int j = threadIdx.x, nt = kWorkers, row0 = blockIdx.x * R;
   const int W = L.width;
   const float *P = a.params;
   if (j == 0) {
@@ -274,9 +319,8 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
     s_seq.ptr[L.depth] = P + L.heads_W, s_seq.rows[L.depth] = W, s_seq.stride[L.depth] = L.NH;
     seq_finish(s_seq);
   }
-  __syncthreads();
-  SlabPipe pipe;
-  pipe_start(pipe, s_dyn, s_bar, &s_seq);   // the first slabs travel while the encodings are evaluated
+  SlabRing ring;
+  if (ring_start(ring, s_dyn, s_full, s_empty, &s_seq, &s_dead)) return;  // the producer warp: the slabs start to travel
 
   // encodings
   if (j == 0) freq_encode(a.t[0], (L.Et - 1) / 2, a.scale_t, 1, 0, s_te);
@@ -285,7 +329,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
     const int m = row0 + r;
     freq_encode(m < a.M ? a.points[3 * m + c] : 0.0f, (L.Ep / 3 - 1) / 2, a.scale_p, 3, c, s_x0[r]);
   }
-  __syncthreads();
+  workers_sync();
   // time network (the same for every row): hidden = relu(W0^T te + b0), features = W2^T hidden + b2
   if (L.Ht > 0) {
     for (int u = j; u < L.Ht; u += nt) {
@@ -293,7 +337,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
       for (int k = 0; k < L.Et; ++k) acc += s_te[k] * P[L.time0_W + (long long) k * L.Ht + u];
       s_th[u] = fmaxf(acc, 0.0f);
     }
-    __syncthreads();
+    workers_sync();
     // every warp sums its share of the hidden units for all outputs, then the shares are added
     {
       const int lane = j & 31, warp = j >> 5, nw = nt >> 5;
@@ -303,7 +347,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
         for (int k = warp; k < L.Ht; k += nw) acc += s_th[k] * P[L.time2_W + (long long) k * L.To + u];
         part[warp * 64 + u] = acc;
       }
-      __syncthreads();
+      workers_sync();
       for (int u = j; u < L.To; u += nt) {
         float acc = P[L.time2_b + u];
         for (int w = 0; w < nw; ++w) acc += part[w * 64 + u];
@@ -315,21 +359,21 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
   } else {
     for (int u = j; u < L.To; u += nt) s_tf[u] = s_te[u];
   }
-  __syncthreads();
+  workers_sync();
   for (int e = j; e < R * L.To; e += nt) {
     const int r = e / L.To, u = e - r * L.To;
     s_x0[r][L.Ep + u] = s_tf[u];
   }
-  __syncthreads();
+  workers_sync();
   for (int e = j; e < R * L.in0; e += nt) {
     const int r = e / L.in0, k = e - r * L.in0;
     s_in[k * R + r] = s_x0[r][k];
     if (row0 + r < a.M) a.x0[(size_t) (row0 + r) * L.in0 + k] = s_x0[r][k];
   }
-  pipe.await(0);  // block barrier: s_in is complete and slab 0 has landed
+  workers_sync();
 
   for (int i = 0; i < L.depth; ++i) {
-    rowblock_gemm(pipe, i, s_in, s_part);
+    rowblock_gemm(ring, i, s_in, s_part);
     // bias, ReLU; the activations become the next layer's input, preceded by the encodings after the skip layer
     const int lead = (i == L.skip) ? L.in0 : 0;
     rowblock_reduce(s_part, W, [&](int, int n, int half, float4 s) {
@@ -349,7 +393,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
         const int r = e / lead, k = e - r * lead;
         s_in[k * R + r] = s_x0[r][k];
       }
-    __syncthreads();
+    workers_sync();
   }
 
   // heads on the last activations (s_in[0 .. W*R), k major): 4 k-groups x (row, output) pairs, matrix from the ring
@@ -361,21 +405,20 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
     float acc = 0.0f;
     for (int k0 = 0; k0 < W; k0 += sr) {
       const int rows = min(sr, W - k0);
-      const float *w = pipe.slab(L.depth, k0);
+      const float *w = ring.acquire(L.depth, k0);
       if (mine)
         for (int kk = kg; kk < rows; kk += 4) acc += s_in[(k0 + kk) * R + r] * w[kk * NH + o];
-      pipe.advance();
+      ring.release();
     }
     s_part[kg * 128 + e] = acc;
-    __syncthreads();
+    workers_sync();
     if (j < E) {
       const float v = P[L.heads_b + o] + ((s_part[e] + s_part[128 + e]) + (s_part[256 + e] + s_part[384 + e]));
       s_heads[r][o] = v;
       if (row0 + r < a.M) a.heads[(size_t) (row0 + r) * NH + o] = v;
     }
   }
-  pipe.finish();
-  __syncthreads();
+  workers_sync();
   if (j < R && row0 + j < a.M) {
     const int m = row0 + j;
     const float *o = s_heads[j];
@@ -440,14 +483,15 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
   constexpr int R = kMotionRows;
   extern __shared__ __align__(128) float s_dyn[];            // slabs [kSlabBufs][kSlabFloats] | partial sums
   float *s_part = s_dyn + kSlabBufs * kSlabFloats;
-  __shared__ __align__(8) uint64_t s_bar[kSlabBufs];
+  __shared__ __align__(8) uint64_t s_full[kSlabBufs], s_empty[kSlabBufs];
+  __shared__ int s_dead;
   __shared__ MatSeq s_seq;
   __shared__ __align__(16) float s_dy[kMotionMaxIn * R];     // [k][r]: gradient of the current layer's pre-activation
   __shared__ float s_gh[R][kHeadsMax];
   __shared__ float s_gtf[64];
   const MotionDev &a = b.f;
   const MotionLayout &L = a.L;
-  const int j = threadIdx.x, nt = blockDim.x, row0 = blockIdx.x * R, W = L.width, M = a.M;
+  const int j = threadIdx.x, nt = kWorkers, row0 = blockIdx.x * R, W = L.width, M = a.M;
   const float *P = a.params;
   if (j == 0) {
     s_seq.n = L.depth;
@@ -458,9 +502,8 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
     seq_finish(s_seq);
   }
   for (int u = j; u < 64; u += nt) s_gtf[u] = 0.0f;
-  __syncthreads();
-  SlabPipe pipe;
-  pipe_start(pipe, s_dyn, s_bar, &s_seq);
+  SlabRing ring;
+  if (ring_start(ring, s_dyn, s_full, s_empty, &s_seq, &s_dead)) return;  // the producer warp
 
   // the heads' matrix [W][NH] into shared memory (the partial-sum area is idle until the first layer)
   float *s_wh = s_part;
@@ -498,7 +541,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
       for (int o = 0; o < L.NH; ++o) b.dheads[(size_t) m * L.NH + o] = g[o];
     }
   }
-  __syncthreads();
+  workers_sync();
 
   // Through a ReLU: item (column n of layer i, rows 4 half ..) of the gradient dh of layer i's activations becomes the
   // gradient of its pre-activations, kept in global memory for the weight gradients and in s_dy for the next product.
@@ -538,7 +581,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
       through_relu(L.depth - 1, n, half, dh, hv);
     }
   }
-  pipe.await(0);  // block barrier: s_dy complete, s_wh no longer needed, slab 0 landed
+  workers_sync();  // s_dy complete, s_wh no longer needed
 
   for (int i = L.depth - 1, s = 0; i >= 0; --i, ++s) {
     // dX[r][k] = sum_j dY[r][j] W[k][j], as a row-block GEMM on the transposed copy.  Its columns: the encodings
@@ -548,27 +591,27 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
     float hv[2][4];
 #pragma unroll
     for (int slot = 0; slot < 2; ++slot) {  // the previous layer's activations for this thread's items, fetched early
-      const int e = j + slot * kMotionThreads;
+      const int e = j + slot * kWorkers;
       const int half = e >= ip ? 1 : 0, n = e - half * ip - lead;
       if (i > 0 && e < 2 * ip && n >= 0 && n < W) fetch_h(i - 1, n, half, hv[slot]);
       else hv[slot][0] = hv[slot][1] = hv[slot][2] = hv[slot][3] = 0.0f;
     }
-    rowblock_gemm(pipe, s, s_dy, s_part);
+    rowblock_gemm(ring, s, s_dy, s_part);
     rowblock_reduce(s_part, ip, [&](int slot, int k, int half, float4 dx) {
       if (lead && k >= L.Ep && k < L.in0) atomicAdd(&s_gtf[k - L.Ep], (dx.x + dx.y) + (dx.z + dx.w));
       const int n = k - lead;
       if (i > 0 && n >= 0 && n < W) through_relu(i - 1, n, half, dx, hv[slot]);
     });
-    __syncthreads();
+    workers_sync();
   }
-  pipe.finish();
   for (int u = j; u < L.To; u += nt)
     if (s_gtf[u] != 0.0f) atomicAdd(b.g_tf + u, s_gtf[u]);
 }
 
-// Backward pass 2: weight and bias gradients, one block per 16 x 64 tile of one matrix (dW = X^T dY over all M rows);
-// the last block of the grid runs the time network's backward.
-constexpr int kTileK = 16, kTileJ = 64, kTileR = 32;
+// Backward pass 2: weight and bias gradients, one block per 32 x 128 tile of one matrix (dW = X^T dY over all M rows,
+// 4 x 4 outputs per thread, the next 32 rows of X and dY fetched into registers while the current ones are
+// multiplied); the last block of the grid runs the time network's backward.
+constexpr int kTileK = 32, kTileJ = 128, kTileR = 32;
 
 __device__ __forceinline__ void store_grad(float *dst, float v, int accumulate) {
   if (accumulate) *dst += v;
@@ -577,8 +620,8 @@ __device__ __forceinline__ void store_grad(float *dst, float v, int accumulate) 
 
 __global__ void __launch_bounds__(256) motion_backward_weights_kernel(MotionBwdDev b, int tiles_per_layer_k,
     int tiles_j, int n_layer_blocks, int n_head_blocks) {
-  __shared__ float s_x[kTileR][kTileK + 1];
-  __shared__ float s_dy[kTileR][kTileJ];
+  __shared__ __align__(16) float s_x[kTileR][kTileK];
+  __shared__ __align__(16) float s_dy[kTileR][kTileJ];
   const MotionDev &a = b.f;
   const MotionLayout &L = a.L;
   const int tid = threadIdx.x, W = L.width, M = a.M;
@@ -600,42 +643,62 @@ __global__ void __launch_bounds__(256) motion_backward_weights_kernel(MotionBwdD
       in = W, out = L.NH, dY = b.dheads, offW = L.heads_W, offb = L.heads_b;
     }
     const int k0 = kt * kTileK, j0 = jt * kTileJ;
-    if (k0 >= in) return;
-    const int tj = tid & 63, tk = tid >> 6;  // 64 columns x 4 groups of 4 rows of the tile
-    float acc[4] = {0, 0, 0, 0}, accb = 0.0f;
+    if (k0 >= in || j0 >= out) return;
+    // element (m, k) of the layer's input, assembled from the saved pieces
+    auto x_at = [&](int m, int k) -> float {
+      if (m >= M || k >= in) return 0.0f;
+      if (i == 0) return a.x0[(size_t) m * L.in0 + k];
+      if (i == L.skip + 1)
+        return k < L.in0 ? a.x0[(size_t) m * L.in0 + k] : a.h[((size_t) (i - 1) * M + m) * W + (k - L.in0)];
+      return a.h[((size_t) (i - 1) * M + m) * W + k];
+    };
+    float px[4], pdy[16];  // this thread's share of the next 32 rows
+    auto fetch = [&](int r0) {
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int e = tid + n * 256, r = e >> 5, kk = e & 31;
+        px[n] = x_at(r0 + r, k0 + kk);
+      }
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        const int e = tid + n * 256, r = e >> 7, jj = e & 127, m = r0 + r, jcol = j0 + jj;
+        pdy[n] = (m < M && jcol < out) ? dY[(size_t) m * out + jcol] : 0.0f;
+      }
+    };
+    const int tk = tid >> 5, tj = tid & 31;  // 8 groups of 4 rows of the tile x 32 groups of 4 columns
+    float acc[4][4], accb[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
+    fetch(0);
     for (int r0 = 0; r0 < M; r0 += kTileR) {
-      // X tile [32 rows][16 k]: the layer's input, assembled from the saved pieces
-      for (int e = tid; e < kTileR * kTileK; e += 256) {
-        const int r = e / kTileK, kk = e - r * kTileK, m = r0 + r, k = k0 + kk;
-        float v = 0.0f;
-        if (m < M && k < in) {
-          if (i == 0) v = a.x0[(size_t) m * L.in0 + k];
-          else if (i == L.skip + 1) v = k < L.in0 ? a.x0[(size_t) m * L.in0 + k] : a.h[((size_t) (i - 1) * M + m) * W + (k - L.in0)];
-          else v = a.h[((size_t) (i - 1) * M + m) * W + k];
-        }
-        s_x[r][kk] = v;
-      }
-      for (int e = tid; e < kTileR * kTileJ; e += 256) {
-        const int r = e / kTileJ, jj = e - r * kTileJ, m = r0 + r, jcol = j0 + jj;
-        s_dy[r][jj] = (m < M && jcol < out) ? dY[(size_t) m * out + jcol] : 0.0f;
-      }
+      __syncthreads();  // the previous rows have been consumed
+#pragma unroll
+      for (int n = 0; n < 4; ++n) (&s_x[0][0])[tid + n * 256] = px[n];
+#pragma unroll
+      for (int n = 0; n < 16; ++n) (&s_dy[0][0])[tid + n * 256] = pdy[n];
       __syncthreads();
+      if (r0 + kTileR < M) fetch(r0 + kTileR);
 #pragma unroll 8
       for (int r = 0; r < kTileR; ++r) {
-        const float d = s_dy[r][tj];
-        acc[0] += s_x[r][4 * tk] * d, acc[1] += s_x[r][4 * tk + 1] * d;
-        acc[2] += s_x[r][4 * tk + 2] * d, acc[3] += s_x[r][4 * tk + 3] * d;
-        accb += d;
+        const float4 x = *reinterpret_cast<const float4 *>(&s_x[r][4 * tk]);
+        const float4 d = *reinterpret_cast<const float4 *>(&s_dy[r][4 * tj]);
+        acc[0][0] += x.x * d.x, acc[0][1] += x.x * d.y, acc[0][2] += x.x * d.z, acc[0][3] += x.x * d.w;
+        acc[1][0] += x.y * d.x, acc[1][1] += x.y * d.y, acc[1][2] += x.y * d.z, acc[1][3] += x.y * d.w;
+        acc[2][0] += x.z * d.x, acc[2][1] += x.z * d.y, acc[2][2] += x.z * d.z, acc[2][3] += x.z * d.w;
+        acc[3][0] += x.w * d.x, acc[3][1] += x.w * d.y, acc[3][2] += x.w * d.z, acc[3][3] += x.w * d.w;
+        if (tk == 0) accb[0] += d.x, accb[1] += d.y, accb[2] += d.z, accb[3] += d.w;
       }
-      __syncthreads();
     }
-    const int jcol = j0 + tj;
-    if (jcol < out) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int jcol = j0 + 4 * tj + v;
+      if (jcol >= out) break;
+#pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int k = k0 + 4 * tk + u;
-        if (k < in) store_grad(b.g_params + offW + (long long) k * out + jcol, acc[u], b.accumulate);
+        if (k < in) store_grad(b.g_params + offW + (long long) k * out + jcol, acc[u][v], b.accumulate);
       }
-      if (kt == 0 && tk == 0) store_grad(b.g_params + offb + jcol, accb, b.accumulate);
+      if (kt == 0 && tk == 0) store_grad(b.g_params + offb + jcol, accb[v], b.accumulate);
     }
     return;
   }

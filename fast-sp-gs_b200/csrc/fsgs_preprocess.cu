@@ -691,6 +691,7 @@ struct PreBwdDev {
   float *g_opac, *g_shs, *g_sh_rest;
   const float4 *normal_opacity;  // with it, g_opac is the gradient of the opacity LOGIT: g * o * (1 - o)
   float *visible;                // optional [P] 0/1 mask of the Gaussians with radii > 0
+  const long long *overflow;     // optional: != 0 -> the lists were truncated, visible = -inf on every row
   int accumulate;                // add to g_opac / g_shs / g_sh_rest / visible instead of writing them
 };
 
@@ -896,12 +897,16 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
       const float o = a.normal_opacity[i].w;
       g_o = g_o * (1.0f - o) * o;
     }
+    const bool poisoned = a.overflow && *a.overflow != 0;
     if (a.accumulate) {
       if (live) a.g_opac[i] += g_o;
-      if (live && a.visible) a.visible[i] = 1.0f;
+      if (a.visible) {
+        if (poisoned) a.visible[i] = -INFINITY;
+        else if (live && a.visible[i] >= 0.0f) a.visible[i] = 1.0f;  // a poisoned row stays poisoned
+      }
     } else {
       a.g_opac[i] = g_o;
-      if (a.visible) a.visible[i] = live ? 1.0f : 0.0f;
+      if (a.visible) a.visible[i] = poisoned ? -INFINITY : (live ? 1.0f : 0.0f);
     }
     a.g_scales[i] = gs;
     a.g_rots[i] = gq;
@@ -1122,6 +1127,7 @@ extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_
   d.g_means = a->grad_means, d.g_scales = (float2 *) a->grad_scales, d.g_rots = (float4 *) a->grad_rots;
   d.g_opac = a->grad_opac, d.g_shs = a->grad_shs, d.g_sh_rest = d.sh_rest ? a->grad_sh_rest : nullptr;
   d.normal_opacity = (const float4 *) a->normal_opacity, d.visible = a->visible, d.accumulate = a->accumulate;
+  d.overflow = a->counters ? (const long long *) a->counters + FSGS_CNT_OVERFLOW : nullptr;
   if (a->accumulate && a->sh_degree >= 0) {
     // only the layouts whose SH rows are staged through shared memory accumulate: degree 1..3, rows of at most 48
     // floats, the DC coefficient either inside those rows or alone in shs

@@ -223,6 +223,7 @@ extern "C" int fsgs_view_backward(const fsgs_view_args *a, fsgs_stream_t stream)
   p.grad_means = w.g_means, p.grad_scales = w.g_scales, p.grad_rots = w.g_rots;
   p.grad_opac = a->g_opacity_raw, p.grad_shs = a->g_sh_dc, p.grad_sh_rest = a->g_sh_rest;
   p.normal_opacity = w.normal_opacity, p.visible = a->visible, p.accumulate = a->accumulate;
+  p.counters = a->counters;  // an overflowed view poisons the mask: the optimiser then drops the step
   {
     StageTimer t(4, (cudaStream_t) stream);
     rc = fsgs_preprocess_backward(&p, stream);

@@ -74,7 +74,8 @@ class PreprocessBwdArgs(Structure):
                 ("grad_means2D", _vp), ("grad_trans_mat", _vp), ("grad_inverse_m", _vp), ("grad_colors", _vp),
                 ("grad_normal_opacity", _vp),
                 ("grad_means", _vp), ("grad_scales", _vp), ("grad_rots", _vp), ("grad_opac", _vp), ("grad_shs", _vp),
-                ("grad_sh_rest", _vp), ("normal_opacity", _vp), ("visible", _vp), ("accumulate", c_int32)]
+                ("grad_sh_rest", _vp), ("normal_opacity", _vp), ("visible", _vp), ("accumulate", c_int32),
+                ("counters", _vp)]
 
 
 class ViewArgs(Structure):

@@ -78,7 +78,8 @@ class ViewEngine:
         if self.overflowed:
             n, self.overflowed = self.overflowed, 0
             raise RuntimeError(f"fsgs: tile lists overflowed their buffer on {n} earlier view(s); those views are "
-                               "invalid.  The capacity has been raised; run them again.")
+                               "invalid (a training step that used them was dropped by the optimiser).  The "
+                               "capacity has been raised; run them again.")
 
     # ---- one view -----------------------------------------------------------------------------------------------
     def _fill(self, scene, cam, motion):

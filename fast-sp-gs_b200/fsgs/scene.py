@@ -209,9 +209,17 @@ class DynamicScene:
             late.wait()
         self.optimizer.step_visible(only=[self.xyz, self.opacity, self.scaling, self.rotation])
         if self.dense_optimizer is not None:
+            # a view whose tile lists overflowed (on any rank) left -inf in the mask: the masked Adam above passed no
+            # row, and the fused Adam of the dense parameters skips on the same signal
+            self.dense_optimizer.found_inf = torch.isinf(b.extra[0]).to(torch.float32)
             self.dense_optimizer.step()
         self._drop_grads()
         return eng
+
+    def last_step_dropped(self):
+        """True when the last ``train_views`` step was dropped on the device because a view's tile lists overflowed
+        their buffer on some rank (one scalar read: synchronises).  The same on every rank."""
+        return self.bucket is not None and bool(torch.isinf(self.bucket.extra[0]))
 
     def train_step(self, cam, size, motion, g_images, g_opacity, group=None, distributed=False, g_aux=None):
         """One iteration on one view with the given upstream gradients on images [3,H,W] and opacity [H,W] (and, with

@@ -399,10 +399,15 @@ typedef struct fsgs_preprocess_bwd_args {
    *    visible is raised to 1 where visible, never lowered -- the gradients of several views summed in place, in
    *    call order.  grad_means / grad_scales / grad_rots are always written (they feed the LBS adjoint, which has its
    *    own accumulate flag).  Supported for sh_degree < 0 and for degrees 1..3 with SH rows of at most 48 floats;
-   *    otherwise FSGS_ERR_UNSUPPORTED. */
+   *    otherwise FSGS_ERR_UNSUPPORTED;
+   *  counters (the binning's, of the view these gradients come from): when counters[FSGS_CNT_OVERFLOW] != 0 the
+   *    tile lists were truncated and the gradients are wrong; visible is then written as -infinity on EVERY row, and
+   *    a row that is -infinity is never raised again.  -infinity survives the summation over views and over ranks,
+   *    is "not visible" to the masked Adam, and so drops the whole step, on every rank, on the device. */
   const float *normal_opacity;
   float *visible;
   int32_t accumulate;
+  const int64_t *counters;
 } fsgs_preprocess_bwd_args;
 
 int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *args /* host */, fsgs_stream_t stream);

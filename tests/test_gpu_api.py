@@ -198,6 +198,26 @@ def test_list_overflow_is_reported():
         eng.forward(scene, cam, motion_at(sp, sp["centres"], "cuda"))
         eng.check()
         assert bool(torch.isfinite(eng.images).all())
+        # a training step on an overflowed view is dropped on the device: the view's backward writes -inf into the
+        # mask, which no row of the masked Adam passes; the report comes with the next call
+        before = {k: getattr(scene, k).detach().clone() for k in ("xyz", "opacity", "sh_dc", "scaling")}
+        moments = scene.optimizer.state[scene.xyz]["exp_avg"].clone() if scene.xyz in scene.optimizer.state else None
+        view = dict(cam=cam, motion=motion_at(sp, sp["centres"], "cuda"), g_images=torch.randn(3, H, W, device="cuda"),
+                    g_opacity=torch.randn(H, W, device="cuda"))
+        eng.high_water = 0
+        eng._reserve(16)
+        scene.train_views([view], (W, H))
+        assert scene.last_step_dropped()
+        for k, v in before.items():
+            assert torch.equal(getattr(scene, k).detach(), v), k
+        if moments is not None:
+            assert torch.equal(scene.optimizer.state[scene.xyz]["exp_avg"], moments)
+        with pytest.raises(RuntimeError, match="overflowed"):
+            scene.check()
+        scene.train_views([view], (W, H))   # capacity raised: this step counts
+        scene.check()
+        assert not scene.last_step_dropped()
+        assert not torch.equal(scene.xyz.detach(), before["xyz"])
     finally:
         if saved is not None:
             renderer._capacity[key] = saved
