@@ -133,7 +133,8 @@ constexpr int kSplitMax = 8;
 constexpr int kPartFloats = kSplitMax * kMotionRows * (kMotionMaxWidth + 4);
 constexpr int kMotionDynFloats = kSlabBufs * kSlabFloats + kPartFloats;
 static_assert(kMotionRows == 8, "the register blocks and the [k][8] activation layout assume 8 rows per block");
-static_assert(2 * kMotionMaxIn <= 2 * kWorkers, "the reduction visits at most two items per thread");
+constexpr int kItemSlots = (2 * kMotionMaxIn + kWorkers - 1) / kWorkers;  // reduction items per thread, at most
+constexpr int kHeadGroups = kWorkers / 128;                              // k-groups of the heads product
 
 // barrier over the worker warps only (the producer warp never joins)
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
@@ -178,20 +179,21 @@ struct SlabRing {
   volatile int *dead;    // set by the producer when it gives up
   int next;              // worker: index of the next slab to consume
 
-  // Worker: the slab `next` of the sequence -- rows k0.. of matrix m.  Returns where to read it: the ring buffer, or
-  // global memory when the slab did not arrive.  Lane 0 polls; the others test once after it (already complete).
-  __device__ __forceinline__ const float *acquire(int m, int k0) {
+  // Worker: waits for the slab `next` of the sequence; false when it did not arrive (the caller then reads those rows
+  // from global memory).  Every lane tests once -- the slab was requested three slabs ago and is normally there --
+  // and only then does lane 0 poll, with the producer's give-up flag in view.
+  __device__ __forceinline__ bool acquire() {
     uint64_t *bar = &full[next % kSlabBufs];
     const uint32_t parity = (uint32_t) ((next / kSlabBufs) & 1);
-    bool ok = true;
-    if ((threadIdx.x & 31) == 0) {
-      ok = false;
+    bool ok = mbar_test(bar, parity);
+    if (__all_sync(0xffffffffu, ok)) return true;
+    if ((threadIdx.x & 31) == 0)
       for (int i = 0; i < (1 << 20) && !ok && !*dead; ++i) ok = mbar_test(bar, parity);
-    }
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (ok) ok = mbar_test(bar, parity);
-    return ok ? buf + (next % kSlabBufs) * kSlabFloats : seq->ptr[m] + (size_t) k0 * seq->stride[m];
+    return __all_sync(0xffffffffu, ok);
   }
+  __device__ __forceinline__ int slot() const { return next % kSlabBufs; }
   // Worker: this warp is done with the slab `next`
   __device__ __forceinline__ void release() {
     __syncwarp();
@@ -242,31 +244,42 @@ __device__ __forceinline__ bool ring_start(SlabRing &ring, float *buf, uint64_t 
   return false;
 }
 
+// acc += act^T-block x rows kg, kg + G, ... (n_it of them) of the slab at w (this thread's four columns); act_k0 = the
+// activations of the slab's first row.  Inlined once with w in shared memory and once with w in global memory, so
+// that each copy uses the loads of its own address space.
+__device__ __forceinline__ void slab_fma(const float *w, const float *act_k0, int N, int kg, int G, int n_it,
+    float (&acc)[8][4]) {
+#pragma unroll 4
+  for (int it = 0; it < n_it; ++it) {
+    const int kk = kg + it * G;
+    const float4 wv = *reinterpret_cast<const float4 *>(w + kk * N);
+    const float4 a0 = *reinterpret_cast<const float4 *>(act_k0 + kk * 8);
+    const float4 a1 = *reinterpret_cast<const float4 *>(act_k0 + kk * 8 + 4);
+    const float ar[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      acc[r][0] += ar[r] * wv.x, acc[r][1] += ar[r] * wv.y, acc[r][2] += ar[r] * wv.z, acc[r][3] += ar[r] * wv.w;
+  }
+}
+
 // Partial sums of act^T-block x matrix m (all its rows) into s_part[g][r][N + 4].  Every worker thread calls it; on
-// return the partial sums are complete and s_act is free.
-__device__ __forceinline__ void rowblock_gemm(SlabRing &ring, int m, const float *s_act, float *s_part) {
+// return the partial sums are complete and s_act is free.  s_slabs = the ring's buffers (the kernel's own shared
+// array, so that the compiler sees the address space).
+__device__ __forceinline__ void rowblock_gemm(SlabRing &ring, const float *s_slabs, int m, const float *s_act,
+    float *s_part) {
   const int K = ring.seq->rows[m], N = ring.seq->stride[m], sr = ring.seq->srows[m], t = threadIdx.x;
   const int C = N >> 2, G = gemm_split(N);
   const int kg = t / C, ct = t - kg * C;
   const bool mine = kg < G;
+  const int it_full = mine ? (sr - kg + G - 1) / G : 0;  // this thread's rows of a full slab
   float acc[8][4];
 #pragma unroll
   for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
   for (int k0 = 0; k0 < K; k0 += sr) {
-    const int rows = min(sr, K - k0);
-    const float *w = ring.acquire(m, k0) + 4 * ct;
-    if (mine) {
-#pragma unroll 4
-      for (int kk = kg; kk < rows; kk += G) {
-        const float4 wv = *reinterpret_cast<const float4 *>(w + kk * N);
-        const float4 a0 = *reinterpret_cast<const float4 *>(s_act + (k0 + kk) * 8);
-        const float4 a1 = *reinterpret_cast<const float4 *>(s_act + (k0 + kk) * 8 + 4);
-        const float ar[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          acc[r][0] += ar[r] * wv.x, acc[r][1] += ar[r] * wv.y, acc[r][2] += ar[r] * wv.z, acc[r][3] += ar[r] * wv.w;
-      }
-    }
+    const int rows = K - k0;
+    const int n_it = rows >= sr ? it_full : (mine ? (rows - kg + G - 1) / G : 0);
+    if (ring.acquire()) slab_fma(s_slabs + ring.slot() * kSlabFloats + 4 * ct, s_act + k0 * 8, N, kg, G, n_it, acc);
+    else slab_fma(ring.seq->ptr[m] + (size_t) k0 * N + 4 * ct, s_act + k0 * 8, N, kg, G, n_it, acc);
     ring.release();
   }
   if (mine) {
@@ -279,12 +292,12 @@ __device__ __forceinline__ void rowblock_gemm(SlabRing &ring, int m, const float
 }
 
 // Adds the G partial blocks: item (n, half) -- column n, rows 4 half .. 4 half + 3 -- goes to epi(slot, n, half, sums)
-// with slot = 0 or 1 counting the items of this thread (so that the caller can pair them with values it fetched ahead).
+// with slot = 0, 1, .. counting the items of this thread (so that the caller can pair them with values it fetched ahead).
 template <class F>
 __device__ __forceinline__ void rowblock_reduce(const float *s_part, int N, F epi) {
   const int G = gemm_split(N), Np = N + 4;
 #pragma unroll
-  for (int slot = 0; slot < 2; ++slot) {
+  for (int slot = 0; slot < kItemSlots; ++slot) {
     const int e = threadIdx.x + slot * kWorkers;
     if (e >= 2 * N) break;
     const int half = e >= N ? 1 : 0, n = e - half * N;
@@ -373,7 +386,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
   workers_sync();
 
   for (int i = 0; i < L.depth; ++i) {
-    rowblock_gemm(ring, i, s_in, s_part);
+    rowblock_gemm(ring, s_dyn, i, s_in, s_part);
     // bias, ReLU; the activations become the next layer's input, preceded by the encodings after the skip layer
     const int lead = (i == L.skip) ? L.in0 : 0;
     rowblock_reduce(s_part, W, [&](int, int n, int half, float4 s) {
@@ -396,7 +409,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
     workers_sync();
   }
 
-  // heads on the last activations (s_in[0 .. W*R), k major): 4 k-groups x (row, output) pairs, matrix from the ring
+  // heads on the last activations (s_in[0 .. W*R), k major): kHeadGroups k-groups x (row, output) pairs, matrix from the ring
   {
     const int NH = L.NH, E = R * NH, kg = j >> 7, e = j & 127;
     const int r = e / NH, o = e - r * NH;
@@ -405,15 +418,17 @@ __global__ void __launch_bounds__(kMotionThreads) motion_forward_kernel(MotionDe
     float acc = 0.0f;
     for (int k0 = 0; k0 < W; k0 += sr) {
       const int rows = min(sr, W - k0);
-      const float *w = ring.acquire(L.depth, k0);
+      const float *w = ring.acquire() ? s_dyn + ring.slot() * kSlabFloats : P + L.heads_W + (size_t) k0 * NH;
       if (mine)
-        for (int kk = kg; kk < rows; kk += 4) acc += s_in[(k0 + kk) * R + r] * w[kk * NH + o];
+        for (int kk = kg; kk < rows; kk += kHeadGroups) acc += s_in[(k0 + kk) * R + r] * w[kk * NH + o];
       ring.release();
     }
     s_part[kg * 128 + e] = acc;
     workers_sync();
     if (j < E) {
-      const float v = P[L.heads_b + o] + ((s_part[e] + s_part[128 + e]) + (s_part[256 + e] + s_part[384 + e]));
+      float v = P[L.heads_b + o];
+#pragma unroll
+      for (int g = 0; g < kHeadGroups; ++g) v += s_part[g * 128 + e];
       s_heads[r][o] = v;
       if (row0 + r < a.M) a.heads[(size_t) (row0 + r) * NH + o] = v;
     }
@@ -567,8 +582,7 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
 
   // gradient of the last activations: dh[n][r] = sum_o g[r][o] Wh[n][o]
   {
-    const int e = j;  // 2 W <= 512 items
-    if (e < 2 * W) {
+    for (int e = j; e < 2 * W; e += nt) {
       const int half = e >= W ? 1 : 0, n = e - half * W;
       float hv[4];
       fetch_h(L.depth - 1, n, half, hv);
@@ -588,15 +602,15 @@ __global__ void __launch_bounds__(kMotionThreads) motion_backward_rows_kernel(Mo
     // first where the layer has them (only their time features carry a gradient on), then the previous activations.
     const int ip = b.in_pad[i];
     const int lead = (i == 0 || i == L.skip + 1) ? L.in0 : 0;
-    float hv[2][4];
+    float hv[kItemSlots][4];
 #pragma unroll
-    for (int slot = 0; slot < 2; ++slot) {  // the previous layer's activations for this thread's items, fetched early
+    for (int slot = 0; slot < kItemSlots; ++slot) {  // the previous layer's activations for this thread's items, fetched early
       const int e = j + slot * kWorkers;
       const int half = e >= ip ? 1 : 0, n = e - half * ip - lead;
       if (i > 0 && e < 2 * ip && n >= 0 && n < W) fetch_h(i - 1, n, half, hv[slot]);
       else hv[slot][0] = hv[slot][1] = hv[slot][2] = hv[slot][3] = 0.0f;
     }
-    rowblock_gemm(ring, s, s_dy, s_part);
+    rowblock_gemm(ring, s_dyn, s, s_dy, s_part);
     rowblock_reduce(s_part, ip, [&](int slot, int k, int half, float4 dx) {
       if (lead && k >= L.Ep && k < L.in0) atomicAdd(&s_gtf[k - L.Ep], (dx.x + dx.y) + (dx.z + dx.w));
       const int n = k - lead;
