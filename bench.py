@@ -58,6 +58,9 @@ def parse():
     ap.add_argument("--repeats", type=int, default=5, help="timed runs of --steps steps; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_300k_800")
+    ap.add_argument("--exchange", default="factors", choices=["factors", "rows"],
+                    help="multi-GPU: all-gather the six SH-gradient factors per Gaussian and view (default) or "
+                         "all-reduce the 48 SH gradient floats themselves")
     ap.add_argument("--views", type=int, default=1, help="views per rank per step (weak scaling)")
     ap.add_argument("--batch-views", type=int, default=0, help="views per step in total, sharded over the ranks")
     ap.add_argument("--no-baselines", action="store_true", help="skip the CPU / reference-CUDA / k-NN legs")
@@ -499,6 +502,8 @@ def run_ours(args):
         scaling, total_views = "weak", world * args.views
     wlk = build_workload(args.workload, view_ids)
     W, H, P, K, M = wlk["W"], wlk["H"], wlk["P"], wlk["K"], wlk["M"]
+    # view slots per rank in the exchange (the same number on every rank) and the form of the exchange
+    xch = dict(views_per_rank=max(1, -(-total_views // world)), exchange=args.exchange)
     knn_every_step = args.workload.startswith("stress")  # that configuration recomputes the k-NN every step
     lr = 1.6e-4  # every group at the position learning rate
     new_scene = lambda: DynamicScene(wlk["surf"], wlk["centres"], K=K, device=dev,
@@ -549,14 +554,14 @@ def run_ours(args):
         tick[0] += 1
         if knn_every_step:
             scene.refresh_knn()
-        scene.train_views([v[k] for v in dev_views], (W, H), distributed=distributed)
+        scene.train_views([v[k] for v in dev_views], (W, H), distributed=distributed, **xch)
 
     def fwd_only():
         eng = scene._engine((W, H))
         for v in dev_views:
             eng.forward(scene, v[0]["cam"], v[0]["motion"])
 
-    allreduce_ms = None
+    allreduce_ms, exchange_ms = None, {}
     if distributed:
         # communicator set-up: NCCL builds its channels lazily at the first collectives of each size class, which
         # would otherwise land in the first timed steps; these exchanges carry zeros and touch no training state.
@@ -570,6 +575,18 @@ def run_ours(args):
             dist.barrier()
             allreduce_ms.append(round(_event_ms(lambda: dist.all_reduce(z), 10, 0), 4))
             del z
+        # the factor exchange's all-gather (6 floats per Gaussian and view slot) and its small all-reduce (the mask)
+        zs = torch.zeros(xch["views_per_rank"] * 6 * P, device=dev)
+        zr = torch.zeros(world * zs.numel(), device=dev)
+        zm = torch.zeros(P, device=dev)
+        for _ in range(5):
+            dist.all_gather_into_tensor(zr, zs)
+            dist.all_reduce(zm)
+        torch.cuda.synchronize()
+        dist.barrier()
+        exchange_ms["all_gather_6P_per_slot"] = round(_event_ms(lambda: dist.all_gather_into_tensor(zr, zs), 10, 0), 4)
+        exchange_ms["all_reduce_P"] = round(_event_ms(lambda: dist.all_reduce(zm), 10, 0), 4)
+        del zs, zr, zm
     sampler = ClockSampler(local) if rank == 0 else None  # its child process starts while the warm-up runs
     for _ in range(max(args.warmup, 3)):
         step()
@@ -626,13 +643,13 @@ def run_ours(args):
         if knn_every_step:
             scene.refresh_knn()
         if not n_views:
-            scene.train_views([], (W, H), distributed=distributed)
+            scene.train_views([], (W, H), distributed=distributed, **xch)
             return
         feed.stage(hosts[tick[0] & 1])   # the next step's upload runs beside this step's kernels
         x = feed.take()
         views = [dict(cam=x[f"v{j}"]["cam"], motion=x[f"v{j}"]["motion"], g_images=x[f"v{j}"]["g_img"],
                       g_opacity=x[f"v{j}"]["g_op"]) for j in range(n_views)]
-        eng = scene.train_views(views, (W, H), distributed=distributed)
+        eng = scene.train_views(views, (W, H), distributed=distributed, **xch)
         feed.release()
         reader.push(eng.opacity.mean())
         val = reader.pop()               # device -> host read of the previous step's result, every step
@@ -659,7 +676,7 @@ def run_ours(args):
         def step_aux():
             k = tick[0] & 1
             tick[0] += 1
-            scene.train_views([v[k] for v in aux_views], (W, H), distributed=distributed)
+            scene.train_views([v[k] for v in aux_views], (W, H), distributed=distributed, **xch)
 
         for _ in range(3):
             step_aux()
@@ -698,7 +715,7 @@ def run_ours(args):
         def step_motion():
             k = tick[0] & 1
             tick[0] += 1
-            scene_m.train_views([v[k] for v in t_views], (W, H), distributed=distributed)
+            scene_m.train_views([v[k] for v in t_views], (W, H), distributed=distributed, **xch)
 
         for _ in range(3):
             step_motion()
@@ -732,15 +749,25 @@ def run_ours(args):
             two.append(dict(cam={k: t.to(dev) for k, t in v["cam"].items()}, motion=motion_at(v["sp"], wlk["centres"], dev),
                             g_images=v["g_img"].to(dev), g_opacity=v["g_op"].to(dev)))
         a, b = new_scene(), new_scene()
-        for _ in range(2):
-            a.train_views([two[rank]] if rank < 2 else [], (W, H), distributed=True)
+        # The summed gradients of the first step (same parameters on both sides: only the summation differs), then
+        # the parameters after a second step.  Adam's first steps are lr * g / |g|: a gradient within summation noise
+        # of zero moves its parameter by +-lr either way, the second step's gradients then see different parameters,
+        # and the parameter comparison sits a decade or two above the gradient comparison.
+        rel, rel_g = torch.zeros(1, device=dev), torch.zeros(1, device=dev)
+        for it in range(2):
+            a.train_views([two[rank]] if rank < 2 else [], (W, H), distributed=True, views_per_rank=1, exchange=args.exchange)
             b.train_views(two, (W, H), distributed=False)
-        rel = torch.zeros(1, device=dev)
+            if it == 0:
+                for x, y in zip(a.params, b.params):
+                    gx, gy = a.bucket.view_of(x), b.bucket.view_of(y)
+                    rel_g = torch.maximum(rel_g, ((gx - gy).norm() / gy.norm().clamp_min(1e-30)).reshape(1))
         for x, y in zip(a.params, b.params):
-            rel = torch.maximum(rel, ((x - y).norm() / y.norm().clamp_min(1e-30)).reshape(1))
+            rel = torch.maximum(rel, ((x.detach() - y.detach()).norm() / y.detach().norm().clamp_min(1e-30)).reshape(1))
         dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+        dist.all_reduce(rel_g, op=dist.ReduceOp.MAX)
         checks = {"replica_max_abs_diff_after_run": float(worst),
-                  "two_views_on_two_ranks_vs_serial_rel_l2": float(rel)}
+                  "two_views_on_two_ranks_vs_serial_rel_l2": float(rel),
+                  "two_views_on_two_ranks_vs_serial_first_step_gradients_rel_l2": float(rel_g)}
         del a, b
 
     if rank == 0:
@@ -795,6 +822,7 @@ def run_ours(args):
             "config": {"workload": args.workload, "surfels": P, "image": [W, H], "superpoints": M, "knn": K,
                        "sh_degree": 3, "adam_lr": lr, "views_per_step": total_views,
                        "views_per_step_on_rank0": n_views, "knn_recomputed_every_step": knn_every_step,
+                       "exchange": args.exchange if world > 1 else None,
                        "visible_on_view0": V, "pairs_on_view0": R, "pairs_first_last": [pairs_first, pairs_last],
                        "upstream_gradient": "fixed random image gradient per view, sign flipped every step",
                        "l2": "per-step working set (parameters, Adam state, gradients, records, images: > 400 MB) "
@@ -821,7 +849,7 @@ def run_ours(args):
                                  "peak_kind": peak_kind}},
             "stages": stages,
             "host_ms_per_step": {k: round(med(v), 4) for k, v in host_ms.items()},
-            "allreduce_ms_49P_10P_floats": allreduce_ms,
+            "allreduce_ms_49P_10P_floats": allreduce_ms, "factor_exchange_ms": exchange_ms or None,
             "multi_gpu_checks": checks,
             "clocks": clocks,
         }

@@ -692,6 +692,7 @@ struct PreBwdDev {
   const float4 *normal_opacity;  // with it, g_opac is the gradient of the opacity LOGIT: g * o * (1 - o)
   float *visible;                // optional [P] 0/1 mask of the Gaussians with radii > 0
   const long long *overflow;     // optional: != 0 -> the lists were truncated, visible = -inf on every row
+  float *sh_source;              // optional [P,6]: clamped colour gradient and view direction
   int accumulate;                // add to g_opac / g_shs / g_sh_rest / visible instead of writing them
 };
 
@@ -776,6 +777,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
 
   float *w_row = s_mem + kBwdWide + t * wide;   // this thread's SH coefficients, then their gradient
   float3 gm = make_float3(0, 0, 0), gdc = make_float3(0, 0, 0);
+  float3 src_g = make_float3(0, 0, 0), src_d = make_float3(0, 0, 0);  // the SH gradient's two factors
   float2 gs = make_float2(0, 0);
   float4 gq = make_float4(0, 0, 0, 0);
   if (live) {
@@ -846,6 +848,7 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
       sh_basis(a.sh_degree, x, y, z, b);
       const int nb = (a.sh_degree + 1) * (a.sh_degree + 1);
       gdc = make_float3(grgb.x * b[0], grgb.y * b[0], grgb.z * b[0]);
+      src_g = grgb, src_d = make_float3(x, y, z);
       float dx = 0, dy = 0, dz = 0;
       // coefficient k >= 1 lives at row offset 3*(k - first)
       const int first = a.sh_rest ? 1 : 0;
@@ -892,6 +895,10 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
     }
   }
   if (i < a.P) {
+    if (a.sh_source) {
+      float2 *o = reinterpret_cast<float2 *>(a.sh_source + (size_t) i * 6);
+      o[0] = make_float2(src_g.x, src_g.y), o[1] = make_float2(src_g.z, src_d.x), o[2] = make_float2(src_d.y, src_d.z);
+    }
     float g_o = gno.w;
     if (a.normal_opacity) {
       const float o = a.normal_opacity[i].w;
@@ -946,6 +953,54 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
     }
   }
   if (out_bulk && t == 0) bulk_store_wait();
+}
+
+// Summed SH gradient of several views from their factors: one Gaussian per thread, 128 per block; the 48 sums of a
+// Gaussian stay in registers over the views, then leave through shared memory as whole 16-byte vectors.
+struct ShSlots {
+  int n;
+  int order[FSGS_MAX_VIEW_SLOTS];
+};
+
+__global__ void __launch_bounds__(kPreBlock) sh_grad_from_views_kernel(int P, int sh_degree, int n_rest, ShSlots slots,
+    const float *__restrict__ sh_source, long long slot_stride, float *__restrict__ g_dc, float *__restrict__ g_rest) {
+  __shared__ __align__(16) float s_out[kPreBlock * 45];
+  const int t = threadIdx.x, base = blockIdx.x * kPreBlock, rows = min(kPreBlock, P - base), i = base + t;
+  const int nb = (sh_degree + 1) * (sh_degree + 1);
+  float acc[16][3];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) acc[k][0] = acc[k][1] = acc[k][2] = 0.0f;
+  if (i < P) {
+    for (int s = 0; s < slots.n; ++s) {
+      const float2 *src = reinterpret_cast<const float2 *>(sh_source + (size_t) slots.order[s] * slot_stride + (size_t) i * 6);
+      const float2 a = __ldg(src), b2 = __ldg(src + 1), c = __ldg(src + 2);
+      const float gr = a.x, gg = a.y, gb = b2.x;
+      if (gr == 0.0f && gg == 0.0f && gb == 0.0f) continue;
+      float b[16];
+      sh_basis(sh_degree, b2.y, c.x, c.y, b);
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        if (k < nb) acc[k][0] += gr * b[k], acc[k][1] += gg * b[k], acc[k][2] += gb * b[k];
+    }
+    g_dc[(size_t) i * 3] = acc[0][0], g_dc[(size_t) i * 3 + 1] = acc[0][1], g_dc[(size_t) i * 3 + 2] = acc[0][2];
+  }
+  if (n_rest <= 0 || !g_rest) return;
+  const int wide = n_rest * 3;  // <= 45
+#pragma unroll
+  for (int k = 1; k < 16; ++k)
+    if (k - 1 < n_rest) {
+      s_out[t * wide + 3 * (k - 1)] = acc[k][0];
+      s_out[t * wide + 3 * (k - 1) + 1] = acc[k][1];
+      s_out[t * wide + 3 * (k - 1) + 2] = acc[k][2];
+    }
+  __syncthreads();
+  float *dst = g_rest + (size_t) base * wide;
+  const int n = rows * wide;
+  if ((((uintptr_t) dst) & 15) == 0 && (n & 3) == 0) {
+    for (int e = t; e < n / 4; e += kPreBlock) reinterpret_cast<float4 *>(dst)[e] = reinterpret_cast<const float4 *>(s_out)[e];
+  } else {
+    for (int e = t; e < n; e += kPreBlock) dst[e] = s_out[e];
+  }
 }
 
 }  // namespace fsgs
@@ -1128,6 +1183,7 @@ extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_
   d.g_opac = a->grad_opac, d.g_shs = a->grad_shs, d.g_sh_rest = d.sh_rest ? a->grad_sh_rest : nullptr;
   d.normal_opacity = (const float4 *) a->normal_opacity, d.visible = a->visible, d.accumulate = a->accumulate;
   d.overflow = a->counters ? (const long long *) a->counters + FSGS_CNT_OVERFLOW : nullptr;
+  d.sh_source = a->sh_degree >= 0 ? a->sh_source : nullptr;
   if (a->accumulate && a->sh_degree >= 0) {
     // only the layouts whose SH rows are staged through shared memory accumulate: degree 1..3, rows of at most 48
     // floats, the DC coefficient either inside those rows or alone in shs
@@ -1136,6 +1192,26 @@ extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_
   }
   if (a->sh_degree > 3) preprocess_backward_kernel<true><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
   else preprocess_backward_kernel<false><<<ceil_div(a->P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(d);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+
+extern "C" int fsgs_sh_grad_from_views(int P, int sh_degree, int n_rest, int n_slots, const int32_t *order,
+    const float *sh_source, int64_t slot_stride, float *g_sh_dc, float *g_sh_rest, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && sh_degree >= 0 && sh_degree <= 3 && n_rest >= 0 && n_rest <= 15);
+  FSGS_REQUIRE(n_slots >= 0 && n_slots <= FSGS_MAX_VIEW_SLOTS && (n_slots == 0 || (order && sh_source)) && g_sh_dc);
+  FSGS_REQUIRE(n_rest == 0 || g_sh_rest);
+  FSGS_REQUIRE((sh_degree + 1) * (sh_degree + 1) - 1 <= n_rest || n_rest == 0);
+  if (P == 0) return FSGS_OK;
+  ShSlots slots;
+  slots.n = n_slots;
+  for (int s = 0; s < n_slots; ++s) {
+    FSGS_REQUIRE(order[s] >= 0 && order[s] < n_slots);
+    slots.order[s] = order[s];
+  }
+  sh_grad_from_views_kernel<<<ceil_div(P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(P, sh_degree, n_rest, slots,
+      sh_source, (long long) slot_stride, g_sh_dc, g_sh_rest);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

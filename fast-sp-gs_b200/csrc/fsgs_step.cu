@@ -189,8 +189,9 @@ extern "C" int fsgs_stage_times(float *ms, int32_t *launches) {
 
 extern "C" int fsgs_view_backward(const fsgs_view_args *a, fsgs_stream_t stream) {
   FSGS_REQUIRE(view_args_ok(a) && a->dL_dcolor);
-  FSGS_REQUIRE(a->g_xyz && a->g_scaling_raw && a->g_rotation_raw && a->g_opacity_raw && a->g_sh_dc);
-  FSGS_REQUIRE(a->sh_rest == nullptr || a->n_rest == 0 || a->g_sh_rest);
+  FSGS_REQUIRE(a->g_xyz && a->g_scaling_raw && a->g_rotation_raw && a->g_opacity_raw);
+  // the SH gradient leaves either as rows (g_sh_dc, g_sh_rest) or as its two factors (g_sh_source), or both
+  FSGS_REQUIRE(a->g_sh_source || (a->g_sh_dc && (a->sh_rest == nullptr || a->n_rest == 0 || a->g_sh_rest)));
   const int K = a->lbs->K, M = a->lbs->M;
   const ViewWorkspace w = carve_view(a->workspace, a->P, a->W, a->H, a->list_capacity, K, M);
   if (a->workspace_bytes < w.total) return FSGS_ERR_WORKSPACE;
@@ -224,6 +225,7 @@ extern "C" int fsgs_view_backward(const fsgs_view_args *a, fsgs_stream_t stream)
   p.grad_opac = a->g_opacity_raw, p.grad_shs = a->g_sh_dc, p.grad_sh_rest = a->g_sh_rest;
   p.normal_opacity = w.normal_opacity, p.visible = a->visible, p.accumulate = a->accumulate;
   p.counters = a->counters;  // an overflowed view poisons the mask: the optimiser then drops the step
+  p.sh_source = a->g_sh_source;
   {
     StageTimer t(4, (cudaStream_t) stream);
     rc = fsgs_preprocess_backward(&p, stream);

@@ -75,7 +75,7 @@ class PreprocessBwdArgs(Structure):
                 ("grad_normal_opacity", _vp),
                 ("grad_means", _vp), ("grad_scales", _vp), ("grad_rots", _vp), ("grad_opac", _vp), ("grad_shs", _vp),
                 ("grad_sh_rest", _vp), ("normal_opacity", _vp), ("visible", _vp), ("accumulate", c_int32),
-                ("counters", _vp)]
+                ("counters", _vp), ("sh_source", _vp)]
 
 
 class ViewArgs(Structure):
@@ -90,7 +90,7 @@ class ViewArgs(Structure):
                 ("g_sh_dc", _vp), ("g_sh_rest", _vp),
                 ("g_knn_w", _vp), ("g_sp_q", _vp), ("g_sp_t", _vp), ("g_sp_dr", _vp), ("g_sp_ds", _vp),
                 ("visible", _vp), ("viewspace_grad", _vp), ("accumulate", c_int32), ("phase", c_int32),
-                ("list_capacity", c_int64), ("workspace", _vp), ("workspace_bytes", c_size_t)]
+                ("list_capacity", c_int64), ("workspace", _vp), ("workspace_bytes", c_size_t), ("g_sh_source", _vp)]
 
 
 class MotionCfg(Structure):
@@ -147,6 +147,7 @@ SYMBOLS = {
     "fsgs_render_forward": (c_int, [POINTER(RenderArgs), _vp]),
     "fsgs_render_backward": (c_int, [POINTER(RenderBwdArgs), _vp]),
     "fsgs_preprocess_backward": (c_int, [POINTER(PreprocessBwdArgs), _vp]),
+    "fsgs_sh_grad_from_views": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int32), _vp, c_int64, _vp, _vp, _vp]),
     "fsgs_compact_workspace_bytes": (c_size_t, [c_int64]),
     "fsgs_compact_plan": (c_int, [c_int64, _vp, _vp, c_size_t, _vp, _vp]),
     "fsgs_compact_rows": (c_int, [c_int, POINTER(RowTensor), c_int64, _vp, _vp, _vp]),

@@ -115,11 +115,13 @@ class ViewEngine:
         self._pending.append((ev, host))
         return self
 
-    def backward(self, g_images, g_opacity, g_extras, grads, accumulate=False, phase=0):
+    def backward(self, g_images, g_opacity, g_extras, grads, accumulate=False, phase=0, sh_source=None):
         """Queue the backward of the view last passed to ``forward``.  ``g_images [3,H,W]``; ``g_opacity [H,W]`` or
         None; ``g_extras [8,H,W]`` or None.  ``grads``: dict of destination tensors ``xyz, scaling, rotation, opacity,
         sh_dc, sh_rest`` and optionally ``knn_w, sp_q, sp_t, sp_dr, sp_ds, visible``.  ``phase`` 1 stops after the
-        preprocess adjoint (SH and opacity gradients and the mask are then final), 2 runs the rest (LBS adjoint)."""
+        preprocess adjoint (SH and opacity gradients and the mask are then final), 2 runs the rest (LBS adjoint).
+        ``sh_source [P,6]``: receives the two factors of this view's SH gradient (clamped colour gradient, view
+        direction); ``grads["sh_dc"]`` / ``grads["sh_rest"]`` may then be None (``ops.sh_grad_from_views``)."""
         a = self._args
         if g_extras is not None and g_opacity is None:  # the adjoint with auxiliary channels reads an opacity gradient
             if self._zero_opacity is None:
@@ -134,6 +136,7 @@ class ViewEngine:
         a.g_opacity_raw, a.g_sh_dc, a.g_sh_rest = p("opacity"), p("sh_dc"), p("sh_rest")
         a.g_knn_w, a.g_sp_q, a.g_sp_t, a.g_sp_dr, a.g_sp_ds = p("knn_w"), p("sp_q"), p("sp_t"), p("sp_dr"), p("sp_ds")
         a.visible = p("visible")
+        a.g_sh_source = 0 if sh_source is None else sh_source.data_ptr()
         a.accumulate, a.phase = int(bool(accumulate)), int(phase)
         check(lib().fsgs_view_backward(ctypes.byref(a), _stream()), "fsgs_view_backward")
 

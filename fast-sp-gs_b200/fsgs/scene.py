@@ -7,6 +7,7 @@ calls per view, gradients of several views summed in place, one exchange per ste
 operator ``GS_2D_fast_render`` for everything else.
 """
 import torch
+import torch.distributed as dist
 
 from . import ops
 from .dist import GradBucket
@@ -76,6 +77,7 @@ class DynamicScene:
         self.optimizer = SparseGaussianAdam(groups, lr=0.0, eps=eps)
         self.bucket = None
         self.engine = None
+        self.sh_send = self.sh_recv = None   # SH-gradient factors of the views: this rank's slots, everybody's
         self.track_densification = False
 
     @property
@@ -130,13 +132,22 @@ class DynamicScene:
             self.motion_buf = dict(sp_q=z(4), sp_t=z(3), sp_dr=z(4), sp_ds=z(2))
         return self.bucket
 
-    def train_views(self, views, size, group=None, distributed=False):
+    def train_views(self, views, size, group=None, distributed=False, views_per_rank=None, exchange="factors"):
         """One iteration over the views this rank owns: for each view forward and backward (``libfsgs`` launches only,
         two C calls per view), the per-Gaussian gradients of the views summed in place in call order; then -- when
-        ``distributed`` -- ONE exchange of the summed gradients and the visibility mask with the other ranks
-        (split in two all-reduces so that the first overlaps the last view's LBS adjoint and the second the SH part
-        of the optimiser); then the fused visibility-masked Adam.  The reference's serial loop over a batch of views,
-        ``fast_2d_gs/network.py:683-745``, followed by ``train.py:402-405``.
+        ``distributed`` -- ONE exchange with the other ranks; then the fused visibility-masked Adam.  The reference's
+        serial loop over a batch of views, ``fast_2d_gs/network.py:683-745``, followed by ``train.py:402-405``.
+
+        The exchange.  48 of the 59 gradient floats of a Gaussian are SH coefficients, and a view's SH gradient is an
+        outer product: (clamped colour gradient, 3 floats) x (SH basis of the view direction, a function of 3 floats).
+        ``exchange="factors"`` therefore all-gathers those six floats per Gaussian and view (started after the last
+        view's preprocess adjoint, under its LBS adjoint), all-reduces the mask next to it and the remaining ten
+        floats (plus the dense parameters' gradients) after the LBS adjoint, and rebuilds the summed SH gradient on
+        every rank in view order (``ops.sh_grad_from_views``): every rank forms the same bits, the replicas stay
+        identical, and 6 V floats per Gaussian travel instead of 48 through an all-reduce.  ``views_per_rank``: the
+        number of view slots every rank contributes -- the same on all ranks; default ``max(len(views), 1)``, to be
+        passed explicitly when ranks hold different numbers of views.  ``exchange="rows"`` all-reduces the gradient
+        rows themselves (two all-reduces: SH and mask first, the rest behind).
 
         ``views``: list of dicts with ``cam`` (``Tw2v, Tv2s, campos``), ``motion`` (``sp_q, sp_t, sp_dr, sp_ds``) -- or,
         with a motion network, ``t`` (float32 CUDA tensor with one element: the motion is then evaluated by the network
@@ -146,10 +157,23 @@ class DynamicScene:
         view's backward has been queued, while ``self.motion_grads`` hold this view's superpoint-motion gradients).
         Returns the engine, whose ``images / opacity / extras / radii`` are those of the last view."""
         eng, b = self._engine(size), self._grad_bucket()
+        world = dist.get_world_size(group) if distributed and dist.is_available() and dist.is_initialized() else 1
+        factors = distributed and world > 1 and exchange == "factors" and eng.sh_degree <= 3
+        n_slots = max(len(views), 1) if views_per_rank is None else int(views_per_rank)
+        if factors and len(views) > n_slots:
+            raise ValueError("more views than views_per_rank")
         dst = dict(xyz=b.view_of(self.xyz), scaling=b.view_of(self.scaling), rotation=b.view_of(self.rotation),
-                   opacity=b.view_of(self.opacity), sh_dc=b.view_of(self.sh_dc), sh_rest=b.view_of(self.sh_rest),
+                   opacity=b.view_of(self.opacity), sh_dc=None if factors else b.view_of(self.sh_dc),
+                   sh_rest=None if factors else b.view_of(self.sh_rest),
                    visible=b.extra, knn_w=self.g_knn_w, **self.motion_grads)
-        early = late = None
+        if factors:
+            P = self.num_points
+            if self.sh_send is None or tuple(self.sh_send.shape) != (n_slots, P, 6) or self.sh_recv.shape[0] != world * n_slots:
+                self.sh_send = torch.zeros(n_slots, P, 6, device=self.xyz.device)
+                self.sh_recv = torch.empty(world * n_slots, P, 6, device=self.xyz.device)
+            if len(views) < n_slots:
+                self.sh_send[len(views):].zero_()   # slots without a view add nothing
+        early = late = gather = None
         last_seg = len(b.bounds) - 1
         net, n_timed = self.motion_net, 0
         if self.sp_radius is not None:  # the kernel weights follow their parameters: one launch per step
@@ -175,6 +199,15 @@ class DynamicScene:
                                         self.knn_idx.superpoint_pairs, b.view_of(self.sp_radius),
                                         None if self.sp_weight is None else b.view_of(self.sp_weight))
 
+        def first_exchange():
+            """What is final after the last view's preprocess adjoint leaves while its LBS adjoint runs."""
+            nonlocal early, gather
+            if factors:
+                gather = dist.all_gather_into_tensor(self.sh_recv.view(-1), self.sh_send.view(-1), group=group, async_op=True)
+                early = b.reduce_span(b.extra_segment, b.extra_segment, group)   # the mask
+            else:
+                early = b.reduce_span(0, 2, group)   # SH gradients and the mask
+
         for j, v in enumerate(views):
             motion = net.forward(self.centres, v["t"], out=self.motion_buf) if "t" in v else v["motion"]
             eng.forward(self, v["cam"], motion)
@@ -182,26 +215,33 @@ class DynamicScene:
             if callable(g_images):
                 g_images = g_images(eng)
             args = (g_images, v.get("g_opacity"), v.get("g_extras"), dst)
+            src = self.sh_send[j] if factors else None
             if distributed and j == len(views) - 1:
-                eng.backward(*args, accumulate=j > 0, phase=1)
-                early = b.reduce_span(0, 2, group)   # SH gradients and the mask leave while the LBS adjoint runs
-                eng.backward(*args, accumulate=j > 0, phase=2)
+                eng.backward(*args, accumulate=j > 0, phase=1, sh_source=src)
+                first_exchange()
+                eng.backward(*args, accumulate=j > 0, phase=2, sh_source=src)
                 after_view(v)
                 after_last_view()
                 late = b.reduce_span(3, last_seg, group)
             else:
-                eng.backward(*args, accumulate=j > 0)
+                eng.backward(*args, accumulate=j > 0, sh_source=src)
                 after_view(v)
                 if j == len(views) - 1:
                     after_last_view()
         if not views:  # a rank without a view this step still takes part in the exchange, with zeros
             b.flat.zero_()
             if distributed:
-                early, late = b.reduce_span(0, 2, group), b.reduce_span(3, last_seg, group)
+                first_exchange()
+                late = b.reduce_span(3, last_seg, group)
         elif net is not None and n_timed == 0:
             b.view_of(net.params).zero_()
         b.adopt()
         self.optimizer.set_before_step(b.extra, self.num_points)  # float mask: visible where > 0
+        if gather is not None:
+            gather.wait()
+            # slot r * n_slots + j holds view r + j * world (shard_views): summed in view order on every rank
+            order = [r * n_slots + j for j in range(n_slots) for r in range(world)]
+            ops.sh_grad_from_views(self.sh_recv, order, eng.sh_degree, b.view_of(self.sh_dc), b.view_of(self.sh_rest))
         if early is not None:
             early.wait()
         self.optimizer.step_visible(only=[self.sh_dc, self.sh_rest])

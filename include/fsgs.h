@@ -408,9 +408,26 @@ typedef struct fsgs_preprocess_bwd_args {
   float *visible;
   int32_t accumulate;
   const int64_t *counters;
+  /* sh_source [P,6] (optional, sh_degree >= 0): the two factors of this view's SH gradient, which is their outer
+   * product -- the colour gradient after the clamp (3) and the unit direction camera -> Gaussian (3); zeros for
+   * culled Gaussians.  grad_shs / grad_sh_rest may then be NULL: six floats per Gaussian and view travel between
+   * ranks instead of 48, and fsgs_sh_grad_from_views rebuilds the summed gradient on every rank. */
+  float *sh_source;
 } fsgs_preprocess_bwd_args;
 
 int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *args /* host */, fsgs_stream_t stream);
+
+/* Summed SH gradient of n_slots views from their factors (the rank-1 structure of preprocess_backward's SH part,
+ * gs_2d_fast_preprocess.cu:536-609 with the SH adjoint of utils/ops_3d/spherical_harmonics.py:242-302):
+ *   g_sh[i][k][c] = sum over slots s, in the order given, of basis_k(dir[s][i]) * g_colour[s][i][c]
+ * sh_source: slot s at sh_source + s * slot_stride floats, [P,6] as written by fsgs_preprocess_backward; a slot of
+ * zeros adds nothing.  order[n_slots] (host, values < n_slots): the slots in summation order (view order, so that
+ * every rank forms the same bits).  g_sh_dc [P,3] and g_sh_rest [P,n_rest,3] are WRITTEN (zeros beyond the active
+ * degree).  sh_degree 0..3, n_slots <= FSGS_MAX_VIEW_SLOTS. */
+#define FSGS_MAX_VIEW_SLOTS 64
+int fsgs_sh_grad_from_views(int P, int sh_degree, int n_rest, int n_slots, const int32_t *order /* host */,
+                            const float *sh_source, int64_t slot_stride, float *g_sh_dc, float *g_sh_rest,
+                            fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Per-pixel epilogue of GS_2D_fast_render, one kernel each way.
@@ -528,6 +545,9 @@ typedef struct fsgs_view_args {
   int64_t list_capacity;
   void *workspace;
   size_t workspace_bytes;
+  /* backward only, optional: [P,6] factors of this view's SH gradient (fsgs_preprocess_bwd_args.sh_source);
+   * g_sh_dc / g_sh_rest may then be NULL */
+  float *g_sh_source;
 } fsgs_view_args;
 
 size_t fsgs_view_workspace_bytes(int P, int W, int H, int64_t list_capacity, int K, int M);

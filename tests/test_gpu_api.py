@@ -381,6 +381,52 @@ def test_view_gradients_accumulate_in_call_order():
         assert rel_l2(both[k], g1[k]) < 1e-5, k
 
 
+def test_sh_gradient_rebuilt_from_its_factors():
+    """The SH gradient of a view is (clamped colour gradient) x (SH basis of the view direction): the backward can hand
+    out those six floats per Gaussian instead of the 48-float rows, and ``ops.sh_grad_from_views`` rebuilds the rows --
+    bit-equal for one view, and for two views equal to the rows accumulated in the same order."""
+    from fsgs import ops
+    from fsgs import workloads as wl
+    from fsgs.scene import DynamicScene, motion_at
+    W, H, P = 160, 120, 4001
+    surf = wl.surfels(P, seed=6, log_scale_mean=-2.5)
+    sp = [wl.superpoints(surf["means"], M=64, seed=k) for k in (1, 2)]
+    centres = sp[0]["centres"]
+    cams = [{k: v.cuda() for k, v in wl.camera(W, H, eye=e).items()} for e in ((0.0, 0.0, 4.0), (2.5, 0.5, 2.0))]
+    g = torch.Generator().manual_seed(1)
+    ups = [(torch.randn(3, H, W, generator=g).cuda(), torch.randn(H, W, generator=g).cuda()) for _ in range(2)]
+    s = DynamicScene(surf, centres, K=3, device="cuda")
+    eng = s._engine((W, H))
+    s._grad_bucket()  # creates the motion-gradient buffers
+    names = dict(xyz=s.xyz, scaling=s.scaling, rotation=s.rotation, opacity=s.opacity, sh_dc=s.sh_dc, sh_rest=s.sh_rest)
+    nan = lambda t: torch.full_like(t, float("nan"))
+    rows = {k: nan(p) for k, p in names.items()}
+    rows.update(visible=torch.zeros(P, device="cuda"), knn_w=nan(s.knn_w), **{k: nan(v) for k, v in s.motion_grads.items()})
+    no_rows = dict(rows, sh_dc=None, sh_rest=None)
+    no_rows.update({k: nan(names[k]) for k in ("xyz", "scaling", "rotation", "opacity")})
+    factors = torch.full((3, P, 6), float("nan"), device="cuda")
+    factors[2].zero_()  # an empty slot
+    for j in (0, 1):
+        eng.forward(s, cams[j], motion_at(sp[j], centres, "cuda"))
+        eng.backward(ups[j][0], ups[j][1], None, rows, accumulate=j > 0, sh_source=factors[j])   # rows and factors
+        if j == 0:
+            first = {k: rows[k].clone() for k in ("sh_dc", "sh_rest")}
+            alone = torch.full((P, 6), float("nan"), device="cuda")
+            eng.backward(ups[j][0], ups[j][1], None, no_rows, sh_source=alone)                    # factors alone
+            for k in ("xyz", "scaling", "rotation", "opacity"):  # equal up to the order of the compositing atomics
+                assert rel_l2(no_rows[k], rows[k]) < 1e-6, k
+            assert rel_l2(alone, factors[0]) < 1e-6
+    assert bool(torch.isfinite(factors).all())
+    culled = eng.radii <= 0
+    assert bool((factors[1][culled] == 0).all())
+    dc, rest = nan(s.sh_dc), nan(s.sh_rest)
+    ops.sh_grad_from_views(factors, [0], 3, dc, rest)
+    assert torch.equal(dc, first["sh_dc"]) and torch.equal(rest, first["sh_rest"])
+    ops.sh_grad_from_views(factors, [0, 2, 1], 3, dc, rest)
+    assert rel_l2(dc, rows["sh_dc"]) < 1e-6 and rel_l2(rest, rows["sh_rest"]) < 1e-6
+    assert float(rest.abs().max()) > 0
+
+
 @pytest.mark.parametrize("P", [3613, 4001, 130])
 def test_training_step_with_odd_gaussian_counts(P):
     """Gaussian counts that are no multiple of 2 or 4: every per-Gaussian view of the flat gradient blocks (and of
