@@ -12,6 +12,14 @@ def shard_views(n_views, rank, world_size):
     return list(range(rank, n_views, world_size))
 
 
+def slot_order(world_size, slots_per_rank):
+    """All-gathered view slots in view order.  After an all-gather of ``slots_per_rank`` slots from each of
+    ``world_size`` ranks, slot ``r * slots_per_rank + j`` holds rank r's j-th view, which ``shard_views`` numbers
+    ``r + j * world_size``; the returned list names the slots by ascending view number (views past the end of a batch
+    are empty slots and sort where their number would be)."""
+    return [r * slots_per_rank + j for j in range(slots_per_rank) for r in range(world_size)]
+
+
 class GradBucket:
     """A flat fp32 buffer holding the gradients of ``params`` back to back, plus ``extra`` floats that ride in the
     same collectives (the visibility mask as 0/1), placed after parameter number ``extra_after`` (default: at the

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 
 from . import ops
-from .dist import GradBucket
+from .dist import GradBucket, slot_order
 from .optim import SparseGaussianAdam
 from .renderer import GS_2D_fast_render, check_overflow, group_pairs_by_superpoint
 
@@ -239,9 +239,9 @@ class DynamicScene:
         self.optimizer.set_before_step(b.extra, self.num_points)  # float mask: visible where > 0
         if gather is not None:
             gather.wait()
-            # slot r * n_slots + j holds view r + j * world (shard_views): summed in view order on every rank
-            order = [r * n_slots + j for j in range(n_slots) for r in range(world)]
-            ops.sh_grad_from_views(self.sh_recv, order, eng.sh_degree, b.view_of(self.sh_dc), b.view_of(self.sh_rest))
+            # summed in view order on every rank
+            ops.sh_grad_from_views(self.sh_recv, slot_order(world, n_slots), eng.sh_degree, b.view_of(self.sh_dc),
+                                   b.view_of(self.sh_rest))
         if early is not None:
             early.wait()
         self.optimizer.step_visible(only=[self.sh_dc, self.sh_rest])

@@ -63,6 +63,17 @@ def _worker(rank, world, port, out):
     ok &= (split.extra > 0).tolist() == [True, True, False, True, True, False, True]
     ok &= split.span(0, 1).numel() >= 7 * 3 + 7 and split.span(2, 3).numel() >= 7 * 45 + 7
     ok &= all(v.data_ptr() % 256 == split.flat.data_ptr() % 256 for v in split.views)   # segments keep alignment
+    # the factor exchange of the training step: every rank contributes the same number of view slots (empty ones are
+    # zero), an all-gather delivers them rank-major, slot_order names them in view order
+    from fsgs.dist import slot_order
+    slots = 3                                       # ceil(5 views / 2 ranks)
+    send = torch.zeros(slots, 4, 6)
+    for j, v in enumerate(views):
+        send[j] = float(v + 1)                      # view number + 1; 0 marks an empty slot
+    recv = torch.empty(world * slots, 4, 6)
+    dist.all_gather_into_tensor(recv.view(-1), send.view(-1))
+    seen = [int(recv[k, 0, 0]) for k in slot_order(world, slots)]
+    ok &= seen == [1, 2, 3, 4, 5, 0]
     radii = torch.tensor([rank, 5 - rank, 2], dtype=torch.int32)
     ok &= reduce_max_(radii).tolist() == [1, 5, 2]
     out[rank] = (bool(ok), views)
