@@ -955,6 +955,35 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
   if (out_bulk && t == 0) bulk_store_wait();
 }
 
+// The two factors of a view's SH gradient and the visibility mask, straight from what the compositing adjoint and the
+// forward pass left behind: everything the exchange between ranks needs from this view, available before the
+// preprocess adjoint has run.  Same values as preprocess_backward_kernel writes (sh_source, visible).
+__global__ void __launch_bounds__(256) sh_factors_kernel(int P, const float *__restrict__ means,
+    const float *__restrict__ colors, const float *__restrict__ g_colors, const int32_t *__restrict__ radii,
+    const float *__restrict__ campos, const long long *__restrict__ overflow, int accumulate,
+    float *__restrict__ sh_source, float *__restrict__ visible) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  const bool live = radii[i] > 0;
+  float3 g = make_float3(0, 0, 0), d = make_float3(0, 0, 0);
+  if (live) {
+    const float ux = means[3 * i] - campos[0], uy = means[3 * i + 1] - campos[1], uz = means[3 * i + 2] - campos[2];
+    const float n = rsqrtf(ux * ux + uy * uy + uz * uz + 1e-12f);
+    d = make_float3(ux * n, uy * n, uz * n);
+    g.x = colors[3 * i] > 0 ? g_colors[3 * i] : 0.0f;
+    g.y = colors[3 * i + 1] > 0 ? g_colors[3 * i + 1] : 0.0f;
+    g.z = colors[3 * i + 2] > 0 ? g_colors[3 * i + 2] : 0.0f;
+  }
+  float2 *o = reinterpret_cast<float2 *>(sh_source + (size_t) i * 6);
+  o[0] = make_float2(g.x, g.y), o[1] = make_float2(g.z, d.x), o[2] = make_float2(d.y, d.z);
+  if (visible) {
+    const bool poisoned = overflow && *overflow != 0;
+    if (poisoned) visible[i] = -INFINITY;
+    else if (!accumulate) visible[i] = live ? 1.0f : 0.0f;
+    else if (live && visible[i] >= 0.0f) visible[i] = 1.0f;  // a poisoned row stays poisoned
+  }
+}
+
 // Summed SH gradient of several views from their factors: one Gaussian per thread, 128 per block; the 48 sums of a
 // Gaussian stay in registers over the views, then leave through shared memory as whole 16-byte vectors.
 struct ShSlots {
@@ -1212,6 +1241,17 @@ extern "C" int fsgs_sh_grad_from_views(int P, int sh_degree, int n_rest, int n_s
   }
   sh_grad_from_views_kernel<<<ceil_div(P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(P, sh_degree, n_rest, slots,
       sh_source, (long long) slot_stride, g_sh_dc, g_sh_rest);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_sh_factors(int P, const float *means, const float *colors, const float *grad_colors,
+    const int32_t *radii, const float *campos, const int64_t *counters, int accumulate, float *sh_source,
+    float *visible, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && (P == 0 || (means && colors && grad_colors && radii && campos && sh_source)));
+  if (P == 0) return FSGS_OK;
+  sh_factors_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, means, colors, grad_colors, radii, campos,
+      counters ? (const long long *) counters + FSGS_CNT_OVERFLOW : nullptr, accumulate, sh_source, visible);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

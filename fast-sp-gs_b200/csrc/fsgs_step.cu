@@ -196,9 +196,12 @@ extern "C" int fsgs_view_backward(const fsgs_view_args *a, fsgs_stream_t stream)
   const ViewWorkspace w = carve_view(a->workspace, a->P, a->W, a->H, a->list_capacity, K, M);
   if (a->workspace_bytes < w.total) return FSGS_ERR_WORKSPACE;
   float *g_means2D = a->viewspace_grad ? a->viewspace_grad : w.g_means2D;
-  FSGS_REQUIRE(a->phase >= 0 && a->phase <= 2);
+  FSGS_REQUIRE(a->phase >= 0 && a->phase <= 4 && (a->phase != 3 || a->g_sh_source));
   int rc = FSGS_OK;
-  if (a->phase != 2) {
+  const bool do_blend = a->phase == 0 || a->phase == 1 || a->phase == 3;
+  const bool do_pre = a->phase == 0 || a->phase == 1 || a->phase == 4;
+  const bool do_lbs = a->phase == 0 || a->phase == 2 || a->phase == 4;
+  if (do_blend) {
   fsgs_render_bwd_args r = {};
   r.P = a->P, r.W = a->W, r.H = a->H, r.near_n = a->near_n, r.far_n = a->far_n;
   r.records = w.records, r.point_list = w.point_list, r.ranges = w.ranges, r.tile_order = w.tile_order;
@@ -212,7 +215,13 @@ extern "C" int fsgs_view_backward(const fsgs_view_args *a, fsgs_stream_t stream)
     rc = fsgs_render_backward(&r, stream);
   }
   if (rc != FSGS_OK) return rc;
-
+  }
+  if (a->phase == 3) {
+    StageTimer t(4, (cudaStream_t) stream);
+    return fsgs_sh_factors(a->P, w.warped_means, w.colors, w.g_colors, a->radii ? a->radii : w.radii, a->campos,
+        a->counters, a->accumulate, a->g_sh_source, a->visible, stream);
+  }
+  if (do_pre) {
   fsgs_preprocess_bwd_args p = {};
   p.P = a->P, p.W = a->W, p.H = a->H, p.sh_degree = a->sh_degree, p.n_dc = a->n_dc, p.n_rest = a->n_rest;
   p.means = w.warped_means, p.scales = w.warped_scales, p.rots = w.warped_rots;
@@ -223,16 +232,18 @@ extern "C" int fsgs_view_backward(const fsgs_view_args *a, fsgs_stream_t stream)
   p.grad_colors = w.g_colors, p.grad_normal_opacity = w.g_normal_opacity;
   p.grad_means = w.g_means, p.grad_scales = w.g_scales, p.grad_rots = w.g_rots;
   p.grad_opac = a->g_opacity_raw, p.grad_shs = a->g_sh_dc, p.grad_sh_rest = a->g_sh_rest;
-  p.normal_opacity = w.normal_opacity, p.visible = a->visible, p.accumulate = a->accumulate;
+  p.normal_opacity = w.normal_opacity, p.accumulate = a->accumulate;
   p.counters = a->counters;  // an overflowed view poisons the mask: the optimiser then drops the step
-  p.sh_source = a->g_sh_source;
+  // after phase 3 the factors and the mask are already out (and may be travelling)
+  p.visible = a->phase == 4 ? nullptr : a->visible;
+  p.sh_source = a->phase == 4 ? nullptr : a->g_sh_source;
   {
     StageTimer t(4, (cudaStream_t) stream);
     rc = fsgs_preprocess_backward(&p, stream);
   }
   if (rc != FSGS_OK) return rc;
   }
-  if (a->phase == 1) return FSGS_OK;
+  if (!do_lbs) return FSGS_OK;
 
   fsgs_lbs_grads g = {};
   g.g_xyz = a->g_xyz, g.g_scaling_raw = a->g_scaling_raw, g.g_rotation_raw = a->g_rotation_raw;

@@ -119,7 +119,9 @@ class ViewEngine:
         """Queue the backward of the view last passed to ``forward``.  ``g_images [3,H,W]``; ``g_opacity [H,W]`` or
         None; ``g_extras [8,H,W]`` or None.  ``grads``: dict of destination tensors ``xyz, scaling, rotation, opacity,
         sh_dc, sh_rest`` and optionally ``knn_w, sp_q, sp_t, sp_dr, sp_ds, visible``.  ``phase`` 1 stops after the
-        preprocess adjoint (SH and opacity gradients and the mask are then final), 2 runs the rest (LBS adjoint).
+        preprocess adjoint (SH and opacity gradients and the mask are then final), 2 runs the rest (LBS adjoint);
+        3 stops after the compositing adjoint and writes ``sh_source`` and the mask from what is known by then, 4 runs
+        the rest after 3 (preprocess and LBS adjoints).
         ``sh_source [P,6]``: receives the two factors of this view's SH gradient (clamped colour gradient, view
         direction); ``grads["sh_dc"]`` / ``grads["sh_rest"]`` may then be None (``ops.sh_grad_from_views``)."""
         a = self._args

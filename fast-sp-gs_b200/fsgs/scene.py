@@ -141,7 +141,7 @@ class DynamicScene:
         The exchange.  48 of the 59 gradient floats of a Gaussian are SH coefficients, and a view's SH gradient is an
         outer product: (clamped colour gradient, 3 floats) x (SH basis of the view direction, a function of 3 floats).
         ``exchange="factors"`` therefore all-gathers those six floats per Gaussian and view (started after the last
-        view's preprocess adjoint, under its LBS adjoint), all-reduces the mask next to it and the remaining ten
+        view's compositing adjoint, under its preprocess and LBS adjoints), all-reduces the mask next to it and the remaining ten
         floats (plus the dense parameters' gradients) after the LBS adjoint, and rebuilds the summed SH gradient on
         every rank in view order (``ops.sh_grad_from_views``): every rank forms the same bits, the replicas stay
         identical, and 6 V floats per Gaussian travel instead of 48 through an all-reduce.  ``views_per_rank``: the
@@ -217,9 +217,12 @@ class DynamicScene:
             args = (g_images, v.get("g_opacity"), v.get("g_extras"), dst)
             src = self.sh_send[j] if factors else None
             if distributed and j == len(views) - 1:
-                eng.backward(*args, accumulate=j > 0, phase=1, sh_source=src)
+                # factors: they and the mask are known once the compositing adjoint has run (phase 3), and travel
+                # under the preprocess and LBS adjoints (phase 4); rows: the SH rows need the preprocess adjoint
+                # (phase 1) and travel under the LBS adjoint (phase 2)
+                eng.backward(*args, accumulate=j > 0, phase=3 if factors else 1, sh_source=src)
                 first_exchange()
-                eng.backward(*args, accumulate=j > 0, phase=2, sh_source=src)
+                eng.backward(*args, accumulate=j > 0, phase=4 if factors else 2, sh_source=src)
                 after_view(v)
                 after_last_view()
                 late = b.reduce_span(3, last_seg, group)

@@ -424,6 +424,13 @@ int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *args /* host */, fs
  * zeros adds nothing.  order[n_slots] (host, values < n_slots): the slots in summation order (view order, so that
  * every rank forms the same bits).  g_sh_dc [P,3] and g_sh_rest [P,n_rest,3] are WRITTEN (zeros beyond the active
  * degree).  sh_degree 0..3, n_slots <= FSGS_MAX_VIEW_SLOTS. */
+/* The same factors (and the same mask, with the same accumulate / counters semantics) without the preprocess adjoint:
+ * from the forward pass's warped means [P,3] and colours [P,3] (pre-clamp sign: colour > 0), the compositing adjoint's
+ * colour gradient [P,3] and radii.  Lets the exchange between ranks start before the preprocess adjoint runs. */
+int fsgs_sh_factors(int P, const float *means, const float *colors, const float *grad_colors, const int32_t *radii,
+                    const float *campos, const int64_t *counters, int accumulate, float *sh_source, float *visible,
+                    fsgs_stream_t stream);
+
 #define FSGS_MAX_VIEW_SLOTS 64
 int fsgs_sh_grad_from_views(int P, int sh_degree, int n_rest, int n_slots, const int32_t *order /* host */,
                             const float *sh_source, int64_t slot_stride, float *g_sh_dc, float *g_sh_rest,
@@ -540,7 +547,10 @@ typedef struct fsgs_view_args {
   float *viewspace_grad; /* [P,2] or NULL */
   int32_t accumulate;
   /* backward only: 0 = everything; 1 = up to and including the preprocess adjoint (g_sh_*, g_opacity_raw and visible
-   * are then final in stream order: their exchange may start); 2 = the remaining LBS adjoint */
+   * are then final in stream order: their exchange may start); 2 = the remaining LBS adjoint;
+   * 3 = the compositing adjoint, then g_sh_source and visible by fsgs_sh_factors (final in stream order before the
+   * preprocess adjoint has run: needs g_sh_source); 4 = the rest after 3: preprocess adjoint (which leaves
+   * g_sh_source and visible alone) and LBS adjoint */
   int32_t phase;
   int64_t list_capacity;
   void *workspace;

@@ -416,6 +416,19 @@ def test_sh_gradient_rebuilt_from_its_factors():
             for k in ("xyz", "scaling", "rotation", "opacity"):  # equal up to the order of the compositing atomics
                 assert rel_l2(no_rows[k], rows[k]) < 1e-6, k
             assert rel_l2(alone, factors[0]) < 1e-6
+    # the same factors and mask from the early kernel (phase 3), the rest behind it (phase 4)
+    early = torch.full((P, 6), float("nan"), device="cuda")
+    split = dict(no_rows, visible=torch.full((P,), float("nan"), device="cuda"))
+    split.update({k: nan(names[k]) for k in ("xyz", "scaling", "rotation", "opacity")})
+    eng.backward(ups[1][0], ups[1][1], None, split, phase=3, sh_source=early)
+    eng.backward(ups[1][0], ups[1][1], None, split, phase=4, sh_source=early)
+    whole = dict(no_rows, visible=torch.full((P,), float("nan"), device="cuda"))
+    whole.update({k: nan(names[k]) for k in ("xyz", "scaling", "rotation", "opacity")})
+    late = torch.full((P, 6), float("nan"), device="cuda")
+    eng.backward(ups[1][0], ups[1][1], None, whole, sh_source=late)
+    assert rel_l2(early, late) < 1e-6 and torch.equal(split["visible"], whole["visible"])
+    for k in ("xyz", "scaling", "rotation", "opacity"):
+        assert rel_l2(split[k], whole[k]) < 1e-4, k   # run-to-run order of the compositing atomics
     assert bool(torch.isfinite(factors).all())
     culled = eng.radii <= 0
     assert bool((factors[1][culled] == 0).all())
