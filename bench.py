@@ -493,7 +493,13 @@ def run_ours(args):
         algo = os.environ.get("FSGS_BENCH_NCCL_ALGO", "Ring" if world >= 4 else "default")
         if algo != "default":
             os.environ.setdefault("NCCL_ALGO", algo)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # NCCL's kernels on a high-priority stream: the step's collectives are meant to run under the adjoint and
+        # optimiser kernels, whose grids fill every SM; at equal priority a collective's blocks (which each want most
+        # of an SM) were not placed until those grids had drained, and the exchange ran after them instead of beside
+        # them (FSGS_BENCH_NCCL_PRIORITY=0 restores torch's default)
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.is_high_priority_stream = os.environ.get("FSGS_BENCH_NCCL_PRIORITY", "1") != "0"
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=opts)
     dev = torch.device("cuda", local)
     if args.batch_views > 0:
         view_ids, scaling, total_views = shard_views(args.batch_views, rank, world), "strong", args.batch_views

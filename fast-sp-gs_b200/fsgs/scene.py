@@ -78,6 +78,7 @@ class DynamicScene:
         self.bucket = None
         self.engine = None
         self.sh_send = self.sh_recv = None   # SH-gradient factors of the views: this rank's slots, everybody's
+        self.trace = None                    # a list: train_views appends (label, CUDA event) at its phase boundaries
         self.track_densification = False
 
     @property
@@ -157,6 +158,14 @@ class DynamicScene:
         view's backward has been queued, while ``self.motion_grads`` hold this view's superpoint-motion gradients).
         Returns the engine, whose ``images / opacity / extras / radii`` are those of the last view."""
         eng, b = self._engine(size), self._grad_bucket()
+
+        def mark(label):
+            if self.trace is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                self.trace.append((label, ev))
+
+        mark("start")
         world = dist.get_world_size(group) if distributed and dist.is_available() and dist.is_initialized() else 1
         factors = distributed and world > 1 and exchange == "factors" and eng.sh_degree <= 3
         n_slots = max(len(views), 1) if views_per_rank is None else int(views_per_rank)
@@ -221,10 +230,12 @@ class DynamicScene:
                 # under the preprocess and LBS adjoints (phase 4); rows: the SH rows need the preprocess adjoint
                 # (phase 1) and travel under the LBS adjoint (phase 2)
                 eng.backward(*args, accumulate=j > 0, phase=3 if factors else 1, sh_source=src)
+                mark("first part of the last backward")
                 first_exchange()
                 eng.backward(*args, accumulate=j > 0, phase=4 if factors else 2, sh_source=src)
                 after_view(v)
                 after_last_view()
+                mark("rest of the last backward")
                 late = b.reduce_span(3, last_seg, group)
             else:
                 eng.backward(*args, accumulate=j > 0, sh_source=src)
@@ -242,15 +253,21 @@ class DynamicScene:
         self.optimizer.set_before_step(b.extra, self.num_points)  # float mask: visible where > 0
         if gather is not None:
             gather.wait()
+            mark("all-gather arrived")
             # summed in view order on every rank
             ops.sh_grad_from_views(self.sh_recv, slot_order(world, n_slots), eng.sh_degree, b.view_of(self.sh_dc),
                                    b.view_of(self.sh_rest))
+            mark("SH rows rebuilt")
         if early is not None:
             early.wait()
+            mark("first all-reduce arrived")
         self.optimizer.step_visible(only=[self.sh_dc, self.sh_rest])
+        mark("SH Adam")
         if late is not None:
             late.wait()
+            mark("last all-reduce arrived")
         self.optimizer.step_visible(only=[self.xyz, self.opacity, self.scaling, self.rotation])
+        mark("rest of Adam")
         if self.dense_optimizer is not None:
             # a view whose tile lists overflowed (on any rank) left -inf in the mask: the masked Adam above passed no
             # row, and the fused Adam of the dense parameters skips on the same signal
