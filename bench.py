@@ -738,6 +738,21 @@ def run_ours(args):
                      "net": f"{net.cfg.depth} x {net.cfg.width}, {M} superpoints, {net.params.numel()} parameters"}
         del scene_m
 
+    # ---- where the time of a multi-rank step goes: CUDA events at the phase boundaries of train_views, one step at a
+    # time (synchronised, so the absolute times sit a little above the pipelined step), rank 0, outside timed regions
+    timeline = None
+    if distributed and n_views:
+        acc, n_trace = {}, 20
+        for it in range(n_trace):
+            scene.trace = []
+            step()
+            torch.cuda.synchronize()
+            t0 = scene.trace[0][1]
+            for label, ev in scene.trace[1:]:
+                acc[label] = acc.get(label, 0.0) + t0.elapsed_time(ev)
+        scene.trace = None
+        timeline = {k: round(v / n_trace, 4) for k, v in acc.items()}
+
     # ---- replicas must stay identical; a split batch must equal the serial one (outside every timed region) ----
     checks = None
     if distributed:
@@ -870,7 +885,7 @@ def run_ours(args):
             "stages": stages,
             "host_ms_per_step": {k: round(med(v), 4) for k, v in host_ms.items()},
             "allreduce_ms_49P_10P_floats": allreduce_ms, "factor_exchange_ms": exchange_ms or None,
-            "multi_gpu_checks": checks,
+            "multi_gpu_checks": checks, "step_timeline_ms_rank0": timeline,
             "clocks": clocks,
         }
         if world == 1 and not args.no_baselines:
