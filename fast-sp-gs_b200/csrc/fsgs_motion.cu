@@ -760,33 +760,45 @@ __global__ void __launch_bounds__(256) lbs_weights_forward_kernel(int P, int K, 
   for (int k = 0; k < K; ++k) w[(size_t) i * K + k] = u[k] / s;
 }
 
-// one block per superpoint over its grouped pairs: no atomics, fixed order
-__global__ void __launch_bounds__(256) lbs_weights_backward_kernel(int K, const float *__restrict__ d2,
+// Adjoint of the kernel weights in two passes.  Pass 1, one thread per Gaussian (coalesced rows, the exponentials
+// once per pair): the contribution of every pair (i, k) to the gradient of its superpoint's raw radius and raw weight.
+// Pass 2, one block per superpoint over its grouped pairs: sums them in a fixed order, no atomics -- a superpoint
+// that owns many times the average number of pairs only costs more two-load iterations.  (Doing all of pass 1's
+// arithmetic inside pass 2's loop made the most popular superpoint's block the whole kernel: 70 us at 300 k x 3.)
+__global__ void __launch_bounds__(256) lbs_weights_backward_pairs_kernel(int P, int K, const float *__restrict__ d2,
     const int64_t *__restrict__ idx, const float *__restrict__ raw_radius, const float *__restrict__ raw_weight,
-    const float *__restrict__ g_w, const int32_t *__restrict__ offsets, const int32_t *__restrict__ pairs,
-    float *__restrict__ g_radius, float *__restrict__ g_weight, int accumulate) {
+    const float *__restrict__ g_w, float2 *__restrict__ contrib) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  float ek[FSGS_KNN_MAX_K], uk[FSGS_KNN_MAX_K], rk[FSGS_KNN_MAX_K], sk[FSGS_KNN_MAX_K];
+  float S = 0.0f, gdotw = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    const int mk = (int) idx[(size_t) i * K + k];
+    rk[k] = expf(raw_radius[mk]);
+    sk[k] = raw_weight ? 1.0f / (1.0f + expf(-raw_weight[mk])) : 1.0f;
+    ek[k] = expf(-d2[(size_t) i * K + k] / (2.0f * rk[k] * rk[k]));
+    uk[k] = ek[k] * sk[k] + 1e-7f;
+    S += uk[k];
+    gdotw += g_w[(size_t) i * K + k] * uk[k];
+  }
+  for (int k = 0; k < K; ++k) {
+    const float gu = (g_w[(size_t) i * K + k] - gdotw / S) / S;  // dL/du of this pair
+    const float d = d2[(size_t) i * K + k];
+    // d u / d raw_radius = e * sigma * d / r^2 ;  d u / d raw_weight = e * sigma (1 - sigma)
+    contrib[(size_t) i * K + k] = make_float2(gu * ek[k] * sk[k] * d / (rk[k] * rk[k]), gu * ek[k] * sk[k] * (1.0f - sk[k]));
+  }
+}
+
+__global__ void __launch_bounds__(256) lbs_weights_backward_sum_kernel(const float2 *__restrict__ contrib,
+    const int32_t *__restrict__ offsets, const int32_t *__restrict__ pairs, int has_weight, float *__restrict__ g_radius,
+    float *__restrict__ g_weight, int accumulate) {
   __shared__ float s_a[8], s_b[8];
   const int m = blockIdx.x;
-  const float r = expf(raw_radius[m]);
-  const float sg = raw_weight ? 1.0f / (1.0f + expf(-raw_weight[m])) : 1.0f;
   float ga = 0.0f, gb = 0.0f;
+#pragma unroll 4
   for (int e = offsets[m] + threadIdx.x; e < offsets[m + 1]; e += blockDim.x) {
-    const int pair = pairs[e], i = pair / K, kk = pair - i * K;
-    // the row's normalisation: u_k, S, and sum_j g_j w_j
-    float S = 0.0f, gdotw = 0.0f, e_self = 0.0f;
-    for (int k = 0; k < K; ++k) {
-      const int mk = (int) idx[(size_t) i * K + k];
-      const float rk = expf(raw_radius[mk]);
-      const float ek = expf(-d2[(size_t) i * K + k] / (2.0f * rk * rk));
-      const float uk = ek * (raw_weight ? 1.0f / (1.0f + expf(-raw_weight[mk])) : 1.0f) + 1e-7f;
-      S += uk;
-      gdotw += g_w[(size_t) i * K + k] * uk;
-      if (k == kk) e_self = ek;
-    }
-    const float gu = (g_w[pair] - gdotw / S) / S;  // dL/du of this pair
-    const float d = d2[pair];
-    ga += gu * e_self * sg * d / (r * r);          // d u / d raw_radius = e * sigma * d / r^2
-    gb += gu * e_self * sg * (1.0f - sg);          // d u / d raw_weight = e * sigma (1 - sigma)
+    const float2 c = contrib[pairs[e]];
+    ga += c.x, gb += c.y;
   }
   for (int o = 16; o > 0; o >>= 1) ga += __shfl_xor_sync(0xffffffffu, ga, o), gb += __shfl_xor_sync(0xffffffffu, gb, o);
   if ((threadIdx.x & 31) == 0) s_a[threadIdx.x >> 5] = ga, s_b[threadIdx.x >> 5] = gb;
@@ -795,7 +807,7 @@ __global__ void __launch_bounds__(256) lbs_weights_backward_kernel(int K, const 
     float ta = 0.0f, tb = 0.0f;
     for (int w = 0; w < 8; ++w) ta += s_a[w], tb += s_b[w];
     store_grad(g_radius + m, ta, accumulate);
-    if (g_weight) store_grad(g_weight + m, raw_weight ? tb : 0.0f, accumulate);
+    if (g_weight) store_grad(g_weight + m, has_weight ? tb : 0.0f, accumulate);
   }
 }
 
@@ -926,13 +938,26 @@ extern "C" int fsgs_lbs_weights_forward(int P, int K, const float *d2, const int
   return FSGS_OK;
 }
 
+extern "C" size_t fsgs_lbs_weights_backward_workspace_bytes(int P, int K) {
+  return P > 0 && K > 0 ? sizeof(float2) * (size_t) P * K : 0;
+}
+
 extern "C" int fsgs_lbs_weights_backward(int P, int K, int M, const float *d2, const int64_t *idx,
     const float *raw_radius, const float *raw_weight, const float *g_weights, const int32_t *sp_pair_offsets,
-    const int32_t *sp_pairs, float *g_raw_radius, float *g_raw_weight, int accumulate, fsgs_stream_t stream) {
+    const int32_t *sp_pairs, float *g_raw_radius, float *g_raw_weight, int accumulate, void *workspace,
+    size_t workspace_bytes, fsgs_stream_t stream) {
   FSGS_REQUIRE(P >= 0 && K > 0 && K <= FSGS_KNN_MAX_K && M > 0 && d2 && idx && raw_radius && g_weights);
   FSGS_REQUIRE(sp_pair_offsets && sp_pairs && g_raw_radius);
-  lbs_weights_backward_kernel<<<M, 256, 0, (cudaStream_t) stream>>>(K, d2, idx, raw_radius, raw_weight, g_weights,
-      sp_pair_offsets, sp_pairs, g_raw_radius, g_raw_weight, accumulate);
+  if (workspace_bytes < fsgs_lbs_weights_backward_workspace_bytes(P, K) || (P > 0 && !workspace)) return FSGS_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t) stream;
+  float2 *contrib = (float2 *) workspace;
+  if (P > 0) {
+    lbs_weights_backward_pairs_kernel<<<ceil_div(P, 256), 256, 0, st>>>(P, K, d2, idx, raw_radius, raw_weight, g_weights,
+        contrib);
+    FSGS_LAUNCH_CHECK();
+  }
+  lbs_weights_backward_sum_kernel<<<M, 256, 0, st>>>(contrib, sp_pair_offsets, sp_pairs, raw_weight != nullptr,
+      g_raw_radius, g_raw_weight, accumulate);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

@@ -127,8 +127,9 @@ SYMBOLS = {
     "fsgs_motion_forward": (c_int, [POINTER(MotionArgs), _vp]),
     "fsgs_motion_backward": (c_int, [POINTER(MotionArgs), _vp]),
     "fsgs_lbs_weights_forward": (c_int, [c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_lbs_weights_backward_workspace_bytes": (c_size_t, [c_int, c_int]),
     "fsgs_lbs_weights_backward": (c_int, [c_int, c_int, c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, c_int,
-                                          _vp]),
+                                          _vp, c_size_t, _vp]),
     "fsgs_view_pair_counts": (c_int, [POINTER(ViewArgs), _vp, _vp]),
     "fsgs_stage_timing": (c_int, [c_int]),
     "fsgs_stage_times": (c_int, [POINTER(c_float), POINTER(c_int32)]),

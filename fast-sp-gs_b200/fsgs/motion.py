@@ -138,6 +138,8 @@ def kernel_weights_backward(d2, idx, raw_radius, raw_weight, g_w, pairs, g_radiu
     """``pairs`` = ``renderer.group_pairs_by_superpoint(idx, M)``; gradients of the raw radius / raw weight [M]."""
     P, K = d2.shape
     offsets, ids = pairs
+    scratch = torch.empty(int(lib().fsgs_lbs_weights_backward_workspace_bytes(P, K)), dtype=torch.uint8, device=d2.device)
     check(lib().fsgs_lbs_weights_backward(P, K, raw_radius.shape[0], _ptr(d2), _ptr(idx), _ptr(raw_radius),
                                           _ptr(raw_weight), _ptr(g_w), _ptr(offsets), _ptr(ids), _ptr(g_radius),
-                                          _ptr(g_weight), int(bool(accumulate)), _stream()), "fsgs_lbs_weights_backward")
+                                          _ptr(g_weight), int(bool(accumulate)), _ptr(scratch), scratch.numel(),
+                                          _stream()), "fsgs_lbs_weights_backward")

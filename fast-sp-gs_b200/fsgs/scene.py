@@ -11,7 +11,7 @@ import torch.distributed as dist
 
 from . import ops
 from .dist import GradBucket, slot_order
-from .optim import SparseGaussianAdam
+from .optim import DenseAdam, SparseGaussianAdam
 from .renderer import GS_2D_fast_render, check_overflow, group_pairs_by_superpoint
 
 # learning rates of exps/d_nerf.yaml (position lr at its initial value)
@@ -67,8 +67,7 @@ class DynamicScene:
             self.sp_weight = P(kernel_weights[1]) if kernel_weights[1] is not None else None
         self.dense_params = ([motion_net.params] if motion_net is not None else []) + \
             [p for p in (self.sp_radius, self.sp_weight) if p is not None]
-        self.dense_optimizer = torch.optim.Adam(self.dense_params, lr=lr_deform, eps=eps, fused=True) \
-            if self.dense_params else None
+        self.dense_optimizer = DenseAdam(self.dense_params, lr=lr_deform, eps=eps) if self.dense_params else None
         self.refresh_knn()
         LRS = dict(globals()["LRS"], **(lrs or {}))
         groups = [dict(params=[self.xyz], lr=LRS["xyz"]), dict(params=[self.sh_dc], lr=LRS["sh_dc"]),
@@ -270,9 +269,8 @@ class DynamicScene:
         mark("rest of Adam")
         if self.dense_optimizer is not None:
             # a view whose tile lists overflowed (on any rank) left -inf in the mask: the masked Adam above passed no
-            # row, and the fused Adam of the dense parameters skips on the same signal
-            self.dense_optimizer.found_inf = torch.isinf(b.extra[0]).to(torch.float32)
-            self.dense_optimizer.step()
+            # row, and the dense parameters' Adam is gated by the same element (mask values are >= 0 otherwise)
+            self.dense_optimizer.step_gated(b.extra[:1] + 1.0)
         self._drop_grads()
         return eng
 

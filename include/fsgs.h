@@ -503,13 +503,16 @@ int fsgs_motion_backward(const fsgs_motion_args *args /* host */, fsgs_stream_t 
 
 /* weights [P,K] = normalise(exp(-d2 / (2 r^2)) * sigma + 1e-7), r = exp(raw_radius[idx]), sigma =
  * sigmoid(raw_weight[idx]) (raw_weight NULL: 1).  Backward: g_weights [P,K] -> g_raw_radius [M], g_raw_weight [M]
- * (written, or added to when accumulate != 0), one block per superpoint over the grouped pairs (the same
- * sp_pair_offsets / sp_pairs as in fsgs_lbs; no atomics); the distances are treated as constants. */
+ * (written, or added to when accumulate != 0): every pair's term once per Gaussian, then one block per superpoint
+ * sums its grouped pairs (the same sp_pair_offsets / sp_pairs as in fsgs_lbs) in a fixed order, no atomics; the
+ * distances are treated as constants. */
 int fsgs_lbs_weights_forward(int P, int K, const float *d2, const int64_t *idx, const float *raw_radius,
     const float *raw_weight, float *weights, fsgs_stream_t stream);
+size_t fsgs_lbs_weights_backward_workspace_bytes(int P, int K); /* 8 P K: one (radius, weight) term per pair */
 int fsgs_lbs_weights_backward(int P, int K, int M, const float *d2, const int64_t *idx, const float *raw_radius,
     const float *raw_weight, const float *g_weights, const int32_t *sp_pair_offsets, const int32_t *sp_pairs,
-    float *g_raw_radius, float *g_raw_weight, int accumulate, fsgs_stream_t stream);
+    float *g_raw_radius, float *g_raw_weight, int accumulate, void *workspace, size_t workspace_bytes,
+    fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * One view of a training iteration in two calls (forward, backward), all intermediates in one workspace.

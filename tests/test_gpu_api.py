@@ -133,6 +133,38 @@ def test_sparse_adam_fused_equals_per_tensor():
     assert opt.state[params[0]]["step"].item() == 3.0
 
 
+def test_dense_adam_equals_torch_adam_and_obeys_its_gate():
+    """``DenseAdam`` (dense tensors through the masked Adam kernel, one row each behind a one-element gate) against
+    ``torch.optim.Adam`` over five steps; a gate <= 0 leaves parameters and moments alone."""
+    from fsgs.optim import DenseAdam
+    g = torch.Generator().manual_seed(2)
+    shapes = [(523312,), (512,), (37, 5)]
+    mine = [torch.nn.Parameter(torch.randn(s, generator=g).cuda()) for s in shapes]
+    theirs = [torch.nn.Parameter(p.detach().clone()) for p in mine]
+    a, b = DenseAdam(mine, lr=1e-3, eps=1e-15), torch.optim.Adam(theirs, lr=1e-3, eps=1e-15)
+    for step in range(5):
+        for p, q in zip(mine, theirs):
+            grad = torch.randn(p.shape, generator=g).cuda() * (10.0 ** (step - 2))
+            p.grad, q.grad = grad.clone(), grad.clone()
+        a.step()
+        b.step()
+        for p, q in zip(mine, theirs):
+            assert float((p.detach() - q.detach()).abs().max()) < 2e-6, step   # steps are ~1e-3: a few ulp of the update
+            assert rel_l2(a.state[p]["exp_avg"], b.state[q]["exp_avg"]) < 1e-6
+            # the kernel forms 1 - beta2 in float32 (as the reference's sparse Adam does), torch in double: 1.3e-5
+            assert rel_l2(a.state[p]["exp_avg_sq"], b.state[q]["exp_avg_sq"]) < 3e-5
+    before = [(p.detach().clone(), a.state[p]["exp_avg"].clone(), a.state[p]["exp_avg_sq"].clone()) for p in mine]
+    for p in mine:
+        p.grad = torch.ones_like(p)
+    a.step(gate=torch.tensor([float("-inf")], device="cuda"))
+    a.step(gate=torch.zeros(1, device="cuda"))
+    for p, (p0, m0, v0) in zip(mine, before):
+        assert torch.equal(p.detach(), p0) and torch.equal(a.state[p]["exp_avg"], m0)
+        assert torch.equal(a.state[p]["exp_avg_sq"], v0)
+    a.step(gate=torch.full((1,), 3.0, device="cuda"))
+    assert not torch.equal(mine[0].detach(), before[0][0])
+
+
 def test_install_exposes_the_reference_operator_names():
     import fsgs
     mod = fsgs.install("fast_2d_gs_test._C._C")

@@ -144,6 +144,7 @@ def test_scene_trains_the_motion_network_and_kernel_weights():
 
     a, net_a = make()
     b, net_b = make()
+    torch_adam = torch.optim.Adam(b.dense_params, lr=1e-3, eps=1e-15)   # the autograd route steps with torch's own
     _, net_a_twin = make()   # same parameters as net_a before the step: supplies the native motion values to route b
     views = [dict(cam=cams[k], t=ts[k], g_images=ups[k][0], g_opacity=ups[k][1]) for k in (0, 1)]
     for _ in range(1):  # one iteration: the second already starts from parameters that differ by sign-like Adam steps
@@ -166,9 +167,9 @@ def test_scene_trains_the_motion_network_and_kernel_weights():
             vis = out["visibility_filter"] if vis is None else vis | out["visibility_filter"]
         b.optimizer.set_before_step(vis, P)
         b.optimizer.step()
-        b.dense_optimizer.step()
+        torch_adam.step()
         b.optimizer.zero_grad(set_to_none=True)
-        b.dense_optimizer.zero_grad(set_to_none=True)
+        torch_adam.zero_grad(set_to_none=True)
     a.check()
     from fsgs.scene import LRS
     lrs = [LRS[k] for k in ("xyz", "sh_dc", "sh_rest", "opacity", "scaling", "rotation")]
@@ -183,6 +184,6 @@ def test_scene_trains_the_motion_network_and_kernel_weights():
     for x, y, x0 in ((net_a.params, net_b.params, MotionNet(M, width=64, local_frame=True, seed=4).params),
                      (a.sp_radius, b.sp_radius, raw_r.cuda()), (a.sp_weight, b.sp_weight, raw_w.cuda())):
         assert float((x.detach() - x0.detach().to(x.device)).abs().max()) > 1e-4
-        ma, mb = a.dense_optimizer.state[x]["exp_avg"], b.dense_optimizer.state[y]["exp_avg"]
+        ma, mb = a.dense_optimizer.state[x]["exp_avg"], torch_adam.state[y]["exp_avg"]
         assert rel_l2(ma, mb) < 1e-4, rel_l2(ma, mb)
         assert float((x.detach() - y.detach()).abs().mean()) < 0.1 * 1e-3
