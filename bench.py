@@ -409,9 +409,12 @@ def reference_cuda(wlk, steps, warmup):
             ref.AdamMasksedUpdated(p.data, p.grad, m, vv, vis, 1.6e-4, 0.9, 0.999, 1e-15, P, p.numel() // P)
             p.grad = None
 
-    ms_step = _event_ms(step, steps, warmup)
+    # its Python synchronises with the device several times per step (debug=True reads counters back), so a step's
+    # time follows the host's mood: median of three runs, all three reported
+    step_runs = sorted(_event_ms(step, steps, warmup if r == 0 else 0) for r in range(3))
+    ms_step = step_runs[1]
     with torch.no_grad():
-        ms_fwd = _event_ms(lambda: forward(True), steps, 2)
+        ms_fwd = sorted(_event_ms(lambda: forward(True), steps, 2 if r == 0 else 0) for r in range(3))[1]
     # every operator alone, debug=False, on the tensors of the last step
     means, scales, rots, opac, pre, fw, gr = (keep[k].detach() if torch.is_tensor(keep[k]) else keep[k]
                                               for k in ("means", "scales", "rots", "opac", "pre", "fw", "gr"))
@@ -434,7 +437,8 @@ def reference_cuda(wlk, steps, warmup):
             p.data, torch.zeros_like(p), m, vv, rad > 0, 1.6e-4, 0.9, 0.999, 1e-15, P, p.numel() // P)
             for p, (m, vv) in zip(leaves, state)], steps),
     }
-    return {"value": 1e3 / ms_step, "unit": UNIT, "ms_per_step": ms_step, "fwd_frames_per_s": 1e3 / ms_fwd,
+    return {"value": 1e3 / ms_step, "unit": UNIT, "ms_per_step": ms_step,
+            "ms_per_step_runs": [round(x, 4) for x in step_runs], "fwd_frames_per_s": 1e3 / ms_fwd,
             "ms_per_fwd_frame": ms_fwd, "operators_alone_ms": {k: round(x, 4) for k, x in ops_ms.items()},
             "operators_alone_sum_ms": round(sum(ops_ms.values()), 4),
             "how": "reference kernels (oracle/_ref, sm_100, -O3). value / fwd: called as its Python calls them "
