@@ -793,11 +793,14 @@ def run_ours(args):
             b.train_views(two, (W, H), distributed=False)
             if it == 0:
                 c.train_views(two, (W, H), distributed=False)
-                for x, y, z in zip(a.params, b.params, c.params):
+                per_tensor = torch.zeros(6, 2, device=dev)   # position, SH DC, SH rest, opacity, scale, rotation
+                for k, (x, y, z) in enumerate(zip(a.params, b.params, c.params)):
                     gx, gy, gz = a.bucket.view_of(x), b.bucket.view_of(y), c.bucket.view_of(z)
-                    rel_g = torch.maximum(rel_g, ((gx - gy).norm() / gy.norm().clamp_min(1e-30)).reshape(1))
-                    rel_noise = torch.maximum(rel_noise, ((gz - gy).norm() / gy.norm().clamp_min(1e-30)).reshape(1))
+                    per_tensor[k, 0] = (gx - gy).norm() / gy.norm().clamp_min(1e-30)
+                    per_tensor[k, 1] = (gz - gy).norm() / gy.norm().clamp_min(1e-30)
+                rel_g, rel_noise = per_tensor[:, 0].max().reshape(1), per_tensor[:, 1].max().reshape(1)
         del c
+        dist.all_reduce(per_tensor, op=dist.ReduceOp.MAX)
         for x, y in zip(a.params, b.params):
             rel = torch.maximum(rel, ((x.detach() - y.detach()).norm() / y.detach().norm().clamp_min(1e-30)).reshape(1))
         dist.all_reduce(rel, op=dist.ReduceOp.MAX)
@@ -806,7 +809,10 @@ def run_ours(args):
         checks = {"replica_max_abs_diff_after_run": float(worst),
                   "three_views_dealt_to_the_ranks_vs_serial_rel_l2": float(rel),
                   "three_views_dealt_to_the_ranks_vs_serial_first_step_gradients_rel_l2": float(rel_g),
-                  "serial_step_run_twice_first_step_gradients_rel_l2": float(rel_noise)}
+                  "serial_step_run_twice_first_step_gradients_rel_l2": float(rel_noise),
+                  "first_step_gradients_rel_l2_per_tensor": {
+                      name: {"dealt_vs_serial": float(per_tensor[k, 0]), "serial_vs_serial": float(per_tensor[k, 1])}
+                      for k, name in enumerate(("xyz", "sh_dc", "sh_rest", "opacity", "scaling", "rotation"))}}
         del a, b
 
     if rank == 0:
