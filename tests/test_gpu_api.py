@@ -472,6 +472,32 @@ def test_sh_gradient_rebuilt_from_its_factors():
     assert float(rest.abs().max()) > 0
 
 
+@pytest.mark.parametrize("degree,n_rest,P", [(0, 15, 1000), (1, 15, 777), (2, 8, 130), (3, 15, 4097), (3, 0, 64)])
+def test_sh_rows_from_factors_vs_the_oracle_basis(degree, n_rest, P):
+    """``ops.sh_grad_from_views`` against sum_v basis(dir_v) x g_v formed with the oracle's SH basis, for every active
+    degree, ragged sizes, slots in a given order and rows beyond the active degree left at zero."""
+    from fsgs import ops
+    g = torch.Generator().manual_seed(P)
+    S = 3
+    d = torch.nn.functional.normalize(torch.randn(S, P, 3, generator=g), dim=-1)
+    c = torch.randn(S, P, 3, generator=g)
+    c[1, ::3] = 0.0                                       # culled in that view: no contribution
+    src = torch.cat([c, d], dim=-1).contiguous().cuda()
+    dc = torch.full((P, 1, 3), float("nan")).cuda()
+    rest = torch.full((P, n_rest, 3), float("nan")).cuda() if n_rest else None
+    ops.sh_grad_from_views(src, [2, 0, 1], degree, dc, rest)
+    nb = (degree + 1) ** 2
+    want = torch.zeros(P, 16, 3, dtype=torch.float64)
+    for v in (2, 0, 1):
+        b = orc.sh_basis(d[v], degree).double()           # [P, nb]
+        want[:, :nb] += b[:, :, None] * c[v].double()[:, None, :]
+    assert float((dc.cpu().double() - want[:, :1]).abs().max()) < 2e-6
+    if n_rest:
+        assert float((rest.cpu().double() - want[:, 1:1 + n_rest]).abs().max()) < 2e-6
+        if nb - 1 < n_rest:
+            assert bool((rest[:, nb - 1:] == 0).all())
+
+
 @pytest.mark.parametrize("P", [3613, 4001, 130])
 def test_training_step_with_odd_gaussian_counts(P):
     """Gaussian counts that are no multiple of 2 or 4: every per-Gaussian view of the flat gradient blocks (and of
