@@ -585,8 +585,8 @@ def run_ours(args):
             dist.barrier()
             allreduce_ms.append(round(_event_ms(lambda: dist.all_reduce(z), 10, 0), 4))
             del z
-        # the factor exchange's all-gather (6 floats per Gaussian and view slot) and its small all-reduce (the mask)
-        zs = torch.zeros(xch["views_per_rank"] * 6 * P, device=dev)
+        # the factor exchange's all-gather (7 floats per Gaussian and view slot); a P-float all-reduce for scale
+        zs = torch.zeros(xch["views_per_rank"] * 7 * P, device=dev)
         zr = torch.zeros(world * zs.numel(), device=dev)
         zm = torch.zeros(P, device=dev)
         for _ in range(5):
@@ -594,7 +594,7 @@ def run_ours(args):
             dist.all_reduce(zm)
         torch.cuda.synchronize()
         dist.barrier()
-        exchange_ms["all_gather_6P_per_slot"] = round(_event_ms(lambda: dist.all_gather_into_tensor(zr, zs), 10, 0), 4)
+        exchange_ms["all_gather_7P_per_slot"] = round(_event_ms(lambda: dist.all_gather_into_tensor(zr, zs), 10, 0), 4)
         exchange_ms["all_reduce_P"] = round(_event_ms(lambda: dist.all_reduce(zm), 10, 0), 4)
         del zs, zr, zm
     sampler = ClockSampler(local) if rank == 0 else None  # its child process starts while the warm-up runs

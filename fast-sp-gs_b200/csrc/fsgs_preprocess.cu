@@ -370,6 +370,7 @@ __device__ __forceinline__ const float *sh_coef(const PreDev &a, int i, int k) {
 // flight while the threads do the geometry, and the 9-float matrices, the colours, the warped means and the 128-byte
 // render records leave through a staging buffer (records by one bulk store).
 constexpr int kPreBlock = 128;
+constexpr int kShSourceFloats = FSGS_SH_SOURCE_FLOATS;  // colour gradient 3 | direction 3 | visibility 1
 constexpr int kWideMax = 48;                                    // SH floats per Gaussian that can be staged
 constexpr int kStageTm = 0, kStageIm = kPreBlock * 9, kStageCol = kPreBlock * 18, kStageWm = kPreBlock * 21;
 constexpr int kStageRec = kPreBlock * 24;                       // float offset of the record staging (16-B aligned)
@@ -895,16 +896,17 @@ __global__ void __launch_bounds__(kPreBlock) preprocess_backward_kernel(PreBwdDe
     }
   }
   if (i < a.P) {
+    const bool poisoned = a.overflow && *a.overflow != 0;
     if (a.sh_source) {
-      float2 *o = reinterpret_cast<float2 *>(a.sh_source + (size_t) i * 6);
-      o[0] = make_float2(src_g.x, src_g.y), o[1] = make_float2(src_g.z, src_d.x), o[2] = make_float2(src_d.y, src_d.z);
+      float *o = a.sh_source + (size_t) i * kShSourceFloats;
+      o[0] = src_g.x, o[1] = src_g.y, o[2] = src_g.z, o[3] = src_d.x, o[4] = src_d.y, o[5] = src_d.z;
+      o[6] = poisoned ? -INFINITY : (live ? 1.0f : 0.0f);
     }
     float g_o = gno.w;
     if (a.normal_opacity) {
       const float o = a.normal_opacity[i].w;
       g_o = g_o * (1.0f - o) * o;
     }
-    const bool poisoned = a.overflow && *a.overflow != 0;
     if (a.accumulate) {
       if (live) a.g_opac[i] += g_o;
       if (a.visible) {
@@ -974,10 +976,11 @@ __global__ void __launch_bounds__(256) sh_factors_kernel(int P, const float *__r
     g.y = colors[3 * i + 1] > 0 ? g_colors[3 * i + 1] : 0.0f;
     g.z = colors[3 * i + 2] > 0 ? g_colors[3 * i + 2] : 0.0f;
   }
-  float2 *o = reinterpret_cast<float2 *>(sh_source + (size_t) i * 6);
-  o[0] = make_float2(g.x, g.y), o[1] = make_float2(g.z, d.x), o[2] = make_float2(d.y, d.z);
+  const bool poisoned = overflow && *overflow != 0;
+  float *o = sh_source + (size_t) i * kShSourceFloats;
+  o[0] = g.x, o[1] = g.y, o[2] = g.z, o[3] = d.x, o[4] = d.y, o[5] = d.z;
+  o[6] = poisoned ? -INFINITY : (live ? 1.0f : 0.0f);
   if (visible) {
-    const bool poisoned = overflow && *overflow != 0;
     if (poisoned) visible[i] = -INFINITY;
     else if (!accumulate) visible[i] = live ? 1.0f : 0.0f;
     else if (live && visible[i] >= 0.0f) visible[i] = 1.0f;  // a poisoned row stays poisoned
@@ -992,7 +995,8 @@ struct ShSlots {
 };
 
 __global__ void __launch_bounds__(kPreBlock) sh_grad_from_views_kernel(int P, int sh_degree, int n_rest, ShSlots slots,
-    const float *__restrict__ sh_source, long long slot_stride, float *__restrict__ g_dc, float *__restrict__ g_rest) {
+    const float *__restrict__ sh_source, long long slot_stride, float *__restrict__ g_dc, float *__restrict__ g_rest,
+    float *__restrict__ visible) {
   __shared__ __align__(16) float s_out[kPreBlock * 45];
   const int t = threadIdx.x, base = blockIdx.x * kPreBlock, rows = min(kPreBlock, P - base), i = base + t;
   const int nb = (sh_degree + 1) * (sh_degree + 1);
@@ -1000,18 +1004,20 @@ __global__ void __launch_bounds__(kPreBlock) sh_grad_from_views_kernel(int P, in
 #pragma unroll
   for (int k = 0; k < 16; ++k) acc[k][0] = acc[k][1] = acc[k][2] = 0.0f;
   if (i < P) {
+    float seen = 0.0f;  // sum of the slots' visibility: > 0 where some view saw the Gaussian, -inf when one overflowed
     for (int s = 0; s < slots.n; ++s) {
-      const float2 *src = reinterpret_cast<const float2 *>(sh_source + (size_t) slots.order[s] * slot_stride + (size_t) i * 6);
-      const float2 a = __ldg(src), b2 = __ldg(src + 1), c = __ldg(src + 2);
-      const float gr = a.x, gg = a.y, gb = b2.x;
+      const float *src = sh_source + (size_t) slots.order[s] * slot_stride + (size_t) i * kShSourceFloats;
+      const float gr = __ldg(src), gg = __ldg(src + 1), gb = __ldg(src + 2);
+      seen += __ldg(src + 6);
       if (gr == 0.0f && gg == 0.0f && gb == 0.0f) continue;
       float b[16];
-      sh_basis(sh_degree, b2.y, c.x, c.y, b);
+      sh_basis(sh_degree, __ldg(src + 3), __ldg(src + 4), __ldg(src + 5), b);
 #pragma unroll
       for (int k = 0; k < 16; ++k)
         if (k < nb) acc[k][0] += gr * b[k], acc[k][1] += gg * b[k], acc[k][2] += gb * b[k];
     }
     g_dc[(size_t) i * 3] = acc[0][0], g_dc[(size_t) i * 3 + 1] = acc[0][1], g_dc[(size_t) i * 3 + 2] = acc[0][2];
+    if (visible) visible[i] = seen;
   }
   if (n_rest <= 0 || !g_rest) return;
   const int wide = n_rest * 3;  // <= 45
@@ -1227,7 +1233,8 @@ extern "C" int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *a, fsgs_
 
 
 extern "C" int fsgs_sh_grad_from_views(int P, int sh_degree, int n_rest, int n_slots, const int32_t *order,
-    const float *sh_source, int64_t slot_stride, float *g_sh_dc, float *g_sh_rest, fsgs_stream_t stream) {
+    const float *sh_source, int64_t slot_stride, float *g_sh_dc, float *g_sh_rest, float *visible,
+    fsgs_stream_t stream) {
   FSGS_REQUIRE(P >= 0 && sh_degree >= 0 && sh_degree <= 3 && n_rest >= 0 && n_rest <= 15);
   FSGS_REQUIRE(n_slots >= 0 && n_slots <= FSGS_MAX_VIEW_SLOTS && (n_slots == 0 || (order && sh_source)) && g_sh_dc);
   FSGS_REQUIRE(n_rest == 0 || g_sh_rest);
@@ -1240,7 +1247,7 @@ extern "C" int fsgs_sh_grad_from_views(int P, int sh_degree, int n_rest, int n_s
     slots.order[s] = order[s];
   }
   sh_grad_from_views_kernel<<<ceil_div(P, kPreBlock), kPreBlock, 0, (cudaStream_t) stream>>>(P, sh_degree, n_rest, slots,
-      sh_source, (long long) slot_stride, g_sh_dc, g_sh_rest);
+      sh_source, (long long) slot_stride, g_sh_dc, g_sh_rest, visible);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

@@ -149,7 +149,7 @@ SYMBOLS = {
     "fsgs_render_backward": (c_int, [POINTER(RenderBwdArgs), _vp]),
     "fsgs_preprocess_backward": (c_int, [POINTER(PreprocessBwdArgs), _vp]),
     "fsgs_sh_factors": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, c_int, _vp, _vp, _vp]),
-    "fsgs_sh_grad_from_views": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int32), _vp, c_int64, _vp, _vp, _vp]),
+    "fsgs_sh_grad_from_views": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int32), _vp, c_int64, _vp, _vp, _vp, _vp]),
     "fsgs_compact_workspace_bytes": (c_size_t, [c_int64]),
     "fsgs_compact_plan": (c_int, [c_int64, _vp, _vp, c_size_t, _vp, _vp]),
     "fsgs_compact_rows": (c_int, [c_int, POINTER(RowTensor), c_int64, _vp, _vp, _vp]),

@@ -122,8 +122,8 @@ class ViewEngine:
         preprocess adjoint (SH and opacity gradients and the mask are then final), 2 runs the rest (LBS adjoint);
         3 stops after the compositing adjoint and writes ``sh_source`` and the mask from what is known by then, 4 runs
         the rest after 3 (preprocess and LBS adjoints).
-        ``sh_source [P,6]``: receives the two factors of this view's SH gradient (clamped colour gradient, view
-        direction); ``grads["sh_dc"]`` / ``grads["sh_rest"]`` may then be None (``ops.sh_grad_from_views``)."""
+        ``sh_source [P,7]``: receives the two factors of this view's SH gradient (clamped colour gradient, view
+        direction) and its visibility; ``grads["sh_dc"]`` / ``grads["sh_rest"]`` may then be None (``ops.sh_grad_from_views``)."""
         a = self._args
         if g_extras is not None and g_opacity is None:  # the adjoint with auxiliary channels reads an opacity gradient
             if self._zero_opacity is None:

@@ -523,21 +523,26 @@ def gather_rows(tensors, index):
     return out
 
 
-def sh_grad_from_views(sh_source, order, sh_degree, g_sh_dc, g_sh_rest):
-    """Summed SH gradient of several views from their factors.  ``sh_source [S,P,6]``: per slot and Gaussian the clamped
-    colour gradient and the unit view direction, as the preprocess adjoint writes them (``sh_source=`` of the training
-    engine's backward); slots of zeros add nothing.  ``order``: the slots in summation order.  Writes ``g_sh_dc
-    [P,1,3]`` and ``g_sh_rest [P,n_rest,3]`` (reference SH adjoint: utils/ops_3d/spherical_harmonics.py:242-302)."""
+SH_SOURCE_FLOATS = 7  # a row of the SH-gradient factors: colour gradient 3 | view direction 3 | visibility 1
+
+
+def sh_grad_from_views(sh_source, order, sh_degree, g_sh_dc, g_sh_rest, visible=None):
+    """Summed SH gradient of several views from their factors.  ``sh_source [S,P,7]``: per slot and Gaussian the clamped
+    colour gradient, the unit view direction and the view's visibility (1 / 0, -inf from an overflowed view), as the
+    training engine's backward writes them (``sh_source=``); slots of zeros add nothing.  ``order``: the slots in
+    summation order.  Writes ``g_sh_dc [P,1,3]``, ``g_sh_rest [P,n_rest,3]`` and, when given, ``visible [P]`` = the sum
+    of the slots' visibility entries (reference SH adjoint: utils/ops_3d/spherical_harmonics.py:242-302)."""
     _need(sh_source.is_cuda and sh_source.is_contiguous() and sh_source.dtype == torch.float32 and sh_source.dim() == 3
-          and sh_source.shape[2] == 6, "sh_source: contiguous float32 CUDA [S,P,6]")
+          and sh_source.shape[2] == SH_SOURCE_FLOATS, "sh_source: contiguous float32 CUDA [S,P,7]")
     S, P = int(sh_source.shape[0]), int(sh_source.shape[1])
     _need(len(order) <= S, "more slots in order than in sh_source")
-    for t in (g_sh_dc, g_sh_rest):
-        _need(t is None or (t.is_cuda and t.is_contiguous() and t.dtype == torch.float32), "gradients: float32 CUDA")
+    for t in (g_sh_dc, g_sh_rest, visible):
+        _need(t is None or (t.is_cuda and t.is_contiguous() and t.dtype == torch.float32), "outputs: float32 CUDA")
     n_rest = 0 if g_sh_rest is None else int(g_sh_rest.shape[1])
     arr = (ctypes.c_int32 * max(len(order), 1))(*[int(o) for o in order])
-    check(lib().fsgs_sh_grad_from_views(P, int(sh_degree), n_rest, len(order), arr, _ptr(sh_source), P * 6, _ptr(g_sh_dc),
-                                        _ptr(g_sh_rest), _stream()), "fsgs_sh_grad_from_views")
+    check(lib().fsgs_sh_grad_from_views(P, int(sh_degree), n_rest, len(order), arr, _ptr(sh_source),
+                                        P * SH_SOURCE_FLOATS, _ptr(g_sh_dc), _ptr(g_sh_rest), _ptr(visible), _stream()),
+          "fsgs_sh_grad_from_views")
 
 
 def densify_select(accum, denom, scaling_raw, grad_threshold, scale_threshold):

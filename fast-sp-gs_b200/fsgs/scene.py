@@ -140,11 +140,12 @@ class DynamicScene:
 
         The exchange.  48 of the 59 gradient floats of a Gaussian are SH coefficients, and a view's SH gradient is an
         outer product: (clamped colour gradient, 3 floats) x (SH basis of the view direction, a function of 3 floats).
-        ``exchange="factors"`` therefore all-gathers those six floats per Gaussian and view (started after the last
-        view's compositing adjoint, under its preprocess and LBS adjoints), all-reduces the mask next to it and the remaining ten
-        floats (plus the dense parameters' gradients) after the LBS adjoint, and rebuilds the summed SH gradient on
-        every rank in view order (``ops.sh_grad_from_views``): every rank forms the same bits, the replicas stay
-        identical, and 6 V floats per Gaussian travel instead of 48 through an all-reduce.  ``views_per_rank``: the
+        ``exchange="factors"`` therefore all-gathers those six floats per Gaussian and view, with the view's visibility
+        as a seventh (started after the last view's compositing adjoint, under its preprocess and LBS adjoints),
+        all-reduces the remaining ten floats (plus the dense parameters' gradients) after the LBS adjoint, and rebuilds
+        the summed SH gradient and the summed mask on every rank in view order (``ops.sh_grad_from_views``): every rank
+        forms the same bits, the replicas stay identical, and 7 V floats per Gaussian travel instead of 49 through an
+        all-reduce.  ``views_per_rank``: the
         number of view slots every rank contributes -- the same on all ranks; default ``max(len(views), 1)``, to be
         passed explicitly when ranks hold different numbers of views.  ``exchange="rows"`` all-reduces the gradient
         rows themselves (two all-reduces: SH and mask first, the rest behind).
@@ -173,12 +174,14 @@ class DynamicScene:
         dst = dict(xyz=b.view_of(self.xyz), scaling=b.view_of(self.scaling), rotation=b.view_of(self.rotation),
                    opacity=b.view_of(self.opacity), sh_dc=None if factors else b.view_of(self.sh_dc),
                    sh_rest=None if factors else b.view_of(self.sh_rest),
-                   visible=b.extra, knn_w=self.g_knn_w, **self.motion_grads)
+                   visible=None if factors else b.extra,   # factors: every view's visibility rides in its slot
+                   knn_w=self.g_knn_w, **self.motion_grads)
         if factors:
             P = self.num_points
-            if self.sh_send is None or tuple(self.sh_send.shape) != (n_slots, P, 6) or self.sh_recv.shape[0] != world * n_slots:
-                self.sh_send = torch.zeros(n_slots, P, 6, device=self.xyz.device)
-                self.sh_recv = torch.empty(world * n_slots, P, 6, device=self.xyz.device)
+            F = ops.SH_SOURCE_FLOATS
+            if self.sh_send is None or tuple(self.sh_send.shape) != (n_slots, P, F) or self.sh_recv.shape[0] != world * n_slots:
+                self.sh_send = torch.zeros(n_slots, P, F, device=self.xyz.device)
+                self.sh_recv = torch.empty(world * n_slots, P, F, device=self.xyz.device)
             if len(views) < n_slots:
                 self.sh_send[len(views):].zero_()   # slots without a view add nothing
         early = late = gather = None
@@ -212,7 +215,6 @@ class DynamicScene:
             nonlocal early, gather
             if factors:
                 gather = dist.all_gather_into_tensor(self.sh_recv.view(-1), self.sh_send.view(-1), group=group, async_op=True)
-                early = b.reduce_span(b.extra_segment, b.extra_segment, group)   # the mask
             else:
                 early = b.reduce_span(0, 2, group)   # SH gradients and the mask
 
@@ -255,8 +257,8 @@ class DynamicScene:
             mark("all-gather arrived")
             # summed in view order on every rank
             ops.sh_grad_from_views(self.sh_recv, slot_order(world, n_slots), eng.sh_degree, b.view_of(self.sh_dc),
-                                   b.view_of(self.sh_rest))
-            mark("SH rows rebuilt")
+                                   b.view_of(self.sh_rest), visible=b.extra)
+            mark("SH rows and mask rebuilt")
         if early is not None:
             early.wait()
             mark("first all-reduce arrived")

@@ -381,6 +381,7 @@ int fsgs_ssim_backward(int B, int C, int H, int W, float C1, float C2, const flo
  * so the outputs need no initialisation (the reference's Python zero-fills them before its kernel, which
  * writes visible rows only: same result).  grad_means2D rows of culled Gaussians are left as they are.
  * ---------------------------------------------------------------------------------------------- */
+#define FSGS_SH_SOURCE_FLOATS 7 /* row of sh_source: colour gradient 3 | view direction 3 | visibility 1 */
 typedef struct fsgs_preprocess_bwd_args {
   int32_t P, W, H, sh_degree, n_dc, n_rest;
   const float *means, *scales, *rots, *shs, *sh_rest;
@@ -408,10 +409,11 @@ typedef struct fsgs_preprocess_bwd_args {
   float *visible;
   int32_t accumulate;
   const int64_t *counters;
-  /* sh_source [P,6] (optional, sh_degree >= 0): the two factors of this view's SH gradient, which is their outer
-   * product -- the colour gradient after the clamp (3) and the unit direction camera -> Gaussian (3); zeros for
-   * culled Gaussians.  grad_shs / grad_sh_rest may then be NULL: six floats per Gaussian and view travel between
-   * ranks instead of 48, and fsgs_sh_grad_from_views rebuilds the summed gradient on every rank. */
+  /* sh_source [P,FSGS_SH_SOURCE_FLOATS] (optional, sh_degree >= 0): the two factors of this view's SH gradient, which
+   * is their outer product -- the colour gradient after the clamp (3) and the unit direction camera -> Gaussian (3);
+   * zeros for culled Gaussians -- and this view's visibility (1: 1 visible, 0 culled, -infinity when counters report
+   * an overflow).  grad_shs / grad_sh_rest may then be NULL: seven floats per Gaussian and view travel between ranks
+   * instead of 48 + 1, and fsgs_sh_grad_from_views rebuilds the summed gradient and the summed mask on every rank. */
   float *sh_source;
 } fsgs_preprocess_bwd_args;
 
@@ -420,11 +422,14 @@ int fsgs_preprocess_backward(const fsgs_preprocess_bwd_args *args /* host */, fs
 /* Summed SH gradient of n_slots views from their factors (the rank-1 structure of preprocess_backward's SH part,
  * gs_2d_fast_preprocess.cu:536-609 with the SH adjoint of utils/ops_3d/spherical_harmonics.py:242-302):
  *   g_sh[i][k][c] = sum over slots s, in the order given, of basis_k(dir[s][i]) * g_colour[s][i][c]
- * sh_source: slot s at sh_source + s * slot_stride floats, [P,6] as written by fsgs_preprocess_backward; a slot of
- * zeros adds nothing.  order[n_slots] (host, values < n_slots): the slots in summation order (view order, so that
- * every rank forms the same bits).  g_sh_dc [P,3] and g_sh_rest [P,n_rest,3] are WRITTEN (zeros beyond the active
- * degree).  sh_degree 0..3, n_slots <= FSGS_MAX_VIEW_SLOTS. */
-/* The same factors (and the same mask, with the same accumulate / counters semantics) without the preprocess adjoint:
+ * sh_source: slot s at sh_source + s * slot_stride floats, [P,FSGS_SH_SOURCE_FLOATS] as written by
+ * fsgs_preprocess_backward; a slot of zeros adds nothing.  order[n_slots] (host, values < n_slots): the slots in
+ * summation order (view order, so that every rank forms the same bits).  g_sh_dc [P,3] and g_sh_rest [P,n_rest,3] are
+ * WRITTEN (zeros beyond the active degree); visible [P] (optional) receives the sum of the slots' visibility
+ * entries: > 0 where some view saw the Gaussian, -infinity when any view overflowed -- the float mask of
+ * fsgs_adam_masked_multi_fmask.  sh_degree 0..3, n_slots <= FSGS_MAX_VIEW_SLOTS. */
+/* The same rows (and, optionally, the same separate mask with the same accumulate / counters semantics) without the
+ * preprocess adjoint:
  * from the forward pass's warped means [P,3] and colours [P,3] (pre-clamp sign: colour > 0), the compositing adjoint's
  * colour gradient [P,3] and radii.  Lets the exchange between ranks start before the preprocess adjoint runs. */
 int fsgs_sh_factors(int P, const float *means, const float *colors, const float *grad_colors, const int32_t *radii,
@@ -434,7 +439,7 @@ int fsgs_sh_factors(int P, const float *means, const float *colors, const float 
 #define FSGS_MAX_VIEW_SLOTS 64
 int fsgs_sh_grad_from_views(int P, int sh_degree, int n_rest, int n_slots, const int32_t *order /* host */,
                             const float *sh_source, int64_t slot_stride, float *g_sh_dc, float *g_sh_rest,
-                            fsgs_stream_t stream);
+                            float *visible, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Per-pixel epilogue of GS_2D_fast_render, one kernel each way.
@@ -558,7 +563,8 @@ typedef struct fsgs_view_args {
   int64_t list_capacity;
   void *workspace;
   size_t workspace_bytes;
-  /* backward only, optional: [P,6] factors of this view's SH gradient (fsgs_preprocess_bwd_args.sh_source);
+  /* backward only, optional: [P,FSGS_SH_SOURCE_FLOATS] factors of this view's SH gradient and its visibility
+   * (fsgs_preprocess_bwd_args.sh_source);
    * g_sh_dc / g_sh_rest may then be NULL */
   float *g_sh_source;
 } fsgs_view_args;

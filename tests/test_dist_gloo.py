@@ -67,10 +67,10 @@ def _worker(rank, world, port, out):
     # zero), an all-gather delivers them rank-major, slot_order names them in view order
     from fsgs.dist import slot_order
     slots = 3                                       # ceil(5 views / 2 ranks)
-    send = torch.zeros(slots, 4, 6)
+    send = torch.zeros(slots, 4, 7)
     for j, v in enumerate(views):
         send[j] = float(v + 1)                      # view number + 1; 0 marks an empty slot
-    recv = torch.empty(world * slots, 4, 6)
+    recv = torch.empty(world * slots, 4, 7)
     dist.all_gather_into_tensor(recv.view(-1), send.view(-1))
     seen = [int(recv[k, 0, 0]) for k in slot_order(world, slots)]
     ok &= seen == [1, 2, 3, 4, 5, 0]

@@ -436,29 +436,30 @@ def test_sh_gradient_rebuilt_from_its_factors():
     rows.update(visible=torch.zeros(P, device="cuda"), knn_w=nan(s.knn_w), **{k: nan(v) for k, v in s.motion_grads.items()})
     no_rows = dict(rows, sh_dc=None, sh_rest=None)
     no_rows.update({k: nan(names[k]) for k in ("xyz", "scaling", "rotation", "opacity")})
-    factors = torch.full((3, P, 6), float("nan"), device="cuda")
+    factors = torch.full((3, P, 7), float("nan"), device="cuda")
     factors[2].zero_()  # an empty slot
     for j in (0, 1):
         eng.forward(s, cams[j], motion_at(sp[j], centres, "cuda"))
         eng.backward(ups[j][0], ups[j][1], None, rows, accumulate=j > 0, sh_source=factors[j])   # rows and factors
         if j == 0:
             first = {k: rows[k].clone() for k in ("sh_dc", "sh_rest")}
-            alone = torch.full((P, 6), float("nan"), device="cuda")
+            alone = torch.full((P, 7), float("nan"), device="cuda")
             eng.backward(ups[j][0], ups[j][1], None, no_rows, sh_source=alone)                    # factors alone
             for k in ("xyz", "scaling", "rotation", "opacity"):  # equal up to the order of the compositing atomics
                 assert rel_l2(no_rows[k], rows[k]) < 1e-6, k
             assert rel_l2(alone, factors[0]) < 1e-6
     # the same factors and mask from the early kernel (phase 3), the rest behind it (phase 4)
-    early = torch.full((P, 6), float("nan"), device="cuda")
+    early = torch.full((P, 7), float("nan"), device="cuda")
     split = dict(no_rows, visible=torch.full((P,), float("nan"), device="cuda"))
     split.update({k: nan(names[k]) for k in ("xyz", "scaling", "rotation", "opacity")})
     eng.backward(ups[1][0], ups[1][1], None, split, phase=3, sh_source=early)
     eng.backward(ups[1][0], ups[1][1], None, split, phase=4, sh_source=early)
     whole = dict(no_rows, visible=torch.full((P,), float("nan"), device="cuda"))
     whole.update({k: nan(names[k]) for k in ("xyz", "scaling", "rotation", "opacity")})
-    late = torch.full((P, 6), float("nan"), device="cuda")
+    late = torch.full((P, 7), float("nan"), device="cuda")
     eng.backward(ups[1][0], ups[1][1], None, whole, sh_source=late)
     assert rel_l2(early, late) < 1e-6 and torch.equal(split["visible"], whole["visible"])
+    assert torch.equal(early[:, 6], whole["visible"]) and torch.equal(late[:, 6], whole["visible"])   # the seventh float
     for k in ("xyz", "scaling", "rotation", "opacity"):
         assert rel_l2(split[k], whole[k]) < 1e-4, k   # run-to-run order of the compositing atomics
     assert bool(torch.isfinite(factors).all())
@@ -467,8 +468,10 @@ def test_sh_gradient_rebuilt_from_its_factors():
     dc, rest = nan(s.sh_dc), nan(s.sh_rest)
     ops.sh_grad_from_views(factors, [0], 3, dc, rest)
     assert torch.equal(dc, first["sh_dc"]) and torch.equal(rest, first["sh_rest"])
-    ops.sh_grad_from_views(factors, [0, 2, 1], 3, dc, rest)
+    seen = torch.full((P,), float("nan"), device="cuda")
+    ops.sh_grad_from_views(factors, [0, 2, 1], 3, dc, rest, visible=seen)
     assert rel_l2(dc, rows["sh_dc"]) < 1e-6 and rel_l2(rest, rows["sh_rest"]) < 1e-6
+    assert torch.equal(seen > 0, rows["visible"] > 0) and torch.equal(seen, factors[0][:, 6] + factors[1][:, 6])
     assert float(rest.abs().max()) > 0
 
 
@@ -482,10 +485,14 @@ def test_sh_rows_from_factors_vs_the_oracle_basis(degree, n_rest, P):
     d = torch.nn.functional.normalize(torch.randn(S, P, 3, generator=g), dim=-1)
     c = torch.randn(S, P, 3, generator=g)
     c[1, ::3] = 0.0                                       # culled in that view: no contribution
-    src = torch.cat([c, d], dim=-1).contiguous().cuda()
+    vis = (torch.rand(S, P, 1, generator=g) > 0.3).float()
+    vis[2, 5] = float("-inf")                              # an overflowed view poisons the sum
+    src = torch.cat([c, d, vis], dim=-1).contiguous().cuda()
     dc = torch.full((P, 1, 3), float("nan")).cuda()
     rest = torch.full((P, n_rest, 3), float("nan")).cuda() if n_rest else None
-    ops.sh_grad_from_views(src, [2, 0, 1], degree, dc, rest)
+    seen = torch.full((P,), float("nan")).cuda()
+    ops.sh_grad_from_views(src, [2, 0, 1], degree, dc, rest, visible=seen)
+    assert torch.equal(seen.cpu(), vis[2, :, 0] + vis[0, :, 0] + vis[1, :, 0]) and float(seen[5]) == float("-inf")
     nb = (degree + 1) ** 2
     want = torch.zeros(P, 16, 3, dtype=torch.float64)
     for v in (2, 0, 1):
