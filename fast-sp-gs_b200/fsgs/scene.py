@@ -145,10 +145,10 @@ class DynamicScene:
         all-reduces the remaining ten floats (plus the dense parameters' gradients) after the LBS adjoint, and rebuilds
         the summed SH gradient and the summed mask on every rank in view order (``ops.sh_grad_from_views``): every rank
         forms the same bits, the replicas stay identical, and 7 V floats per Gaussian travel instead of 49 through an
-        all-reduce.  ``views_per_rank``: the
-        number of view slots every rank contributes -- the same on all ranks; default ``max(len(views), 1)``, to be
-        passed explicitly when ranks hold different numbers of views.  ``exchange="rows"`` all-reduces the gradient
-        rows themselves (two all-reduces: SH and mask first, the rest behind).
+        all-reduce.  ``views_per_rank``: the number of view slots every rank contributes -- the same on all ranks;
+        default ``max(len(views), 1)``, to be passed explicitly when ranks hold different numbers of views.
+        ``exchange="rows"`` all-reduces the gradient rows themselves (two all-reduces: SH and mask first, the rest
+        behind).  ``self.trace``: set it to a list and the phase boundaries are appended as (label, CUDA event).
 
         ``views``: list of dicts with ``cam`` (``Tw2v, Tv2s, campos``), ``motion`` (``sp_q, sp_t, sp_dr, sp_ds``) -- or,
         with a motion network, ``t`` (float32 CUDA tensor with one element: the motion is then evaluated by the network
@@ -211,7 +211,7 @@ class DynamicScene:
                                         None if self.sp_weight is None else b.view_of(self.sp_weight))
 
         def first_exchange():
-            """What is final after the last view's preprocess adjoint leaves while its LBS adjoint runs."""
+            """What is final by now leaves while the rest of the last view's backward runs."""
             nonlocal early, gather
             if factors:
                 gather = dist.all_gather_into_tensor(self.sh_recv.view(-1), self.sh_send.view(-1), group=group, async_op=True)
