@@ -672,6 +672,66 @@ __global__ void __launch_bounds__(256) transmat_backward_kernel(int P, const flo
   g_rots[i] = gq;
 }
 
+// The same two operators in double precision (the reference dispatches them over the floating types,
+// gs_2d_fast_preprocess.cu:889,936).  Nothing on the rendering path calls them; plain arithmetic, no contraction pins.
+__device__ __forceinline__ void rot_columns_f64(const double *q, double *R) {  // q = (x, y, z, w), R row major
+  const double x = q[0], y = q[1], z = q[2], w = q[3];
+  R[0] = 1 - 2 * (y * y + z * z), R[1] = 2 * (x * y - z * w), R[2] = 2 * (y * w + x * z);
+  R[3] = 2 * (x * y + z * w), R[4] = 1 - 2 * (x * x + z * z), R[5] = 2 * (y * z - x * w);
+  R[6] = 2 * (x * z - y * w), R[7] = 2 * (x * w + y * z), R[8] = 1 - 2 * (x * x + y * y);
+}
+
+__global__ void __launch_bounds__(256) transmat_forward_f64_kernel(int P, const double *__restrict__ means,
+    const double *__restrict__ scales, const double *__restrict__ rots, const double *__restrict__ Tw2v,
+    const double *__restrict__ Tv2s, double *__restrict__ trans_mat, double *__restrict__ normals) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  double R[9], L[9], t[9];
+  rot_columns_f64(rots + 4 * (size_t) i, R);
+  const double sx = scales[2 * (size_t) i], sy = scales[2 * (size_t) i + 1];
+  for (int r = 0; r < 3; ++r) L[3 * r] = R[3 * r] * sx, L[3 * r + 1] = R[3 * r + 1] * sy, L[3 * r + 2] = means[3 * (size_t) i + r];
+  for (int a = 0; a < 3; ++a)
+    for (int b = 0; b < 3; ++b)
+      t[3 * a + b] = Tw2v[4 * a] * L[b] + Tw2v[4 * a + 1] * L[3 + b] + Tw2v[4 * a + 2] * L[6 + b];
+  t[8] += Tw2v[11];
+  for (int a = 0; a < 3; ++a)
+    for (int b = 0; b < 3; ++b)
+      trans_mat[9 * (size_t) i + 3 * a + b] = Tv2s[3 * a] * t[b] + Tv2s[3 * a + 1] * t[3 + b] + Tv2s[3 * a + 2] * t[6 + b];
+  for (int a = 0; a < 3; ++a)
+    normals[3 * (size_t) i + a] = Tw2v[4 * a] * R[2] + Tw2v[4 * a + 1] * R[5] + Tw2v[4 * a + 2] * R[8];
+}
+
+__global__ void __launch_bounds__(256) transmat_backward_f64_kernel(int P, const double *__restrict__ scales,
+    const double *__restrict__ rots, const double *__restrict__ Tw2v, const double *__restrict__ Tv2s,
+    const double *__restrict__ g_trans_mat, const double *__restrict__ g_normals, double *__restrict__ g_means,
+    double *__restrict__ g_scales, double *__restrict__ g_rots) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  const double *gT = g_trans_mat + 9 * (size_t) i, *q = rots + 4 * (size_t) i;
+  double gt[9], dL[9], R[9];
+  for (int a = 0; a < 3; ++a)       // dL/dt = Tv2s^T gT
+    for (int b = 0; b < 3; ++b) gt[3 * a + b] = Tv2s[a] * gT[b] + Tv2s[3 + a] * gT[3 + b] + Tv2s[6 + a] * gT[6 + b];
+  for (int a = 0; a < 3; ++a)       // dL/dL = Tw2v[:3,:3]^T dL/dt
+    for (int b = 0; b < 3; ++b) dL[3 * a + b] = Tw2v[a] * gt[b] + Tw2v[4 + a] * gt[3 + b] + Tw2v[8 + a] * gt[6 + b];
+  for (int r = 0; r < 3; ++r) g_means[3 * (size_t) i + r] = dL[3 * r + 2];
+  rot_columns_f64(q, R);
+  const double sx = scales[2 * (size_t) i], sy = scales[2 * (size_t) i + 1];
+  g_scales[2 * (size_t) i] = dL[0] * R[0] + dL[3] * R[3] + dL[6] * R[6];
+  g_scales[2 * (size_t) i + 1] = dL[1] * R[1] + dL[4] * R[4] + dL[7] * R[7];
+  double dR[9];                     // dL/dR: scaled columns 0, 1; column 2 from the normal
+  for (int r = 0; r < 3; ++r) {
+    dR[3 * r] = dL[3 * r] * sx, dR[3 * r + 1] = dL[3 * r + 1] * sy;
+    dR[3 * r + 2] = g_normals[3 * (size_t) i] * Tw2v[r] + g_normals[3 * (size_t) i + 1] * Tw2v[4 + r] +
+                    g_normals[3 * (size_t) i + 2] * Tw2v[8 + r];
+  }
+  const double x = q[0], y = q[1], z = q[2], w = q[3];
+  double *g = g_rots + 4 * (size_t) i;
+  g[0] = 2 * (-2 * x * (dR[4] + dR[8]) + y * (dR[1] + dR[3]) + z * (dR[2] + dR[6]) + w * (dR[7] - dR[5]));
+  g[1] = 2 * (x * (dR[1] + dR[3]) - 2 * y * (dR[0] + dR[8]) + z * (dR[5] + dR[7]) + w * (dR[2] - dR[6]));
+  g[2] = 2 * (x * (dR[2] + dR[6]) + y * (dR[5] + dR[7]) - 2 * z * (dR[0] + dR[4]) + w * (dR[3] - dR[1]));
+  g[3] = 2 * (x * (dR[7] - dR[5]) + y * (dR[2] - dR[6]) + z * (dR[3] - dR[1]));
+}
+
 // ------------------------------------------------------------------------------------------------
 // preprocess backward  (reference gs_2d_fast_preprocess.cu:516-609)
 // ------------------------------------------------------------------------------------------------
@@ -1259,6 +1319,28 @@ extern "C" int fsgs_sh_factors(int P, const float *means, const float *colors, c
   if (P == 0) return FSGS_OK;
   sh_factors_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, means, colors, grad_colors, radii, campos,
       counters ? (const long long *) counters + FSGS_CNT_OVERFLOW : nullptr, accumulate, sh_source, visible);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_transmat_forward_f64(int P, const double *means, const double *scales, const double *rots,
+    const double *Tw2v, const double *Tv2s, double *trans_mat, double *normals, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && means && scales && rots && Tw2v && Tv2s && trans_mat && normals);
+  if (P == 0) return FSGS_OK;
+  transmat_forward_f64_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, means, scales, rots, Tw2v, Tv2s,
+      trans_mat, normals);
+  FSGS_LAUNCH_CHECK();
+  return FSGS_OK;
+}
+
+extern "C" int fsgs_transmat_backward_f64(int P, const double *scales, const double *rots, const double *Tw2v,
+    const double *Tv2s, const double *grad_trans_mat, const double *grad_normals, double *grad_means,
+    double *grad_scales, double *grad_rots, fsgs_stream_t stream) {
+  FSGS_REQUIRE(P >= 0 && scales && rots && Tw2v && Tv2s && grad_trans_mat && grad_normals && grad_means &&
+               grad_scales && grad_rots);
+  if (P == 0) return FSGS_OK;
+  transmat_backward_f64_kernel<<<ceil_div(P, 256), 256, 0, (cudaStream_t) stream>>>(P, scales, rots, Tw2v, Tv2s,
+      grad_trans_mat, grad_normals, grad_means, grad_scales, grad_rots);
   FSGS_LAUNCH_CHECK();
   return FSGS_OK;
 }

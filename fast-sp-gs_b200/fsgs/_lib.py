@@ -138,6 +138,8 @@ SYMBOLS = {
     "fsgs_view_backward": (c_int, [POINTER(ViewArgs), _vp]),
     "fsgs_transmat_forward": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_transmat_backward": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_transmat_forward_f64": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsgs_transmat_backward_f64": (c_int, [c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsgs_lbs_warp_forward": (c_int, [c_int, POINTER(LBS), _vp, _vp, _vp, _vp]),
     "fsgs_lbs_warp_backward": (c_int, [c_int, POINTER(LBS), _vp, _vp, _vp, POINTER(LBSGrads), _vp]),
     "fsgs_preprocess_forward": (c_int, [POINTER(PreprocessArgs), _vp]),

@@ -374,32 +374,40 @@ def gs_2d_fast_preprocess_backward(W, H, sh_degree, is_opengl, means3D, scales, 
 
 
 def gs_2d_fast_compute_transmat_forward(means3D, scales, rotations, Tw2v, Tv2s):
-    """``gs_2d_fast_compute_trans_mat_forward`` (gs_2d_fast_preprocess.cu:871-909) -> ``(trans_mat, normals)``.
-    The camera matrices stay on the device (the reference copies them to the host, which synchronises)."""
+    """``gs_2d_fast_compute_trans_mat_forward`` (gs_2d_fast_preprocess.cu:871-909) -> ``(trans_mat, normals)``, float32
+    or float64 like the reference (``AT_DISPATCH_FLOATING_TYPES``, :889); the camera matrices are taken in the
+    inputs' type.  They stay on the device (the reference copies them to the host, which synchronises)."""
     P = means3D.shape[0]
-    _check_input(means3D, "means3D", (P, 3))
-    _check_input(scales, "scales", (P, 2))
-    _check_input(rotations, "rotations", (P, 4))
-    _check_input(Tw2v, "Tw2v", (4, 4))
-    _check_input(Tv2s, "Tv2s", (3, 3))
-    trans_mat = torch.empty(P, 3, 3, device=means3D.device, dtype=torch.float32)
-    normals = torch.empty(P, 3, device=means3D.device, dtype=torch.float32)
-    check(lib().fsgs_transmat_forward(P, _ptr(means3D), _ptr(scales), _ptr(rotations), _ptr(Tw2v), _ptr(Tv2s),
-                                      _ptr(trans_mat), _ptr(normals), _stream()), "fsgs_transmat_forward")
+    dt = means3D.dtype
+    _need(dt in (torch.float32, torch.float64), "means3D must be a float32 or float64 tensor")
+    _check_input(means3D, "means3D", (P, 3), dt)
+    _check_input(scales, "scales", (P, 2), dt)
+    _check_input(rotations, "rotations", (P, 4), dt)
+    Tw2v, Tv2s = Tw2v.to(dt).contiguous(), Tv2s.to(dt).contiguous()
+    _check_input(Tw2v, "Tw2v", (4, 4), dt)
+    _check_input(Tv2s, "Tv2s", (3, 3), dt)
+    trans_mat = torch.empty(P, 3, 3, device=means3D.device, dtype=dt)
+    normals = torch.empty(P, 3, device=means3D.device, dtype=dt)
+    fn = lib().fsgs_transmat_forward if dt == torch.float32 else lib().fsgs_transmat_forward_f64
+    check(fn(P, _ptr(means3D), _ptr(scales), _ptr(rotations), _ptr(Tw2v), _ptr(Tv2s), _ptr(trans_mat), _ptr(normals),
+             _stream()), "fsgs_transmat_forward")
     return trans_mat, normals
 
 
 def gs_2d_fast_compute_trans_mat_backward(means3D, scales, rotations, Tw2v, Tv2s, grad_matrix, grad_normals):
     """``gs_2d_fast_compute_trans_mat_backward`` (gs_2d_fast_preprocess.cu:923-958) ->
-    ``[grad_means3D, grad_scales, grad_rotations]``."""
+    ``[grad_means3D, grad_scales, grad_rotations]``, float32 or float64 (:936)."""
     P = means3D.shape[0]
-    _check_input(grad_matrix, "grad_matrix", (P, 3, 3))
-    _check_input(grad_normals, "grad_normals", (P, 3))
-    f32 = dict(device=means3D.device, dtype=torch.float32)
-    g_m, g_s, g_r = torch.empty(P, 3, **f32), torch.empty(P, 2, **f32), torch.empty(P, 4, **f32)
-    check(lib().fsgs_transmat_backward(P, _ptr(scales.contiguous()), _ptr(rotations.contiguous()), _ptr(Tw2v.contiguous()),
-                                       _ptr(Tv2s.contiguous()), _ptr(grad_matrix), _ptr(grad_normals), _ptr(g_m),
-                                       _ptr(g_s), _ptr(g_r), _stream()), "fsgs_transmat_backward")
+    dt = means3D.dtype
+    _need(dt in (torch.float32, torch.float64), "means3D must be a float32 or float64 tensor")
+    _check_input(grad_matrix, "grad_matrix", (P, 3, 3), dt)
+    _check_input(grad_normals, "grad_normals", (P, 3), dt)
+    kw = dict(device=means3D.device, dtype=dt)
+    g_m, g_s, g_r = torch.empty(P, 3, **kw), torch.empty(P, 2, **kw), torch.empty(P, 4, **kw)
+    fn = lib().fsgs_transmat_backward if dt == torch.float32 else lib().fsgs_transmat_backward_f64
+    check(fn(P, _ptr(scales.to(dt).contiguous()), _ptr(rotations.to(dt).contiguous()), _ptr(Tw2v.to(dt).contiguous()),
+             _ptr(Tv2s.to(dt).contiguous()), _ptr(grad_matrix), _ptr(grad_normals), _ptr(g_m), _ptr(g_s), _ptr(g_r),
+             _stream()), "fsgs_transmat_backward")
     return [g_m, g_s, g_r]
 
 

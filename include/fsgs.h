@@ -113,6 +113,12 @@ int fsgs_transmat_forward(int P, const float *means, const float *scales, const 
 int fsgs_transmat_backward(int P, const float *scales, const float *rots, const float *Tw2v, const float *Tv2s,
     const float *grad_trans_mat, const float *grad_normals, float *grad_means, float *grad_scales, float *grad_rots,
     fsgs_stream_t stream);
+/* The same in double precision (the reference dispatches both over the floating types, :889,936). */
+int fsgs_transmat_forward_f64(int P, const double *means, const double *scales, const double *rots, const double *Tw2v,
+    const double *Tv2s, double *trans_mat, double *normals, fsgs_stream_t stream);
+int fsgs_transmat_backward_f64(int P, const double *scales, const double *rots, const double *Tw2v, const double *Tv2s,
+    const double *grad_trans_mat, const double *grad_normals, double *grad_means, double *grad_scales,
+    double *grad_rots, fsgs_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Superpoint LBS warp (rigid blend), optionally fused into the preprocess.

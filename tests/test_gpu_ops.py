@@ -627,6 +627,35 @@ def test_transmat_golden(ops):
     assert rel_l2(gm, g["g_means"]) < 1e-4 and rel_l2(gs, g["g_scales"]) < 1e-4 and rel_l2(gr, g["g_rots"]) < 1e-4
 
 
+def test_transmat_double_precision(ops):
+    """The standalone splat-matrix operators in float64 (the reference dispatches them over the floating types):
+    against the same golden fixture at its float32 accuracy, and against a torch float64 restatement with autograd to
+    1e-12."""
+    g = load_golden("transmat.npz", "cuda")
+    d = {k: (v.double().contiguous() if torch.is_tensor(v) and v.is_floating_point() else v) for k, v in g.items()}
+    M, n = ops.gs_2d_fast_compute_transmat_forward(d["means"], d["scales"], d["rots"], d["Tw2v"], d["Tv2s"])
+    assert M.dtype == torch.float64 and n.dtype == torch.float64
+    assert torch.allclose(M, d["M"], rtol=1e-5, atol=1e-4) and torch.allclose(n, d["normal"], rtol=1e-5, atol=1e-6)
+    gm, gs, gr = ops.gs_2d_fast_compute_trans_mat_backward(d["means"], d["scales"], d["rots"], d["Tw2v"], d["Tv2s"],
+                                                           d["gM"], d["gn"])
+    assert rel_l2(gm, g["g_means"]) < 1e-4 and rel_l2(gs, g["g_scales"]) < 1e-4 and rel_l2(gr, g["g_rots"]) < 1e-4
+    # torch restatement: M = Tv2s (Tw2v[:3,:3] [R diag(s) | p] + e_z e_z^T Tw2v[2,3]), normal = Tw2v[:3,:3] R[:,2]
+    p, s, q = (d[k].clone().requires_grad_() for k in ("means", "scales", "rots"))
+    x, y, z, w = q.unbind(-1)
+    R = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (y * w + x * z),
+                     2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w),
+                     2 * (x * z - y * w), 2 * (x * w + y * z), 1 - 2 * (x * x + y * y)], dim=-1).view(-1, 3, 3)
+    L = torch.stack([R[:, :, 0] * s[:, :1], R[:, :, 1] * s[:, 1:], p], dim=-1)
+    t = d["Tw2v"][:3, :3] @ L
+    shift = torch.zeros(3, 3, dtype=torch.float64, device="cuda")
+    shift[2, 2] = d["Tw2v"][2, 3]
+    M_ref = d["Tv2s"] @ (t + shift)
+    n_ref = R[:, :, 2] @ d["Tw2v"][:3, :3].T
+    assert float((M - M_ref).abs().max()) < 1e-10 and float((n - n_ref).abs().max()) < 1e-12
+    torch.autograd.backward([M_ref, n_ref], [d["gM"], d["gn"]])
+    assert rel_l2(gm, p.grad) < 1e-12 and rel_l2(gs, s.grad) < 1e-12 and rel_l2(gr, q.grad) < 1e-12
+
+
 def test_rasterize_golden(ops):
     """Forward + backward against the reference's python compositor (fixture made on CPU)."""
     g = load_golden("rasterize.npz", "cuda")
