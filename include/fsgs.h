@@ -278,8 +278,8 @@ typedef struct fsgs_render_args {
 
 /* Not provided: the five extra outputs of the reference's bucketed forward (max_contrib, bucket_to_tile, sampled_T,
  * sampled_acc, sampled_aux; gs_2d_fast_redner.cu:872-888), which exist to feed its bucketed backward.  The backward
- * here needs no samples; the Python operator accepts per_tile_bucket_offset, ignores it and returns empty tensors in
- * those five positions. */
+ * here needs no samples; the Python operator accepts per_tile_bucket_offset, ignores it and returns placeholders in
+ * those five positions (max_contrib all zero, the others empty). */
 int fsgs_render_forward(const fsgs_render_args *args /* host */, fsgs_stream_t stream);
 
 /* Work counter (diagnostic; no counterpart in the reference): replays every pixel's walk over its tile's list with
