@@ -98,6 +98,32 @@ def test_oracle_adam_against_torch():
     assert torch.allclose(m[vis], m_ref[vis], rtol=1e-5, atol=1e-8) and bool((m[~vis] == 0).all())
 
 
+def test_dense_adam_rewrite_of_the_bias_corrected_update():
+    """``DenseAdam`` feeds torch's bias-corrected Adam to a kernel that computes ``p -= lr' m / (sqrt(v) + eps')``: with
+    ``lr' = lr sqrt(1 - b2^t) / (1 - b1^t)`` and ``eps' = eps sqrt(1 - b2^t)`` the two are the same update.  Checked
+    here on the CPU with the oracle's masked Adam (one row per tensor behind a one-element gate) against
+    ``torch.optim.Adam`` over six steps, and a closed gate leaves everything alone."""
+    g = torch.Generator().manual_seed(3)
+    lr, eps, b1, b2 = 3e-3, 1e-8, 0.9, 0.999
+    p = torch.randn(1, 77, generator=g)
+    q = torch.nn.Parameter(p.clone())
+    ref = torch.optim.Adam([q], lr=lr, eps=eps, betas=(b1, b2))
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    gate = torch.ones(1, dtype=torch.bool)
+    for t in range(1, 7):
+        grad = torch.randn(1, 77, generator=g) * 10.0 ** (t - 3)
+        q.grad = grad.clone()
+        ref.step()
+        root = (1.0 - b2 ** t) ** 0.5
+        orc.adam(p, grad, m, v, gate, lr * root / (1.0 - b1 ** t), b1, b2, eps * root, 1, 77)
+        assert torch.allclose(p, q.detach(), rtol=2e-5, atol=1e-7), t
+        assert torch.allclose(m, ref.state[q]["exp_avg"], rtol=1e-5, atol=1e-9)
+        assert torch.allclose(v, ref.state[q]["exp_avg_sq"], rtol=3e-5, atol=1e-12)
+    before = (p.clone(), m.clone(), v.clone())
+    orc.adam(p, torch.ones(1, 77), m, v, torch.zeros(1, dtype=torch.bool), 1.0, b1, b2, eps, 1, 77)
+    assert torch.equal(p, before[0]) and torch.equal(m, before[1]) and torch.equal(v, before[2])
+
+
 def test_generated_sh_polynomials_match_the_golden_basis_and_their_generator(tmp_path):
     """csrc/fsgs_sh_high.h (degrees 4..7 as Cartesian polynomials) is plain C: compile it for the host, compare the
     bands with the reference's general definition (golden fixture) and the adjoint with central differences."""
