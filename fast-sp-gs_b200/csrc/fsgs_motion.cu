@@ -1,7 +1,8 @@
 // Per-step superpoint motion: frequency encoding of the superpoint centres and of the time, the time network, the
 // deformation MLP (depth x width, one skip connection), its heads, quaternion normalisation and the re-centring of
-// the translation about each superpoint's own centre -- one kernel forward, two backward -- and the kernel-weighted
-// LBS weights with their adjoint.  Restates, in fp32 SIMT,
+// the translation about each superpoint's own centre -- one kernel forward; backward: transposed weight copies, the
+// row blocks back through the layers, the weight gradients -- and the kernel-weighted LBS weights with their
+// two-pass adjoint.  Restates, in fp32 SIMT,
 //   fast_2d_gs/network.py:1670-1776  (SC_GS_DeformNetwork: encoders, timenet, linear[], heads)
 //   fast_2d_gs/_C/src/nerf/freqencoder.cu:8-32  (output order: x, then sin(2^d s x), cos(2^d s x) per degree)
 //   fast_2d_gs/network.py:545-549    (q = normalize(g_rot + (0,0,0,1)); t' = t + c - R(q) c, 'LBS_c')
@@ -9,8 +10,9 @@
 // The network is 0.5 GFLOP per evaluation on M = 512 rows: a latency problem, not a throughput one.  Each block owns
 // 8 rows and carries them through every layer with the activations in shared memory, so the eight dependent layers
 // cost no launches and no grid synchronisation; the weights ([in, out] row major) stream from L2 through shared
-// memory by bulk asynchronous copies, and every thread keeps an 8 x 4 block of outputs in registers.  Tensor cores are
-// not used: the path is specified in fp32 and the whole evaluation is tens of microseconds on the FP32 pipe.
+// memory by bulk asynchronous copies issued by a producer warp, and every worker thread keeps an 8 x 4 block of
+// partial outputs in registers (column threads x k groups).  Tensor cores are not used: the path is specified in fp32
+// and the whole evaluation is tens of microseconds on the FP32 pipe.
 #include "fsgs_common.cuh"
 #include "fsgs_tma.cuh"
 
