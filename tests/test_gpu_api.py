@@ -291,7 +291,7 @@ def test_epilogue_kernel_vs_torch_chain():
 
 
 def test_host_feed_and_scalar_reader():
-    """Double-buffered uploads arrive intact and in order; the scalar reader returns values one step late."""
+    """Buffered uploads arrive intact and in order; the scalar reader returns values one step late."""
     from fsgs.feed import HostFeed, ScalarReader
     feed, reader = HostFeed("cuda"), ScalarReader(lag=1)
     batches = [{"a": torch.full((1 << 20,), float(i)).pin_memory(),
@@ -313,7 +313,7 @@ def test_host_feed_and_scalar_reader():
     assert got == [2.0 * i for i in range(6)]
     with pytest.raises(RuntimeError):
         feed.stage({"a": torch.zeros(1 << 20)})                 # large and not pinned
-    feed2 = HostFeed("cuda")
+    feed2 = HostFeed("cuda", slots=2)
     feed2.stage(batches[0]); feed2.stage(batches[1])
     with pytest.raises(RuntimeError):
         feed2.stage(batches[2])                                 # both slots staged
